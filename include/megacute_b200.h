@@ -1,0 +1,132 @@
+/* C ABI of the B200 persistent-megakernel runtime (libmegacute_b200.so).
+ *
+ * The reference runtime reaches its device code through one JIT-compiled callable,
+ *     compiled(views, insts, waits, arrives, counters, trace, epoch)
+ * built in megacute/runtime.py:312-317 and invoked once per step in megacute/runtime.py:383-384
+ * (device entry megacute/kernel.py:242-249).  This header is the ahead-of-time replacement of
+ * that boundary: plain pointers and sizes, no torch types.  A host runtime (the Python package in
+ * this repository, or any other binding) builds the tables and calls these functions.
+ *
+ * All device pointers are raw CUDA device addresses owned by the caller.  The library allocates
+ * only its own tables (instruction words, wait/arrive tables, dependency counters, op
+ * descriptors, status, trace); it never allocates or frees caller tensors.
+ * Every function returns 0 on success or a negative MK_E_* code; mk_strerror() names it.
+ */
+#ifndef MEGACUTE_B200_H
+#define MEGACUTE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- device op kinds (one descriptor per graph op; instructions index descriptors) ---------- */
+enum {
+    MK_OP_GEMV = 1,        /* linear with <= 8 activation rows: weight rows streamed through smem */
+    MK_OP_GEMM = 2,        /* tiled linear, optional split-K partial (reduce-add)                   */
+    MK_OP_FINALIZE = 3,    /* out = act(ws + bias) + residual; ws = 0                               */
+    MK_OP_ELTWISE = 4,     /* unary / binary / swiglu / modulate / rope tiles                       */
+    MK_OP_NORM = 5,        /* RMSNorm / LayerNorm rows                                              */
+    MK_OP_ATTENTION = 6,   /* prefill flash attention tile                                          */
+    MK_OP_ROPE_APPEND = 7, /* decode: rotate q,k of the new token, append k,v                       */
+    MK_OP_DECODE_ATTN = 8, /* decode attention over the cache (optionally fused rope+append, split) */
+    MK_OP_INCREMENT = 9    /* pos += 1                                                              */
+};
+
+#define MK_MAX_PTRS 12
+#define MK_INST_WORDS 16
+
+/* One graph op as the kernel sees it.  `ptr[k]` is the device byte address of the first element
+ * of operand k's view (0 when absent), `ld[k]` its row stride in elements.  The meaning of
+ * ptr/i/f per kind is listed in megacute_b200/encode.py next to the code that fills them and in
+ * csrc/megakernel.cu next to the code that reads them.  sizeof == 256. */
+typedef struct mk_op_desc {
+    int32_t  kind;
+    int32_t  flags;
+    int32_t  i[22];
+    float    f[4];
+    uint64_t ptr[MK_MAX_PTRS];
+    int32_t  ld[MK_MAX_PTRS];
+} mk_op_desc;
+
+typedef struct mk_caps {
+    int32_t sm_count;
+    int32_t cc_major, cc_minor;
+    int32_t max_smem_optin;     /* bytes of dynamic shared memory one CTA may request */
+    int32_t kernel_smem;        /* bytes the megakernel requests                        */
+    int32_t kernel_threads;
+    int32_t kernel_regs;        /* registers per thread of the non-tracing kernel       */
+    int32_t reserved;
+} mk_caps;
+
+/* status words written by the device and returned by mk_program_status() */
+enum { MK_ST_CODE = 0, MK_ST_CTA, MK_ST_WARP, MK_ST_SEQ, MK_ST_WHERE, MK_ST_A, MK_ST_B, MK_ST_C, MK_ST_WORDS = 16 };
+/* MK_ST_CODE values */
+enum { MK_DEV_OK = 0, MK_DEV_TIMEOUT_COUNTER = 1, MK_DEV_TIMEOUT_BARRIER = 2, MK_DEV_BAD_INST = 3 };
+
+enum {
+    MK_OK = 0,
+    MK_E_CUDA = -1,          /* a CUDA runtime call failed: see mk_last_cuda_error()        */
+    MK_E_ARG = -2,           /* null / out-of-range argument                                 */
+    MK_E_ARCH = -3,          /* the device is not compute capability 10.x                    */
+    MK_E_DEVICE = -4,        /* the kernel reported an error in the status buffer            */
+    MK_E_NOMEM = -5
+};
+
+typedef struct mk_program mk_program;
+
+const char* mk_strerror(int code);
+const char* mk_last_cuda_error(void);
+
+/* Replaces: torch.cuda.get_device_properties(0).multi_processor_count (runtime.py:234). */
+int mk_query(int device, mk_caps* caps);
+
+/* Upload the tables of one compiled graph.  Replaces the table upload and counter / trace
+ * allocation of Program.compile (runtime.py:297-305).
+ *   insts    [n_insts][16] int32   word 0 = 1 + op index (0 never appears), 1..7 args, 8 = #waits,
+ *                                  9 = first wait pair, 10 = #arrives, 11 = first arrive, 12 = seq
+ *   waits    [n_waits][2]  int32   (counter, arrivals per launch)
+ *   arrives  [n_arrives]   int32   counter ids
+ *   grid                            CTAs to launch (normally the SM count); CTA c runs
+ *                                  instructions c, c + grid, ...
+ *   trace_cap                      per-(CTA, role) trace records, 0 = tracing off                 */
+int mk_program_create(int device, const int32_t* insts, int n_insts, const int32_t* waits, int n_waits,
+                      const int32_t* arrives, int n_arrives, int n_counters, int n_ops, int grid,
+                      int trace_cap, mk_program** out);
+
+/* (Re)bind operand addresses: copy n_ops descriptors to the device on `stream`.  Replaces the
+ * per-call strided-view tuple of Program._view_tensors (runtime.py:356-369). */
+int mk_program_set_ops(mk_program* p, const mk_op_desc* ops, int n_ops, void* stream);
+
+/* One launch of the persistent kernel on `stream` (asynchronous).  Replaces
+ * self._compiled(views, insts, waits, arrives, counters, trace, epoch) (runtime.py:383-384);
+ * the launch epoch is kept inside the program and the counters are cleared only before it would
+ * overflow (runtime.py:377-380). */
+int mk_launch(mk_program* p, void* stream);
+
+/* Longest time any device-side wait may spin before the launch gives up with MK_DEV_TIMEOUT_*. */
+int mk_program_set_timeout(mk_program* p, uint64_t nanoseconds);
+
+/* Synchronise `stream`, copy the 16 status words out, return MK_E_DEVICE if the kernel reported
+ * an error (the status is cleared so the program can be reused after mk_program_reset). */
+int mk_program_status(mk_program* p, void* stream, int32_t status[MK_ST_WORDS]);
+
+/* Zero the dependency counters and the epoch (after an error, or to resume from saved state). */
+int mk_program_reset(mk_program* p, void* stream);
+
+/* Debug / test access to runtime-owned tables (synchronise the stream first). */
+int mk_program_epoch(mk_program* p);
+int mk_program_read_counters(mk_program* p, int32_t* out, int n);
+int mk_program_read_trace(mk_program* p, int64_t* out, size_t n_words);
+int mk_program_clear_trace(mk_program* p, void* stream);
+/* Overwrite one (counter, target) wait pair: host-side fault injection for the timeout tests. */
+int mk_program_poke_wait(mk_program* p, int wait_index, int counter, int target);
+
+void mk_program_destroy(mk_program* p);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

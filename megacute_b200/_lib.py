@@ -1,0 +1,124 @@
+"""Build and load ``libmegacute_b200.so`` (the CUDA kernel + C ABI of include/megacute_b200.h).
+
+The library is compiled in-tree with nvcc for sm_100a only.  There is no fallback: if the library
+is missing or does not load, every entry point of the runtime raises.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+import pathlib
+import shutil
+import subprocess
+
+PKG = pathlib.Path(__file__).resolve().parent
+CSRC = PKG / "csrc"
+LIB_PATH = PKG / "libmegacute_b200.so"
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-shared",
+              "-Xcompiler", "-fPIC"]
+
+ST_WORDS = 16
+MAX_PTRS = 12
+
+
+class OpDesc(ctypes.Structure):
+    """mk_op_desc (256 bytes)."""
+    _fields_ = [("kind", ctypes.c_int32), ("flags", ctypes.c_int32), ("i", ctypes.c_int32 * 22),
+                ("f", ctypes.c_float * 4), ("ptr", ctypes.c_uint64 * MAX_PTRS), ("ld", ctypes.c_int32 * MAX_PTRS)]
+
+
+class Caps(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int32) for n in ("sm_count", "cc_major", "cc_minor", "max_smem_optin", "kernel_smem",
+                                              "kernel_threads", "kernel_regs", "reserved")]
+
+
+assert ctypes.sizeof(OpDesc) == 256
+
+# name -> (restype, argtypes); every symbol include/megacute_b200.h declares
+_P = ctypes.c_void_p
+_I32P = ctypes.POINTER(ctypes.c_int32)
+SYMBOLS = {
+    "mk_strerror": (ctypes.c_char_p, [ctypes.c_int]),
+    "mk_last_cuda_error": (ctypes.c_char_p, []),
+    "mk_query": (ctypes.c_int, [ctypes.c_int, ctypes.POINTER(Caps)]),
+    "mk_program_create": (ctypes.c_int, [ctypes.c_int, _P, ctypes.c_int, _P, ctypes.c_int, _P, ctypes.c_int,
+                                         ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.POINTER(_P)]),
+    "mk_program_set_ops": (ctypes.c_int, [_P, _P, ctypes.c_int, _P]),
+    "mk_launch": (ctypes.c_int, [_P, _P]),
+    "mk_program_set_timeout": (ctypes.c_int, [_P, ctypes.c_uint64]),
+    "mk_program_status": (ctypes.c_int, [_P, _P, _I32P]),
+    "mk_program_reset": (ctypes.c_int, [_P, _P]),
+    "mk_program_epoch": (ctypes.c_int, [_P]),
+    "mk_program_read_counters": (ctypes.c_int, [_P, _I32P, ctypes.c_int]),
+    "mk_program_read_trace": (ctypes.c_int, [_P, _P, ctypes.c_size_t]),
+    "mk_program_clear_trace": (ctypes.c_int, [_P, _P]),
+    "mk_program_poke_wait": (ctypes.c_int, [_P, ctypes.c_int, ctypes.c_int, ctypes.c_int]),
+    "mk_program_destroy": (None, [_P]),
+}
+
+
+def sources():
+    return sorted(CSRC.glob("*.cu")) + sorted(CSRC.glob("*.cuh")) + [PKG.parent / "include" / "megacute_b200.h"]
+
+
+def needs_build() -> bool:
+    if not LIB_PATH.exists():
+        return True
+    t = LIB_PATH.stat().st_mtime
+    return any(s.stat().st_mtime > t for s in sources())
+
+
+def build(force: bool = False, verbose: bool = False) -> pathlib.Path:
+    """Compile the library with nvcc (cross-compiles without a GPU)."""
+    if not force and not needs_build():
+        return LIB_PATH
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    cmd = [nvcc, *NVCC_FLAGS, "-o", str(LIB_PATH), str(CSRC / "megakernel.cu")]
+    if verbose:
+        cmd.insert(1, "-Xptxas")
+        cmd.insert(2, "-v")
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"nvcc failed:\n{' '.join(cmd)}\n{r.stdout}\n{r.stderr}")
+    if verbose:
+        print(r.stderr)
+    return LIB_PATH
+
+
+_lib = None
+
+
+def load():
+    """The loaded library.  Raises if it has not been built (no CPU fallback exists)."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            if os.environ.get("MEGACUTE_B200_AUTOBUILD", "1") == "1" and (CSRC / "megakernel.cu").exists():
+                build()
+            else:
+                raise RuntimeError(f"{LIB_PATH} is missing: run `python -c 'import __graft_entry__ as e; e.build()'`")
+        lib = ctypes.CDLL(str(LIB_PATH))
+        for name, (res, args) in SYMBOLS.items():
+            fn = getattr(lib, name)          # AttributeError if the library lacks a declared symbol
+            fn.restype, fn.argtypes = res, args
+        _lib = lib
+    return _lib
+
+
+class MegakernelError(RuntimeError):
+    pass
+
+
+class MegakernelTimeout(MegakernelError):
+    """A device-side wait exceeded its limit; the launch ended with an error status."""
+
+
+def check(rc: int, what: str = ""):
+    if rc == 0:
+        return
+    lib = load()
+    msg = lib.mk_strerror(rc).decode()
+    if rc == -1:
+        msg += ": " + lib.mk_last_cuda_error().decode()
+    raise MegakernelError(f"{what}: {msg}" if what else msg)

@@ -1,0 +1,53 @@
+"""Constants shared by the host scheduler and the CUDA kernel (mirrored in csrc/mk_abi.h).
+
+The reference keeps its equivalents in ``megacute/config.py`` (CTA shape, tile sizes, instruction
+word layout) and ``megacute/runtime.py:28-29`` (split cost model); the values here are this
+runtime's own choices.
+"""
+
+# ---- CTA shape: 8 compute warps + 1 producer warp that streams weights ahead of the compute warps
+COMPUTE_WARPS = 8
+COMPUTE_THREADS = 32 * COMPUTE_WARPS
+NUM_THREADS = COMPUTE_THREADS + 32
+
+# ---- weight-streaming GEMV path (linear with <= 8 activation rows)
+GEMV_MAX_ROWS = 8
+GEMV_XBUF_BYTES = 65536         # fp32 copy of the activation rows held in shared memory
+GEMV_ROWS_PER_STAGE = 8         # weight rows per ring stage
+GEMV_KCHUNK = 2048              # elements of a weight row per stage (8 per compute thread)
+GEMV_STAGE_BYTES = GEMV_ROWS_PER_STAGE * GEMV_KCHUNK * 2
+GEMV_STAGES = 4
+
+# ---- tile GEMM path
+GEMM_BM, GEMM_BN, GEMM_BK = 128, 128, 32
+MIN_SPLIT_KTILES = 8            # k-tiles (of GEMM_BK) per K split
+MAX_K_SPLITS = 8
+INST_US, SM_GBPS = 2.0, 40.0    # split-K cost model: fixed us per instruction, GB/s one SM draws from HBM
+
+# ---- pointwise / norm / attention tiling
+EW_ROWS, EW_COLS = 32, 512
+NORM_ROWS = COMPUTE_WARPS       # rows per norm instruction (one per warp); 1 when the op has few rows
+WIDE_NORM_ROWS = 256
+ROPE_APPEND_ROWS = COMPUTE_WARPS
+ATTN_BQ, ATTN_BK = 128, 64
+DECODE_KEYS_PER_TILE = 64
+MIN_SPLIT_KEYS = 64
+MAX_KV_SPLITS = 32
+
+# ---- instruction word layout (16 x int32)
+IW = 16
+W_OP = 0                        # 0 = stop, else 1 + op index
+W_ARG0 = 1                      # args in words 1..7
+N_ARGS = 7
+W_NWAIT, W_WAIT_OFF = 8, 9      # wait table slice: pairs (counter, target)
+W_NARRIVE, W_ARRIVE_OFF = 10, 11
+W_SEQ = 12                      # global instruction index
+
+# ---- device op kinds (mk_abi.h: MK_OP_*)
+OP_GEMV, OP_GEMM, OP_FINALIZE, OP_ELTWISE, OP_NORM, OP_ATTENTION, OP_ROPE_APPEND, OP_DECODE_ATTN, OP_INCREMENT = \
+    range(1, 10)
+
+ACT_CODE = {None: 0, "identity": 0, "relu": 1, "silu": 2, "gelu_tanh": 3, "gelu": 3, "exp": 4, "neg": 5,
+            "sigmoid": 6, "square": 7, "swiglu": 8}
+BINARY_CODE = {"add": 0, "sub": 1, "mul": 2, "max": 3, "min": 4}
+EW_UNARY, EW_BINARY, EW_SWIGLU, EW_MODULATE, EW_ROPE = range(5)

@@ -1,0 +1,354 @@
+// The persistent megakernel and its C ABI (include/megacute_b200.h).  sm_100a only.
+//
+// One launch executes a whole graph.  grid = number of SMs, one CTA per SM, 9 warps:
+//   warps 0-7  compute: fetch this CTA's next instruction (global indices c, c+grid, ...), wait
+//              for its dependency counters (acquire), run the op, publish its arrivals (release);
+//   warp 8     producer: walks the same instruction list ahead of the compute warps and streams
+//              the weight rows of every GEMV instruction into the shared-memory ring with bulk
+//              copies, across instruction boundaries -- weights depend on nothing in the launch,
+//              so HBM keeps streaming while the compute warps sit in a dependency hop.
+// This replaces the reference's JIT-traced kernel (megacute/kernel.py:251-571) and its per-op
+// role bodies (megacute/ops/*.py).
+#include <cstdio>
+#include <cstring>
+#include <new>
+
+#include "mk_device.cuh"
+#include "op_decode.cuh"
+#include "op_gemm.cuh"
+#include "op_attention.cuh"
+#include "op_gemv.cuh"
+#include "op_pointwise.cuh"
+
+namespace mk {
+
+template <bool TRACE>
+__global__ void __launch_bounds__(kThreads, 1) megakernel(const Params p) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    uint8_t* ring = smem;
+    uint8_t* work = smem + kRingBytes;
+    Ctrl* c = reinterpret_cast<Ctrl*>(smem + kRingBytes + kWorkBytes);
+    const int warp = threadIdx.x >> 5;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&c->full[s], 1);
+            mbar_init(&c->empty[s], kComputeWarps);
+        }
+        c->abort = 0;
+        c->flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    if (warp == kProducerWarp) {
+        // ---------------- producer warp ----------------
+        RingPos pos;
+        int slot = 0;
+        for (int idx = blockIdx.x; idx < p.n_insts; idx += gridDim.x, ++slot) {
+            const Inst in = fetch_inst(p, idx);
+            const int opi = in.op() - 1;
+            if (opi < 0 || opi >= p.n_ops) break;
+            const mk_op_desc* op = p.ops + opi;
+            if (op->kind != MK_OP_GEMV) continue;
+            const long long t0 = TRACE ? (long long)globaltimer() : 0;
+            if (!gemv_produce(p, c, ring, op, in, pos)) break;
+            if ((threadIdx.x & 31) == 0) trace_rec<TRACE>(p, 0, slot, in.seq(), t0, t0, (long long)globaltimer());
+        }
+    } else {
+        // ---------------- compute warps ----------------
+        RingPos pos;
+        int slot = 0;
+        for (int idx = blockIdx.x; idx < p.n_insts; idx += gridDim.x, ++slot) {
+            const Inst in = fetch_inst(p, idx);
+            const int opi = in.op() - 1;
+            if (opi < 0 || opi >= p.n_ops) {
+                if (threadIdx.x == 0) report(p, c, MK_DEV_BAD_INST, in.seq(), 0, in.op(), idx, 0);
+                break;
+            }
+            const mk_op_desc* op = p.ops + opi;
+            const long long t0 = TRACE ? (long long)globaltimer() : 0;
+            if (wait_deps(p, c, in)) break;
+            const long long t1 = TRACE ? (long long)globaltimer() : 0;
+            bool bad = false;
+            {
+                switch (op->kind) {
+                    case MK_OP_GEMV: {
+                        const int M = op->i[0];
+                        if (M <= 1) gemv_compute<1>(p, c, ring, work, op, in, pos);
+                        else if (M <= 2) gemv_compute<2>(p, c, ring, work, op, in, pos);
+                        else if (M <= 4) gemv_compute<4>(p, c, ring, work, op, in, pos);
+                        else gemv_compute<8>(p, c, ring, work, op, in, pos);
+                        break;
+                    }
+                    case MK_OP_GEMM: op_gemm(op, in, work); break;
+                    case MK_OP_FINALIZE: op_finalize(op, in); break;
+                    case MK_OP_ELTWISE: op_eltwise(op, in); break;
+                    case MK_OP_NORM: op_norm(op, in, work); break;
+                    case MK_OP_ATTENTION:
+                        if (op->i[5] == 64) op_attention<64>(op, in, work);
+                        else op_attention<128>(op, in, work);
+                        break;
+                    case MK_OP_ROPE_APPEND: op_rope_append(op, in); break;
+                    case MK_OP_DECODE_ATTN: {
+                        const int D = op->i[3], G = op->i[1] / op->i[2];
+                        if (D == 64) {
+                            if (G <= 4) op_decode_attn<64, 4>(p, c, op, in, work);
+                            else op_decode_attn<64, 8>(p, c, op, in, work);
+                        } else {
+                            if (G <= 4) op_decode_attn<128, 4>(p, c, op, in, work);
+                            else op_decode_attn<128, 8>(p, c, op, in, work);
+                        }
+                        break;
+                    }
+                    case MK_OP_INCREMENT: op_increment(op); break;
+                    default: bad = true; break;
+                }
+            }
+            if (bad) {
+                if (threadIdx.x == 0) report(p, c, MK_DEV_BAD_INST, in.seq(), 1, op->kind, idx, 0);
+            }
+            const bool aborting = publish(p, c, in);
+            if (threadIdx.x == 0) trace_rec<TRACE>(p, 1, slot, in.seq(), t0, t1, (long long)globaltimer());
+            if (aborting) break;
+        }
+    }
+    __syncthreads();
+    // Abort path only: bulk copies may still be landing in the ring.  Wait (bounded) for the
+    // latest fill of every stage before the CTA gives its shared memory back.
+    if (c->abort && threadIdx.x == kProducerWarp * 32) {
+        for (int s = 0; s < kStages; ++s) {
+            unsigned long long t0 = globaltimer();
+            // a stage whose fill was issued has a pending phase; both parities are polled because
+            // the role that knew the parity has already left its loop
+            while (!(mbar_try_wait(&c->full[s], 0) || mbar_try_wait(&c->full[s], 1))) {
+                if (globaltimer() - t0 > 20000000ull) break;      // 20 ms
+            }
+        }
+        unsigned long long t0 = globaltimer();
+        while (globaltimer() - t0 < 200000ull) {}                  // let in-flight copies retire
+    }
+    __syncthreads();
+}
+
+}  // namespace mk
+
+// =================================================================================================
+// Host side: C ABI
+// =================================================================================================
+
+struct mk_program {
+    int device = 0;
+    int grid = 0;
+    int n_insts = 0, n_waits = 0, n_arrives = 0, n_counters = 0, n_ops = 0, trace_cap = 0;
+    int32_t* d_insts = nullptr;
+    int32_t* d_waits = nullptr;
+    int32_t* d_arrives = nullptr;
+    int32_t* d_counters = nullptr;
+    mk_op_desc* d_ops = nullptr;
+    mk_op_desc* h_ops = nullptr;     // pinned staging copy
+    int64_t* d_trace = nullptr;
+    int32_t* d_status = nullptr;
+    int32_t* h_status = nullptr;     // pinned
+    int epoch = 0;
+    int max_target = 1;
+    unsigned long long timeout_ns = 2000000000ull;
+};
+
+static thread_local char g_cuda_err[256] = "";
+
+static int cuda_fail(cudaError_t e, const char* what) {
+    snprintf(g_cuda_err, sizeof g_cuda_err, "%s: %s", what, cudaGetErrorString(e));
+    return MK_E_CUDA;
+}
+#define MK_CUDA(call)                                        \
+    do {                                                     \
+        cudaError_t e_ = (call);                             \
+        if (e_ != cudaSuccess) return cuda_fail(e_, #call);  \
+    } while (0)
+
+extern "C" {
+
+const char* mk_strerror(int code) {
+    switch (code) {
+        case MK_OK: return "ok";
+        case MK_E_CUDA: return "CUDA runtime error";
+        case MK_E_ARG: return "invalid argument";
+        case MK_E_ARCH: return "device is not compute capability 10.x (sm_100a kernel)";
+        case MK_E_DEVICE: return "megakernel reported a device-side error (see status words)";
+        case MK_E_NOMEM: return "out of memory";
+        default: return "unknown error";
+    }
+}
+
+const char* mk_last_cuda_error(void) { return g_cuda_err; }
+
+int mk_query(int device, mk_caps* caps) {
+    if (!caps) return MK_E_ARG;
+    cudaDeviceProp prop;
+    MK_CUDA(cudaGetDeviceProperties(&prop, device));
+    memset(caps, 0, sizeof *caps);
+    caps->sm_count = prop.multiProcessorCount;
+    caps->cc_major = prop.major;
+    caps->cc_minor = prop.minor;
+    caps->max_smem_optin = (int)prop.sharedMemPerBlockOptin;
+    caps->kernel_smem = mk::kSmemBytes;
+    caps->kernel_threads = mk::kThreads;
+    cudaFuncAttributes fa;
+    if (cudaFuncGetAttributes(&fa, mk::megakernel<false>) == cudaSuccess) caps->kernel_regs = fa.numRegs;
+    else (void)cudaGetLastError();
+    if (prop.major != 10) return MK_E_ARCH;
+    return MK_OK;
+}
+
+int mk_program_create(int device, const int32_t* insts, int n_insts, const int32_t* waits, int n_waits,
+                      const int32_t* arrives, int n_arrives, int n_counters, int n_ops, int grid, int trace_cap,
+                      mk_program** out) {
+    if (!out || !insts || n_insts <= 0 || n_ops <= 0 || grid <= 0 || n_waits < 0 || n_arrives < 0) return MK_E_ARG;
+    if ((n_waits && !waits) || (n_arrives && !arrives)) return MK_E_ARG;
+    mk_caps caps;
+    int rc = mk_query(device, &caps);
+    if (rc != MK_OK) return rc;
+    if (caps.max_smem_optin < mk::kSmemBytes) return MK_E_ARCH;
+    MK_CUDA(cudaSetDevice(device));
+    mk_program* p = new (std::nothrow) mk_program();
+    if (!p) return MK_E_NOMEM;
+    p->device = device; p->grid = grid; p->n_insts = n_insts; p->n_waits = n_waits; p->n_arrives = n_arrives;
+    p->n_counters = n_counters > 0 ? n_counters : 1; p->n_ops = n_ops; p->trace_cap = trace_cap;
+    for (int k = 0; k < n_waits; ++k) {
+        if (waits[2 * k] < 0 || waits[2 * k] >= p->n_counters) { delete p; return MK_E_ARG; }
+        if (waits[2 * k + 1] > p->max_target) p->max_target = waits[2 * k + 1];
+    }
+    for (int k = 0; k < n_arrives; ++k)
+        if (arrives[k] < 0 || arrives[k] >= p->n_counters) { delete p; return MK_E_ARG; }
+#define MK_TRY(call) do { cudaError_t e_ = (call); if (e_ != cudaSuccess) { cuda_fail(e_, #call); mk_program_destroy(p); return MK_E_CUDA; } } while (0)
+    MK_TRY(cudaMalloc(&p->d_insts, (size_t)n_insts * MK_INST_WORDS * 4));
+    MK_TRY(cudaMemcpy(p->d_insts, insts, (size_t)n_insts * MK_INST_WORDS * 4, cudaMemcpyHostToDevice));
+    MK_TRY(cudaMalloc(&p->d_waits, (size_t)(n_waits > 0 ? n_waits : 1) * 8));
+    if (n_waits) MK_TRY(cudaMemcpy(p->d_waits, waits, (size_t)n_waits * 8, cudaMemcpyHostToDevice));
+    MK_TRY(cudaMalloc(&p->d_arrives, (size_t)(n_arrives > 0 ? n_arrives : 1) * 4));
+    if (n_arrives) MK_TRY(cudaMemcpy(p->d_arrives, arrives, (size_t)n_arrives * 4, cudaMemcpyHostToDevice));
+    MK_TRY(cudaMalloc(&p->d_counters, (size_t)p->n_counters * 4));
+    MK_TRY(cudaMemset(p->d_counters, 0, (size_t)p->n_counters * 4));
+    MK_TRY(cudaMalloc(&p->d_ops, (size_t)n_ops * sizeof(mk_op_desc)));
+    MK_TRY(cudaMallocHost(&p->h_ops, (size_t)n_ops * sizeof(mk_op_desc)));
+    MK_TRY(cudaMalloc(&p->d_status, MK_ST_WORDS * 4));
+    MK_TRY(cudaMemset(p->d_status, 0, MK_ST_WORDS * 4));
+    MK_TRY(cudaMallocHost(&p->h_status, MK_ST_WORDS * 4));
+    if (trace_cap > 0) {
+        size_t words = (size_t)grid * 2 * trace_cap * 4;
+        MK_TRY(cudaMalloc(&p->d_trace, words * 8));
+        MK_TRY(cudaMemset(p->d_trace, 0, words * 8));
+    }
+    MK_TRY(cudaFuncSetAttribute(mk::megakernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, mk::kSmemBytes));
+    MK_TRY(cudaFuncSetAttribute(mk::megakernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, mk::kSmemBytes));
+#undef MK_TRY
+    *out = p;
+    return MK_OK;
+}
+
+int mk_program_set_ops(mk_program* p, const mk_op_desc* ops, int n_ops, void* stream) {
+    if (!p || !ops || n_ops != p->n_ops) return MK_E_ARG;
+    cudaStream_t st = (cudaStream_t)stream;
+    // the staging copy may still be in flight from an earlier rebind on this stream
+    MK_CUDA(cudaStreamSynchronize(st));
+    memcpy(p->h_ops, ops, (size_t)n_ops * sizeof(mk_op_desc));
+    MK_CUDA(cudaMemcpyAsync(p->d_ops, p->h_ops, (size_t)n_ops * sizeof(mk_op_desc), cudaMemcpyHostToDevice, st));
+    return MK_OK;
+}
+
+int mk_program_set_timeout(mk_program* p, uint64_t ns) {
+    if (!p || ns == 0) return MK_E_ARG;
+    p->timeout_ns = ns;
+    return MK_OK;
+}
+
+int mk_launch(mk_program* p, void* stream) {
+    if (!p) return MK_E_ARG;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int max_epoch = 0x7fffffff / (p->max_target > 0 ? p->max_target : 1) - 1;
+    if (p->epoch >= max_epoch) {
+        MK_CUDA(cudaMemsetAsync(p->d_counters, 0, (size_t)p->n_counters * 4, st));
+        p->epoch = 0;
+    }
+    p->epoch += 1;
+    mk::Params prm;
+    prm.insts = reinterpret_cast<const int4*>(p->d_insts);
+    prm.n_insts = p->n_insts;
+    prm.waits = reinterpret_cast<const int2*>(p->d_waits);
+    prm.arrives = p->d_arrives;
+    prm.counters = p->d_counters;
+    prm.ops = p->d_ops;
+    prm.n_ops = p->n_ops;
+    prm.trace = reinterpret_cast<long long*>(p->d_trace);
+    prm.trace_cap = p->trace_cap;
+    prm.status = p->d_status;
+    prm.epoch = p->epoch;
+    prm.timeout_ns = p->timeout_ns;
+    if (p->trace_cap > 0) mk::megakernel<true><<<p->grid, mk::kThreads, mk::kSmemBytes, st>>>(prm);
+    else mk::megakernel<false><<<p->grid, mk::kThreads, mk::kSmemBytes, st>>>(prm);
+    MK_CUDA(cudaGetLastError());
+    return MK_OK;
+}
+
+int mk_program_status(mk_program* p, void* stream, int32_t status[MK_ST_WORDS]) {
+    if (!p) return MK_E_ARG;
+    cudaStream_t st = (cudaStream_t)stream;
+    MK_CUDA(cudaMemcpyAsync(p->h_status, p->d_status, MK_ST_WORDS * 4, cudaMemcpyDeviceToHost, st));
+    MK_CUDA(cudaStreamSynchronize(st));
+    if (status) memcpy(status, p->h_status, MK_ST_WORDS * 4);
+    if (p->h_status[MK_ST_CODE] != 0) {
+        MK_CUDA(cudaMemsetAsync(p->d_status, 0, MK_ST_WORDS * 4, st));
+        return MK_E_DEVICE;
+    }
+    return MK_OK;
+}
+
+int mk_program_reset(mk_program* p, void* stream) {
+    if (!p) return MK_E_ARG;
+    cudaStream_t st = (cudaStream_t)stream;
+    MK_CUDA(cudaMemsetAsync(p->d_counters, 0, (size_t)p->n_counters * 4, st));
+    MK_CUDA(cudaMemsetAsync(p->d_status, 0, MK_ST_WORDS * 4, st));
+    p->epoch = 0;
+    return MK_OK;
+}
+
+int mk_program_epoch(mk_program* p) { return p ? p->epoch : MK_E_ARG; }
+
+int mk_program_read_counters(mk_program* p, int32_t* out, int n) {
+    if (!p || !out || n < 0 || n > p->n_counters) return MK_E_ARG;
+    MK_CUDA(cudaMemcpy(out, p->d_counters, (size_t)n * 4, cudaMemcpyDeviceToHost));
+    return MK_OK;
+}
+
+int mk_program_read_trace(mk_program* p, int64_t* out, size_t n_words) {
+    if (!p || !out || !p->d_trace) return MK_E_ARG;
+    if (n_words > (size_t)p->grid * 2 * p->trace_cap * 4) return MK_E_ARG;
+    MK_CUDA(cudaMemcpy(out, p->d_trace, n_words * 8, cudaMemcpyDeviceToHost));
+    return MK_OK;
+}
+
+int mk_program_clear_trace(mk_program* p, void* stream) {
+    if (!p) return MK_E_ARG;
+    if (!p->d_trace) return MK_OK;
+    MK_CUDA(cudaMemsetAsync(p->d_trace, 0, (size_t)p->grid * 2 * p->trace_cap * 4 * 8, (cudaStream_t)stream));
+    return MK_OK;
+}
+
+int mk_program_poke_wait(mk_program* p, int wait_index, int counter, int target) {
+    if (!p || wait_index < 0 || wait_index >= p->n_waits || counter < 0 || counter >= p->n_counters) return MK_E_ARG;
+    int32_t pair[2] = {counter, target};
+    MK_CUDA(cudaMemcpy(p->d_waits + 2 * wait_index, pair, 8, cudaMemcpyHostToDevice));
+    return MK_OK;
+}
+
+void mk_program_destroy(mk_program* p) {
+    if (!p) return;
+    cudaFree(p->d_insts); cudaFree(p->d_waits); cudaFree(p->d_arrives); cudaFree(p->d_counters);
+    cudaFree(p->d_ops); cudaFree(p->d_trace); cudaFree(p->d_status);
+    if (p->h_ops) cudaFreeHost(p->h_ops);
+    if (p->h_status) cudaFreeHost(p->h_status);
+    delete p;
+}
+
+}  // extern "C"

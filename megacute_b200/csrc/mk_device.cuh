@@ -1,0 +1,333 @@
+// Device-side building blocks of the persistent megakernel: PTX wrappers, bounded waits,
+// dependency counters, trace records.  sm_100a only.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/megacute_b200.h"
+
+namespace mk {
+
+// ---- CTA shape (mirrors megacute_b200/config.py) --------------------------------------------
+constexpr int kComputeWarps = 8;
+constexpr int kComputeThreads = kComputeWarps * 32;
+constexpr int kThreads = kComputeThreads + 32;           // + one producer warp
+constexpr int kProducerWarp = kComputeWarps;
+
+// ---- shared memory map -----------------------------------------------------------------------
+constexpr int kGemvRows = 8;                              // weight rows per ring stage
+constexpr int kGemvKChunk = 2048;                         // elements of a row per stage (8 per thread)
+constexpr int kStageBytes = kGemvRows * kGemvKChunk * 2;  // 32 KB
+constexpr int kStages = 4;
+constexpr int kRingBytes = kStages * kStageBytes;         // 128 KB, written only by bulk copies
+constexpr int kWorkBytes = 96 * 1024;                     // scratch of the instruction being executed
+constexpr int kXbufBytes = 64 * 1024;                     // GEMV: fp32 activation rows (front of work)
+constexpr int kCtrlBytes = 1024;                          // mbarriers, flags
+constexpr int kSmemBytes = kRingBytes + kWorkBytes + kCtrlBytes;
+
+struct Params {
+    const int4* insts;            // [n_insts][4]
+    int n_insts;
+    const int2* waits;            // (counter, target)
+    const int* arrives;
+    int* counters;
+    const mk_op_desc* ops;
+    int n_ops;
+    long long* trace;             // [grid][2 roles][cap][4] or null
+    int trace_cap;
+    int* status;                  // MK_ST_WORDS words; word 0 != 0 aborts every waiter
+    int epoch;
+    unsigned long long timeout_ns;
+};
+
+struct Ctrl {                     // lives in the last kCtrlBytes of shared memory
+    unsigned long long full[kStages];
+    unsigned long long empty[kStages];
+    int abort;                    // set once a wait of this CTA gave up or saw the global abort
+    int flag;                     // scratch broadcast word (split-KV last arriver)
+};
+
+// ---- small PTX wrappers ------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ unsigned long long globaltimer() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
+    asm volatile("{ .reg .b64 st; mbarrier.arrive.shared::cta.b64 st, [%0]; }" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(unsigned long long* bar, uint32_t bytes) {
+    asm volatile("{ .reg .b64 st; mbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1; }" ::"r"(smem_u32(bar)),
+                 "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// 1-D bulk copy global -> shared, completion counted in bytes on an mbarrier (no multicast).
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, unsigned long long* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_u32(dst)),
+                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_prefetch_l2(const void* src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+    int sz = valid ? 16 : 0;      // src-size 0: the 16 bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(sz) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+__device__ __forceinline__ int ld_acquire(const int* p) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void red_release_add(int* p, int v) {
+    asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_volatile(const int* p) {
+    int v;
+    asm volatile("ld.volatile.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+// named barrier over the compute warps only (the producer warp never joins it)
+__device__ __forceinline__ void compute_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kComputeThreads) : "memory"); }
+
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float rcp(float x) {
+    float y;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float rsqrt_approx(float x) {
+    float y;
+    asm("rsqrt.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float tanh_approx(float x) {
+    float y;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+constexpr float kLog2e = 1.4426950408889634f;
+__device__ __forceinline__ float sigmoidf_(float x) { return rcp(1.0f + ex2(-x * kLog2e)); }
+
+// activation codes (config.py ACT_CODE)
+enum { ACT_NONE = 0, ACT_RELU, ACT_SILU, ACT_GELU, ACT_EXP, ACT_NEG, ACT_SIGMOID, ACT_SQUARE, ACT_SWIGLU };
+__device__ __forceinline__ float apply_act(int act, float x) {
+    switch (act) {
+        case ACT_RELU: return fmaxf(x, 0.0f);
+        case ACT_SILU: return x * sigmoidf_(x);
+        case ACT_GELU: return 0.5f * x * (1.0f + tanh_approx(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+        case ACT_EXP: return ex2(x * kLog2e);
+        case ACT_NEG: return -x;
+        case ACT_SIGMOID: return sigmoidf_(x);
+        case ACT_SQUARE: return x * x;
+        default: return x;
+    }
+}
+
+__device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+__device__ __forceinline__ void unpack8(const uint4& v, float* f) {
+    f[0] = bf16_lo(v.x); f[1] = bf16_hi(v.x); f[2] = bf16_lo(v.y); f[3] = bf16_hi(v.y);
+    f[4] = bf16_lo(v.z); f[5] = bf16_hi(v.z); f[6] = bf16_lo(v.w); f[7] = bf16_hi(v.w);
+}
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ uint4 pack8(const float* f) {
+    return make_uint4(pack2(f[0], f[1]), pack2(f[2], f[3]), pack2(f[4], f[5]), pack2(f[6], f[7]));
+}
+__device__ __forceinline__ float round_bf16(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// load 8 consecutive elements as fp32 from a bf16 (dtype 0) or fp32 (dtype 1) row; 16-byte aligned
+__device__ __forceinline__ void load8(const void* base, long long elem, int dtype, float* f) {
+    if (dtype == 0) {
+        uint4 v = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(base) + elem);
+        unpack8(v, f);
+    } else {
+        const float4* p = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + elem);
+        float4 a = p[0], b = p[1];
+        f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+    }
+}
+__device__ __forceinline__ void store8(void* base, long long elem, int dtype, const float* f) {
+    if (dtype == 0) {
+        *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(base) + elem) = pack8(f);
+    } else {
+        float4* p = reinterpret_cast<float4*>(reinterpret_cast<float*>(base) + elem);
+        p[0] = make_float4(f[0], f[1], f[2], f[3]);
+        p[1] = make_float4(f[4], f[5], f[6], f[7]);
+    }
+}
+__device__ __forceinline__ float load1(const void* base, long long elem, int dtype) {
+    return dtype == 0 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(base)[elem])
+                      : reinterpret_cast<const float*>(base)[elem];
+}
+__device__ __forceinline__ void store1(void* base, long long elem, int dtype, float v) {
+    if (dtype == 0) reinterpret_cast<__nv_bfloat16*>(base)[elem] = __float2bfloat16_rn(v);
+    else reinterpret_cast<float*>(base)[elem] = v;
+}
+
+// ---- error reporting and bounded waits ---------------------------------------------------------
+// Every spin in the kernel goes through one of the two waits below.  A wait gives up when the
+// global abort word is set or when it has spun longer than Params::timeout_ns; it then records
+// who gave up (first writer wins), raises the global abort word so every other waiter leaves too,
+// and returns false.  Callers keep going through their barriers and leave at the next uniform
+// check of Ctrl::abort, so a failed launch always terminates and the context stays usable.
+__device__ __noinline__ void report(const Params& p, Ctrl* c, int code, int seq, int where, int a, int b, int cc) {
+    c->abort = 1;
+    if (atomicCAS(&p.status[MK_ST_CODE], 0, code) == 0) {
+        p.status[MK_ST_CTA] = blockIdx.x;
+        p.status[MK_ST_WARP] = threadIdx.x >> 5;
+        p.status[MK_ST_SEQ] = seq;
+        p.status[MK_ST_WHERE] = where;
+        p.status[MK_ST_A] = a;
+        p.status[MK_ST_B] = b;
+        p.status[MK_ST_C] = cc;
+        __threadfence();
+    }
+}
+
+enum { WHERE_RING_FULL = 1, WHERE_RING_EMPTY = 2, WHERE_DEP = 3, WHERE_DRAIN = 4 };
+
+__device__ __forceinline__ bool wait_barrier(const Params& p, Ctrl* c, unsigned long long* bar, uint32_t parity,
+                                             int seq, int where) {
+    if (mbar_try_wait(bar, parity)) return true;
+    unsigned long long t0 = 0;
+    for (uint32_t it = 1;; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 255u) == 0) {
+            if (*(volatile int*)&c->abort) return false;
+            if (ld_volatile(&p.status[MK_ST_CODE]) != 0) { c->abort = 1; return false; }
+            unsigned long long now = globaltimer();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > p.timeout_ns) {
+                report(p, c, MK_DEV_TIMEOUT_BARRIER, seq, where, (int)(bar - c->full), (int)parity, 0);
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ bool wait_counter(const Params& p, Ctrl* c, int counter, int target, int seq) {
+    const int* addr = p.counters + counter;
+    const int want = target * p.epoch;
+    unsigned long long t0 = 0;
+    for (uint32_t it = 1;; ++it) {
+        int v = ld_acquire(addr);
+        if (v >= want) return true;
+        if ((it & 63u) == 0) {
+            if (*(volatile int*)&c->abort) return false;
+            if (ld_volatile(&p.status[MK_ST_CODE]) != 0) { c->abort = 1; return false; }
+            unsigned long long now = globaltimer();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > p.timeout_ns) {
+                report(p, c, MK_DEV_TIMEOUT_COUNTER, seq, WHERE_DEP, counter, v, want);
+                return false;
+            }
+        }
+    }
+}
+
+// Instruction word accessors
+struct Inst {
+    int4 w[4];
+    __device__ __forceinline__ int op() const { return w[0].x; }
+    __device__ __forceinline__ int arg(int k) const {
+        const int* a = reinterpret_cast<const int*>(w);
+        return a[1 + k];
+    }
+    __device__ __forceinline__ int nwait() const { return w[2].x; }
+    __device__ __forceinline__ int wait_off() const { return w[2].y; }
+    __device__ __forceinline__ int narrive() const { return w[2].z; }
+    __device__ __forceinline__ int arrive_off() const { return w[2].w; }
+    __device__ __forceinline__ int seq() const { return w[3].x; }
+};
+__device__ __forceinline__ Inst fetch_inst(const Params& p, int idx) {
+    Inst i;
+    const int4* src = p.insts + (long long)idx * 4;
+    i.w[0] = __ldg(src); i.w[1] = __ldg(src + 1); i.w[2] = __ldg(src + 2); i.w[3] = __ldg(src + 3);
+    return i;
+}
+
+// Barrier over the compute warps that also ORs a predicate: the result is the same in every thread.
+__device__ __forceinline__ bool compute_sync_or(int pred) {
+    int out;
+    asm volatile(
+        "{ .reg .pred p, q; setp.ne.s32 p, %1, 0; bar.red.or.pred q, 1, %2, p; selp.s32 %0, 1, 0, q; }"
+        : "=r"(out)
+        : "r"(pred), "n"(kComputeThreads)
+        : "memory");
+    return out != 0;
+}
+
+// All compute threads call this.  Threads take waits round-robin.  Returns (uniformly) whether
+// the CTA is aborting.
+__device__ __forceinline__ bool wait_deps(const Params& p, Ctrl* c, const Inst& in) {
+    const int n = in.nwait();
+    for (int k = threadIdx.x; k < n; k += kComputeThreads) {
+        int2 w = __ldg(p.waits + in.wait_off() + k);
+        wait_counter(p, c, w.x, w.y, in.seq());
+    }
+    return compute_sync_or(*(volatile int*)&c->abort);
+}
+// All compute threads call this after their global writes of the instruction.  Returns
+// (uniformly) whether the CTA is aborting; arrivals are skipped in that case.
+__device__ __forceinline__ bool publish(const Params& p, Ctrl* c, const Inst& in) {
+    __threadfence();
+    if (compute_sync_or(*(volatile int*)&c->abort)) return true;
+    const int n = in.narrive();
+    for (int k = threadIdx.x; k < n; k += kComputeThreads) red_release_add(p.counters + __ldg(p.arrives + in.arrive_off() + k), 1);
+    return false;
+}
+
+template <bool TRACE>
+__device__ __forceinline__ void trace_rec(const Params& p, int role, int slot, long long seq, long long t0, long long t1,
+                                          long long t2) {
+    if constexpr (TRACE) {
+        if (slot < p.trace_cap) {
+            long long* r = p.trace + (((long long)blockIdx.x * 2 + role) * p.trace_cap + slot) * 4;
+            r[0] = seq; r[1] = t0; r[2] = t1; r[3] = t2;
+        }
+    }
+}
+
+}  // namespace mk

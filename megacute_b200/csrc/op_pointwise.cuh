@@ -1,0 +1,232 @@
+// Vectorised (128-bit) pointwise, norm and small decode ops.  All read and write global memory
+// directly with 16-byte accesses: they are bandwidth / latency bound and need no staging.
+#pragma once
+#include "mk_device.cuh"
+
+namespace mk {
+
+constexpr int kEwRows = 32, kEwCols = 512;                 // config.py EW_ROWS / EW_COLS
+enum { EW_UNARY = 0, EW_BINARY, EW_SWIGLU, EW_MODULATE, EW_ROPE };
+enum { BIN_ADD = 0, BIN_SUB, BIN_MUL, BIN_MAX, BIN_MIN };
+
+__device__ __forceinline__ float apply_bin(int fn, float a, float b) {
+    switch (fn) {
+        case BIN_ADD: return a + b;
+        case BIN_SUB: return a - b;
+        case BIN_MUL: return a * b;
+        case BIN_MAX: return fmaxf(a, b);
+        default: return fminf(a, b);
+    }
+}
+
+// MK_OP_FINALIZE: out = act(ws + bias) + residual; ws = 0.
+// ptr 0 ws (fp32), 1 out, 2 bias, 3 residual; i 0 R, 1 C, 2 act, 3 out dtype, 4 residual dtype
+// args: 0 row tile, 1 col tile (kEwRows x kEwCols)
+__device__ __noinline__ void op_finalize(const mk_op_desc* op, const Inst& in) {
+    const int R = op->i[0], Cc = op->i[1], act = op->i[2];
+    const int r0 = in.arg(0) * kEwRows, c0 = in.arg(1) * kEwCols;
+    const int rows = min(kEwRows, R - r0), cols = min(kEwCols, Cc - c0);
+    const int vpr = cols >> 3;
+    float* ws = reinterpret_cast<float*>(op->ptr[0]);
+    for (int v = threadIdx.x; v < rows * vpr; v += kComputeThreads) {
+        const int r = r0 + v / vpr, cidx = c0 + (v % vpr) * 8;
+        float f[8], b[8];
+        load8(ws, (long long)r * op->ld[0] + cidx, 1, f);
+        if (op->ptr[2]) {
+            load8(reinterpret_cast<const void*>(op->ptr[2]), cidx, 0, b);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) f[e] += b[e];
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] = apply_act(act, f[e]);
+        if (op->ptr[3]) {
+            load8(reinterpret_cast<const void*>(op->ptr[3]), (long long)r * op->ld[3] + cidx, op->i[4], b);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) f[e] += b[e];
+        }
+        store8(reinterpret_cast<void*>(op->ptr[1]), (long long)r * op->ld[1] + cidx, op->i[3], f);
+        const float z[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        store8(ws, (long long)r * op->ld[0] + cidx, 1, z);
+    }
+}
+
+// MK_OP_ELTWISE.  ptr 0 a (x / gate), 1 b (b / up / scale / cos), 2 c (shift / sin), 3 out
+// i 0 R, 1 C, 2 mode, 3 fn (activation or binary code), 4 group (rows of a per row of b; rope: seq),
+//   5 head_dim (rope).  All operands bf16.  args: 0 row tile, 1 col tile.
+__device__ __noinline__ void op_eltwise(const mk_op_desc* op, const Inst& in) {
+    const int R = op->i[0], Cc = op->i[1], mode = op->i[2], fn = op->i[3], group = op->i[4];
+    const int r0 = in.arg(0) * kEwRows, c0 = in.arg(1) * kEwCols;
+    const int rows = min(kEwRows, R - r0), cols = min(kEwCols, Cc - c0);
+    const void* A = reinterpret_cast<const void*>(op->ptr[0]);
+    const void* B = reinterpret_cast<const void*>(op->ptr[1]);
+    const void* Cp = reinterpret_cast<const void*>(op->ptr[2]);
+    void* O = reinterpret_cast<void*>(op->ptr[3]);
+    if (mode == EW_ROPE) {
+        const int D = op->i[5], half = D >> 1, hv = half >> 3;        // vectors per half head
+        const int heads = cols / D;
+        const int units = rows * heads * hv;
+        for (int u = threadIdx.x; u < units; u += kComputeThreads) {
+            const int r = r0 + u / (heads * hv);
+            const int rem = u % (heads * hv);
+            const int col = c0 + (rem / hv) * D + (rem % hv) * 8;
+            const int tok = r % group, dc = (rem % hv) * 8;
+            float x1[8], x2[8], c1[8], c2[8], s1[8], s2[8], o1[8], o2[8];
+            load8(A, (long long)r * op->ld[0] + col, 0, x1);
+            load8(A, (long long)r * op->ld[0] + col + half, 0, x2);
+            load8(B, (long long)tok * op->ld[1] + dc, 0, c1);
+            load8(B, (long long)tok * op->ld[1] + dc + half, 0, c2);
+            load8(Cp, (long long)tok * op->ld[2] + dc, 0, s1);
+            load8(Cp, (long long)tok * op->ld[2] + dc + half, 0, s2);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                o1[e] = x1[e] * c1[e] - x2[e] * s1[e];
+                o2[e] = x2[e] * c2[e] + x1[e] * s2[e];
+            }
+            store8(O, (long long)r * op->ld[3] + col, 0, o1);
+            store8(O, (long long)r * op->ld[3] + col + half, 0, o2);
+        }
+        return;
+    }
+    const int vpr = cols >> 3;
+    for (int v = threadIdx.x; v < rows * vpr; v += kComputeThreads) {
+        const int r = r0 + v / vpr, col = c0 + (v % vpr) * 8;
+        float a[8], b[8], cc[8];
+        load8(A, (long long)r * op->ld[0] + col, 0, a);
+        if (mode == EW_UNARY) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) a[e] = apply_act(fn, a[e]);
+        } else if (mode == EW_BINARY) {
+            load8(B, (long long)(r / group) * op->ld[1] + col, 0, b);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) a[e] = apply_bin(fn, a[e], b[e]);
+        } else if (mode == EW_SWIGLU) {
+            load8(B, (long long)r * op->ld[1] + col, 0, b);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) a[e] = apply_act(fn, a[e]) * b[e];
+        } else {  // EW_MODULATE: x * (1 + scale[g]) + shift[g]
+            load8(B, (long long)(r / group) * op->ld[1] + col, 0, b);
+            load8(Cp, (long long)(r / group) * op->ld[2] + col, 0, cc);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) a[e] = a[e] * (1.0f + b[e]) + cc[e];
+        }
+        store8(O, (long long)r * op->ld[3] + col, 0, a);
+    }
+}
+
+// MK_OP_NORM.  ptr 0 x, 1 out, 2 weight, 3 bias; i 0 R, 1 C, 2 rms, 3 rows per instruction (8: one
+// row per warp, 1: one row over the whole CTA); f 0 eps.  args: 0 row tile.
+// var = E[x^2] - mean^2 in fp32 (as the reference's norm kernel, megacute/ops/norm.py:94-114).
+__device__ __noinline__ void op_norm(const mk_op_desc* op, const Inst& in, uint8_t* work) {
+    const int R = op->i[0], Cc = op->i[1], rms = op->i[2], rpi = op->i[3];
+    const float eps = op->f[0];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const void* X = reinterpret_cast<const void*>(op->ptr[0]);
+    void* O = reinterpret_cast<void*>(op->ptr[1]);
+    const void* W = reinterpret_cast<const void*>(op->ptr[2]);
+    const void* Bv = reinterpret_cast<const void*>(op->ptr[3]);
+    const int nvec = Cc >> 3;
+    int r, first, step;
+    if (rpi == 1) { r = in.arg(0); first = threadIdx.x; step = kComputeThreads; }
+    else { r = in.arg(0) * kComputeWarps + warp; first = lane; step = 32; }
+    const bool live = r < R;
+    float s = 0.f, ss = 0.f;
+    if (live)
+        for (int v = first; v < nvec; v += step) {
+            float f[8];
+            load8(X, (long long)r * op->ld[0] + v * 8, 0, f);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) { s += f[e]; ss += f[e] * f[e]; }
+        }
+    s = warp_sum(s);
+    ss = warp_sum(ss);
+    if (rpi == 1) {
+        float* sh = reinterpret_cast<float*>(work);
+        if (lane == 0) { sh[warp * 2] = s; sh[warp * 2 + 1] = ss; }
+        compute_sync();
+        s = 0.f; ss = 0.f;
+#pragma unroll
+        for (int w8 = 0; w8 < kComputeWarps; ++w8) { s += sh[w8 * 2]; ss += sh[w8 * 2 + 1]; }
+    }
+    if (!live) return;
+    const float mean = rms ? 0.f : s / (float)Cc;
+    const float var = ss / (float)Cc - mean * mean;
+    const float rstd = rsqrt_approx(var + eps);
+    for (int v = first; v < nvec; v += step) {
+        float f[8], g[8];
+        load8(X, (long long)r * op->ld[0] + v * 8, 0, f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] = (f[e] - mean) * rstd;
+        if (W) {
+            load8(W, v * 8, 0, g);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) f[e] *= g[e];
+        }
+        if (Bv) {
+            load8(Bv, v * 8, 0, g);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) f[e] += g[e];
+        }
+        store8(O, (long long)r * op->ld[1] + v * 8, 0, f);
+    }
+}
+
+// Rotate-half of one 8-wide chunk pair.  x1/x2: chunks at d and d + D/2; result rounded to bf16.
+__device__ __forceinline__ void rope8(const float* x1, const float* x2, const void* cosr, const void* sinr, int d,
+                                      int half, float* o1, float* o2) {
+    float c1[8], c2[8], s1[8], s2[8];
+    load8(cosr, d, 0, c1); load8(cosr, d + half, 0, c2);
+    load8(sinr, d, 0, s1); load8(sinr, d + half, 0, s2);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        o1[e] = round_bf16(x1[e] * c1[e] - x2[e] * s1[e]);
+        o2[e] = round_bf16(x2[e] * c2[e] + x1[e] * s2[e]);
+    }
+}
+
+// MK_OP_ROPE_APPEND.  ptr 0 qkv, 1 cos, 2 sin, 3 pos, 4 q_out, 5 k_cache, 6 v_cache
+// i 0 B, 1 H, 2 KVH, 3 D, 4 max_seq, 5 qkv dtype.  args: 0 row tile (8 sequences).
+// Cache row written for sequence b: b * max_seq + pos (reference: graph.py:375-379).
+__device__ __noinline__ void op_rope_append(const mk_op_desc* op, const Inst& in) {
+    const int B = op->i[0], H = op->i[1], KVH = op->i[2], D = op->i[3], L = op->i[4], qdt = op->i[5];
+    const int pos = *reinterpret_cast<const int*>(op->ptr[3]);
+    const int half = D >> 1, hv = half >> 3;
+    const int r0 = in.arg(0) * kComputeWarps;
+    const int rows = min(kComputeWarps, B - r0);
+    const void* qkv = reinterpret_cast<const void*>(op->ptr[0]);
+    const __nv_bfloat16* cosr = reinterpret_cast<const __nv_bfloat16*>(op->ptr[1]) + (long long)pos * op->ld[1];
+    const __nv_bfloat16* sinr = reinterpret_cast<const __nv_bfloat16*>(op->ptr[2]) + (long long)pos * op->ld[2];
+    const int units = (H + KVH) * hv;
+    for (int u = threadIdx.x; u < rows * units; u += kComputeThreads) {
+        const int b = r0 + u / units, rem = u % units;
+        const int hh = rem / hv, d = (rem % hv) * 8;
+        float x1[8], x2[8], o1[8], o2[8];
+        load8(qkv, (long long)b * op->ld[0] + hh * D + d, qdt, x1);
+        load8(qkv, (long long)b * op->ld[0] + hh * D + d + half, qdt, x2);
+        rope8(x1, x2, cosr, sinr, d, half, o1, o2);
+        if (hh < H) {
+            store8(reinterpret_cast<void*>(op->ptr[4]), (long long)b * op->ld[4] + hh * D + d, 0, o1);
+            store8(reinterpret_cast<void*>(op->ptr[4]), (long long)b * op->ld[4] + hh * D + d + half, 0, o2);
+        } else {
+            const long long row = (long long)b * L + pos;
+            store8(reinterpret_cast<void*>(op->ptr[5]), row * op->ld[5] + (hh - H) * D + d, 0, o1);
+            store8(reinterpret_cast<void*>(op->ptr[5]), row * op->ld[5] + (hh - H) * D + d + half, 0, o2);
+        }
+    }
+    const int nv = (KVH * D) >> 3;
+    for (int u = threadIdx.x; u < rows * nv; u += kComputeThreads) {
+        const int b = r0 + u / nv, v = u % nv;
+        float f[8];
+        load8(qkv, (long long)b * op->ld[0] + (H + KVH) * D + v * 8, qdt, f);
+        store8(reinterpret_cast<void*>(op->ptr[6]), ((long long)b * L + pos) * op->ld[6] + v * 8, 0, f);
+    }
+}
+
+// MK_OP_INCREMENT.  ptr 0 pos.
+__device__ __forceinline__ void op_increment(const mk_op_desc* op) {
+    if (threadIdx.x == 0) {
+        int* pos = reinterpret_cast<int*>(op->ptr[0]);
+        *pos = *pos + 1;
+    }
+}
+
+}  // namespace mk

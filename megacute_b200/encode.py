@@ -1,0 +1,135 @@
+"""Graph op -> device descriptor (``mk_op_desc``).
+
+One descriptor per op of the rewritten graph.  The reference has no such table: its per-op
+parameters are Python constants traced into the JIT kernel by the node classes
+(``megacute/ops/*.py`` ``__init__`` / ``host``).  Here the kernel is compiled once, ahead of time,
+and reads shapes, strides, flags and operand addresses from this table at run time.
+
+``fill(desc, op, addr)`` writes the fields; ``addr(view)`` returns the device byte address of the
+view's first element.  Field meaning per kind (the kernel side repeats it next to the reader):
+
+  GEMV         ptr x, w, out, bias, residual, norm gain; i M, N_out, K, act, x dtype, out dtype,
+               residual dtype; f eps; flags 1 = swiglu, 2 = rms-normalise x
+  GEMM         ptr x, w, out, bias, residual; i M, N (weight rows), K, act, splits, out dtype,
+               accumulate, residual dtype, swiglu
+  FINALIZE     ptr ws, out, bias, residual; i R, C, act, out dtype, residual dtype
+  ELTWISE      ptr a, b, c, out; i R, C, mode, fn, group, head_dim
+  NORM         ptr x, out, weight, bias; i R, C, rms, rows per instruction; f eps
+  ATTENTION    ptr q, k, v, out; i batch, seq_q, seq_k, heads, kv_heads, head_dim, causal; f scale
+  ROPE_APPEND  ptr qkv, cos, sin, pos, q_out, k_cache, v_cache; i B, H, KVH, D, max_seq, qkv dtype
+  DECODE_ATTN  ptr q, k_cache, v_cache, pos, out, k_new, v_new, cos, sin, part, count;
+               i B, H, KVH, D, max_seq, splits, fused, q dtype; f scale
+  INCREMENT    ptr pos
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import config as C
+from .graph import DTYPE_CODE, ELEM_BYTES, Op, View
+from .schedule import is_gemv, norm_rows
+
+BF16 = torch.bfloat16
+
+
+def _aligned(v: View, what: str):
+    if (v.col0 * ELEM_BYTES[v.buf.dtype]) % 16:
+        raise ValueError(f"{v}: column offset is not 16-byte aligned ({what})")
+
+
+def _want(v, dtypes, what):
+    if v is not None and v.buf.dtype not in dtypes:
+        raise TypeError(f"{what}: operand {v} has dtype {v.buf.dtype}, supported: {dtypes}")
+
+
+def validate(op: Op):
+    """Alignment and dtype rules of the kernel, checked once at compile time."""
+    for name, v in op.view_fields():
+        if v.buf.dtype != torch.int32:
+            _aligned(v, f"{op.kind}.{name}")
+    k = op.kind
+    if k in ("Linear", "LinearSplit"):
+        _want(op.w, (BF16,), k)
+        if op.x.cols % 8:
+            raise ValueError(f"{k}: K={op.x.cols} must be a multiple of 8")
+        if not is_gemv(op):
+            _want(op.x, (BF16,), k)
+    if k in ("Unary", "Binary", "SwiGLU", "Modulate", "Rope", "Norm"):
+        for name, v in op.view_fields():
+            _want(v, (BF16,), f"{k}.{name}")
+        if op.out.cols % 8:
+            raise ValueError(f"{k}: column count {op.out.cols} must be a multiple of 8")
+    if k == "Attention":
+        for name, v in op.view_fields():
+            _want(v, (BF16,), f"{k}.{name}")
+
+
+def fill(d, op: Op, addr) -> None:
+    """Write op's descriptor into ``d`` (an ``_lib.OpDesc``)."""
+    ptrs: list = []
+    ints: list = []
+    d.flags = 0
+    dt = lambda v: DTYPE_CODE[v.buf.dtype] if v is not None else 0
+    k = op.kind
+    if k == "Linear" and is_gemv(op):
+        d.kind = C.OP_GEMV
+        ptrs = [op.x, op.w, op.out, op.bias, op.residual, op.norm_w]
+        ints = [op.x.rows, op.out.cols, op.x.cols, C.ACT_CODE[op.act], dt(op.x), dt(op.out), dt(op.residual)]
+        d.f[0] = float(op.rms_eps or 0.0)
+        d.flags = (1 if op.act == "swiglu" else 0) | (2 if op.rms_eps is not None else 0)
+    elif k in ("Linear", "LinearSplit"):
+        d.kind = C.OP_GEMM
+        split = k == "LinearSplit"
+        out = op.ws if split else op.out
+        ptrs = [op.x, op.w, out, None if split else op.bias, None if split else op.residual]
+        act = None if split else op.act
+        ints = [op.x.rows, op.w.rows, op.x.cols, C.ACT_CODE[act], op.splits if split else 1, dt(out), int(split),
+                0 if split else dt(op.residual), int(act == "swiglu")]
+    elif k == "SplitFinalize":
+        d.kind = C.OP_FINALIZE
+        ptrs = [op.ws, op.out, op.bias, op.residual]
+        ints = [op.out.rows, op.out.cols, C.ACT_CODE[op.act], dt(op.out), dt(op.residual)]
+    elif k in ("Unary", "Binary", "SwiGLU", "Modulate", "Rope"):
+        d.kind = C.OP_ELTWISE
+        R, Cc = op.out.shape
+        if k == "Unary":
+            ptrs, ints = [op.x, None, None, op.out], [R, Cc, C.EW_UNARY, C.ACT_CODE[op.fn], 1, 0]
+        elif k == "Binary":
+            ptrs, ints = [op.a, op.b, None, op.out], [R, Cc, C.EW_BINARY, C.BINARY_CODE[op.fn], op.b_group, 0]
+        elif k == "SwiGLU":
+            ptrs, ints = [op.gate, op.up, None, op.out], [R, Cc, C.EW_SWIGLU, C.ACT_CODE[op.act], 1, 0]
+        elif k == "Modulate":
+            ptrs, ints = [op.x, op.scale, op.shift, op.out], [R, Cc, C.EW_MODULATE, 0, op.group, 0]
+        else:
+            ptrs, ints = [op.x, op.cos, op.sin, op.out], [R, Cc, C.EW_ROPE, 0, op.seq, op.head_dim]
+    elif k == "Norm":
+        d.kind = C.OP_NORM
+        ptrs = [op.x, op.out, op.weight, op.bias]
+        ints = [op.x.rows, op.x.cols, int(bool(op.rms)), norm_rows(op.x.rows)]
+        d.f[0] = float(op.eps)
+    elif k == "Attention":
+        d.kind = C.OP_ATTENTION
+        ptrs = [op.q, op.k, op.v, op.out]
+        ints = [op.batch, op.seq_q, op.seq_k, op.heads, op.kv_heads, op.head_dim, int(op.causal)]
+        d.f[0] = float(op.scale)
+    elif k == "RopeAppend":
+        d.kind = C.OP_ROPE_APPEND
+        ptrs = [op.qkv, op.cos, op.sin, op.pos, op.q_out, op.k_cache, op.v_cache]
+        ints = [op.qkv.rows, op.heads, op.kv_heads, op.head_dim, op.max_seq, dt(op.qkv)]
+    elif k == "DecodeAttention":
+        d.kind = C.OP_DECODE_ATTN
+        ptrs = [op.q, op.k_cache, op.v_cache, op.pos, op.out, op.k_new, op.v_new, op.cos, op.sin, op.part, op.count]
+        ints = [op.batch, op.heads, op.kv_heads, op.head_dim, op.max_seq, op.splits, int(op.k_new is not None),
+                dt(op.q)]
+        d.f[0] = float(op.scale)
+    elif k == "Increment":
+        d.kind = C.OP_INCREMENT
+        ptrs = [op.pos]
+    else:
+        raise NotImplementedError(k)
+    for n, v in enumerate(ints):
+        d.i[n] = int(v)
+    for n, v in enumerate(ptrs):
+        d.ptr[n] = addr(v) if v is not None else 0
+        d.ld[n] = v.buf.cols if v is not None else 0

@@ -1,0 +1,186 @@
+"""Graph rewrites applied by ``compile`` before scheduling: Graph -> Graph, each on a derived copy.
+
+Same pass names and intent as the reference (``megacute/runtime.py:44-199``), re-decided for this
+runtime's kernel:
+
+  fold_norms           few-row RMSNorm feeding only linears -> computed inside those linears.
+                       The reference folds the gain into a derived copy of the weights and applies
+                       rstd in the GEMM epilogue; here the consuming instruction normalises its own
+                       copy of the (<= 8 row) activation in shared memory before streaming weights,
+                       so no second copy of any weight (e.g. the 525 MB lm_head) is made.
+  split_k              tile GEMMs that cannot fill the SMs are split along K into partial
+                       instructions that reduce-add into an fp32 workspace (+ SplitFinalize) or, for
+                       a residual linear, straight into the residual stream.
+  fuse_rope_attention  RopeAppend feeding only the next DecodeAttention -> one fused op.
+  split_kv             decode attention instructions are multiplied along the key axis so that every
+                       SM streams keys; the last split of a (sequence, kv head) pair to finish
+                       combines the partials inside the op.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import config as C
+from .graph import Graph, Op, View
+
+
+def _reads_buffer(ops, buf, outputs=()) -> bool:
+    return any(v.buf is buf for op in ops for v in op.reads) or any(v.buf is buf for v in outputs)
+
+
+def gemv_eligible(M: int, K: int) -> bool:
+    """Does a linear with M activation rows of length K run on the weight-streaming GEMV path?
+    The whole activation is kept in shared memory as fp32."""
+    return M <= C.GEMV_MAX_ROWS and M * K * 4 <= C.GEMV_XBUF_BYTES
+
+
+def fold_norms(g: Graph) -> Graph:
+    out = g.derive()
+    ops = list(g.ops)
+    drop = set()
+    for i, op in enumerate(ops):
+        if not (op.kind == "Norm" and op.rms and op.bias is None and op.out.buf.kind == "temp"):
+            continue
+        if not gemv_eligible(op.x.rows, op.x.cols):
+            continue
+        users = [j for j in range(i + 1, len(ops)) if any(v.buf is op.out.buf for v in ops[j].reads)]
+        ok = bool(users) and not _reads_buffer((), op.out.buf, g.outputs)
+        for j in users:
+            u = ops[j]
+            ok = ok and u.kind == "Linear" and op.out.same(u.x) and u.rms_eps is None
+            ok = ok and all(v is None or v.buf is not op.out.buf for v in (u.residual, u.bias))
+        # the raw input must not be rewritten between the norm and its last user
+        if ok:
+            between = ops[i + 1:users[-1]]
+            ok = not any(w.buf is op.x.buf for o in between for w in o.writes)
+        if not ok:
+            continue
+        for j in users:
+            ops[j] = ops[j].clone(x=op.x, norm_w=op.weight, rms_eps=float(op.eps))
+        drop.add(i)
+    out.ops = [o for i, o in enumerate(ops) if i not in drop]
+    return out
+
+
+def fuse_rope_attention(g: Graph) -> Graph:
+    out = g.derive()
+    ops: list[Op] = []
+    for i, op in enumerate(g.ops):
+        prev = ops[-1] if ops else None
+        if (op.kind == "DecodeAttention" and op.k_new is None and prev is not None and prev.kind == "RopeAppend"
+                and op.q.same(prev.q_out) and op.k_cache.same(prev.k_cache) and op.v_cache.same(prev.v_cache)
+                and op.pos.same(prev.pos) and prev.q_out.buf.kind == "temp"
+                and not _reads_buffer(g.ops[i + 1:], prev.q_out.buf, g.outputs)):
+            H, KVH, D = prev.heads, prev.kv_heads, prev.head_dim
+            qkv = prev.qkv
+            ops[-1] = op.clone(q=qkv.cols_slice(0, H * D), k_new=qkv.cols_slice(H * D, KVH * D),
+                               v_new=qkv.cols_slice((H + KVH) * D, KVH * D), cos=prev.cos, sin=prev.sin)
+            continue
+        ops.append(op)
+    out.ops = ops
+    return out
+
+
+def kv_splits(pairs: int, max_seq: int, sm_count: int) -> int:
+    """Instructions per (sequence, kv head) pair.  Few pairs: one wave that covers the SMs.  Many
+    pairs: the smallest split count whose last wave is at least 90 % full, as long as a split
+    still has >= MIN_SPLIT_KEYS keys of room."""
+    cap = max(1, max_seq // C.MIN_SPLIT_KEYS)
+    if pairs <= sm_count:
+        return max(1, min(cap, sm_count // pairs, C.MAX_KV_SPLITS))
+    best, best_eff = 1, 0.0
+    for s in range(1, min(cap, 8) + 1):
+        n = pairs * s
+        eff = n / (-(-n // sm_count) * sm_count)
+        if eff > best_eff + 1e-9:
+            best, best_eff = s, eff
+        if eff >= 0.9:
+            break
+    return best
+
+
+def split_kv(g: Graph, sm_count: int) -> Graph:
+    out = g.derive()
+    ops = []
+    for op in g.ops:
+        if op.kind == "DecodeAttention" and op.splits == 1:
+            pairs = op.batch * op.kv_heads
+            s = kv_splits(pairs, op.max_seq, sm_count)
+            if s > 1:
+                G, D = op.heads // op.kv_heads, op.head_dim
+                cols = -(-(G * D + 2 * G) // 4) * 4          # per split: O (G x D), running max (G), sum (G)
+                part = out.workspace((pairs * s, cols), torch.float32)
+                count = out.workspace((pairs, 1), torch.int32)
+                op = op.clone(splits=s, part=part, count=count)
+        ops.append(op)
+    out.ops = ops
+    return out
+
+
+def _retarget(v, alias):
+    if v is None or v.buf.id not in alias:
+        return v
+    r = alias[v.buf.id]
+    return View(r.buf, r.row0 + v.row0, r.col0 + v.col0, v.rows, v.cols)
+
+
+def choose_k_splits(M: int, N: int, K: int, sm_count: int) -> int:
+    """Split count for a tile GEMM.  Cost of a plan = waves x (fixed cost per instruction + operand
+    bytes of one instruction at one SM's share of HBM bandwidth)."""
+    bm, bn, bk = C.GEMM_BM, C.GEMM_BN, C.GEMM_BK
+    mt, nt, kt = -(-M // bm), -(-N // bn), K // bk
+    rows = min(M, bm)
+
+    def cost(n_inst, k):
+        return -(-n_inst // sm_count) * (C.INST_US + (bn + rows) * k * 2 / (C.SM_GBPS * 1e3))
+
+    best, best_cost = 1, cost(mt * nt, K)
+    if mt * nt >= sm_count:
+        return 1
+    for s in range(2, C.MAX_K_SPLITS + 1):
+        if kt % s or kt // s < C.MIN_SPLIT_KTILES:
+            continue
+        c = cost(mt * nt * s, K // s)
+        if c < best_cost:
+            best, best_cost = s, c
+    return best
+
+
+def split_k(g: Graph, sm_count: int) -> Graph:
+    out = g.derive()
+    alias: dict[int, View] = {}      # id of a dropped output buffer -> residual view that now holds it
+    ops: list[Op] = []
+    src = list(g.ops)
+    for i, op0 in enumerate(src):
+        op = op0.clone(**{k: _retarget(v, alias) for k, v in op0.view_fields()}) if alias else op0
+        if op.kind == "Linear" and op.act != "swiglu" and not gemv_eligible(op.x.rows, op.x.cols):
+            M, K = op.x.shape
+            s = choose_k_splits(M, op.w.rows, K, sm_count)
+            if s > 1:
+                r = op.residual
+                whole = op.out.rect == (0, op.out.buf.rows, 0, op.out.buf.cols)
+                inplace = (r is not None and op.bias is None and op.act is None and op.norm_w is None
+                           and r.buf.kind in ("temp", "state") and op.out.buf.kind == "temp" and whole
+                           and not _reads_buffer(src[i + 1:], r.buf))
+                if inplace:
+                    alias[op.out.buf.id] = r
+                    new = Op("LinearSplit", x=op.x, w=op.w, ws=r, splits=s)
+                    new.layer = op.layer
+                    ops.append(new)
+                    continue
+                ws = out.workspace(op.out.shape, torch.float32)
+                part = Op("LinearSplit", x=op.x, w=op.w, ws=ws, splits=s)
+                fin = Op("SplitFinalize", ws=ws, out=op.out, bias=op.bias, act=op.act, residual=op.residual)
+                part.layer = fin.layer = op.layer
+                ops += [part, fin]
+                continue
+        ops.append(op)
+    out.ops = ops
+    out.outputs = [_retarget(v, alias) for v in g.outputs]
+    return out
+
+
+def run_all(g: Graph, sm_count: int) -> Graph:
+    """The pass pipeline of ``compile`` (reference order: runtime.py:235)."""
+    return split_kv(fuse_rope_attention(split_k(fold_norms(g), sm_count)), sm_count)
