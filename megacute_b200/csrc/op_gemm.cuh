@@ -1,6 +1,167 @@
-// MK_OP_GEMM placeholder (filled in below in the same file once the tile GEMM lands).
+// MK_OP_GEMM: tiled linear for more than 8 activation rows.
+//   out[128 x 128 tile] = act(x @ w^T + bias) + residual        (one instruction per output tile)
+//   ws += x[:, Kj] @ w[:, Kj]^T                                  (split-K partial: reduce-add)
+// Operands stream through a 4-stage cp.async pipeline of 128 x 32 tiles; the math is warp-level
+// mma.sync m16n8k16 bf16 -> fp32 (8 warps as 2 x 4, warp tile 64 x 32).  This is the portable
+// first implementation of the tile path; the tcgen05 / TMEM version replaces the main loop and
+// keeps this epilogue.
+//
+// ptr 0 x, 1 w, 2 out (or ws), 3 bias, 4 residual
+// i 0 M, 1 N (weight rows), 2 K, 3 act, 4 splits, 5 out dtype, 6 accumulate, 7 residual dtype,
+//   8 swiglu (weight tile = 64 gate rows then 64 up rows; the tile writes 64 output columns)
+// args: 0 m tile, 1 n tile, 2 k split
 #pragma once
 #include "mk_device.cuh"
+
 namespace mk {
-__device__ __forceinline__ void op_gemm(const mk_op_desc*, const Inst&, uint8_t*) {}
+
+constexpr int kGemmBM = 128, kGemmBN = 128, kGemmBK = 32, kGemmStages = 4;
+constexpr int kGemmRowBytes = kGemmBK * 2 + 16;                // padded: conflict-free ldmatrix
+constexpr int kGemmTileBytes = kGemmBM * kGemmRowBytes;        // 10 KB per operand per stage
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void red_add_f32x2(float* p, float a, float b) {
+    asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(p), "f"(a), "f"(b) : "memory");
+}
+__device__ __forceinline__ void red_add_bf16x2(void* p, float a, float b) {
+    const uint32_t v = pack2(a, b);
+    asm volatile("red.global.add.noftz.bf16x2 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+__device__ __noinline__ void op_gemm(const mk_op_desc* op, const Inst& in, uint8_t* work) {
+    const int M = op->i[0], N = op->i[1], K = op->i[2], act = op->i[3], splits = op->i[4];
+    const int odt = op->i[5], accum = op->i[6], rdt = op->i[7], swi = op->i[8];
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const int wm = warp >> 2, wn = warp & 3;
+    const int m0 = in.arg(0) * kGemmBM, n0 = in.arg(1) * kGemmBN;
+    const int kc = K / splits, kbeg = in.arg(2) * kc, nk = kc / kGemmBK;
+    const __nv_bfloat16* X = reinterpret_cast<const __nv_bfloat16*>(op->ptr[0]);
+    const __nv_bfloat16* Wt = reinterpret_cast<const __nv_bfloat16*>(op->ptr[1]);
+    const long long ldx = op->ld[0], ldw = op->ld[1];
+    uint8_t* sa = work;
+    uint8_t* sb = work + kGemmStages * kGemmTileBytes;
+
+    auto issue = [&](int kt) {
+        const int st = kt % kGemmStages;
+        const int k0 = kbeg + kt * kGemmBK;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int v = t + i * kComputeThreads;              // 512 chunks of 16 bytes per operand
+            const int r = v >> 2, ch = v & 3;
+            const bool va = m0 + r < M, vb = n0 + r < N;
+            cp_async16(sa + st * kGemmTileBytes + r * kGemmRowBytes + ch * 16,
+                       X + (long long)(va ? m0 + r : m0) * ldx + k0 + ch * 8, va);
+            cp_async16(sb + st * kGemmTileBytes + r * kGemmRowBytes + ch * 16,
+                       Wt + (long long)(vb ? n0 + r : n0) * ldw + k0 + ch * 8, vb);
+        }
+    };
+
+    float acc[4][4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[i][j][e] = 0.f;
+
+#pragma unroll
+    for (int s = 0; s < kGemmStages - 1; ++s) {
+        if (s < nk) issue(s);
+        cp_async_commit();
+    }
+    // weight-tile row of the first of each pair of n-fragments owned by this warp
+    const int brow0 = swi ? wn * 16 : wn * 32, brow1 = swi ? 64 + wn * 16 : wn * 32 + 16;
+    for (int kt = 0; kt < nk; ++kt) {
+        cp_async_wait<kGemmStages - 2>();
+        compute_sync();
+        if (kt + kGemmStages - 1 < nk) issue(kt + kGemmStages - 1);
+        cp_async_commit();
+        const uint32_t a_base = smem_u32(sa + (kt % kGemmStages) * kGemmTileBytes);
+        const uint32_t b_base = smem_u32(sb + (kt % kGemmStages) * kGemmTileBytes);
+#pragma unroll
+        for (int kk = 0; kk < kGemmBK / 16; ++kk) {
+            uint32_t af[4][4], bf[4][2];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                ldmatrix_x4(a_base + (wm * 64 + i * 16 + (lane & 15)) * kGemmRowBytes + (kk * 16 + (lane >> 4) * 8) * 2,
+                            af[i][0], af[i][1], af[i][2], af[i][3]);
+#pragma unroll
+            for (int pr = 0; pr < 2; ++pr) {
+                const int row = (pr ? brow1 : brow0) + (lane & 7) + (lane >> 4) * 8;
+                ldmatrix_x4(b_base + row * kGemmRowBytes + (kk * 16 + ((lane >> 3) & 1) * 8) * 2, bf[pr * 2][0],
+                            bf[pr * 2][1], bf[pr * 2 + 1][0], bf[pr * 2 + 1][1]);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) mma_bf16(acc[i][j], af[i], bf[j][0], bf[j][1]);
+        }
+    }
+    cp_async_wait<0>();
+
+    // ---- epilogue: thread holds rows (lane/4, +8) and column pairs 2*(lane%4) of each fragment ----
+    const int n_out = swi ? N / 2 : N;
+    const int col_base = swi ? in.arg(1) * 64 + wn * 16 : n0 + wn * 32;
+    void* O = reinterpret_cast<void*>(op->ptr[2]);
+    const long long ldo = op->ld[2];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+#pragma unroll
+        for (int hrow = 0; hrow < 2; ++hrow) {
+            const int r = m0 + wm * 64 + i * 16 + (lane >> 2) + hrow * 8;
+            if (r >= M) continue;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (swi && j >= 2) continue;
+                const int col = col_base + j * 8 + (lane & 3) * 2;
+                if (col >= n_out) continue;
+                float v0 = acc[i][j][hrow * 2], v1 = acc[i][j][hrow * 2 + 1];
+                if (swi) {
+                    const float u0 = acc[i][j + 2][hrow * 2], u1 = acc[i][j + 2][hrow * 2 + 1];
+                    v0 = v0 * sigmoidf_(v0) * u0;
+                    v1 = v1 * sigmoidf_(v1) * u1;
+                } else if (!accum) {
+                    if (op->ptr[3]) {
+                        const __nv_bfloat16* bias = reinterpret_cast<const __nv_bfloat16*>(op->ptr[3]);
+                        v0 += __bfloat162float(bias[col]);
+                        v1 += __bfloat162float(bias[col + 1]);
+                    }
+                    v0 = apply_act(act, v0);
+                    v1 = apply_act(act, v1);
+                    if (op->ptr[4]) {
+                        const void* R = reinterpret_cast<const void*>(op->ptr[4]);
+                        v0 += load1(R, (long long)r * op->ld[4] + col, rdt);
+                        v1 += load1(R, (long long)r * op->ld[4] + col + 1, rdt);
+                    }
+                }
+                const long long e = (long long)r * ldo + col;
+                if (accum) {
+                    if (odt == 1) red_add_f32x2(reinterpret_cast<float*>(O) + e, v0, v1);
+                    else red_add_bf16x2(reinterpret_cast<__nv_bfloat16*>(O) + e, v0, v1);
+                } else if (odt == 1) {
+                    *reinterpret_cast<float2*>(reinterpret_cast<float*>(O) + e) = make_float2(v0, v1);
+                } else {
+                    *reinterpret_cast<uint32_t*>(reinterpret_cast<__nv_bfloat16*>(O) + e) = pack2(v0, v1);
+                }
+            }
+        }
+    }
+    compute_sync();          // the tile buffers are free for the next instruction
+}
+
 }  // namespace mk
