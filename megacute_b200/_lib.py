@@ -14,9 +14,13 @@ import subprocess
 
 PKG = pathlib.Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
-LIB_PATH = PKG / "libmegacute_b200.so"
-NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-shared",
-              "-Xcompiler", "-fPIC"]
+LIB_PATH = pathlib.Path(os.environ.get("MEGACUTE_B200_LIB", PKG / "libmegacute_b200.so"))
+# Relocatable device code: each op body is its own translation unit so that ptxas allocates its
+# registers independently (csrc/ops.cuh says why).  -maxrregcount is the cap of a 9-warp CTA
+# (three warps share one SM sub-partition's 16 K registers); callees in other translation units do
+# not see the kernel's __launch_bounds__.
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-rdc=true",
+              "-maxrregcount=168", "-shared", "-Xcompiler", "-fPIC"]
 
 ST_WORDS = 16
 MAX_PTRS = 12
@@ -74,7 +78,7 @@ def build(force: bool = False, verbose: bool = False) -> pathlib.Path:
     if not force and not needs_build():
         return LIB_PATH
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
-    cmd = [nvcc, *NVCC_FLAGS, "-o", str(LIB_PATH), str(CSRC / "megakernel.cu")]
+    cmd = [nvcc, *NVCC_FLAGS, "-o", str(LIB_PATH), *[str(f) for f in sorted(CSRC.glob("*.cu"))]]
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")

@@ -13,9 +13,9 @@ NUM_THREADS = COMPUTE_THREADS + 32
 # ---- weight-streaming GEMV path (linear with <= 8 activation rows)
 GEMV_MAX_ROWS = 8
 GEMV_XBUF_BYTES = 65536         # fp32 copy of the activation rows held in shared memory
-GEMV_ROWS_PER_STAGE = 8         # weight rows per ring stage
-GEMV_KCHUNK = 2048              # elements of a weight row per stage (8 per compute thread)
-GEMV_STAGE_BYTES = GEMV_ROWS_PER_STAGE * GEMV_KCHUNK * 2
+GEMV_ROWS_PER_STAGE = 16        # weight rows per ring stage
+GEMV_SEGMENT = 1024             # elements of a weight row per stage
+GEMV_STAGE_BYTES = GEMV_ROWS_PER_STAGE * (GEMV_SEGMENT * 2 + 16)
 GEMV_STAGES = 4
 
 # ---- tile GEMM path

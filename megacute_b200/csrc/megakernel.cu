@@ -14,16 +14,13 @@
 #include <new>
 
 #include "mk_device.cuh"
-#include "op_decode.cuh"
-#include "op_gemm.cuh"
-#include "op_attention.cuh"
-#include "op_gemv.cuh"
-#include "op_pointwise.cuh"
+#include "op_gemv_common.cuh"
+#include "ops.cuh"
 
 namespace mk {
 
 template <bool TRACE>
-__global__ void __launch_bounds__(kThreads, 1) megakernel(const Params p) {
+__global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant__ Params p) {
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* ring = smem;
     uint8_t* work = smem + kRingBytes;
@@ -47,13 +44,13 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const Params p) {
         int slot = 0;
         for (int idx = blockIdx.x; idx < p.n_insts; idx += gridDim.x, ++slot) {
             const Inst in = fetch_inst(p, idx);
-            const int opi = in.op() - 1;
+            const int opi = in.opi - 1;
             if (opi < 0 || opi >= p.n_ops) break;
             const mk_op_desc* op = p.ops + opi;
             if (op->kind != MK_OP_GEMV) continue;
             const long long t0 = TRACE ? (long long)globaltimer() : 0;
-            if (!gemv_produce(p, c, ring, op, in, pos)) break;
-            if ((threadIdx.x & 31) == 0) trace_rec<TRACE>(p, 0, slot, in.seq(), t0, t0, (long long)globaltimer());
+            if (!gemv_produce(p, c, ring, op, in.a0, in.a1, in.seq, pos)) break;
+            if ((threadIdx.x & 31) == 0) trace_rec<TRACE>(p, 0, slot, in.seq, t0, t0, (long long)globaltimer());
         }
     } else {
         // ---------------- compute warps ----------------
@@ -61,55 +58,46 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const Params p) {
         int slot = 0;
         for (int idx = blockIdx.x; idx < p.n_insts; idx += gridDim.x, ++slot) {
             const Inst in = fetch_inst(p, idx);
-            const int opi = in.op() - 1;
+            const int opi = in.opi - 1;
             if (opi < 0 || opi >= p.n_ops) {
-                if (threadIdx.x == 0) report(p, c, MK_DEV_BAD_INST, in.seq(), 0, in.op(), idx, 0);
+                if (threadIdx.x == 0) report(p, c, MK_DEV_BAD_INST, in.seq, 0, in.opi, idx, 0);
                 break;
             }
             const mk_op_desc* op = p.ops + opi;
             const long long t0 = TRACE ? (long long)globaltimer() : 0;
-            if (wait_deps(p, c, in)) break;
-            const long long t1 = TRACE ? (long long)globaltimer() : 0;
-            bool bad = false;
-            {
-                switch (op->kind) {
-                    case MK_OP_GEMV: {
-                        const int M = op->i[0];
-                        if (M <= 1) gemv_compute<1>(p, c, ring, work, op, in, pos);
-                        else if (M <= 2) gemv_compute<2>(p, c, ring, work, op, in, pos);
-                        else if (M <= 4) gemv_compute<4>(p, c, ring, work, op, in, pos);
-                        else gemv_compute<8>(p, c, ring, work, op, in, pos);
-                        break;
+            // the single-row streaming linear and decode attention wait for their dependencies
+            // themselves, after requesting what depends on nothing in this launch
+            const bool self_wait = (op->kind == MK_OP_GEMV && (op->flags & GEMV_F_UNITS)) || op->kind == MK_OP_DECODE_ATTN;
+            if (!self_wait && wait_deps(p, c, in.nwait, in.wait_off, in.seq)) break;
+            long long t1 = TRACE ? (long long)globaltimer() : 0;
+            const int ppos = pos.stage | ((int)pos.phase << 8);
+            int npos = ppos;
+            bool known = true;
+            switch (op->kind) {
+                case MK_OP_GEMV:
+                    if (op->flags & GEMV_F_UNITS) {
+                        npos = mk_op_gemv_units(p, op, in.a0, in.a1, in.seq, ppos, in.nwait, in.wait_off);
+                        if (TRACE) t1 = c->t_dep;
+                    } else {
+                        npos = mk_op_gemv_general(p, op, in.a0, in.a1, in.seq, ppos);
                     }
-                    case MK_OP_GEMM: op_gemm(op, in, work); break;
-                    case MK_OP_FINALIZE: op_finalize(op, in); break;
-                    case MK_OP_ELTWISE: op_eltwise(op, in); break;
-                    case MK_OP_NORM: op_norm(op, in, work); break;
-                    case MK_OP_ATTENTION:
-                        if (op->i[5] == 64) op_attention<64>(op, in, work);
-                        else op_attention<128>(op, in, work);
-                        break;
-                    case MK_OP_ROPE_APPEND: op_rope_append(op, in); break;
-                    case MK_OP_DECODE_ATTN: {
-                        const int D = op->i[3], G = op->i[1] / op->i[2];
-                        if (D == 64) {
-                            if (G <= 4) op_decode_attn<64, 4>(p, c, op, in, work);
-                            else op_decode_attn<64, 8>(p, c, op, in, work);
-                        } else {
-                            if (G <= 4) op_decode_attn<128, 4>(p, c, op, in, work);
-                            else op_decode_attn<128, 8>(p, c, op, in, work);
-                        }
-                        break;
-                    }
-                    case MK_OP_INCREMENT: op_increment(op); break;
-                    default: bad = true; break;
-                }
+                    break;
+                case MK_OP_GEMM: mk_op_gemm(op, in.a0, in.a1, in.a2); break;
+                case MK_OP_ATTENTION: mk_op_attention(op, in.a0, in.a1, in.a2); break;
+                case MK_OP_DECODE_ATTN:
+                    mk_op_decode_attn(p, op, in.a0, in.a1, in.a2, in.nwait, in.wait_off, in.seq);
+                    if (TRACE) t1 = c->t_dep;
+                    break;
+                default: known = mk_op_pointwise(op, in.a0, in.a1); break;
             }
-            if (bad) {
-                if (threadIdx.x == 0) report(p, c, MK_DEV_BAD_INST, in.seq(), 1, op->kind, idx, 0);
+            if (!known && threadIdx.x == 0) report(p, c, MK_DEV_BAD_INST, in.seq, 1, op->kind, idx, 0);
+            pos.stage = npos & 0xff;
+            pos.phase = (uint32_t)(npos >> 8);
+            const bool aborting = publish(p, c, in.narrive, in.arrive_off);
+            if (threadIdx.x == 0) {
+                trace_rec<TRACE>(p, 1, slot, in.seq, t0, t1, (long long)globaltimer());
+                if (TRACE && self_wait) trace_rec<TRACE>(p, 2, slot, in.seq, c->t_phase[0], c->t_phase[1], c->t_phase[2]);
             }
-            const bool aborting = publish(p, c, in);
-            if (threadIdx.x == 0) trace_rec<TRACE>(p, 1, slot, in.seq(), t0, t1, (long long)globaltimer());
             if (aborting) break;
         }
     }
@@ -236,7 +224,7 @@ int mk_program_create(int device, const int32_t* insts, int n_insts, const int32
     MK_TRY(cudaMemset(p->d_status, 0, MK_ST_WORDS * 4));
     MK_TRY(cudaMallocHost(&p->h_status, MK_ST_WORDS * 4));
     if (trace_cap > 0) {
-        size_t words = (size_t)grid * 2 * trace_cap * 4;
+        size_t words = (size_t)grid * mk::kTraceRoles * trace_cap * 4;
         MK_TRY(cudaMalloc(&p->d_trace, words * 8));
         MK_TRY(cudaMemset(p->d_trace, 0, words * 8));
     }
@@ -323,7 +311,7 @@ int mk_program_read_counters(mk_program* p, int32_t* out, int n) {
 
 int mk_program_read_trace(mk_program* p, int64_t* out, size_t n_words) {
     if (!p || !out || !p->d_trace) return MK_E_ARG;
-    if (n_words > (size_t)p->grid * 2 * p->trace_cap * 4) return MK_E_ARG;
+    if (n_words > (size_t)p->grid * mk::kTraceRoles * p->trace_cap * 4) return MK_E_ARG;
     MK_CUDA(cudaMemcpy(out, p->d_trace, n_words * 8, cudaMemcpyDeviceToHost));
     return MK_OK;
 }
@@ -331,7 +319,7 @@ int mk_program_read_trace(mk_program* p, int64_t* out, size_t n_words) {
 int mk_program_clear_trace(mk_program* p, void* stream) {
     if (!p) return MK_E_ARG;
     if (!p->d_trace) return MK_OK;
-    MK_CUDA(cudaMemsetAsync(p->d_trace, 0, (size_t)p->grid * 2 * p->trace_cap * 4 * 8, (cudaStream_t)stream));
+    MK_CUDA(cudaMemsetAsync(p->d_trace, 0, (size_t)p->grid * mk::kTraceRoles * p->trace_cap * 4 * 8, (cudaStream_t)stream));
     return MK_OK;
 }
 

@@ -19,9 +19,14 @@ constexpr int kProducerWarp = kComputeWarps;
 // ---- shared memory map -----------------------------------------------------------------------
 constexpr int kGemvRows = 8;                              // weight rows per ring stage
 constexpr int kGemvKChunk = 2048;                         // elements of a row per stage (8 per thread)
-constexpr int kStageBytes = kGemvRows * kGemvKChunk * 2;  // 32 KB
+// A ring stage holds 16 weight-row segments of 1024 elements, each padded by 16 bytes so that the
+// 8 rows an ldmatrix touches fall in different banks (tensor-core path), or 8 rows x 2048 elements
+// (general path).
+constexpr int kSegElems = 1024;
+constexpr int kSegStride = kSegElems * 2 + 16;            // bytes between row segments of a stage
+constexpr int kStageBytes = 16 * kSegStride;              // 33 024 B
 constexpr int kStages = 4;
-constexpr int kRingBytes = kStages * kStageBytes;         // 128 KB, written only by bulk copies
+constexpr int kRingBytes = kStages * kStageBytes;         // 129 KB, written only by bulk copies
 constexpr int kWorkBytes = 96 * 1024;                     // scratch of the instruction being executed
 constexpr int kXbufBytes = 64 * 1024;                     // GEMV: fp32 activation rows (front of work)
 constexpr int kCtrlBytes = 1024;                          // mbarriers, flags
@@ -35,7 +40,7 @@ struct Params {
     int* counters;
     const mk_op_desc* ops;
     int n_ops;
-    long long* trace;             // [grid][2 roles][cap][4] or null
+    long long* trace;             // [grid][kTraceRoles][cap][4] or null
     int trace_cap;
     int* status;                  // MK_ST_WORDS words; word 0 != 0 aborts every waiter
     int epoch;
@@ -47,7 +52,11 @@ struct Ctrl {                     // lives in the last kCtrlBytes of shared memo
     unsigned long long empty[kStages];
     int abort;                    // set once a wait of this CTA gave up or saw the global abort
     int flag;                     // scratch broadcast word (split-KV last arriver)
+    long long t_dep;              // tracing: when the dependencies of the current instruction were met
+    long long t_phase[3];         // tracing: op-internal phase marks (role 2 records)
 };
+constexpr int kTraceRoles = 3;    // 0 producer, 1 compute, 2 op-internal phases
+__device__ __forceinline__ void phase_mark(const Params& p, Ctrl* c, int k);
 
 // ---- small PTX wrappers ------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -177,14 +186,16 @@ __device__ __forceinline__ float warp_max(float v) {
     return v;
 }
 
-// load 8 consecutive elements as fp32 from a bf16 (dtype 0) or fp32 (dtype 1) row; 16-byte aligned
+// load 8 consecutive elements as fp32 from a bf16 (dtype 0) or fp32 (dtype 1) row; 16-byte aligned.
+// Loads go to L2 (ld.global.cg): activations are rewritten by other SMs inside one launch and L1
+// is not coherent, so a line cached by an earlier instruction of this SM could be stale.
 __device__ __forceinline__ void load8(const void* base, long long elem, int dtype, float* f) {
     if (dtype == 0) {
-        uint4 v = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(base) + elem);
+        uint4 v = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(base) + elem));
         unpack8(v, f);
     } else {
         const float4* p = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + elem);
-        float4 a = p[0], b = p[1];
+        float4 a = __ldcg(p), b = __ldcg(p + 1);
         f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
     }
 }
@@ -198,8 +209,11 @@ __device__ __forceinline__ void store8(void* base, long long elem, int dtype, co
     }
 }
 __device__ __forceinline__ float load1(const void* base, long long elem, int dtype) {
-    return dtype == 0 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(base)[elem])
-                      : reinterpret_cast<const float*>(base)[elem];
+    if (dtype == 0) {
+        const unsigned short u = __ldcg(reinterpret_cast<const unsigned short*>(base) + elem);
+        return __uint_as_float((uint32_t)u << 16);
+    }
+    return __ldcg(reinterpret_cast<const float*>(base) + elem);
 }
 __device__ __forceinline__ void store1(void* base, long long elem, int dtype, float v) {
     if (dtype == 0) reinterpret_cast<__nv_bfloat16*>(base)[elem] = __float2bfloat16_rn(v);
@@ -212,7 +226,7 @@ __device__ __forceinline__ void store1(void* base, long long elem, int dtype, fl
 // who gave up (first writer wins), raises the global abort word so every other waiter leaves too,
 // and returns false.  Callers keep going through their barriers and leave at the next uniform
 // check of Ctrl::abort, so a failed launch always terminates and the context stays usable.
-__device__ __noinline__ void report(const Params& p, Ctrl* c, int code, int seq, int where, int a, int b, int cc) {
+__device__ __forceinline__ void report(const Params& p, Ctrl* c, int code, int seq, int where, int a, int b, int cc) {
     c->abort = 1;
     if (atomicCAS(&p.status[MK_ST_CODE], 0, code) == 0) {
         p.status[MK_ST_CTA] = blockIdx.x;
@@ -267,24 +281,19 @@ __device__ __forceinline__ bool wait_counter(const Params& p, Ctrl* c, int count
     }
 }
 
-// Instruction word accessors
+// One decoded instruction, held in registers (never address-taken, so it is never demoted to
+// local memory: with 227 KB of the SM given to shared memory the L1 left for local traffic is tiny).
 struct Inst {
-    int4 w[4];
-    __device__ __forceinline__ int op() const { return w[0].x; }
-    __device__ __forceinline__ int arg(int k) const {
-        const int* a = reinterpret_cast<const int*>(w);
-        return a[1 + k];
-    }
-    __device__ __forceinline__ int nwait() const { return w[2].x; }
-    __device__ __forceinline__ int wait_off() const { return w[2].y; }
-    __device__ __forceinline__ int narrive() const { return w[2].z; }
-    __device__ __forceinline__ int arrive_off() const { return w[2].w; }
-    __device__ __forceinline__ int seq() const { return w[3].x; }
+    int opi;                      // 1 + op index
+    int a0, a1, a2, a3;           // op-specific arguments
+    int nwait, wait_off, narrive, arrive_off, seq;
 };
 __device__ __forceinline__ Inst fetch_inst(const Params& p, int idx) {
-    Inst i;
     const int4* src = p.insts + (long long)idx * 4;
-    i.w[0] = __ldg(src); i.w[1] = __ldg(src + 1); i.w[2] = __ldg(src + 2); i.w[3] = __ldg(src + 3);
+    const int4 w0 = __ldg(src), w1 = __ldg(src + 1), w2 = __ldg(src + 2), w3 = __ldg(src + 3);
+    Inst i;
+    i.opi = w0.x; i.a0 = w0.y; i.a1 = w0.z; i.a2 = w0.w; i.a3 = w1.x;
+    i.nwait = w2.x; i.wait_off = w2.y; i.narrive = w2.z; i.arrive_off = w2.w; i.seq = w3.x;
     return i;
 }
 
@@ -301,22 +310,25 @@ __device__ __forceinline__ bool compute_sync_or(int pred) {
 
 // All compute threads call this.  Threads take waits round-robin.  Returns (uniformly) whether
 // the CTA is aborting.
-__device__ __forceinline__ bool wait_deps(const Params& p, Ctrl* c, const Inst& in) {
-    const int n = in.nwait();
-    for (int k = threadIdx.x; k < n; k += kComputeThreads) {
-        int2 w = __ldg(p.waits + in.wait_off() + k);
-        wait_counter(p, c, w.x, w.y, in.seq());
+__device__ __forceinline__ bool wait_deps(const Params& p, Ctrl* c, int nwait, int wait_off, int seq) {
+    for (int k = threadIdx.x; k < nwait; k += kComputeThreads) {
+        int2 w = __ldg(p.waits + wait_off + k);
+        wait_counter(p, c, w.x, w.y, seq);
     }
     return compute_sync_or(*(volatile int*)&c->abort);
 }
 // All compute threads call this after their global writes of the instruction.  Returns
 // (uniformly) whether the CTA is aborting; arrivals are skipped in that case.
-__device__ __forceinline__ bool publish(const Params& p, Ctrl* c, const Inst& in) {
-    __threadfence();
+__device__ __forceinline__ bool publish(const Params& p, Ctrl* c, int narrive, int arrive_off) {
+    // The barrier orders every compute thread's global writes before the arriving threads'
+    // red.release.gpu, whose release is cumulative over them: no per-thread gpu-scope fence needed.
     if (compute_sync_or(*(volatile int*)&c->abort)) return true;
-    const int n = in.narrive();
-    for (int k = threadIdx.x; k < n; k += kComputeThreads) red_release_add(p.counters + __ldg(p.arrives + in.arrive_off() + k), 1);
+    for (int k = threadIdx.x; k < narrive; k += kComputeThreads) red_release_add(p.counters + __ldg(p.arrives + arrive_off + k), 1);
     return false;
+}
+
+__device__ __forceinline__ void phase_mark(const Params& p, Ctrl* c, int k) {
+    if (p.trace_cap > 0 && threadIdx.x == 0) c->t_phase[k] = (long long)globaltimer();
 }
 
 template <bool TRACE>
@@ -324,7 +336,7 @@ __device__ __forceinline__ void trace_rec(const Params& p, int role, int slot, l
                                           long long t2) {
     if constexpr (TRACE) {
         if (slot < p.trace_cap) {
-            long long* r = p.trace + (((long long)blockIdx.x * 2 + role) * p.trace_cap + slot) * 4;
+            long long* r = p.trace + (((long long)blockIdx.x * kTraceRoles + role) * p.trace_cap + slot) * 4;
             r[0] = seq; r[1] = t0; r[2] = t1; r[3] = t2;
         }
     }

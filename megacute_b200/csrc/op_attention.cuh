@@ -10,14 +10,14 @@
 // 6 causal; f 0 scale.  args: 0 b, 1 h, 2 query tile.
 #pragma once
 #include "mk_device.cuh"
-#include "op_gemm.cuh"
+#include "mma.cuh"
 
 namespace mk {
 
 constexpr int kAttnBQ = 128, kAttnBK = 64;
 
 template <int D>
-__device__ __noinline__ void op_attention(const mk_op_desc* op, const Inst& in, uint8_t* work) {
+static __device__ __noinline__ void op_attention(const mk_op_desc* op, int a0, int a1, int a2, uint8_t* work) {
     constexpr int ROWB = D * 2 + 16;                       // padded row: conflict-free ldmatrix
     constexpr int KT_BYTES = kAttnBK * ROWB;               // one K or V tile
     constexpr int CPR = D / 8;                             // 16-byte chunks per row
@@ -25,7 +25,7 @@ __device__ __noinline__ void op_attention(const mk_op_desc* op, const Inst& in, 
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     const int Sq = op->i[1], Sk = op->i[2], H = op->i[3], KVH = op->i[4];
     const bool causal = op->i[6] != 0;
-    const int b = in.arg(0), h = in.arg(1), qi = in.arg(2);
+    const int b = a0, h = a1, qi = a2;
     const int hk = h / (H / KVH);
     const float sl2 = op->f[0] * kLog2e;
     const __nv_bfloat16* Q = reinterpret_cast<const __nv_bfloat16*>(op->ptr[0]) + (long long)b * Sq * op->ld[0] + h * D;

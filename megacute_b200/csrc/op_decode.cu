@@ -1,0 +1,18 @@
+// Translation unit of MK_OP_DECODE_ATTN.
+#include "op_decode.cuh"
+#include "ops.cuh"
+
+namespace mk {
+__device__ void mk_op_decode_attn(const Params& p, const mk_op_desc* op, int a0, int a1, int a2, int nwait, int wait_off,
+                                  int seq) {
+    const SmemMap m = smem_map();
+    const int D = op->i[3], G = op->i[1] / op->i[2];
+    if (D == 64) {
+        if (G <= 4) op_decode_attn<64, 4>(p, m.ctrl, op, a0, a1, a2, m.work, nwait, wait_off, seq);
+        else op_decode_attn<64, 8>(p, m.ctrl, op, a0, a1, a2, m.work, nwait, wait_off, seq);
+    } else {
+        if (G <= 4) op_decode_attn<128, 4>(p, m.ctrl, op, a0, a1, a2, m.work, nwait, wait_off, seq);
+        else op_decode_attn<128, 8>(p, m.ctrl, op, a0, a1, a2, m.work, nwait, wait_off, seq);
+    }
+}
+}  // namespace mk

@@ -6,12 +6,15 @@
 // G query heads of the kv head are held in registers.  With S > 1 every split writes an
 // unnormalised partial (O, running max, sum) and bumps an arrival count; the last split to arrive
 // merges the S partials and writes the output (no extra dependency hop).
+// Scores, probabilities and the rotated query stay fp32 (this path runs on CUDA cores, so the
+// reference's bf16 rounding of P and q before its tensor-core products is not needed); the
+// appended k and v are rounded to the cache's bf16 and the new token is scored with those values.
 // Fused mode (rope_append folded in): q, k_new, v_new are the un-rotated columns of the QKV row;
 // the op rotates q and k at pos, the last split also attends the new token from registers and
 // appends k, v to cache row b * max_seq + pos (reference semantics: graph.py:412-418).
 //
 // ptr 0 q, 1 k_cache, 2 v_cache, 3 pos, 4 out, 5 k_new, 6 v_new, 7 cos, 8 sin, 9 part, 10 count
-// i 0 B, 1 H, 2 KVH, 3 D, 4 max_seq, 5 splits, 6 fused, 7 dtype of q / k_new / v_new;  f 0 scale
+// i 0 B, 1 H, 2 KVH, 3 D, 4 max_seq, 5 splits, 6 fused, 7 dtype of q / k_new / v_new, 8 out dtype;  f 0 scale
 // args: 0 b, 1 kv head, 2 split
 #pragma once
 #include "mk_device.cuh"
@@ -19,10 +22,11 @@
 namespace mk {
 
 constexpr int kDecTileKeys = 64;
+constexpr int kMaxKvSplits = 32;          // config.py MAX_KV_SPLITS
 
 template <int D, int GMAX>
-__device__ __noinline__ void op_decode_attn(const Params& p, Ctrl* c, const mk_op_desc* op, const Inst& in,
-                                               uint8_t* work) {
+static __device__ __noinline__ void op_decode_attn(const Params& p, Ctrl* c, const mk_op_desc* op, int a0, int a1, int a2,
+                                                   uint8_t* work, int nwait, int wait_off, int seq) {
     constexpr int DP = D / 8;                         // threads per key (8 dims each)
     constexpr int KPP = kComputeThreads / DP;         // keys per pass
     constexpr int PASSES = kDecTileKeys / KPP;
@@ -36,7 +40,7 @@ __device__ __noinline__ void op_decode_attn(const Params& p, Ctrl* c, const mk_o
     const int H = op->i[1], KVH = op->i[2], L = op->i[4], S = op->i[5], qdt = op->i[7];
     const bool fused = op->i[6] != 0;
     const int G = H / KVH;
-    const int b = in.arg(0), kvh = in.arg(1), s = in.arg(2);
+    const int b = a0, kvh = a1, s = a2;
     const int pos = *reinterpret_cast<const int*>(op->ptr[3]);
     const int n = fused ? pos : pos + 1;
     const int per = (n + S - 1) / S;
@@ -51,6 +55,7 @@ __device__ __noinline__ void op_decode_attn(const Params& p, Ctrl* c, const mk_o
     float* sM = sP + GMAX * kDecTileKeys;                                 // running max   [GMAX]
     float* sL = sM + GMAX;                                                // running sum   [GMAX]
     float* sA = sL + GMAX;                                                // rescale       [GMAX]
+    float* snew = sA + GMAX;                                              // new token: k [D], v [D]
     float* ored = reinterpret_cast<float*>(work);                         // [KPP][G*D] after the loop
 
     const __nv_bfloat16* kc = reinterpret_cast<const __nv_bfloat16*>(op->ptr[1]);
@@ -73,60 +78,74 @@ __device__ __noinline__ void op_decode_attn(const Params& p, Ctrl* c, const mk_o
     };
 
     const int ntiles = (k_end - k_begin + kDecTileKeys - 1) / kDecTileKeys;
+    // Fused mode reads only cache rows below pos, which nothing in this launch writes: the first
+    // tiles and the rope table row are requested before the dependency wait (the op waits for its
+    // own dependencies).  Unfused mode may read the row a RopeAppend of this launch wrote, so it
+    // waits first.
+    if (!fused && wait_deps(p, c, nwait, wait_off, seq)) return;
 #pragma unroll
     for (int i = 0; i < NST - 1; ++i) {
         if (i < ntiles) issue_tile(i);
         cp_async_commit();
     }
+    const int pd = dp < DP / 2 ? dp * 8 + half : dp * 8 - half;     // partner chunk of the rotation
+    const float sign = dp < DP / 2 ? -1.f : 1.f;
+    float cs[8], sn[8];
+    if (fused) {
+        load8(reinterpret_cast<const __nv_bfloat16*>(op->ptr[7]) + (long long)pos * op->ld[7], dp * 8, 0, cs);
+        load8(reinterpret_cast<const __nv_bfloat16*>(op->ptr[8]) + (long long)pos * op->ld[8], dp * 8, 0, sn);
+    }
+    if (t < GMAX) { sM[t] = NEG_INF; sL[t] = 0.f; }
+    if (fused && wait_deps(p, c, nwait, wait_off, seq)) {
+        cp_async_wait<0>();
+        return;
+    }
+    if (t == 0 && p.trace_cap > 0) c->t_dep = (long long)globaltimer();
 
-    // ---- query heads into registers (rotated when fused), pre-scaled to the log2 domain ----
+    // ---- query heads into registers (rotated when fused), pre-scaled to the log2 domain.  All
+    // loads of a batch of four heads are issued before any is used: one L2 round trip per batch. ----
     float qf[GMAX][8];
-    float kn[8], vn[8];                                    // new token's k (rotated) and v chunk
     const float qscale = op->f[0] * kLog2e;
     {
         const void* q = reinterpret_cast<const void*>(op->ptr[0]);
-        const __nv_bfloat16* cosr = nullptr;
-        const __nv_bfloat16* sinr = nullptr;
-        float cs[8], sn[8];
-        const int pd = dp < DP / 2 ? dp * 8 + half : dp * 8 - half;     // partner chunk
-        const float sign = dp < DP / 2 ? -1.f : 1.f;
-        if (fused) {
-            cosr = reinterpret_cast<const __nv_bfloat16*>(op->ptr[7]) + (long long)pos * op->ld[7];
-            sinr = reinterpret_cast<const __nv_bfloat16*>(op->ptr[8]) + (long long)pos * op->ld[8];
-            load8(cosr, dp * 8, 0, cs);
-            load8(sinr, dp * 8, 0, sn);
-        }
-#pragma unroll
-        for (int g = 0; g < GMAX; ++g) {
-            if (g < G) {
-                const long long e0 = (long long)b * op->ld[0] + (kvh * G + g) * D;
-                load8(q, e0 + dp * 8, qdt, qf[g]);
-                if (fused) {
-                    float o[8];
-                    load8(q, e0 + pd, qdt, o);
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) qf[g][e] = round_bf16(qf[g][e] * cs[e] + sign * o[e] * sn[e]);
-                }
-#pragma unroll
-                for (int e = 0; e < 8; ++e) qf[g][e] *= qscale;
-            } else {
-#pragma unroll
-                for (int e = 0; e < 8; ++e) qf[g][e] = 0.f;
-            }
-        }
+        float kn[8], ko[8], vn[8];
         if (has_new) {
-            float o[8];
             const long long ek = (long long)b * op->ld[5] + kvh * D, ev = (long long)b * op->ld[6] + kvh * D;
             load8(reinterpret_cast<const void*>(op->ptr[5]), ek + dp * 8, qdt, kn);
-            load8(reinterpret_cast<const void*>(op->ptr[5]), ek + pd, qdt, o);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) kn[e] = round_bf16(kn[e] * cs[e] + sign * o[e] * sn[e]);
+            load8(reinterpret_cast<const void*>(op->ptr[5]), ek + pd, qdt, ko);
             load8(reinterpret_cast<const void*>(op->ptr[6]), ev + dp * 8, qdt, vn);
+        }
 #pragma unroll
-            for (int e = 0; e < 8; ++e) vn[e] = round_bf16(vn[e]);
+        for (int gb = 0; gb < GMAX; gb += 4) {
+            float a[4][8], o[4][8];
+#pragma unroll
+            for (int g4 = 0; g4 < 4; ++g4) {
+                const int g = gb + g4;
+                if (g < G) {
+                    const long long e0 = (long long)b * op->ld[0] + (kvh * G + g) * D;
+                    load8(q, e0 + dp * 8, qdt, a[g4]);
+                    if (fused) load8(q, e0 + pd, qdt, o[g4]);
+                }
+            }
+#pragma unroll
+            for (int g4 = 0; g4 < 4; ++g4) {
+                const int g = gb + g4;
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    float v = 0.f;
+                    if (g < G) v = fused ? a[g4][e] * cs[e] + sign * o[g4][e] * sn[e] : a[g4][e];
+                    qf[g][e] = v * qscale;
+                }
+            }
+        }
+        if (has_new && kg == 0) {          // new token's rotated k and its v wait in shared memory
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                snew[dp * 8 + e] = round_bf16(kn[e] * cs[e] + sign * ko[e] * sn[e]);
+                snew[D + dp * 8 + e] = round_bf16(vn[e]);
+            }
         }
     }
-    if (t < GMAX) { sM[t] = NEG_INF; sL[t] = 0.f; }
 
     float oacc[GMAX][8];
 #pragma unroll
@@ -134,6 +153,7 @@ __device__ __noinline__ void op_decode_attn(const Params& p, Ctrl* c, const mk_o
 #pragma unroll
         for (int e = 0; e < 8; ++e) oacc[g][e] = 0.f;
 
+#pragma unroll 1
     for (int tile = 0; tile < ntiles; ++tile) {
         if (tile + NST - 1 < ntiles) issue_tile(tile + NST - 1);
         cp_async_commit();
@@ -168,8 +188,8 @@ __device__ __noinline__ void op_decode_attn(const Params& p, Ctrl* c, const mk_o
             const float s0 = sS[warp * kDecTileKeys + lane], s1 = sS[warp * kDecTileKeys + lane + 32];
             const float mo = sM[warp];
             const float mn = fmaxf(mo, warp_max(fmaxf(s0, s1)));
-            const float p0 = s0 == NEG_INF ? 0.f : round_bf16(ex2(s0 - mn));
-            const float p1 = s1 == NEG_INF ? 0.f : round_bf16(ex2(s1 - mn));
+            const float p0 = s0 == NEG_INF ? 0.f : ex2(s0 - mn);
+            const float p1 = s1 == NEG_INF ? 0.f : ex2(s1 - mn);
             sP[warp * kDecTileKeys + lane] = p0;
             sP[warp * kDecTileKeys + lane + 32] = p1;
             const float sum = warp_sum(p0 + p1);
@@ -207,9 +227,13 @@ __device__ __noinline__ void op_decode_attn(const Params& p, Ctrl* c, const mk_o
         compute_sync();
     }
     cp_async_wait<0>();
+    phase_mark(p, c, 0);
 
     // ---- the new token (fused mode, last split): attend it from registers and append it ----
     if (has_new) {
+        float kn[8], vn[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) { kn[e] = snew[dp * 8 + e]; vn[e] = snew[D + dp * 8 + e]; }
         if (kg == 0) {
 #pragma unroll
             for (int g = 0; g < GMAX; ++g) {
@@ -222,7 +246,7 @@ __device__ __noinline__ void op_decode_attn(const Params& p, Ctrl* c, const mk_o
                     const float mo = sM[g];
                     const float mn = fmaxf(mo, a);
                     const float al = mo == NEG_INF ? 0.f : ex2(mo - mn);
-                    const float pn = round_bf16(ex2(a - mn));
+                    const float pn = ex2(a - mn);
                     sA[g] = al;
                     sP[g * kDecTileKeys] = pn;
                     sL[g] = sL[g] * al + pn;
@@ -258,14 +282,15 @@ __device__ __noinline__ void op_decode_attn(const Params& p, Ctrl* c, const mk_o
     }
     compute_sync();
     const int pair = b * KVH + kvh;
-    __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(op->ptr[4]) + (long long)b * op->ld[4] + kvh * GD;
+    void* outp = reinterpret_cast<void*>(op->ptr[4]);
+    const int odt = op->i[8];
     if (S == 1) {
         for (int idx = t; idx < GD; idx += kComputeThreads) {
             float a = 0.f;
 #pragma unroll 8
             for (int k = 0; k < KPP; ++k) a += ored[k * GD + idx];
             const float l = sL[idx / D];
-            out[idx] = __float2bfloat16_rn(l == 0.f ? 0.f : a * rcp(l));
+            store1(outp, (long long)b * op->ld[4] + kvh * GD + idx, odt, l == 0.f ? 0.f : a * rcp(l));
         }
         return;
     }
@@ -283,6 +308,7 @@ __device__ __noinline__ void op_decode_attn(const Params& p, Ctrl* c, const mk_o
     }
     __threadfence();
     compute_sync();
+    phase_mark(p, c, 1);
     int* count = reinterpret_cast<int*>(op->ptr[10]) + (long long)pair * op->ld[10];
     if (t == 0) {
         const int old = atomicAdd(count, 1);
@@ -290,21 +316,34 @@ __device__ __noinline__ void op_decode_attn(const Params& p, Ctrl* c, const mk_o
         if (old == S - 1) *count = 0;          // back to zero for the next launch
     }
     compute_sync();
+    phase_mark(p, c, 2);
     if (!c->flag) return;
     __threadfence();
+    // ---- last split to arrive: merge the S partials.  The S partial rows are copied into shared
+    // memory with one wave of cp.async (one L2 round trip), then every thread merges one output. ----
     const float* base = part + (long long)pair * S * ldp;
+    float* sp = reinterpret_cast<float*>(work);                 // [S][row_f] floats; tile buffers are free
+    const int row_f = (GD + 2 * G + 3) & ~3;                    // floats per partial row, 16-byte multiple
+    const int vec_per_row = row_f >> 2;
+    for (int v = t; v < S * vec_per_row; v += kComputeThreads) {
+        const int k = v / vec_per_row, j = v % vec_per_row;
+        cp_async16(sp + k * row_f + j * 4, base + k * ldp + j * 4, true);
+    }
+    cp_async_commit();
+    cp_async_wait<0>();
+    compute_sync();
     for (int idx = t; idx < GD; idx += kComputeThreads) {
         const int g = idx / D;
         float mx = NEG_INF;
-        for (int k = 0; k < S; ++k) mx = fmaxf(mx, __ldcg(base + k * ldp + GD + g));
+        for (int k = 0; k < S; ++k) mx = fmaxf(mx, sp[k * row_f + GD + g]);
         float a = 0.f, l = 0.f;
         for (int k = 0; k < S; ++k) {
-            const float mk_ = __ldcg(base + k * ldp + GD + g);
+            const float mk_ = sp[k * row_f + GD + g];
             const float w = mk_ == NEG_INF ? 0.f : ex2(mk_ - mx);
-            a = fmaf(w, __ldcg(base + k * ldp + idx), a);
-            l = fmaf(w, __ldcg(base + k * ldp + GD + G + g), l);
+            a = fmaf(w, sp[k * row_f + idx], a);
+            l = fmaf(w, sp[k * row_f + GD + G + g], l);
         }
-        out[idx] = __float2bfloat16_rn(l == 0.f ? 0.f : a * rcp(l));
+        store1(outp, (long long)b * op->ld[4] + kvh * GD + idx, odt, l == 0.f ? 0.f : a * rcp(l));
     }
 }
 

@@ -12,6 +12,7 @@
 // args: 0 m tile, 1 n tile, 2 k split
 #pragma once
 #include "mk_device.cuh"
+#include "mma.cuh"
 
 namespace mk {
 
@@ -19,37 +20,13 @@ constexpr int kGemmBM = 128, kGemmBN = 128, kGemmBK = 32, kGemmStages = 4;
 constexpr int kGemmRowBytes = kGemmBK * 2 + 16;                // padded: conflict-free ldmatrix
 constexpr int kGemmTileBytes = kGemmBM * kGemmRowBytes;        // 10 KB per operand per stage
 
-__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
-                 : "r"(addr));
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
-                 : "r"(addr));
-}
-__device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ void red_add_f32x2(float* p, float a, float b) {
-    asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(p), "f"(a), "f"(b) : "memory");
-}
-__device__ __forceinline__ void red_add_bf16x2(void* p, float a, float b) {
-    const uint32_t v = pack2(a, b);
-    asm volatile("red.global.add.noftz.bf16x2 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-
-__device__ __noinline__ void op_gemm(const mk_op_desc* op, const Inst& in, uint8_t* work) {
+static __device__ __noinline__ void op_gemm(const mk_op_desc* op, int a0, int a1, int a2, uint8_t* work) {
     const int M = op->i[0], N = op->i[1], K = op->i[2], act = op->i[3], splits = op->i[4];
     const int odt = op->i[5], accum = op->i[6], rdt = op->i[7], swi = op->i[8];
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     const int wm = warp >> 2, wn = warp & 3;
-    const int m0 = in.arg(0) * kGemmBM, n0 = in.arg(1) * kGemmBN;
-    const int kc = K / splits, kbeg = in.arg(2) * kc, nk = kc / kGemmBK;
+    const int m0 = a0 * kGemmBM, n0 = a1 * kGemmBN;
+    const int kc = K / splits, kbeg = a2 * kc, nk = kc / kGemmBK;
     const __nv_bfloat16* X = reinterpret_cast<const __nv_bfloat16*>(op->ptr[0]);
     const __nv_bfloat16* Wt = reinterpret_cast<const __nv_bfloat16*>(op->ptr[1]);
     const long long ldx = op->ld[0], ldw = op->ld[1];
@@ -116,7 +93,7 @@ __device__ __noinline__ void op_gemm(const mk_op_desc* op, const Inst& in, uint8
 
     // ---- epilogue: thread holds rows (lane/4, +8) and column pairs 2*(lane%4) of each fragment ----
     const int n_out = swi ? N / 2 : N;
-    const int col_base = swi ? in.arg(1) * 64 + wn * 16 : n0 + wn * 32;
+    const int col_base = swi ? a1 * 64 + wn * 16 : n0 + wn * 32;
     void* O = reinterpret_cast<void*>(op->ptr[2]);
     const long long ldo = op->ld[2];
 #pragma unroll

@@ -1,87 +1,17 @@
-// MK_OP_GEMV: linear with <= 8 activation rows, out = act(norm(x) @ w^T + bias) + residual.
-//
-// Pure weight streaming.  The producer warp copies weight rows into a ring of 32 KB stages with
-// 1-D bulk copies (one per row, completion counted on the stage's mbarrier) and runs ahead of the
-// compute warps across instruction boundaries, because weights never depend on anything in the
-// launch.  A stage holds 8 row slots x 2048 K-elements; compute thread t owns K-elements
-// [8t, 8t+8) of every slot, so its slice of the activation is loaded once per stage and reused
-// for the 8 rows.  Partial dot products are reduced across the CTA once per group of 8 rows.
-//
-// descriptor: ptr 0 x, 1 w, 2 out, 3 bias, 4 residual, 5 norm gain
-//             i 0 M, 1 N_out, 2 K, 3 act, 4 x dtype, 5 out dtype, 6 residual dtype
-//             f 0 rms eps; flags bit0 swiglu (w rows interleaved in 64-row gate/up blocks,
-//             slots 0-3 = gate rows and 4-7 = up rows of 4 outputs), bit1 rms-normalise x first
-// instruction args: 0 o0, 1 o1 -- the output columns [o0, o1) this instruction produces.
+// Compute-warp side of MK_OP_GEMV (see op_gemv_common.cuh for the layout and the producer side).
 #pragma once
-#include "mk_device.cuh"
+#include "op_gemv_common.cuh"
+#include "mma.cuh"
 
 namespace mk {
 
-constexpr int GEMV_F_SWIGLU = 1, GEMV_F_RMS = 2;
-
-struct RingPos {
-    int stage = 0;
-    uint32_t phase = 0;
-    __device__ __forceinline__ void advance() {
-        if (++stage == kStages) { stage = 0; phase ^= 1u; }
-    }
-};
-
-__device__ __forceinline__ int gemv_weight_row(bool swi, int o0, int group, int slot, int* out_col) {
-    if (!swi) {
-        int o = o0 + group * 8 + slot;
-        *out_col = o;
-        return o;
-    }
-    int o = o0 + group * 4 + (slot & 3);
-    *out_col = o;
-    return 128 * (o >> 6) + (o & 63) + ((slot >> 2) << 6);
-}
-
-// Producer warp: issue every stage of one GEMV instruction.  Returns false if a wait gave up.
-__device__ __noinline__ bool gemv_produce(const Params& p, Ctrl* c, uint8_t* ring, const mk_op_desc* op,
-                                             const Inst& in, RingPos& pos) {
-    const int lane = threadIdx.x & 31;
-    const int K = op->i[2];
-    const bool swi = op->flags & GEMV_F_SWIGLU;
-    const int o0 = in.arg(0), o1 = in.arg(1);
-    const int per = swi ? 4 : 8;
-    const int groups = (o1 - o0 + per - 1) / per;
-    const int nkc = (K + kGemvKChunk - 1) / kGemvKChunk;
-    const __nv_bfloat16* w = reinterpret_cast<const __nv_bfloat16*>(op->ptr[1]);
-    const long long ldw = op->ld[1];
-    for (int g = 0; g < groups; ++g) {
-        int col;
-        const int row = gemv_weight_row(swi, o0, g, lane & 7, &col);
-        const bool valid = lane < 8 && col < o1;
-        const int nvalid = swi ? 2 * min(4, o1 - o0 - g * 4) : min(8, o1 - o0 - g * 8);
-        for (int kc = 0; kc < nkc; ++kc) {
-            const int k0 = kc * kGemvKChunk;
-            const int kl = min(kGemvKChunk, K - k0);
-            bool ok = true;
-            if (lane == 0) {
-                ok = wait_barrier(p, c, &c->empty[pos.stage], pos.phase ^ 1u, in.seq(), WHERE_RING_EMPTY);
-                if (ok) mbar_arrive_expect_tx(&c->full[pos.stage], (uint32_t)(nvalid * kl * 2));
-            }
-            ok = __shfl_sync(0xffffffffu, ok, 0);
-            if (!ok) return false;
-            if (valid)
-                bulk_g2s(ring + pos.stage * kStageBytes + (lane & 7) * (kGemvKChunk * 2), w + row * ldw + k0,
-                         (uint32_t)(kl * 2), &c->full[pos.stage]);
-            pos.advance();
-        }
-    }
-    return true;
-}
-
 // Compute warps: consume the stages of one GEMV instruction.  MB = compile-time bound on M.
 template <int MB>
-__device__ __noinline__ void gemv_compute(const Params& p, Ctrl* c, uint8_t* ring, uint8_t* work,
-                                             const mk_op_desc* op, const Inst& in, RingPos& pos) {
+__device__ __forceinline__ RingPos gemv_compute(const Params& p, Ctrl* c, uint8_t* ring, uint8_t* work,
+                                                const mk_op_desc* op, int o0, int o1, int seq, RingPos pos) {
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     const int M = op->i[0], K = op->i[2], act = op->i[3];
     const bool swi = op->flags & GEMV_F_SWIGLU;
-    const int o0 = in.arg(0), o1 = in.arg(1);
     float* xs = reinterpret_cast<float*>(work);                          // [M][K] fp32
     float* red = reinterpret_cast<float*>(work + kXbufBytes);            // [2][8 warps][8 slots][MB]
     float* rowstat = red + 2 * kComputeWarps * 8 * MB;                   // [8 warps][MB] then [MB]
@@ -167,7 +97,7 @@ __device__ __noinline__ void gemv_compute(const Params& p, Ctrl* c, uint8_t* rin
                     }
                 }
             }
-            const bool ok = wait_barrier(p, c, &c->full[pos.stage], pos.phase, in.seq(), WHERE_RING_FULL);
+            const bool ok = wait_barrier(p, c, &c->full[pos.stage], pos.phase, seq, WHERE_RING_FULL);
             if (ok && active) {
                 const uint4* st = reinterpret_cast<const uint4*>(ring + pos.stage * kStageBytes) + t;
 #pragma unroll
@@ -217,6 +147,21 @@ __device__ __noinline__ void gemv_compute(const Params& p, Ctrl* c, uint8_t* rin
         }
         rb ^= 1;
     }
+    return pos;
+}
+
+// The general path behind one call: returns the advanced ring position packed as stage | phase << 8.
+static __device__ __noinline__ int gemv_general(const Params& p, Ctrl* c, uint8_t* ring, uint8_t* work, const mk_op_desc* op,
+                                        int o0, int o1, int seq, int stage, int phase) {
+    RingPos pos;
+    pos.stage = stage;
+    pos.phase = (uint32_t)phase;
+    const int M = op->i[0];
+    if (M <= 1) pos = gemv_compute<1>(p, c, ring, work, op, o0, o1, seq, pos);
+    else if (M <= 2) pos = gemv_compute<2>(p, c, ring, work, op, o0, o1, seq, pos);
+    else if (M <= 4) pos = gemv_compute<4>(p, c, ring, work, op, o0, o1, seq, pos);
+    else pos = gemv_compute<8>(p, c, ring, work, op, o0, o1, seq, pos);
+    return pos.stage | ((int)pos.phase << 8);
 }
 
 }  // namespace mk

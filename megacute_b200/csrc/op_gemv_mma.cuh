@@ -1,0 +1,271 @@
+// Compute-warp side of the tensor-core streaming linear (MK_OP_GEMV with GEMV_F_UNITS):
+//   out[m][o] = act(rstd[m] * sum_k w[o][k] * (x[m][k] * gain[k]) + bias[o]) + residual[m][o],  m < M <= 8
+// Stage layout, flag and producer side: op_gemv_common.cuh.
+//
+// Shared memory (work region):
+//   xh, xl   [M][K] bf16 high / low halves of x * gain, rows padded by 16 bytes (bank spread)
+//   red      [4 slots][8 warps][32 lanes] float4: per-warp partial 16 x 8 tiles of a row group
+//   gatebuf  [32 lanes] float4: swiglu gate tile between the gate group and the up group
+//   cnt      [4 slots] arrivals of the combine;  rowstat [8 warps][8 rows] partial sums of x^2
+#pragma once
+#include "mma.cuh"
+#include "op_gemv_common.cuh"
+
+namespace mk {
+
+constexpr int kMmaRedOff = 66 * 1024;                      // xh + xl take at most 64 KB + 256 B
+constexpr int kMmaGateOff = kMmaRedOff + 4 * 8 * 32 * 16;  // + 16 KB
+constexpr int kMmaCntOff = kMmaGateOff + 32 * 16;
+constexpr int kMmaStatOff = kMmaCntOff + 64;
+
+__device__ __forceinline__ float4 lds_volatile4(const float4* p) {
+    float4 v;
+    asm volatile("ld.volatile.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(smem_u32(p)) : "memory");
+    return v;
+}
+__device__ __forceinline__ void sts_volatile4(float4* p, float4 v) {
+    asm volatile("st.volatile.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(smem_u32(p)), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+
+// The op waits for its own dependencies so that loads which depend on nothing in the launch (the
+// norm gain) are already in flight when the wait ends.
+// SC = number of K segments whose B fragments (this warp's slices of x) stay in registers for the
+// whole instruction: 1 or 2 when K is exactly 1 or 2 segments, 0 = reload them from shared memory
+// every stage (longer or ragged K).
+template <int SC>
+__device__ __forceinline__ void gemv_mma(const Params& p, Ctrl* c, uint8_t* ring, uint8_t* work, const mk_op_desc* op,
+                                         int o0, int o1, int seq, RingPos& pos, int nwait, int wait_off) {
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const int M = op->i[0], K = op->i[2], act = op->i[3], odt = op->i[5], rdt = op->i[6];
+    const bool swi = op->flags & GEMV_F_SWIGLU, rms = op->flags & GEMV_F_RMS;
+    const int S = (K + kSegElems - 1) / kSegElems;
+    const int xs_stride = K * 2 + 16;                                         // bytes per padded row
+    uint8_t* xh = work;
+    uint8_t* xl = work + M * xs_stride;
+    float4* red = reinterpret_cast<float4*>(work + kMmaRedOff);
+    float4* gatebuf = reinterpret_cast<float4*>(work + kMmaGateOff);
+    int* cnt = reinterpret_cast<int*>(work + kMmaCntOff);
+    float* rowstat = reinterpret_cast<float*>(work + kMmaStatOff);
+
+    // ---- before the dependency wait: the norm gain of this thread's vectors (K <= 16384) ----
+    const int nv = K >> 3;
+    uint4 graw[8];
+    {
+        const uint4* gain = reinterpret_cast<const uint4*>(op->ptr[5]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int v = t + i * kComputeThreads;
+            graw[i] = (rms && gain && v < nv) ? __ldg(gain + v) : make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u);
+        }
+        if (t < 4) cnt[t] = 0;
+    }
+    if (wait_deps(p, c, nwait, wait_off, seq)) return;
+    if (t == 0 && p.trace_cap > 0) c->t_dep = (long long)globaltimer();
+
+    // ---- stage x * gain as bf16 high + low parts; accumulate sum(x^2) per row ----
+    {
+        const int xdt = op->i[4];
+        const void* x = reinterpret_cast<const void*>(op->ptr[0]);
+        const long long ldx = op->ld[0];
+        float ss[8];
+#pragma unroll
+        for (int m = 0; m < 8; ++m) {
+            ss[m] = 0.f;
+            if (m < M) {
+                // all loads of the row are issued before any is used: one L2 round trip per row
+                float f[8][8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int v = t + i * kComputeThreads;
+                    if (v < nv) load8(x, m * ldx + v * 8, xdt, f[i]);
+                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int v = t + i * kComputeThreads;
+                    if (v < nv) {
+                        float g[8], hi[8], lo[8];
+                        unpack8(graw[i], g);
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) {
+                            ss[m] += f[i][e] * f[i][e];
+                            const float y = f[i][e] * g[e];
+                            hi[e] = round_bf16(y);
+                            lo[e] = y - hi[e];
+                        }
+                        *reinterpret_cast<uint4*>(xh + m * xs_stride + v * 16) = pack8(hi);
+                        *reinterpret_cast<uint4*>(xl + m * xs_stride + v * 16) = pack8(lo);
+                    }
+                }
+            }
+        }
+        if (rms) {
+#pragma unroll
+            for (int m = 0; m < 8; ++m) {
+                if (m < M) {
+                    const float s = warp_sum(ss[m]);
+                    if (lane == 0) rowstat[warp * 8 + m] = s;
+                }
+            }
+        }
+        compute_sync();
+    }
+    phase_mark(p, c, 0);
+    // this lane's output columns of a 16 x 8 accumulator tile are activation rows m0 and m0 + 1
+    const int m0 = 2 * (lane & 3);
+    float rs[2] = {1.f, 1.f};
+    if (rms) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            if (m0 + j < M) {
+                float sq = 0.f;
+#pragma unroll
+                for (int w8 = 0; w8 < kComputeWarps; ++w8) sq += rowstat[w8 * 8 + m0 + j];
+                rs[j] = rsqrt_approx(sq / (float)K + op->f[0]);
+            }
+        }
+    }
+
+    const int n = o1 - o0;
+    const int ngroups = (swi ? 2 : 1) * ((n + 15) / 16);
+    const void* biasp = reinterpret_cast<const void*>(op->ptr[3]);
+    const void* resp = reinterpret_cast<const void*>(op->ptr[4]);
+    void* outp = reinterpret_cast<void*>(op->ptr[2]);
+    const long long ldo = op->ld[2], ldr = op->ld[4];
+    const int kw = warp * 128;                                                // this warp's K slice of a segment
+    const int bm = lane >> 2;                                                 // B-operand column = activation row
+    const uint32_t a_lane = (uint32_t)((lane & 15) * kSegStride + ((lane >> 4) * 8) * 2);
+    const uint32_t bmask = bm < M ? 0xffffffffu : 0u;                        // lanes of absent rows feed zeros
+    const uint32_t xh_lane = smem_u32(xh) + (bm < M ? bm : 0) * xs_stride + (lane & 3) * 4;
+    const uint32_t xl_lane = smem_u32(xl) + (bm < M ? bm : 0) * xs_stride + (lane & 3) * 4;
+    auto load_b = [&](uint32_t off, uint32_t* b) {
+        asm volatile("ld.shared.b32 %0, [%1];" : "=r"(b[0]) : "r"(xh_lane + off));
+        asm volatile("ld.shared.b32 %0, [%1];" : "=r"(b[1]) : "r"(xh_lane + off + 16));
+        asm volatile("ld.shared.b32 %0, [%1];" : "=r"(b[2]) : "r"(xl_lane + off));
+        asm volatile("ld.shared.b32 %0, [%1];" : "=r"(b[3]) : "r"(xl_lane + off + 16));
+        b[0] &= bmask; b[1] &= bmask; b[2] &= bmask; b[3] &= bmask;
+    };
+    constexpr int NC = SC > 0 ? SC : 1;
+    uint32_t bq[NC][8][4];
+    if (SC > 0) {
+#pragma unroll
+        for (int sg = 0; sg < NC; ++sg)
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) load_b((uint32_t)((sg * kSegElems + kw + ks * 16) * 2), bq[sg][ks]);
+    }
+
+    for (int g = 0; g < ngroups; ++g) {
+        const int ob = o0 + (swi ? g >> 1 : g) * 16 + (lane >> 2);            // this lane's rows: ob, ob + 8
+        // epilogue operands are requested before the stage waits so their latency is hidden
+        float bias_v[2] = {0.f, 0.f}, res_v[4] = {0.f, 0.f, 0.f, 0.f};
+        if (!swi) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int o = ob + h * 8;
+                if (o < o1) {
+                    if (biasp) bias_v[h] = load1(biasp, o, 0);
+                    if (resp) {
+                        if (m0 < M) res_v[h * 2] = load1(resp, (long long)m0 * ldr + o, rdt);
+                        if (m0 + 1 < M) res_v[h * 2 + 1] = load1(resp, (long long)(m0 + 1) * ldr + o, rdt);
+                    }
+                }
+            }
+        }
+        // four independent accumulator tiles (even / odd k-step x high / low part of x) keep the
+        // chain of dependent MMAs short; they are summed once per row group
+        float accs[4][4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) accs[q][e] = 0.f;
+        bool ok = true;
+        int last_stage = 0;
+        const int nseg = SC > 0 ? SC : S;
+#pragma unroll(NC)
+        for (int seg = 0; seg < nseg; ++seg) {
+            ok = wait_barrier(p, c, &c->full[pos.stage], pos.phase, seq, WHERE_RING_FULL) && ok;
+            if (g == 0 && seg == 0) phase_mark(p, c, 1);
+            const int seglen = SC > 0 ? kSegElems : min(kSegElems, K - seg * kSegElems);
+            if (ok) {
+                const uint32_t a_base = smem_u32(ring + pos.stage * kStageBytes) + a_lane + kw * 2;
+                uint32_t a[8][4];
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks)
+                    if (SC > 0 || kw + ks * 16 < seglen) ldmatrix_x4(a_base + ks * 32, a[ks][0], a[ks][1], a[ks][2], a[ks][3]);
+                if (SC > 0) {
+#pragma unroll
+                    for (int ks = 0; ks < 8; ++ks) {
+                        mma_bf16(accs[(ks & 1) * 2], a[ks], bq[seg][ks][0], bq[seg][ks][1]);
+                        mma_bf16(accs[(ks & 1) * 2 + 1], a[ks], bq[seg][ks][2], bq[seg][ks][3]);
+                    }
+                } else {
+                    uint32_t b[8][4];
+#pragma unroll
+                    for (int ks = 0; ks < 8; ++ks)
+                        if (kw + ks * 16 < seglen) load_b((uint32_t)((seg * kSegElems + kw + ks * 16) * 2), b[ks]);
+#pragma unroll
+                    for (int ks = 0; ks < 8; ++ks) {
+                        if (kw + ks * 16 < seglen) {
+                            mma_bf16(accs[(ks & 1) * 2], a[ks], b[ks][0], b[ks][1]);
+                            mma_bf16(accs[(ks & 1) * 2 + 1], a[ks], b[ks][2], b[ks][3]);
+                        }
+                    }
+                }
+            }
+            last_stage = pos.stage;
+            if (seg + 1 < nseg) {
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&c->empty[pos.stage]);
+                pos.advance();
+            }
+        }
+        float acc[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[e] = (accs[0][e] + accs[1][e]) + (accs[2][e] + accs[3][e]);
+        // ---- combine the 8 warps' K slices: the last warp to arrive owns the epilogue ----
+        float4* slot = red + last_stage * (8 * 32);
+        sts_volatile4(&slot[warp * 32 + lane], make_float4(acc[0], acc[1], acc[2], acc[3]));
+        __syncwarp();
+        int fin = 0;
+        if (lane == 0) {
+            __threadfence_block();
+            fin = atomicAdd(&cnt[last_stage], 1) == kComputeWarps - 1;
+            if (fin) cnt[last_stage] = 0;
+            __threadfence_block();
+        }
+        fin = __shfl_sync(0xffffffffu, fin, 0);
+        if (fin && ok) {
+            float v[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int w8 = 0; w8 < kComputeWarps; ++w8) {
+                const float4 q = lds_volatile4(&slot[w8 * 32 + lane]);
+                v[0] += q.x; v[1] += q.y; v[2] += q.z; v[3] += q.w;
+            }
+            // v[0], v[1]: row ob, activation rows m0, m0 + 1;  v[2], v[3]: row ob + 8
+            if (swi && !(g & 1)) {
+                sts_volatile4(&gatebuf[lane], make_float4(v[0] * rs[0], v[1] * rs[1], v[2] * rs[0], v[3] * rs[1]));
+            } else {
+                float gt[4] = {0.f, 0.f, 0.f, 0.f};
+                if (swi) {
+                    const float4 q = lds_volatile4(&gatebuf[lane]);
+                    gt[0] = q.x; gt[1] = q.y; gt[2] = q.z; gt[3] = q.w;
+                }
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int o = ob + (e >> 1) * 8, m = m0 + (e & 1);
+                    if (o < o1 && m < M) {
+                        float y = v[e] * rs[e & 1];
+                        if (swi) y = gt[e] * sigmoidf_(gt[e]) * y;
+                        else y = apply_act(act, y + bias_v[e >> 1]) + res_v[e];
+                        store1(outp, (long long)m * ldo + o, odt, y);
+                    }
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&c->empty[pos.stage]);
+        pos.advance();
+    }
+    phase_mark(p, c, 2);
+}
+
+}  // namespace mk

@@ -22,9 +22,9 @@ __device__ __forceinline__ float apply_bin(int fn, float a, float b) {
 // MK_OP_FINALIZE: out = act(ws + bias) + residual; ws = 0.
 // ptr 0 ws (fp32), 1 out, 2 bias, 3 residual; i 0 R, 1 C, 2 act, 3 out dtype, 4 residual dtype
 // args: 0 row tile, 1 col tile (kEwRows x kEwCols)
-__device__ __noinline__ void op_finalize(const mk_op_desc* op, const Inst& in) {
+static __device__ __noinline__ void op_finalize(const mk_op_desc* op, int a0, int a1) {
     const int R = op->i[0], Cc = op->i[1], act = op->i[2];
-    const int r0 = in.arg(0) * kEwRows, c0 = in.arg(1) * kEwCols;
+    const int r0 = a0 * kEwRows, c0 = a1 * kEwCols;
     const int rows = min(kEwRows, R - r0), cols = min(kEwCols, Cc - c0);
     const int vpr = cols >> 3;
     float* ws = reinterpret_cast<float*>(op->ptr[0]);
@@ -53,9 +53,9 @@ __device__ __noinline__ void op_finalize(const mk_op_desc* op, const Inst& in) {
 // MK_OP_ELTWISE.  ptr 0 a (x / gate), 1 b (b / up / scale / cos), 2 c (shift / sin), 3 out
 // i 0 R, 1 C, 2 mode, 3 fn (activation or binary code), 4 group (rows of a per row of b; rope: seq),
 //   5 head_dim (rope).  All operands bf16.  args: 0 row tile, 1 col tile.
-__device__ __noinline__ void op_eltwise(const mk_op_desc* op, const Inst& in) {
+static __device__ __noinline__ void op_eltwise(const mk_op_desc* op, int a0, int a1) {
     const int R = op->i[0], Cc = op->i[1], mode = op->i[2], fn = op->i[3], group = op->i[4];
-    const int r0 = in.arg(0) * kEwRows, c0 = in.arg(1) * kEwCols;
+    const int r0 = a0 * kEwRows, c0 = a1 * kEwCols;
     const int rows = min(kEwRows, R - r0), cols = min(kEwCols, Cc - c0);
     const void* A = reinterpret_cast<const void*>(op->ptr[0]);
     const void* B = reinterpret_cast<const void*>(op->ptr[1]);
@@ -114,10 +114,10 @@ __device__ __noinline__ void op_eltwise(const mk_op_desc* op, const Inst& in) {
 }
 
 // MK_OP_NORM.  ptr 0 x, 1 out, 2 weight, 3 bias; i 0 R, 1 C, 2 rms, 3 rows per instruction (8: one
-// row per warp, 1: one row over the whole CTA); f 0 eps.  args: 0 row tile.
+// row per warp, 1: one row over the whole CTA), 4 x dtype; f 0 eps.  args: 0 row tile.
 // var = E[x^2] - mean^2 in fp32 (as the reference's norm kernel, megacute/ops/norm.py:94-114).
-__device__ __noinline__ void op_norm(const mk_op_desc* op, const Inst& in, uint8_t* work) {
-    const int R = op->i[0], Cc = op->i[1], rms = op->i[2], rpi = op->i[3];
+static __device__ __noinline__ void op_norm(const mk_op_desc* op, int a0, uint8_t* work) {
+    const int R = op->i[0], Cc = op->i[1], rms = op->i[2], rpi = op->i[3], xdt = op->i[4];
     const float eps = op->f[0];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const void* X = reinterpret_cast<const void*>(op->ptr[0]);
@@ -126,14 +126,14 @@ __device__ __noinline__ void op_norm(const mk_op_desc* op, const Inst& in, uint8
     const void* Bv = reinterpret_cast<const void*>(op->ptr[3]);
     const int nvec = Cc >> 3;
     int r, first, step;
-    if (rpi == 1) { r = in.arg(0); first = threadIdx.x; step = kComputeThreads; }
-    else { r = in.arg(0) * kComputeWarps + warp; first = lane; step = 32; }
+    if (rpi == 1) { r = a0; first = threadIdx.x; step = kComputeThreads; }
+    else { r = a0 * kComputeWarps + warp; first = lane; step = 32; }
     const bool live = r < R;
     float s = 0.f, ss = 0.f;
     if (live)
         for (int v = first; v < nvec; v += step) {
             float f[8];
-            load8(X, (long long)r * op->ld[0] + v * 8, 0, f);
+            load8(X, (long long)r * op->ld[0] + v * 8, xdt, f);
 #pragma unroll
             for (int e = 0; e < 8; ++e) { s += f[e]; ss += f[e] * f[e]; }
         }
@@ -153,7 +153,7 @@ __device__ __noinline__ void op_norm(const mk_op_desc* op, const Inst& in, uint8
     const float rstd = rsqrt_approx(var + eps);
     for (int v = first; v < nvec; v += step) {
         float f[8], g[8];
-        load8(X, (long long)r * op->ld[0] + v * 8, 0, f);
+        load8(X, (long long)r * op->ld[0] + v * 8, xdt, f);
 #pragma unroll
         for (int e = 0; e < 8; ++e) f[e] = (f[e] - mean) * rstd;
         if (W) {
@@ -186,11 +186,11 @@ __device__ __forceinline__ void rope8(const float* x1, const float* x2, const vo
 // MK_OP_ROPE_APPEND.  ptr 0 qkv, 1 cos, 2 sin, 3 pos, 4 q_out, 5 k_cache, 6 v_cache
 // i 0 B, 1 H, 2 KVH, 3 D, 4 max_seq, 5 qkv dtype.  args: 0 row tile (8 sequences).
 // Cache row written for sequence b: b * max_seq + pos (reference: graph.py:375-379).
-__device__ __noinline__ void op_rope_append(const mk_op_desc* op, const Inst& in) {
+static __device__ __noinline__ void op_rope_append(const mk_op_desc* op, int a0) {
     const int B = op->i[0], H = op->i[1], KVH = op->i[2], D = op->i[3], L = op->i[4], qdt = op->i[5];
     const int pos = *reinterpret_cast<const int*>(op->ptr[3]);
     const int half = D >> 1, hv = half >> 3;
-    const int r0 = in.arg(0) * kComputeWarps;
+    const int r0 = a0 * kComputeWarps;
     const int rows = min(kComputeWarps, B - r0);
     const void* qkv = reinterpret_cast<const void*>(op->ptr[0]);
     const __nv_bfloat16* cosr = reinterpret_cast<const __nv_bfloat16*>(op->ptr[1]) + (long long)pos * op->ld[1];

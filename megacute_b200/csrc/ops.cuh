@@ -1,0 +1,42 @@
+// Entry points of the op bodies.  Every op body lives in its own translation unit and the library
+// is built as relocatable device code: measured on sm_100a, when the bodies share one translation
+// unit with the kernel, ptxas' whole-program register allocation spills the inner loop of the
+// streaming linear to local memory (with 227 KB of the SM given to shared memory almost no L1 is
+// left, so each spill is an L2 round trip: 6x slower), however the calls are arranged.  Compiled
+// separately, each body gets its own allocation under the 168-register cap of a 9-warp CTA.
+//
+// All take the op descriptor and the instruction's arguments by value and find the CTA's shared
+// memory through the kernel's dynamic shared-memory window.
+#pragma once
+#include "mk_device.cuh"
+
+namespace mk {
+
+// ring position in / out is packed as stage | phase << 8
+// (this op waits for its own dependencies: see gemv_units)
+__device__ int mk_op_gemv_units(const Params& p, const mk_op_desc* op, int o0, int o1, int seq, int packed_pos, int nwait,
+                                int wait_off);
+__device__ int mk_op_gemv_general(const Params& p, const mk_op_desc* op, int o0, int o1, int seq, int packed_pos);
+__device__ void mk_op_gemm(const mk_op_desc* op, int a0, int a1, int a2);
+__device__ void mk_op_attention(const mk_op_desc* op, int a0, int a1, int a2);
+// (waits for its own dependencies: see op_decode_attn)
+__device__ void mk_op_decode_attn(const Params& p, const mk_op_desc* op, int a0, int a1, int a2, int nwait, int wait_off,
+                                  int seq);
+// finalize / eltwise / norm / rope_append / increment; returns false for an unknown kind
+__device__ bool mk_op_pointwise(const mk_op_desc* op, int a0, int a1);
+
+struct SmemMap {
+    uint8_t* ring;
+    uint8_t* work;
+    Ctrl* ctrl;
+};
+__device__ __forceinline__ SmemMap smem_map() {
+    extern __shared__ __align__(1024) uint8_t mk_smem[];
+    SmemMap m;
+    m.ring = mk_smem;
+    m.work = mk_smem + kRingBytes;
+    m.ctrl = reinterpret_cast<Ctrl*>(mk_smem + kRingBytes + kWorkBytes);
+    return m;
+}
+
+}  // namespace mk

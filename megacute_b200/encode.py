@@ -9,16 +9,16 @@ and reads shapes, strides, flags and operand addresses from this table at run ti
 view's first element.  Field meaning per kind (the kernel side repeats it next to the reader):
 
   GEMV         ptr x, w, out, bias, residual, norm gain; i M, N_out, K, act, x dtype, out dtype,
-               residual dtype; f eps; flags 1 = swiglu, 2 = rms-normalise x
+               residual dtype; f eps; flags 1 = swiglu, 2 = rms-normalise x, 4 = tensor-core streaming path
   GEMM         ptr x, w, out, bias, residual; i M, N (weight rows), K, act, splits, out dtype,
                accumulate, residual dtype, swiglu
   FINALIZE     ptr ws, out, bias, residual; i R, C, act, out dtype, residual dtype
   ELTWISE      ptr a, b, c, out; i R, C, mode, fn, group, head_dim
-  NORM         ptr x, out, weight, bias; i R, C, rms, rows per instruction; f eps
+  NORM         ptr x, out, weight, bias; i R, C, rms, rows per instruction, x dtype; f eps
   ATTENTION    ptr q, k, v, out; i batch, seq_q, seq_k, heads, kv_heads, head_dim, causal; f scale
   ROPE_APPEND  ptr qkv, cos, sin, pos, q_out, k_cache, v_cache; i B, H, KVH, D, max_seq, qkv dtype
   DECODE_ATTN  ptr q, k_cache, v_cache, pos, out, k_new, v_new, cos, sin, part, count;
-               i B, H, KVH, D, max_seq, splits, fused, q dtype; f scale
+               i B, H, KVH, D, max_seq, splits, fused, q dtype, out dtype; f scale
   INCREMENT    ptr pos
 """
 
@@ -57,12 +57,19 @@ def validate(op: Op):
             _want(op.x, (BF16,), k)
     if k in ("Unary", "Binary", "SwiGLU", "Modulate", "Rope", "Norm"):
         for name, v in op.view_fields():
-            _want(v, (BF16,), f"{k}.{name}")
+            if not (k == "Norm" and name == "x"):          # the norm reads bf16 or fp32 rows
+                _want(v, (BF16,), f"{k}.{name}")
         if op.out.cols % 8:
             raise ValueError(f"{k}: column count {op.out.cols} must be a multiple of 8")
     if k == "Attention":
         for name, v in op.view_fields():
             _want(v, (BF16,), f"{k}.{name}")
+
+
+def gemv_units(op: Op) -> bool:
+    """Streaming linear whose K is a multiple of 16: the kernel's tensor-core path (GEMV_F_UNITS).
+    Other K fall back to the general CUDA-core path."""
+    return op.x.cols % 16 == 0
 
 
 def fill(d, op: Op, addr) -> None:
@@ -77,7 +84,7 @@ def fill(d, op: Op, addr) -> None:
         ptrs = [op.x, op.w, op.out, op.bias, op.residual, op.norm_w]
         ints = [op.x.rows, op.out.cols, op.x.cols, C.ACT_CODE[op.act], dt(op.x), dt(op.out), dt(op.residual)]
         d.f[0] = float(op.rms_eps or 0.0)
-        d.flags = (1 if op.act == "swiglu" else 0) | (2 if op.rms_eps is not None else 0)
+        d.flags = (1 if op.act == "swiglu" else 0) | (2 if op.rms_eps is not None else 0) | (4 if gemv_units(op) else 0)
     elif k in ("Linear", "LinearSplit"):
         d.kind = C.OP_GEMM
         split = k == "LinearSplit"
@@ -106,7 +113,7 @@ def fill(d, op: Op, addr) -> None:
     elif k == "Norm":
         d.kind = C.OP_NORM
         ptrs = [op.x, op.out, op.weight, op.bias]
-        ints = [op.x.rows, op.x.cols, int(bool(op.rms)), norm_rows(op.x.rows)]
+        ints = [op.x.rows, op.x.cols, int(bool(op.rms)), norm_rows(op.x.rows), dt(op.x)]
         d.f[0] = float(op.eps)
     elif k == "Attention":
         d.kind = C.OP_ATTENTION
@@ -121,7 +128,9 @@ def fill(d, op: Op, addr) -> None:
         d.kind = C.OP_DECODE_ATTN
         ptrs = [op.q, op.k_cache, op.v_cache, op.pos, op.out, op.k_new, op.v_new, op.cos, op.sin, op.part, op.count]
         ints = [op.batch, op.heads, op.kv_heads, op.head_dim, op.max_seq, op.splits, int(op.k_new is not None),
-                dt(op.q)]
+                dt(op.q), dt(op.out)]
+        assert op.k_new is None or dt(op.k_new) == dt(op.v_new) == dt(op.q)
+        assert op.splits <= C.MAX_KV_SPLITS
         d.f[0] = float(op.scale)
     elif k == "Increment":
         d.kind = C.OP_INCREMENT

@@ -190,7 +190,7 @@ class Program:
         if not self.trace:
             raise RuntimeError("compile with trace=True to record a timeline")
         torch.cuda.synchronize(self.device)
-        buf = np.zeros((self.sm_count, 2, self.trace_cap, 4), np.int64)
+        buf = np.zeros((self.sm_count, 3, self.trace_cap, 4), np.int64)
         _lib.check(_lib.load().mk_program_read_trace(self._handle, buf.ctypes.data, buf.size))
         return Timeline(self, buf)
 

@@ -4,9 +4,12 @@
     tl = prog.timeline(); print(tl.summary()); tl.save_chrome("trace.json")
 
 Same surface as the reference's ``megacute/trace.py:22-91`` (records, span_us, summary,
-chrome_events, save_chrome).  This kernel has two traced roles per SM:
+chrome_events, save_chrome).  This kernel has three record kinds per SM:
   role 0 "producer": (seq, start of weight streaming, -, all copies of the instruction issued)
   role 1 "compute":  (seq, instruction fetched, dependencies met, arrivals published)
+  role 2 "phases":   (seq, three op-internal marks) for the ops that wait for their own
+                     dependencies: streaming linear (x staged, first stage landed, last group
+                     done) and decode attention (tiles done, partial written, merged)
 Times are globaltimer nanoseconds rebased to the earliest record.
 """
 
