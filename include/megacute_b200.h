@@ -72,7 +72,8 @@ enum {
     MK_E_ARG = -2,           /* null / out-of-range argument                                 */
     MK_E_ARCH = -3,          /* the device is not compute capability 10.x                    */
     MK_E_DEVICE = -4,        /* the kernel reported an error in the status buffer            */
-    MK_E_NOMEM = -5
+    MK_E_NOMEM = -5,
+    MK_E_TOO_LARGE = -6      /* mk_launch_noalloc: more counters than the static scratch holds */
 };
 
 typedef struct mk_program mk_program;
@@ -125,6 +126,33 @@ int mk_program_clear_trace(mk_program* p, void* stream);
 int mk_program_poke_wait(mk_program* p, int wait_index, int counter, int target);
 
 void mk_program_destroy(mk_program* p);
+
+/* One launch that allocates nothing.  (No counterpart in the reference, whose runtime always
+ * allocates its counters through torch.)
+ *
+ * For hosts that cannot call cudaMalloc: a server whose own pool already owns all device memory,
+ * or a loop that cannot take the device-wide synchronisation an allocation implies.  The
+ * dependency counters and status words -- the only memory the kernel needs beyond the caller's
+ * tensors and tables -- live in a static device array inside the library instead
+ * (MK_NOALLOC_MAX_COUNTERS counters; about 64 KB held by every GPU that loads the library until
+ * the process exits).  A graph that needs more counters is refused with MK_E_TOO_LARGE.
+ *
+ *   d_insts / d_waits / d_arrives / d_ops   the same tables as mk_program_create / mk_program_set_ops,
+ *                                           but already in DEVICE memory owned by the caller
+ *   status                                  NULL: return right after the launch is enqueued;
+ *                                           else: wait for `stream`, copy the 16 status words here
+ *                                           and return MK_E_DEVICE if the kernel reported an error
+ *
+ * Calls no cudaMalloc / cudaFree or other allocating routine.  The first call on a device looks up
+ * the array's address and sets the kernel's shared-memory attribute, so make that first call
+ * outside any stream capture.  Every call on a device shares the one array and starts by clearing
+ * the counters it uses on `stream`; two calls whose kernels may overlap on the GPU (different
+ * streams) race on it -- serialise them.  Split-KV workspaces named by the descriptors must be zero
+ * on entry, as for mk_launch. */
+#define MK_NOALLOC_MAX_COUNTERS 16384
+int mk_launch_noalloc(int device, const int32_t* d_insts, int n_insts, const int32_t* d_waits, int n_waits,
+                      const int32_t* d_arrives, int n_arrives, const mk_op_desc* d_ops, int n_ops,
+                      int n_counters, int grid, void* stream, int32_t status[MK_ST_WORDS]);
 
 #ifdef __cplusplus
 }

@@ -59,6 +59,8 @@ SYMBOLS = {
     "mk_program_clear_trace": (ctypes.c_int, [_P, _P]),
     "mk_program_poke_wait": (ctypes.c_int, [_P, ctypes.c_int, ctypes.c_int, ctypes.c_int]),
     "mk_program_destroy": (None, [_P]),
+    "mk_launch_noalloc": (ctypes.c_int, [ctypes.c_int, _P, ctypes.c_int, _P, ctypes.c_int, _P, ctypes.c_int, _P, ctypes.c_int,
+                                         ctypes.c_int, ctypes.c_int, _P, _I32P]),
 }
 
 

@@ -165,6 +165,7 @@ const char* mk_strerror(int code) {
         case MK_E_ARCH: return "device is not compute capability 10.x (sm_100a kernel)";
         case MK_E_DEVICE: return "megakernel reported a device-side error (see status words)";
         case MK_E_NOMEM: return "out of memory";
+        case MK_E_TOO_LARGE: return "graph needs more dependency counters than MK_NOALLOC_MAX_COUNTERS (static scratch of mk_launch_noalloc)";
         default: return "unknown error";
     }
 }
@@ -340,3 +341,72 @@ void mk_program_destroy(mk_program* p) {
 }
 
 }  // extern "C"
+
+// -------------------------------------------------------------------------------------------------
+// mk_launch_noalloc: the same kernel for hosts that must not allocate device memory.
+//
+// The megakernel needs scratch beyond the caller's tensors: its dependency counters and its status
+// words.  mk_program_create() gets them from cudaMalloc.  Some hosts cannot do that -- an inference
+// server that has already handed all of HBM to its own pool, or a latency-critical loop that cannot
+// afford the device-wide synchronisation a cudaMalloc / cudaFree implies.  For them the scratch
+// lives in this file-scope device array: MK_NOALLOC_MAX_COUNTERS counters + MK_ST_WORDS status
+// words, about 64 KB that every GPU which loads the library holds until the process exits.
+//
+// `g_noalloc_scratch` below is, in host code, only a handle for the symbol -- not a device
+// address.  The address is looked up once per device with cudaGetSymbolAddress (that device
+// current) and cached; kernels are only ever given that looked-up pointer.
+// -------------------------------------------------------------------------------------------------
+static __device__ __align__(256) int32_t g_noalloc_scratch[MK_NOALLOC_MAX_COUNTERS + MK_ST_WORDS];
+
+static const int kMaxDevices = 64;
+static int32_t* g_noalloc_ptr[kMaxDevices];          // per device: looked-up address of the array, or null
+
+extern "C" int mk_launch_noalloc(int device, const int32_t* d_insts, int n_insts, const int32_t* d_waits, int n_waits,
+                                 const int32_t* d_arrives, int n_arrives, const mk_op_desc* d_ops, int n_ops,
+                                 int n_counters, int grid, void* stream, int32_t status[MK_ST_WORDS]) {
+    if (device < 0 || device >= kMaxDevices || !d_insts || n_insts <= 0 || !d_ops || n_ops <= 0 || grid <= 0 ||
+        n_waits < 0 || n_arrives < 0 || n_counters < 0 || (n_waits && !d_waits) || (n_arrives && !d_arrives))
+        return MK_E_ARG;
+    if (n_counters > MK_NOALLOC_MAX_COUNTERS) return MK_E_TOO_LARGE;
+    cudaStream_t st = (cudaStream_t)stream;
+    int current = -1;
+    MK_CUDA(cudaGetDevice(&current));
+    if (current != device) MK_CUDA(cudaSetDevice(device));
+    if (!g_noalloc_ptr[device]) {
+        // one-time set-up for this device (do this first call outside any stream capture)
+        mk_caps caps;
+        int rc = mk_query(device, &caps);
+        if (rc != MK_OK) return rc;
+        if (caps.max_smem_optin < mk::kSmemBytes) return MK_E_ARCH;
+        int32_t* ptr = nullptr;
+        MK_CUDA(cudaGetSymbolAddress((void**)&ptr, g_noalloc_scratch));
+        MK_CUDA(cudaFuncSetAttribute(mk::megakernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, mk::kSmemBytes));
+        g_noalloc_ptr[device] = ptr;
+    }
+    int32_t* scratch = g_noalloc_ptr[device];
+    int32_t* d_status = scratch + MK_NOALLOC_MAX_COUNTERS;
+    // the array keeps the previous call's contents: counters and status must start at zero
+    if (n_counters > 0) MK_CUDA(cudaMemsetAsync(scratch, 0, (size_t)n_counters * 4, st));
+    MK_CUDA(cudaMemsetAsync(d_status, 0, MK_ST_WORDS * 4, st));
+    mk::Params prm;
+    prm.insts = reinterpret_cast<const int4*>(d_insts);
+    prm.n_insts = n_insts;
+    prm.waits = reinterpret_cast<const int2*>(d_waits);
+    prm.arrives = d_arrives;
+    prm.counters = scratch;
+    prm.ops = d_ops;
+    prm.n_ops = n_ops;
+    prm.trace = nullptr;
+    prm.trace_cap = 0;
+    prm.status = d_status;
+    prm.epoch = 1;
+    prm.timeout_ns = 2000000000ull;
+    mk::megakernel<false><<<grid, mk::kThreads, mk::kSmemBytes, st>>>(prm);
+    MK_CUDA(cudaGetLastError());
+    if (status) {
+        MK_CUDA(cudaMemcpyAsync(status, d_status, MK_ST_WORDS * 4, cudaMemcpyDeviceToHost, st));
+        MK_CUDA(cudaStreamSynchronize(st));
+        if (status[MK_ST_CODE] != 0) return MK_E_DEVICE;
+    }
+    return MK_OK;
+}
