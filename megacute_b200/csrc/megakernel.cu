@@ -10,6 +10,7 @@
 // This replaces the reference's JIT-traced kernel (megacute/kernel.py:251-571) and its per-op
 // role bodies (megacute/ops/*.py).
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 
@@ -40,18 +41,7 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
 
     if (warp == kProducerWarp) {
         // ---------------- producer warp ----------------
-        RingPos pos;
-        int slot = 0;
-        for (int idx = blockIdx.x; idx < p.n_insts; idx += gridDim.x, ++slot) {
-            const Inst in = fetch_inst(p, idx);
-            const int opi = in.opi - 1;
-            if (opi < 0 || opi >= p.n_ops) break;
-            const mk_op_desc* op = p.ops + opi;
-            if (op->kind != MK_OP_GEMV) continue;
-            const long long t0 = TRACE ? (long long)globaltimer() : 0;
-            if (!gemv_produce(p, c, ring, op, in.a0, in.a1, in.seq, pos)) break;
-            if ((threadIdx.x & 31) == 0) trace_rec<TRACE>(p, 0, slot, in.seq, t0, t0, (long long)globaltimer());
-        }
+        producer_loop<TRACE>(p, c, ring);
     } else {
         // ---------------- compute warps ----------------
         RingPos pos;
@@ -72,11 +62,13 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
             long long t1 = TRACE ? (long long)globaltimer() : 0;
             const int ppos = pos.stage | ((int)pos.phase << 8);
             int npos = ppos;
-            bool known = true;
+            bool known = true, aborting = false;
             switch (op->kind) {
                 case MK_OP_GEMV:
                     if (op->flags & GEMV_F_UNITS) {
-                        npos = mk_op_gemv_units(p, op, in.a0, in.a1, in.seq, ppos, in.nwait, in.wait_off);
+                        npos = mk_op_gemv_units(p, op, in.a0, in.a1, in.seq, ppos, in.nwait, in.wait_off, in.narrive,
+                                                in.arrive_off);
+                        aborting = npos < 0;
                         if (TRACE) t1 = c->t_dep;
                     } else {
                         npos = mk_op_gemv_general(p, op, in.a0, in.a1, in.seq, ppos);
@@ -85,7 +77,8 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
                 case MK_OP_GEMM: mk_op_gemm(op, in.a0, in.a1, in.a2); break;
                 case MK_OP_ATTENTION: mk_op_attention(op, in.a0, in.a1, in.a2); break;
                 case MK_OP_DECODE_ATTN:
-                    mk_op_decode_attn(p, op, in.a0, in.a1, in.a2, in.nwait, in.wait_off, in.seq);
+                    aborting = mk_op_decode_attn(p, op, in.a0, in.a1, in.a2, in.nwait, in.wait_off, in.seq, in.narrive,
+                                                 in.arrive_off);
                     if (TRACE) t1 = c->t_dep;
                     break;
                 default: known = mk_op_pointwise(op, in.a0, in.a1); break;
@@ -93,7 +86,7 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
             if (!known && threadIdx.x == 0) report(p, c, MK_DEV_BAD_INST, in.seq, 1, op->kind, idx, 0);
             pos.stage = npos & 0xff;
             pos.phase = (uint32_t)(npos >> 8);
-            const bool aborting = publish(p, c, in.narrive, in.arrive_off);
+            if (!self_wait) aborting = publish(p, c, in.narrive, in.arrive_off);
             if (threadIdx.x == 0) {
                 trace_rec<TRACE>(p, 1, slot, in.seq, t0, t1, (long long)globaltimer());
                 if (TRACE && self_wait) trace_rec<TRACE>(p, 2, slot, in.seq, c->t_phase[0], c->t_phase[1], c->t_phase[2]);
@@ -141,6 +134,7 @@ struct mk_program {
     int epoch = 0;
     int max_target = 1;
     unsigned long long timeout_ns = 2000000000ull;
+    int pf_stages = 0;               // L2 prefetch distance of the producer warp, in ring stages (0 = off)
 };
 
 static thread_local char g_cuda_err[256] = "";
@@ -232,6 +226,7 @@ int mk_program_create(int device, const int32_t* insts, int n_insts, const int32
     MK_TRY(cudaFuncSetAttribute(mk::megakernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, mk::kSmemBytes));
     MK_TRY(cudaFuncSetAttribute(mk::megakernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, mk::kSmemBytes));
 #undef MK_TRY
+    if (const char* e = getenv("MEGACUTE_B200_PF_STAGES")) p->pf_stages = atoi(e);
     *out = p;
     return MK_OK;
 }
@@ -274,6 +269,7 @@ int mk_launch(mk_program* p, void* stream) {
     prm.status = p->d_status;
     prm.epoch = p->epoch;
     prm.timeout_ns = p->timeout_ns;
+    prm.pf_stages = p->pf_stages;
     if (p->trace_cap > 0) mk::megakernel<true><<<p->grid, mk::kThreads, mk::kSmemBytes, st>>>(prm);
     else mk::megakernel<false><<<p->grid, mk::kThreads, mk::kSmemBytes, st>>>(prm);
     MK_CUDA(cudaGetLastError());
@@ -401,6 +397,7 @@ extern "C" int mk_launch_noalloc(int device, const int32_t* d_insts, int n_insts
     prm.status = d_status;
     prm.epoch = 1;
     prm.timeout_ns = 2000000000ull;
+    prm.pf_stages = 0;
     mk::megakernel<false><<<grid, mk::kThreads, mk::kSmemBytes, st>>>(prm);
     MK_CUDA(cudaGetLastError());
     if (status) {

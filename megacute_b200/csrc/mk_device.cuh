@@ -45,6 +45,7 @@ struct Params {
     int* status;                  // MK_ST_WORDS words; word 0 != 0 aborts every waiter
     int epoch;
     unsigned long long timeout_ns;
+    int pf_stages;                // how many ring stages ahead of the ring the producer prefetches into L2
 };
 
 struct Ctrl {                     // lives in the last kCtrlBytes of shared memory

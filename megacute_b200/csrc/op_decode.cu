@@ -3,16 +3,16 @@
 #include "ops.cuh"
 
 namespace mk {
-__device__ void mk_op_decode_attn(const Params& p, const mk_op_desc* op, int a0, int a1, int a2, int nwait, int wait_off,
-                                  int seq) {
+__device__ bool mk_op_decode_attn(const Params& p, const mk_op_desc* op, int a0, int a1, int a2, int nwait, int wait_off,
+                                  int seq, int narrive, int arrive_off) {
     const SmemMap m = smem_map();
     const int D = op->i[3], G = op->i[1] / op->i[2];
     if (D == 64) {
-        if (G <= 4) op_decode_attn<64, 4>(p, m.ctrl, op, a0, a1, a2, m.work, nwait, wait_off, seq);
-        else op_decode_attn<64, 8>(p, m.ctrl, op, a0, a1, a2, m.work, nwait, wait_off, seq);
+        if (G <= 4) return op_decode_attn<64, 4>(p, m.ctrl, op, a0, a1, a2, m.work, nwait, wait_off, seq, narrive, arrive_off);
+        return op_decode_attn<64, 8>(p, m.ctrl, op, a0, a1, a2, m.work, nwait, wait_off, seq, narrive, arrive_off);
     } else {
-        if (G <= 4) op_decode_attn<128, 4>(p, m.ctrl, op, a0, a1, a2, m.work, nwait, wait_off, seq);
-        else op_decode_attn<128, 8>(p, m.ctrl, op, a0, a1, a2, m.work, nwait, wait_off, seq);
+        if (G <= 4) return op_decode_attn<128, 4>(p, m.ctrl, op, a0, a1, a2, m.work, nwait, wait_off, seq, narrive, arrive_off);
+        return op_decode_attn<128, 8>(p, m.ctrl, op, a0, a1, a2, m.work, nwait, wait_off, seq, narrive, arrive_off);
     }
 }
 }  // namespace mk

@@ -25,8 +25,8 @@ constexpr int kDecTileKeys = 64;
 constexpr int kMaxKvSplits = 32;          // config.py MAX_KV_SPLITS
 
 template <int D, int GMAX>
-static __device__ __noinline__ void op_decode_attn(const Params& p, Ctrl* c, const mk_op_desc* op, int a0, int a1, int a2,
-                                                   uint8_t* work, int nwait, int wait_off, int seq) {
+__device__ __forceinline__ void decode_body(const Params& p, Ctrl* c, const mk_op_desc* op, int a0, int a1, int a2,
+                                            uint8_t* work, int nwait, int wait_off, int seq) {
     constexpr int DP = D / 8;                         // threads per key (8 dims each)
     constexpr int KPP = kComputeThreads / DP;         // keys per pass
     constexpr int PASSES = kDecTileKeys / KPP;
@@ -345,6 +345,17 @@ static __device__ __noinline__ void op_decode_attn(const Params& p, Ctrl* c, con
         }
         store1(outp, (long long)b * op->ld[4] + kvh * GD + idx, odt, l == 0.f ? 0.f : a * rcp(l));
     }
+}
+
+// The op waits for its own dependencies (see decode_body) and publishes its own arrivals, so the
+// arrivals leave before the function's epilogue (callee-saved register restores come out of local
+// memory, an L2 round trip here).  Returns whether the CTA is aborting.
+template <int D, int GMAX>
+static __device__ __noinline__ bool op_decode_attn(const Params& p, Ctrl* c, const mk_op_desc* op, int a0, int a1, int a2,
+                                                   uint8_t* work, int nwait, int wait_off, int seq, int narrive,
+                                                   int arrive_off) {
+    decode_body<D, GMAX>(p, c, op, a0, a1, a2, work, nwait, wait_off, seq);
+    return publish(p, c, narrive, arrive_off);
 }
 
 }  // namespace mk

@@ -4,15 +4,15 @@
 
 namespace mk {
 
-__device__ int mk_op_gemv_units(const Params& p, const mk_op_desc* op, int o0, int o1, int seq, int packed_pos, int nwait, int wait_off) {
+__device__ int mk_op_gemv_units(const Params& p, const mk_op_desc* op, int o0, int o1, int seq, int packed_pos, int nwait, int wait_off,
+                                int narrive, int arrive_off) {
     const SmemMap m = smem_map();
     RingPos pos;
     pos.stage = packed_pos & 0xff;
     pos.phase = (uint32_t)(packed_pos >> 8);
-    const int K = op->i[2];
-    if (K == kSegElems) gemv_mma<1>(p, m.ctrl, m.ring, m.work, op, o0, o1, seq, pos, nwait, wait_off);
-    else if (K == 2 * kSegElems) gemv_mma<2>(p, m.ctrl, m.ring, m.work, op, o0, o1, seq, pos, nwait, wait_off);
-    else gemv_mma<0>(p, m.ctrl, m.ring, m.work, op, o0, o1, seq, pos, nwait, wait_off);
+    gemv_mma(p, m.ctrl, m.ring, m.work, op, o0, o1, seq, pos, nwait, wait_off);
+    // arrivals leave before the function epilogue restores callee-saved registers from local memory
+    if (publish(p, m.ctrl, narrive, arrive_off)) return -1;
     return pos.stage | ((int)pos.phase << 8);
 }
 

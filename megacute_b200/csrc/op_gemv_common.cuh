@@ -46,69 +46,118 @@ __device__ __forceinline__ int gemv_weight_row(bool swi, int o0, int group, int 
     return 128 * (o >> 6) + (o & 63) + ((slot >> 2) << 6);
 }
 
-// Producer warp: issue every stage of one GEMV instruction.  Returns false if a wait gave up.
-__device__ __forceinline__ bool gemv_produce(const Params& p, Ctrl* c, uint8_t* ring, const mk_op_desc* op,
-                                             int o0, int o1, int seq, RingPos& pos) {
-    const int lane = threadIdx.x & 31;
-    const int K = op->i[2];
-    const bool swi = op->flags & GEMV_F_SWIGLU;
-    const int per = swi ? 4 : 8;
-    const int groups = (o1 - o0 + per - 1) / per;
-    const int nkc = (K + kGemvKChunk - 1) / kGemvKChunk;
-    const __nv_bfloat16* w = reinterpret_cast<const __nv_bfloat16*>(op->ptr[1]);
-    const long long ldw = op->ld[1];
-    if (op->flags & GEMV_F_UNITS) {
-        // stage = 16 rows x K segment `seg`; segments of a row group are consecutive stages; swiglu
-        // alternates a group of 16 gate rows with the group of the matching 16 up rows
-        const int S = (K + kSegElems - 1) / kSegElems;
-        const int n = o1 - o0;
-        const int ngroups = (swi ? 2 : 1) * ((n + 15) / 16);
-        const int r = lane & 15;
-        for (int g = 0; g < ngroups; ++g) {
+// ---- producer side -------------------------------------------------------------------------------
+// The producer warp sees this CTA's streaming linears as one long sequence of ring stages.  A
+// StageCursor names one stage of that sequence (instruction, row group, K segment) and yields,
+// per lane, the weight-row segment that lane copies.  Two cursors walk the sequence: one feeds the
+// shared-memory ring with bulk copies, the other runs up to Params::pf_stages stages further
+// ahead and only asks L2 to fetch the same bytes (cp.async.bulk.prefetch.L2), so HBM keeps
+// streaming while the ring is full and the compute warps sit in a dependency hop.
+struct StageCursor {
+    int idx;                 // global instruction index (this CTA's: idx = cta + k * grid); >= n_insts: end
+    int seq, g, seg;         // instruction sequence number, row group and K segment inside it
+    int ngroups, nseg;       // of the current instruction
+    int o0, o1, K, flags;
+    const __nv_bfloat16* w;
+    long long ldw;
+
+    // position on the next streaming-linear instruction at or after `idx`
+    __device__ __forceinline__ void seek(const Params& p) {
+        for (; idx < p.n_insts; idx += gridDim.x) {
+            const Inst in = fetch_inst(p, idx);
+            const int opi = in.opi - 1;
+            if (opi < 0 || opi >= p.n_ops) { idx = p.n_insts; return; }
+            const mk_op_desc* op = p.ops + opi;
+            if (op->kind != MK_OP_GEMV) continue;
+            seq = in.seq; o0 = in.a0; o1 = in.a1; K = op->i[2]; flags = op->flags;
+            w = reinterpret_cast<const __nv_bfloat16*>(op->ptr[1]);
+            ldw = op->ld[1];
+            const int n = o1 - o0;
+            const bool swi = flags & GEMV_F_SWIGLU;
+            if (flags & GEMV_F_UNITS) {
+                ngroups = (swi ? 2 : 1) * ((n + 15) / 16);
+                nseg = (K + kSegElems - 1) / kSegElems;
+            } else {
+                const int per = swi ? 4 : 8;
+                ngroups = (n + per - 1) / per;
+                nseg = (K + kGemvKChunk - 1) / kGemvKChunk;
+            }
+            g = 0; seg = 0;
+            if (ngroups > 0) return;
+        }
+    }
+    __device__ __forceinline__ bool valid(const Params& p) const { return idx < p.n_insts; }
+    __device__ __forceinline__ void advance(const Params& p) {
+        if (++seg < nseg) return;
+        seg = 0;
+        if (++g < ngroups) return;
+        idx += gridDim.x;
+        seek(p);
+    }
+    // this lane's piece of the stage: source, bytes (0 = none) and offset inside the ring stage
+    __device__ __forceinline__ void piece(int lane, const __nv_bfloat16*& src, int& bytes, int& dst_off) const {
+        const bool swi = flags & GEMV_F_SWIGLU;
+        src = w; bytes = 0; dst_off = 0;
+        if (flags & GEMV_F_UNITS) {
+            const int r = lane & 15;
             const int o = o0 + (swi ? g >> 1 : g) * 16 + r;
             const int row = swi ? 128 * (o >> 6) + (o & 63) + ((g & 1) << 6) : o;
-            const bool valid = lane < 16 && o < o1;
-            for (int seg = 0; seg < S; ++seg) {
-                const int k0 = seg * kSegElems;
-                const int bytes = valid ? min(kSegElems, K - k0) * 2 : 0;
-                const int total = __reduce_add_sync(0xffffffffu, bytes);
-                bool ok = true;
-                if (lane == 0) {
-                    ok = wait_barrier(p, c, &c->empty[pos.stage], pos.phase ^ 1u, seq, WHERE_RING_EMPTY);
-                    if (ok) mbar_arrive_expect_tx(&c->full[pos.stage], (uint32_t)total);
-                }
-                ok = __shfl_sync(0xffffffffu, ok, 0);
-                if (!ok) return false;
-                if (valid)
-                    bulk_g2s(ring + pos.stage * kStageBytes + r * kSegStride, w + row * ldw + k0, (uint32_t)bytes,
-                             &c->full[pos.stage]);
-                pos.advance();
-            }
-        }
-        return true;
-    }
-    for (int g = 0; g < groups; ++g) {
-        int col;
-        const int row = gemv_weight_row(swi, o0, g, lane & 7, &col);
-        const bool valid = lane < 8 && col < o1;
-        const int nvalid = swi ? 2 * min(4, o1 - o0 - g * 4) : min(8, o1 - o0 - g * 8);
-        for (int kc = 0; kc < nkc; ++kc) {
-            const int k0 = kc * kGemvKChunk;
-            const int kl = min(kGemvKChunk, K - k0);
-            bool ok = true;
-            if (lane == 0) {
-                ok = wait_barrier(p, c, &c->empty[pos.stage], pos.phase ^ 1u, seq, WHERE_RING_EMPTY);
-                if (ok) mbar_arrive_expect_tx(&c->full[pos.stage], (uint32_t)(nvalid * kl * 2));
-            }
-            ok = __shfl_sync(0xffffffffu, ok, 0);
-            if (!ok) return false;
-            if (valid)
-                bulk_g2s(ring + pos.stage * kStageBytes + (lane & 7) * (kGemvKChunk * 2), w + row * ldw + k0,
-                         (uint32_t)(kl * 2), &c->full[pos.stage]);
-            pos.advance();
+            const int k0 = seg * kSegElems;
+            if (lane < 16 && o < o1) { src = w + row * ldw + k0; bytes = min(kSegElems, K - k0) * 2; dst_off = r * kSegStride; }
+        } else {
+            int col;
+            const int row = gemv_weight_row(swi, o0, g, lane & 7, &col);
+            const int k0 = seg * kGemvKChunk;
+            if (lane < 8 && col < o1) { src = w + row * ldw + k0; bytes = min(kGemvKChunk, K - k0) * 2; dst_off = (lane & 7) * (kGemvKChunk * 2); }
         }
     }
-    return true;
+};
+
+// Producer warp main loop.  TRACE: role-0 records (seq, first stage issued, -, last stage issued).
+template <bool TRACE>
+__device__ __forceinline__ void producer_loop(const Params& p, Ctrl* c, uint8_t* ring) {
+    const int lane = threadIdx.x & 31;
+    RingPos pos;
+    StageCursor rc, pc;
+    rc.idx = blockIdx.x;
+    rc.seek(p);
+    pc = rc;
+    int ahead = 0;                                   // stages the prefetch cursor is ahead of the ring cursor
+    long long t_first = 0;
+    int slot_first = 0;
+    while (rc.valid(p)) {
+        // one lane looks whether the ring has a free stage (non-blocking)
+        int free_now = 0;
+        if (lane == 0) free_now = mbar_try_wait(&c->empty[pos.stage], pos.phase ^ 1u) ? 1 : 0;
+        free_now = __shfl_sync(0xffffffffu, free_now, 0);
+        if (!free_now && ahead < p.pf_stages && pc.valid(p)) {
+            // ring full: let L2 fetch a stage further down the stream
+            if (ahead == 0) { pc = rc; }
+            const __nv_bfloat16* src; int bytes, off;
+            pc.piece(lane, src, bytes, off);
+            if (bytes) bulk_prefetch_l2(src, (uint32_t)bytes);
+            pc.advance(p);
+            ++ahead;
+            continue;
+        }
+        if (!free_now) {
+            int ok = 1;
+            if (lane == 0) ok = wait_barrier(p, c, &c->empty[pos.stage], pos.phase ^ 1u, rc.seq, WHERE_RING_EMPTY) ? 1 : 0;
+            if (!__shfl_sync(0xffffffffu, ok, 0)) return;
+        }
+        const __nv_bfloat16* src; int bytes, off;
+        rc.piece(lane, src, bytes, off);
+        const int total = __reduce_add_sync(0xffffffffu, bytes);
+        if (lane == 0) mbar_arrive_expect_tx(&c->full[pos.stage], (uint32_t)total);
+        __syncwarp();
+        if (bytes) bulk_g2s(ring + pos.stage * kStageBytes + off, src, (uint32_t)bytes, &c->full[pos.stage]);
+        if (TRACE && rc.g == 0 && rc.seg == 0) { t_first = (long long)globaltimer(); slot_first = (rc.idx - blockIdx.x) / gridDim.x; }
+        const bool last = rc.g == rc.ngroups - 1 && rc.seg == rc.nseg - 1;
+        if (TRACE && last && lane == 0) trace_rec<TRACE>(p, 0, slot_first, rc.seq, t_first, t_first, (long long)globaltimer());
+        pos.advance();
+        rc.advance(p);
+        if (ahead > 0) --ahead;
+    }
 }
 
 }  // namespace mk

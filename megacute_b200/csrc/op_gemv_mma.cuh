@@ -2,8 +2,16 @@
 //   out[m][o] = act(rstd[m] * sum_k w[o][k] * (x[m][k] * gain[k]) + bias[o]) + residual[m][o],  m < M <= 8
 // Stage layout, flag and producer side: op_gemv_common.cuh.
 //
+// The code is deliberately compact (rolled outer loops, one code path for every K): a decode step
+// runs each op body once per instruction, so the bodies execute cold and a large unrolled body is
+// paid for in instruction-cache misses (measured: "no instruction" was the top stall reason).
+//
 // Shared memory (work region):
-//   xh, xl   [M][K] bf16 high / low halves of x * gain, rows padded by 16 bytes (bank spread)
+//   xf       [M][K/16][4 lanes][4 words]: x * gain split into bf16 high and low parts, stored in
+//            MMA B-fragment order: for k-step s and lane quad position j the 16 bytes are
+//            {hi k=2j,2j+1 | hi k=2j+8,2j+9 | lo k=2j,2j+1 | lo k=2j+8,2j+9} of the 16 k of step s,
+//            so a lane fetches its whole B operand of a k-step with one 128-bit load.  Rows are
+//            padded by 64 bytes so the 8 activation rows of a quarter-warp hit different banks.
 //   red      [4 slots][8 warps][32 lanes] float4: per-warp partial 16 x 8 tiles of a row group
 //   gatebuf  [32 lanes] float4: swiglu gate tile between the gate group and the up group
 //   cnt      [4 slots] arrivals of the combine;  rowstat [8 warps][8 rows] partial sums of x^2
@@ -13,7 +21,7 @@
 
 namespace mk {
 
-constexpr int kMmaRedOff = 66 * 1024;                      // xh + xl take at most 64 KB + 256 B
+constexpr int kMmaRedOff = 66 * 1024;                      // xf takes at most 64 KB + 512 B
 constexpr int kMmaGateOff = kMmaRedOff + 4 * 8 * 32 * 16;  // + 16 KB
 constexpr int kMmaCntOff = kMmaGateOff + 32 * 16;
 constexpr int kMmaStatOff = kMmaCntOff + 64;
@@ -26,85 +34,81 @@ __device__ __forceinline__ float4 lds_volatile4(const float4* p) {
 __device__ __forceinline__ void sts_volatile4(float4* p, float4 v) {
     asm volatile("st.volatile.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(smem_u32(p)), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
 }
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
 
 // The op waits for its own dependencies so that loads which depend on nothing in the launch (the
 // norm gain) are already in flight when the wait ends.
-// SC = number of K segments whose B fragments (this warp's slices of x) stay in registers for the
-// whole instruction: 1 or 2 when K is exactly 1 or 2 segments, 0 = reload them from shared memory
-// every stage (longer or ragged K).
-template <int SC>
 __device__ __forceinline__ void gemv_mma(const Params& p, Ctrl* c, uint8_t* ring, uint8_t* work, const mk_op_desc* op,
                                          int o0, int o1, int seq, RingPos& pos, int nwait, int wait_off) {
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     const int M = op->i[0], K = op->i[2], act = op->i[3], odt = op->i[5], rdt = op->i[6];
     const bool swi = op->flags & GEMV_F_SWIGLU, rms = op->flags & GEMV_F_RMS;
     const int S = (K + kSegElems - 1) / kSegElems;
-    const int xs_stride = K * 2 + 16;                                         // bytes per padded row
-    uint8_t* xh = work;
-    uint8_t* xl = work + M * xs_stride;
+    const int xrow = K * 4 + 64;                                              // bytes per activation row of xf
+    uint8_t* xf = work;
     float4* red = reinterpret_cast<float4*>(work + kMmaRedOff);
     float4* gatebuf = reinterpret_cast<float4*>(work + kMmaGateOff);
     int* cnt = reinterpret_cast<int*>(work + kMmaCntOff);
     float* rowstat = reinterpret_cast<float*>(work + kMmaStatOff);
 
-    // ---- before the dependency wait: the norm gain of this thread's vectors (K <= 16384) ----
+    // ---- before the dependency wait: the norm gain of this thread's first vectors ----
     const int nv = K >> 3;
-    uint4 graw[8];
-    {
-        const uint4* gain = reinterpret_cast<const uint4*>(op->ptr[5]);
+    const uint4* gain = (rms && op->ptr[5]) ? reinterpret_cast<const uint4*>(op->ptr[5]) : nullptr;
+    const uint4 ones = make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u);
+    uint4 g0[4];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const int v = t + i * kComputeThreads;
-            graw[i] = (rms && gain && v < nv) ? __ldg(gain + v) : make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u);
-        }
-        if (t < 4) cnt[t] = 0;
+    for (int i = 0; i < 4; ++i) {
+        const int v = t + i * kComputeThreads;
+        g0[i] = (gain && v < nv) ? __ldg(gain + v) : ones;
     }
+    if (t < 4) cnt[t] = 0;
     if (wait_deps(p, c, nwait, wait_off, seq)) return;
     if (t == 0 && p.trace_cap > 0) c->t_dep = (long long)globaltimer();
 
-    // ---- stage x * gain as bf16 high + low parts; accumulate sum(x^2) per row ----
+    // ---- stage x * gain (high + low bf16 parts, fragment order); accumulate sum(x^2) per row ----
     {
         const int xdt = op->i[4];
         const void* x = reinterpret_cast<const void*>(op->ptr[0]);
         const long long ldx = op->ld[0];
-        float ss[8];
+#pragma unroll 1
+        for (int m = 0; m < M; ++m) {
+            float ss = 0.f;
+#pragma unroll 1
+            for (int vb = 0; vb < nv; vb += 4 * kComputeThreads) {            // batches of 4 vectors per thread
+                float f[4][8];
 #pragma unroll
-        for (int m = 0; m < 8; ++m) {
-            ss[m] = 0.f;
-            if (m < M) {
-                // all loads of the row are issued before any is used: one L2 round trip per row
-                float f[8][8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const int v = t + i * kComputeThreads;
+                for (int i = 0; i < 4; ++i) {                                 // all loads of the batch first
+                    const int v = vb + t + i * kComputeThreads;
                     if (v < nv) load8(x, m * ldx + v * 8, xdt, f[i]);
                 }
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const int v = t + i * kComputeThreads;
+                for (int i = 0; i < 4; ++i) {
+                    const int v = vb + t + i * kComputeThreads;
                     if (v < nv) {
-                        float g[8], hi[8], lo[8];
-                        unpack8(graw[i], g);
+                        float gq[8];
+                        unpack8(vb == 0 ? g0[i] : (gain ? __ldg(gain + v) : ones), gq);
+                        uint32_t hi[4], lo[4];
 #pragma unroll
-                        for (int e = 0; e < 8; ++e) {
-                            ss[m] += f[i][e] * f[i][e];
-                            const float y = f[i][e] * g[e];
-                            hi[e] = round_bf16(y);
-                            lo[e] = y - hi[e];
+                        for (int j = 0; j < 4; ++j) {
+                            const float y0 = f[i][2 * j] * gq[2 * j], y1 = f[i][2 * j + 1] * gq[2 * j + 1];
+                            ss += f[i][2 * j] * f[i][2 * j] + f[i][2 * j + 1] * f[i][2 * j + 1];
+                            const float h0 = round_bf16(y0), h1 = round_bf16(y1);
+                            hi[j] = pack2(h0, h1);
+                            lo[j] = pack2(y0 - h0, y1 - h1);
                         }
-                        *reinterpret_cast<uint4*>(xh + m * xs_stride + v * 16) = pack8(hi);
-                        *reinterpret_cast<uint4*>(xl + m * xs_stride + v * 16) = pack8(lo);
+                        uint32_t* d = reinterpret_cast<uint32_t*>(xf + m * xrow + (v >> 1) * 64 + (v & 1) * 4);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) { d[j * 4] = hi[j]; d[j * 4 + 2] = lo[j]; }
                     }
                 }
             }
-        }
-        if (rms) {
-#pragma unroll
-            for (int m = 0; m < 8; ++m) {
-                if (m < M) {
-                    const float s = warp_sum(ss[m]);
-                    if (lane == 0) rowstat[warp * 8 + m] = s;
-                }
+            if (rms) {
+                ss = warp_sum(ss);
+                if (lane == 0) rowstat[warp * 8 + m] = ss;
             }
         }
         compute_sync();
@@ -133,26 +137,11 @@ __device__ __forceinline__ void gemv_mma(const Params& p, Ctrl* c, uint8_t* ring
     const long long ldo = op->ld[2], ldr = op->ld[4];
     const int kw = warp * 128;                                                // this warp's K slice of a segment
     const int bm = lane >> 2;                                                 // B-operand column = activation row
-    const uint32_t a_lane = (uint32_t)((lane & 15) * kSegStride + ((lane >> 4) * 8) * 2);
+    const uint32_t a_lane = (uint32_t)((lane & 15) * kSegStride + ((lane >> 4) * 8) * 2 + kw * 2);
     const uint32_t bmask = bm < M ? 0xffffffffu : 0u;                        // lanes of absent rows feed zeros
-    const uint32_t xh_lane = smem_u32(xh) + (bm < M ? bm : 0) * xs_stride + (lane & 3) * 4;
-    const uint32_t xl_lane = smem_u32(xl) + (bm < M ? bm : 0) * xs_stride + (lane & 3) * 4;
-    auto load_b = [&](uint32_t off, uint32_t* b) {
-        asm volatile("ld.shared.b32 %0, [%1];" : "=r"(b[0]) : "r"(xh_lane + off));
-        asm volatile("ld.shared.b32 %0, [%1];" : "=r"(b[1]) : "r"(xh_lane + off + 16));
-        asm volatile("ld.shared.b32 %0, [%1];" : "=r"(b[2]) : "r"(xl_lane + off));
-        asm volatile("ld.shared.b32 %0, [%1];" : "=r"(b[3]) : "r"(xl_lane + off + 16));
-        b[0] &= bmask; b[1] &= bmask; b[2] &= bmask; b[3] &= bmask;
-    };
-    constexpr int NC = SC > 0 ? SC : 1;
-    uint32_t bq[NC][8][4];
-    if (SC > 0) {
-#pragma unroll
-        for (int sg = 0; sg < NC; ++sg)
-#pragma unroll
-            for (int ks = 0; ks < 8; ++ks) load_b((uint32_t)((sg * kSegElems + kw + ks * 16) * 2), bq[sg][ks]);
-    }
+    const uint32_t b_lane = smem_u32(xf) + (bm < M ? bm : 0) * xrow + (kw >> 4) * 64 + (lane & 3) * 16;
 
+#pragma unroll 1
     for (int g = 0; g < ngroups; ++g) {
         const int ob = o0 + (swi ? g >> 1 : g) * 16 + (lane >> 2);            // this lane's rows: ob, ob + 8
         // epilogue operands are requested before the stage waits so their latency is hidden
@@ -179,51 +168,44 @@ __device__ __forceinline__ void gemv_mma(const Params& p, Ctrl* c, uint8_t* ring
             for (int e = 0; e < 4; ++e) accs[q][e] = 0.f;
         bool ok = true;
         int last_stage = 0;
-        const int nseg = SC > 0 ? SC : S;
-#pragma unroll(NC)
-        for (int seg = 0; seg < nseg; ++seg) {
+#pragma unroll 1
+        for (int seg = 0; seg < S; ++seg) {
             ok = wait_barrier(p, c, &c->full[pos.stage], pos.phase, seq, WHERE_RING_FULL) && ok;
             if (g == 0 && seg == 0) phase_mark(p, c, 1);
-            const int seglen = SC > 0 ? kSegElems : min(kSegElems, K - seg * kSegElems);
-            if (ok) {
-                const uint32_t a_base = smem_u32(ring + pos.stage * kStageBytes) + a_lane + kw * 2;
+            const int left = min(kSegElems, K - seg * kSegElems) - kw;        // K elements of this warp's slice
+            if (ok && left > 0) {
+                const uint32_t a_base = smem_u32(ring + pos.stage * kStageBytes) + a_lane;
+                const uint32_t b_base = b_lane + seg * (kSegElems / 16) * 64;
                 uint32_t a[8][4];
+                uint4 b[8];
 #pragma unroll
-                for (int ks = 0; ks < 8; ++ks)
-                    if (SC > 0 || kw + ks * 16 < seglen) ldmatrix_x4(a_base + ks * 32, a[ks][0], a[ks][1], a[ks][2], a[ks][3]);
-                if (SC > 0) {
-#pragma unroll
-                    for (int ks = 0; ks < 8; ++ks) {
-                        mma_bf16(accs[(ks & 1) * 2], a[ks], bq[seg][ks][0], bq[seg][ks][1]);
-                        mma_bf16(accs[(ks & 1) * 2 + 1], a[ks], bq[seg][ks][2], bq[seg][ks][3]);
+                for (int ks = 0; ks < 8; ++ks) {
+                    if (ks * 16 < left) {
+                        ldmatrix_x4(a_base + ks * 32, a[ks][0], a[ks][1], a[ks][2], a[ks][3]);
+                        b[ks] = lds128(b_base + ks * 64);
                     }
-                } else {
-                    uint32_t b[8][4];
+                }
 #pragma unroll
-                    for (int ks = 0; ks < 8; ++ks)
-                        if (kw + ks * 16 < seglen) load_b((uint32_t)((seg * kSegElems + kw + ks * 16) * 2), b[ks]);
-#pragma unroll
-                    for (int ks = 0; ks < 8; ++ks) {
-                        if (kw + ks * 16 < seglen) {
-                            mma_bf16(accs[(ks & 1) * 2], a[ks], b[ks][0], b[ks][1]);
-                            mma_bf16(accs[(ks & 1) * 2 + 1], a[ks], b[ks][2], b[ks][3]);
-                        }
+                for (int ks = 0; ks < 8; ++ks) {
+                    if (ks * 16 < left) {
+                        mma_bf16(accs[(ks & 1) * 2], a[ks], b[ks].x & bmask, b[ks].y & bmask);
+                        mma_bf16(accs[(ks & 1) * 2 + 1], a[ks], b[ks].z & bmask, b[ks].w & bmask);
                     }
                 }
             }
             last_stage = pos.stage;
-            if (seg + 1 < nseg) {
+            if (seg + 1 < S) {
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&c->empty[pos.stage]);
                 pos.advance();
             }
         }
-        float acc[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) acc[e] = (accs[0][e] + accs[1][e]) + (accs[2][e] + accs[3][e]);
         // ---- combine the 8 warps' K slices: the last warp to arrive owns the epilogue ----
         float4* slot = red + last_stage * (8 * 32);
-        sts_volatile4(&slot[warp * 32 + lane], make_float4(acc[0], acc[1], acc[2], acc[3]));
+        sts_volatile4(&slot[warp * 32 + lane], make_float4((accs[0][0] + accs[1][0]) + (accs[2][0] + accs[3][0]),
+                                                           (accs[0][1] + accs[1][1]) + (accs[2][1] + accs[3][1]),
+                                                           (accs[0][2] + accs[1][2]) + (accs[2][2] + accs[3][2]),
+                                                           (accs[0][3] + accs[1][3]) + (accs[2][3] + accs[3][3])));
         __syncwarp();
         int fin = 0;
         if (lane == 0) {

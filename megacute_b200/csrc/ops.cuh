@@ -13,15 +13,15 @@
 namespace mk {
 
 // ring position in / out is packed as stage | phase << 8
-// (this op waits for its own dependencies: see gemv_units)
+// (this op waits for its own dependencies and publishes its own arrivals; returns -1 when aborting)
 __device__ int mk_op_gemv_units(const Params& p, const mk_op_desc* op, int o0, int o1, int seq, int packed_pos, int nwait,
-                                int wait_off);
+                                int wait_off, int narrive, int arrive_off);
 __device__ int mk_op_gemv_general(const Params& p, const mk_op_desc* op, int o0, int o1, int seq, int packed_pos);
 __device__ void mk_op_gemm(const mk_op_desc* op, int a0, int a1, int a2);
 __device__ void mk_op_attention(const mk_op_desc* op, int a0, int a1, int a2);
-// (waits for its own dependencies: see op_decode_attn)
-__device__ void mk_op_decode_attn(const Params& p, const mk_op_desc* op, int a0, int a1, int a2, int nwait, int wait_off,
-                                  int seq);
+// (waits for its own dependencies and publishes its own arrivals; returns whether the CTA is aborting)
+__device__ bool mk_op_decode_attn(const Params& p, const mk_op_desc* op, int a0, int a1, int a2, int nwait, int wait_off,
+                                  int seq, int narrive, int arrive_off);
 // finalize / eltwise / norm / rope_append / increment; returns false for an unknown kind
 __device__ bool mk_op_pointwise(const mk_op_desc* op, int a0, int a1);
 
