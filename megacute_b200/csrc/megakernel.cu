@@ -44,21 +44,57 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
         producer_loop<TRACE>(p, c, ring);
     } else {
         // ---------------- compute warps ----------------
+        // Instruction metadata runs one instruction ahead in shared memory (Meta): while instruction
+        // i executes, warp 1 has asynchronous copies in flight for the row of i + 2 and, from the
+        // already staged row of i + 1, for that instruction's op descriptor, waits and arrivals.
+        // The barrier that ends instruction i (publish) makes them visible to every thread.
         RingPos pos;
         int slot = 0;
+        Meta* mt = &c->meta;
+        const int lane = threadIdx.x & 31;
+        auto stage_row = [&](int idx, int s3) {       // lanes 0..3 of the calling warp
+            if (idx < p.n_insts && lane < 4) cp_async16(&mt->inst[s3][lane], p.insts + (long long)idx * 4 + lane, true);
+        };
+        auto stage_op = [&](int s3, int s2) {         // whole calling warp; row s3 must be visible already
+            const int4 w0 = mt->inst[s3][0], w2 = mt->inst[s3][2];
+            const int opi = w0.x - 1;
+            if (opi >= 0 && opi < p.n_ops && lane < 16)
+                cp_async16(reinterpret_cast<uint8_t*>(&mt->desc[s2]) + lane * 16, reinterpret_cast<const uint8_t*>(p.ops + opi) + lane * 16, true);
+            if (w2.x <= kMetaWaits && lane < w2.x) cp_async_small(&mt->waits[s2][lane], p.waits + w2.y + lane, 8);
+            if (w2.z <= kMetaArrives && lane >= 16 && lane - 16 < w2.z) cp_async_small(&mt->arrives[s2][lane - 16], p.arrives + w2.w + lane - 16, 4);
+        };
+        if (warp == 1) {
+            stage_row(blockIdx.x, 0);
+            stage_row(blockIdx.x + gridDim.x, 1);
+            cp_async_commit();
+            cp_async_wait<0>();
+            __syncwarp();
+            if (blockIdx.x < p.n_insts) stage_op(0, 0);
+            cp_async_commit();
+            cp_async_wait<0>();
+        }
+        compute_sync();
         for (int idx = blockIdx.x; idx < p.n_insts; idx += gridDim.x, ++slot) {
-            const Inst in = fetch_inst(p, idx);
+            const int s3 = slot % 3, s2 = slot & 1;
+            const Inst in = decode_inst(mt->inst[s3]);
+            if (warp == 1) {
+                stage_row(idx + 2 * gridDim.x, (slot + 2) % 3);
+                if (idx + gridDim.x < p.n_insts) stage_op((slot + 1) % 3, s2 ^ 1);
+                cp_async_commit();
+            }
             const int opi = in.opi - 1;
             if (opi < 0 || opi >= p.n_ops) {
                 if (threadIdx.x == 0) report(p, c, MK_DEV_BAD_INST, in.seq, 0, in.opi, idx, 0);
                 break;
             }
-            const mk_op_desc* op = p.ops + opi;
+            const mk_op_desc* op = &mt->desc[s2];
+            const int wait_off = in.nwait <= kMetaWaits ? -1 - s2 : in.wait_off;
+            const int arrive_off = in.narrive <= kMetaArrives ? -1 - s2 : in.arrive_off;
             const long long t0 = TRACE ? (long long)globaltimer() : 0;
             // the single-row streaming linear and decode attention wait for their dependencies
             // themselves, after requesting what depends on nothing in this launch
             const bool self_wait = (op->kind == MK_OP_GEMV && (op->flags & GEMV_F_UNITS)) || op->kind == MK_OP_DECODE_ATTN;
-            if (!self_wait && wait_deps(p, c, in.nwait, in.wait_off, in.seq)) break;
+            if (!self_wait && wait_deps(p, c, in.nwait, wait_off, in.seq)) break;
             long long t1 = TRACE ? (long long)globaltimer() : 0;
             const int ppos = pos.stage | ((int)pos.phase << 8);
             int npos = ppos;
@@ -66,8 +102,7 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
             switch (op->kind) {
                 case MK_OP_GEMV:
                     if (op->flags & GEMV_F_UNITS) {
-                        npos = mk_op_gemv_units(p, op, in.a0, in.a1, in.seq, ppos, in.nwait, in.wait_off, in.narrive,
-                                                in.arrive_off);
+                        npos = mk_op_gemv_units(p, op, in.a0, in.a1, in.seq, ppos, in.nwait, wait_off, in.narrive, arrive_off);
                         aborting = npos < 0;
                         if (TRACE) t1 = c->t_dep;
                     } else {
@@ -77,8 +112,7 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
                 case MK_OP_GEMM: mk_op_gemm(op, in.a0, in.a1, in.a2); break;
                 case MK_OP_ATTENTION: mk_op_attention(op, in.a0, in.a1, in.a2); break;
                 case MK_OP_DECODE_ATTN:
-                    aborting = mk_op_decode_attn(p, op, in.a0, in.a1, in.a2, in.nwait, in.wait_off, in.seq, in.narrive,
-                                                 in.arrive_off);
+                    aborting = mk_op_decode_attn(p, op, in.a0, in.a1, in.a2, in.nwait, wait_off, in.seq, in.narrive, arrive_off);
                     if (TRACE) t1 = c->t_dep;
                     break;
                 default: known = mk_op_pointwise(op, in.a0, in.a1); break;
@@ -86,13 +120,14 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
             if (!known && threadIdx.x == 0) report(p, c, MK_DEV_BAD_INST, in.seq, 1, op->kind, idx, 0);
             pos.stage = npos & 0xff;
             pos.phase = (uint32_t)(npos >> 8);
-            if (!self_wait) aborting = publish(p, c, in.narrive, in.arrive_off);
+            if (!self_wait) aborting = publish(p, c, in.narrive, arrive_off);
             if (threadIdx.x == 0) {
                 trace_rec<TRACE>(p, 1, slot, in.seq, t0, t1, (long long)globaltimer());
                 if (TRACE && self_wait) trace_rec<TRACE>(p, 2, slot, in.seq, c->t_phase[0], c->t_phase[1], c->t_phase[2]);
             }
             if (aborting) break;
         }
+        asm volatile("cp.async.wait_all;" ::: "memory");      // staged metadata of instructions that never ran
     }
     __syncthreads();
     // Abort path only: bulk copies may still be landing in the ring.  Wait (bounded) for the

@@ -29,7 +29,7 @@ constexpr int kStages = 4;
 constexpr int kRingBytes = kStages * kStageBytes;         // 129 KB, written only by bulk copies
 constexpr int kWorkBytes = 96 * 1024;                     // scratch of the instruction being executed
 constexpr int kXbufBytes = 64 * 1024;                     // GEMV: fp32 activation rows (front of work)
-constexpr int kCtrlBytes = 1024;                          // mbarriers, flags
+constexpr int kCtrlBytes = 2048;                          // mbarriers, flags, staged instruction metadata
 constexpr int kSmemBytes = kRingBytes + kWorkBytes + kCtrlBytes;
 
 struct Params {
@@ -48,7 +48,21 @@ struct Params {
     int pf_stages;                // how many ring stages ahead of the ring the producer prefetches into L2
 };
 
+// Instruction metadata staged in shared memory one instruction ahead of its use.  Everything an
+// instruction needs before its first useful load (its words, its op descriptor, its wait and
+// arrival lists) would otherwise be a chain of dependent global loads, each a round trip to L2 or
+// DRAM on the critical path between two dependent instructions.
+constexpr int kMetaWaits = 16;    // longer lists are read from global memory
+constexpr int kMetaArrives = 8;
+struct Meta {
+    mk_op_desc desc[2];           // current / next instruction's op
+    int4 inst[3][4];              // rows of the current and the next two instructions
+    int2 waits[2][kMetaWaits];
+    int arrives[2][kMetaArrives];
+};
+
 struct Ctrl {                     // lives in the last kCtrlBytes of shared memory
+    Meta meta;
     unsigned long long full[kStages];
     unsigned long long empty[kStages];
     int abort;                    // set once a wait of this CTA gave up or saw the global abort
@@ -95,12 +109,32 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
                  "l"(src), "r"(bytes), "r"(smem_u32(bar))
                  : "memory");
 }
+// Same with an L2 eviction policy (createpolicy).  Streamed weights are read once per launch and
+// are many times the size of L2; marking them evict-first keeps them from pushing out what is
+// read again soon: instruction tables, op descriptors, activations and the KV cache.
+__device__ __forceinline__ unsigned long long l2_policy_evict_first() {
+    unsigned long long pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ void bulk_g2s_hint(void* dst, const void* src, uint32_t bytes, unsigned long long* bar,
+                                              unsigned long long policy) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(
+            smem_u32(dst)),
+        "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
+        : "memory");
+}
 __device__ __forceinline__ void bulk_prefetch_l2(const void* src, uint32_t bytes) {
     asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
     int sz = valid ? 16 : 0;      // src-size 0: the 16 bytes are zero-filled
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(sz) : "memory");
+}
+__device__ __forceinline__ void cp_async_small(void* dst, const void* src, int bytes) {      // 4 or 8 bytes
+    if (bytes == 8) asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+    else asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
@@ -289,6 +323,13 @@ struct Inst {
     int a0, a1, a2, a3;           // op-specific arguments
     int nwait, wait_off, narrive, arrive_off, seq;
 };
+__device__ __forceinline__ Inst decode_inst(const int4* row) {      // row in shared memory
+    const int4 w0 = row[0], w1 = row[1], w2 = row[2], w3 = row[3];
+    Inst i;
+    i.opi = w0.x; i.a0 = w0.y; i.a1 = w0.z; i.a2 = w0.w; i.a3 = w1.x;
+    i.nwait = w2.x; i.wait_off = w2.y; i.narrive = w2.z; i.arrive_off = w2.w; i.seq = w3.x;
+    return i;
+}
 __device__ __forceinline__ Inst fetch_inst(const Params& p, int idx) {
     const int4* src = p.insts + (long long)idx * 4;
     const int4 w0 = __ldg(src), w1 = __ldg(src + 1), w2 = __ldg(src + 2), w3 = __ldg(src + 3);
@@ -310,21 +351,31 @@ __device__ __forceinline__ bool compute_sync_or(int pred) {
 }
 
 // All compute threads call this.  Threads take waits round-robin.  Returns (uniformly) whether
-// the CTA is aborting.
+// the CTA is aborting.  wait_off < 0 names the staged list Meta::waits[-1 - wait_off].
 __device__ __forceinline__ bool wait_deps(const Params& p, Ctrl* c, int nwait, int wait_off, int seq) {
+    const int2* tab = wait_off < 0 ? c->meta.waits[-1 - wait_off] : p.waits + wait_off;
     for (int k = threadIdx.x; k < nwait; k += kComputeThreads) {
-        int2 w = __ldg(p.waits + wait_off + k);
+        const int2 w = tab[k];
         wait_counter(p, c, w.x, w.y, seq);
     }
     return compute_sync_or(*(volatile int*)&c->abort);
 }
 // All compute threads call this after their global writes of the instruction.  Returns
 // (uniformly) whether the CTA is aborting; arrivals are skipped in that case.
+// arrive_off < 0 names the staged list Meta::arrives[-1 - arrive_off].  The barrier also ends the
+// instruction for the metadata staging: copies issued for the next instruction are waited for
+// before it, so every thread sees them after it.
 __device__ __forceinline__ bool publish(const Params& p, Ctrl* c, int narrive, int arrive_off) {
+    asm volatile("cp.async.wait_all;" ::: "memory");
+    // The staged list is read before the barrier: after it, the staging for the instruction after
+    // next may already be overwriting the list.
+    const int* tab = arrive_off < 0 ? c->meta.arrives[-1 - arrive_off] : p.arrives + arrive_off;
+    const int first = (int)threadIdx.x < narrive ? tab[threadIdx.x] : -1;
     // The barrier orders every compute thread's global writes before the arriving threads'
     // red.release.gpu, whose release is cumulative over them: no per-thread gpu-scope fence needed.
     if (compute_sync_or(*(volatile int*)&c->abort)) return true;
-    for (int k = threadIdx.x; k < narrive; k += kComputeThreads) red_release_add(p.counters + __ldg(p.arrives + arrive_off + k), 1);
+    if (first >= 0) red_release_add(p.counters + first, 1);
+    for (int k = threadIdx.x + kComputeThreads; k < narrive; k += kComputeThreads) red_release_add(p.counters + tab[k], 1);
     return false;
 }
 

@@ -125,6 +125,7 @@ __device__ __forceinline__ void producer_loop(const Params& p, Ctrl* c, uint8_t*
     int ahead = 0;                                   // stages the prefetch cursor is ahead of the ring cursor
     long long t_first = 0;
     int slot_first = 0;
+    const unsigned long long stream_policy = l2_policy_evict_first();
     while (rc.valid(p)) {
         // one lane looks whether the ring has a free stage (non-blocking)
         int free_now = 0;
@@ -150,7 +151,7 @@ __device__ __forceinline__ void producer_loop(const Params& p, Ctrl* c, uint8_t*
         const int total = __reduce_add_sync(0xffffffffu, bytes);
         if (lane == 0) mbar_arrive_expect_tx(&c->full[pos.stage], (uint32_t)total);
         __syncwarp();
-        if (bytes) bulk_g2s(ring + pos.stage * kStageBytes + off, src, (uint32_t)bytes, &c->full[pos.stage]);
+        if (bytes) bulk_g2s_hint(ring + pos.stage * kStageBytes + off, src, (uint32_t)bytes, &c->full[pos.stage], stream_policy);
         if (TRACE && rc.g == 0 && rc.seg == 0) { t_first = (long long)globaltimer(); slot_first = (rc.idx - blockIdx.x) / gridDim.x; }
         const bool last = rc.g == rc.ngroups - 1 && rc.seg == rc.nseg - 1;
         if (TRACE && last && lane == 0) trace_rec<TRACE>(p, 0, slot_first, rc.seq, t_first, t_first, (long long)globaltimer());

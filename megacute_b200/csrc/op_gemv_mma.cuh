@@ -214,14 +214,21 @@ __device__ __forceinline__ void gemv_mma(const Params& p, Ctrl* c, uint8_t* ring
             if (fin) cnt[last_stage] = 0;
             __threadfence_block();
         }
-        fin = __shfl_sync(0xffffffffu, fin, 0);
-        if (fin && ok) {
-            float v[4] = {0.f, 0.f, 0.f, 0.f};
+        fin = __shfl_sync(0xffffffffu, fin, 0) && ok;
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+        if (fin) {
 #pragma unroll
             for (int w8 = 0; w8 < kComputeWarps; ++w8) {
                 const float4 q = lds_volatile4(&slot[w8 * 32 + lane]);
                 v[0] += q.x; v[1] += q.y; v[2] += q.z; v[3] += q.w;
             }
+        }
+        // The stage goes back to the producer before the epilogue: the partial slot (named after
+        // the stage) has been read by then.
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&c->empty[pos.stage]);
+        pos.advance();
+        if (fin) {
             // v[0], v[1]: row ob, activation rows m0, m0 + 1;  v[2], v[3]: row ob + 8
             if (swi && !(g & 1)) {
                 sts_volatile4(&gatebuf[lane], make_float4(v[0] * rs[0], v[1] * rs[1], v[2] * rs[0], v[3] * rs[1]));
@@ -243,9 +250,6 @@ __device__ __forceinline__ void gemv_mma(const Params& p, Ctrl* c, uint8_t* ring
                 }
             }
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&c->empty[pos.stage]);
-        pos.advance();
     }
     phase_mark(p, c, 2);
 }
