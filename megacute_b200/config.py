@@ -14,9 +14,9 @@ NUM_THREADS = COMPUTE_THREADS + 32
 GEMV_MAX_ROWS = 8
 GEMV_XBUF_BYTES = 65536         # fp32 copy of the activation rows held in shared memory
 GEMV_ROWS_PER_STAGE = 16        # weight rows per ring stage
-GEMV_SEGMENT = 1024             # elements of a weight row per stage
+GEMV_SEGMENT = 2048             # elements of a weight row per stage (one 4 KB bulk copy)
 GEMV_STAGE_BYTES = GEMV_ROWS_PER_STAGE * (GEMV_SEGMENT * 2 + 16)
-GEMV_STAGES = 4
+GEMV_STAGES = 2
 
 # ---- tile GEMM path
 GEMM_BM, GEMM_BN, GEMM_BK = 128, 128, 32

@@ -19,14 +19,17 @@ constexpr int kProducerWarp = kComputeWarps;
 // ---- shared memory map -----------------------------------------------------------------------
 constexpr int kGemvRows = 8;                              // weight rows per ring stage
 constexpr int kGemvKChunk = 2048;                         // elements of a row per stage (8 per thread)
-// A ring stage holds 16 weight-row segments of 1024 elements, each padded by 16 bytes so that the
+// A ring stage holds 16 weight-row segments of 2048 elements, each padded by 16 bytes so that the
 // 8 rows an ldmatrix touches fall in different banks (tensor-core path), or 8 rows x 2048 elements
-// (general path).
-constexpr int kSegElems = 1024;
+// (general path).  Two large stages rather than several small ones: measured with a consumer that
+// only waits and releases, a ring of 4 x (16 x 2 KB bulk copies) tops out at 4.7 TB/s, 2 x (16 x
+// 4 KB) reaches 6.8 TB/s in the same shared memory: copies of 4 KB and up and fewer stage
+// hand-overs per byte are what the copy engine needs.
+constexpr int kSegElems = 2048;
 constexpr int kSegStride = kSegElems * 2 + 16;            // bytes between row segments of a stage
-constexpr int kStageBytes = 16 * kSegStride;              // 33 024 B
-constexpr int kStages = 4;
-constexpr int kRingBytes = kStages * kStageBytes;         // 129 KB, written only by bulk copies
+constexpr int kStageBytes = 16 * kSegStride;              // 65 792 B
+constexpr int kStages = 2;
+constexpr int kRingBytes = kStages * kStageBytes;         // 128.5 KB, written only by bulk copies
 constexpr int kWorkBytes = 96 * 1024;                     // scratch of the instruction being executed
 constexpr int kXbufBytes = 64 * 1024;                     // GEMV: fp32 activation rows (front of work)
 constexpr int kCtrlBytes = 2048;                          // mbarriers, flags, staged instruction metadata

@@ -109,7 +109,7 @@ __device__ __forceinline__ void decode_body(const Params& p, Ctrl* c, const mk_o
     {
         const void* q = reinterpret_cast<const void*>(op->ptr[0]);
         float kn[8], ko[8], vn[8];
-        if (has_new) {
+        if (has_new && kg == 0) {          // only the first key slot's threads use the new token's k and v
             const long long ek = (long long)b * op->ld[5] + kvh * D, ev = (long long)b * op->ld[6] + kvh * D;
             load8(reinterpret_cast<const void*>(op->ptr[5]), ek + dp * 8, qdt, kn);
             load8(reinterpret_cast<const void*>(op->ptr[5]), ek + pd, qdt, ko);
@@ -230,6 +230,7 @@ __device__ __forceinline__ void decode_body(const Params& p, Ctrl* c, const mk_o
     phase_mark(p, c, 0);
 
     // ---- the new token (fused mode, last split): attend it from registers and append it ----
+    if (ntiles == 0) compute_sync();     // no tile loop ran: its barriers are what orders snew otherwise
     if (has_new) {
         float kn[8], vn[8];
 #pragma unroll

@@ -135,10 +135,10 @@ __device__ __forceinline__ void gemv_mma(const Params& p, Ctrl* c, uint8_t* ring
     const void* resp = reinterpret_cast<const void*>(op->ptr[4]);
     void* outp = reinterpret_cast<void*>(op->ptr[2]);
     const long long ldo = op->ld[2], ldr = op->ld[4];
-    const int kw = warp * 128;                                                // this warp's K slice of a segment
+    constexpr int kSlice = kSegElems / kComputeWarps;                         // 256: a warp's K slice of a segment
+    const int kw = warp * kSlice;
     const int bm = lane >> 2;                                                 // B-operand column = activation row
     const uint32_t a_lane = (uint32_t)((lane & 15) * kSegStride + ((lane >> 4) * 8) * 2 + kw * 2);
-    const uint32_t bmask = bm < M ? 0xffffffffu : 0u;                        // lanes of absent rows feed zeros
     const uint32_t b_lane = smem_u32(xf) + (bm < M ? bm : 0) * xrow + (kw >> 4) * 64 + (lane & 3) * 16;
 
 #pragma unroll 1
@@ -167,41 +167,50 @@ __device__ __forceinline__ void gemv_mma(const Params& p, Ctrl* c, uint8_t* ring
 #pragma unroll
             for (int e = 0; e < 4; ++e) accs[q][e] = 0.f;
         bool ok = true;
-        int last_stage = 0;
 #pragma unroll 1
         for (int seg = 0; seg < S; ++seg) {
             ok = wait_barrier(p, c, &c->full[pos.stage], pos.phase, seq, WHERE_RING_FULL) && ok;
             if (g == 0 && seg == 0) phase_mark(p, c, 1);
-            const int left = min(kSegElems, K - seg * kSegElems) - kw;        // K elements of this warp's slice
-            if (ok && left > 0) {
-                const uint32_t a_base = smem_u32(ring + pos.stage * kStageBytes) + a_lane;
-                const uint32_t b_base = b_lane + seg * (kSegElems / 16) * 64;
-                uint32_t a[8][4];
-                uint4 b[8];
+            int left = min(kSegElems, K - seg * kSegElems) - kw;              // K elements of this warp's slice
+            if (ok) {
+                uint32_t a_base = smem_u32(ring + pos.stage * kStageBytes) + a_lane;
+                uint32_t b_base = b_lane + seg * (kSegElems / 16) * 64;
+#pragma unroll 1
+                for (int half = 0; half < kSlice / 128 && left > 0; ++half) {     // batches of 8 k-steps
+                    uint32_t a[8][4];
+                    uint4 b[8];
 #pragma unroll
-                for (int ks = 0; ks < 8; ++ks) {
-                    if (ks * 16 < left) {
-                        ldmatrix_x4(a_base + ks * 32, a[ks][0], a[ks][1], a[ks][2], a[ks][3]);
-                        b[ks] = lds128(b_base + ks * 64);
+                    for (int ks = 0; ks < 8; ++ks) {
+                        if (ks * 16 < left) {
+                            ldmatrix_x4(a_base + ks * 32, a[ks][0], a[ks][1], a[ks][2], a[ks][3]);
+                            // lanes of absent activation rows feed zeros and stay out of the load:
+                            // with one row only a quarter of the warp touches shared memory
+                            b[ks] = bm < M ? lds128(b_base + ks * 64) : make_uint4(0u, 0u, 0u, 0u);
+                        }
                     }
-                }
 #pragma unroll
-                for (int ks = 0; ks < 8; ++ks) {
-                    if (ks * 16 < left) {
-                        mma_bf16(accs[(ks & 1) * 2], a[ks], b[ks].x & bmask, b[ks].y & bmask);
-                        mma_bf16(accs[(ks & 1) * 2 + 1], a[ks], b[ks].z & bmask, b[ks].w & bmask);
+                    for (int ks = 0; ks < 8; ++ks) {
+                        if (ks * 16 < left) {
+                            mma_bf16(accs[(ks & 1) * 2], a[ks], b[ks].x, b[ks].y);
+                            mma_bf16(accs[(ks & 1) * 2 + 1], a[ks], b[ks].z, b[ks].w);
+                        }
                     }
+                    a_base += 8 * 32;
+                    b_base += 8 * 64;
+                    left -= 128;
                 }
             }
-            last_stage = pos.stage;
-            if (seg + 1 < S) {
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&c->empty[pos.stage]);
-                pos.advance();
-            }
+            // the stage goes back to the producer as soon as this warp has read its slice
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&c->empty[pos.stage]);
+            pos.advance();
         }
-        // ---- combine the 8 warps' K slices: the last warp to arrive owns the epilogue ----
-        float4* slot = red + last_stage * (8 * 32);
+        // ---- combine the 8 warps' K slices: the last warp to arrive owns the epilogue.  Four
+        // partial slots used round-robin: a warp can be at most two row groups ahead of the
+        // slowest one (the ring has two stages and every group takes at least one). ----
+        static_assert(kStages <= 3, "four partial slots cover a run-ahead of at most kStages row groups");
+        const int sl = g & 3;
+        float4* slot = red + sl * (8 * 32);
         sts_volatile4(&slot[warp * 32 + lane], make_float4((accs[0][0] + accs[1][0]) + (accs[2][0] + accs[3][0]),
                                                            (accs[0][1] + accs[1][1]) + (accs[2][1] + accs[3][1]),
                                                            (accs[0][2] + accs[1][2]) + (accs[2][2] + accs[3][2]),
@@ -210,8 +219,8 @@ __device__ __forceinline__ void gemv_mma(const Params& p, Ctrl* c, uint8_t* ring
         int fin = 0;
         if (lane == 0) {
             __threadfence_block();
-            fin = atomicAdd(&cnt[last_stage], 1) == kComputeWarps - 1;
-            if (fin) cnt[last_stage] = 0;
+            fin = atomicAdd(&cnt[sl], 1) == kComputeWarps - 1;
+            if (fin) cnt[sl] = 0;
             __threadfence_block();
         }
         fin = __shfl_sync(0xffffffffu, fin, 0) && ok;
@@ -223,11 +232,6 @@ __device__ __forceinline__ void gemv_mma(const Params& p, Ctrl* c, uint8_t* ring
                 v[0] += q.x; v[1] += q.y; v[2] += q.z; v[3] += q.w;
             }
         }
-        // The stage goes back to the producer before the epilogue: the partial slot (named after
-        // the stage) has been read by then.
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&c->empty[pos.stage]);
-        pos.advance();
         if (fin) {
             // v[0], v[1]: row ob, activation rows m0, m0 + 1;  v[2], v[3]: row ob + 8
             if (swi && !(g & 1)) {
