@@ -156,13 +156,16 @@ def main():
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
-    mc, g, params, st, ids, max_seq = build_workload(a.batch, a.ctx, dev, seed=rank)
+    from megacute_b200.sharding import max_over_ranks, shard_range
+    first_seq, n_seq = shard_range(a.batch * world, world, rank)       # weak scaling: batch_per_gpu sequences each
+    assert n_seq == a.batch
+    mc, g, params, st, ids, max_seq = build_workload(n_seq, a.ctx, dev, seed=rank)
     prog = mc.compile(g)
     emb = params["lm_head"]
     args = dict(params, **st)
 
     def step(ids):
-        st["x"].copy_(emb.index_select(0, ids))
+        torch.index_select(emb, 0, ids, out=st["x"])       # embedding rows of this step's tokens, straight into x
         return prog(**args).argmax(-1)
 
     def reset_state():
@@ -180,12 +183,7 @@ def main():
         fn(n)
         e1.record()
         barrier()
-        ms = e0.elapsed_time(e1) / n
-        if world > 1:
-            t = torch.tensor([ms], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t)
-        return ms
+        return max_over_ranks(e0.elapsed_time(e1) / n, dev)        # device time, slowest rank
 
     cur = [ids]
 
