@@ -66,14 +66,31 @@ __device__ __forceinline__ void gemv_mma(const Params& p, Ctrl* c, uint8_t* ring
         g0[i] = (gain && v < nv) ? __ldg(gain + v) : ones;
     }
     if (t < 4) cnt[t] = 0;
+    // everything below that does not depend on the activations is also set up before the wait:
+    // the op runs once per instruction, cold, and this code would otherwise sit between the
+    // arrival of x and the first MMA
+    // this lane's output columns of a 16 x 8 accumulator tile are activation rows m0 and m0 + 1
+    const int m0 = 2 * (lane & 3);
+    const int n = o1 - o0;
+    const int ngroups = (swi ? 2 : 1) * ((n + 15) / 16);
+    const void* biasp = reinterpret_cast<const void*>(op->ptr[3]);
+    const void* resp = reinterpret_cast<const void*>(op->ptr[4]);
+    void* outp = reinterpret_cast<void*>(op->ptr[2]);
+    const long long ldo = op->ld[2], ldr = op->ld[4];
+    constexpr int kSlice = kSegElems / kComputeWarps;                         // 256: a warp's K slice of a segment
+    const int kw = warp * kSlice;
+    const int bm = lane >> 2;                                                 // B-operand column = activation row
+    const uint32_t a_lane = (uint32_t)((lane & 15) * kSegStride + ((lane >> 4) * 8) * 2 + kw * 2);
+    const uint32_t b_lane = smem_u32(xf) + (bm < M ? bm : 0) * xrow + (kw >> 4) * 64 + (lane & 3) * 16;
+    const int xdt = op->i[4];
+    const void* x = reinterpret_cast<const void*>(op->ptr[0]);
+    const long long ldx = op->ld[0];
+    const float eps = op->f[0];
     if (wait_deps(p, c, nwait, wait_off, seq)) return;
     if (t == 0 && p.trace_cap > 0) c->t_dep = (long long)globaltimer();
 
     // ---- stage x * gain (high + low bf16 parts, fragment order); accumulate sum(x^2) per row ----
     {
-        const int xdt = op->i[4];
-        const void* x = reinterpret_cast<const void*>(op->ptr[0]);
-        const long long ldx = op->ld[0];
 #pragma unroll 1
         for (int m = 0; m < M; ++m) {
             float ss = 0.f;
@@ -114,8 +131,6 @@ __device__ __forceinline__ void gemv_mma(const Params& p, Ctrl* c, uint8_t* ring
         compute_sync();
     }
     phase_mark(p, c, 0);
-    // this lane's output columns of a 16 x 8 accumulator tile are activation rows m0 and m0 + 1
-    const int m0 = 2 * (lane & 3);
     float rs[2] = {1.f, 1.f};
     if (rms) {
 #pragma unroll
@@ -124,22 +139,10 @@ __device__ __forceinline__ void gemv_mma(const Params& p, Ctrl* c, uint8_t* ring
                 float sq = 0.f;
 #pragma unroll
                 for (int w8 = 0; w8 < kComputeWarps; ++w8) sq += rowstat[w8 * 8 + m0 + j];
-                rs[j] = rsqrt_approx(sq / (float)K + op->f[0]);
+                rs[j] = rsqrt_approx(sq / (float)K + eps);
             }
         }
     }
-
-    const int n = o1 - o0;
-    const int ngroups = (swi ? 2 : 1) * ((n + 15) / 16);
-    const void* biasp = reinterpret_cast<const void*>(op->ptr[3]);
-    const void* resp = reinterpret_cast<const void*>(op->ptr[4]);
-    void* outp = reinterpret_cast<void*>(op->ptr[2]);
-    const long long ldo = op->ld[2], ldr = op->ld[4];
-    constexpr int kSlice = kSegElems / kComputeWarps;                         // 256: a warp's K slice of a segment
-    const int kw = warp * kSlice;
-    const int bm = lane >> 2;                                                 // B-operand column = activation row
-    const uint32_t a_lane = (uint32_t)((lane & 15) * kSegStride + ((lane >> 4) * 8) * 2 + kw * 2);
-    const uint32_t b_lane = smem_u32(xf) + (bm < M ? bm : 0) * xrow + (kw >> 4) * 64 + (lane & 3) * 16;
 
 #pragma unroll 1
     for (int g = 0; g < ngroups; ++g) {
