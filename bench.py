@@ -166,7 +166,7 @@ def main():
 
     def step(ids):
         torch.index_select(emb, 0, ids, out=st["x"])       # embedding rows of this step's tokens, straight into x
-        return prog(**args).argmax(-1)
+        return mc.argmax(prog(**args))
 
     def reset_state():
         st["pos"].fill_(a.ctx)

@@ -154,6 +154,13 @@ int mk_launch_noalloc(int device, const int32_t* d_insts, int n_insts, const int
                       const int32_t* d_arrives, int n_arrives, const mk_op_desc* d_ops, int n_ops,
                       int n_counters, int grid, void* stream, int32_t status[MK_ST_WORDS]);
 
+/* Greedy sampling: out[r] = index of the largest element of row r of `logits` (rows x cols, leading
+ * dimension ld in elements; dtype 0 bf16 with ld % 8 == 0 and a 16-byte aligned base, 1 fp32), ties to
+ * the lowest index, NaN never selected.  Asynchronous on `stream`; `out` is device memory of `rows`
+ * int64.  Replaces the torch argmax of the reference's decode loop (examples/llama/llama1b.py:105),
+ * which reduces a 128 256-wide row in a single 512-thread block. */
+int mk_argmax(const void* logits, int dtype, int rows, int cols, long long ld, long long* out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

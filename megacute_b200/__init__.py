@@ -24,4 +24,10 @@ def compile(g, **kw):
     return _compile(g, **kw)
 
 
+def argmax(logits, out=None):
+    """Greedy sampling on the GPU (row-wise argmax of the logits); see ``runtime.argmax``."""
+    from .runtime import argmax as _argmax
+    return _argmax(logits, out)
+
+
 _sys.modules.setdefault("megacute", _sys.modules[__name__])

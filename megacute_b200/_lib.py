@@ -61,6 +61,7 @@ SYMBOLS = {
     "mk_program_destroy": (None, [_P]),
     "mk_launch_noalloc": (ctypes.c_int, [ctypes.c_int, _P, ctypes.c_int, _P, ctypes.c_int, _P, ctypes.c_int, _P, ctypes.c_int,
                                          ctypes.c_int, ctypes.c_int, _P, _I32P]),
+    "mk_argmax": (ctypes.c_int, [_P, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_longlong, _P, _P]),
 }
 
 

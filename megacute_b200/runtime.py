@@ -195,5 +195,20 @@ class Program:
         return Timeline(self, buf)
 
 
+def argmax(logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Greedy sampling: row-wise argmax of a (rows, cols) bf16 or fp32 CUDA tensor (ties to the lowest
+    index), one launch on the current stream.  Stands where the reference's decode loop calls
+    ``logits.argmax(-1)`` (``examples/llama/llama1b.py:105``)."""
+    if logits.dim() != 2 or not logits.is_cuda or logits.stride(1) != 1 or logits.dtype not in (torch.bfloat16, torch.float32):
+        raise ValueError("argmax: expected a 2-D CUDA bf16/fp32 tensor with unit inner stride")
+    rows, cols = logits.shape
+    if out is None:
+        out = torch.empty(rows, dtype=torch.int64, device=logits.device)
+    stream = ctypes.c_void_p(torch.cuda.current_stream(logits.device).cuda_stream)
+    _lib.check(_lib.load().mk_argmax(logits.data_ptr(), 0 if logits.dtype == torch.bfloat16 else 1, rows, cols,
+                                     logits.stride(0), out.data_ptr(), stream), "mk_argmax")
+    return out
+
+
 def compile(g: Graph, **kw) -> Program:
     return Program(g, **kw).compile()

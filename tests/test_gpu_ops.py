@@ -265,3 +265,25 @@ def test_timeline(cuda):
     tl = prog.timeline()
     assert len([r for r in tl.records if r[1] == 1]) == prog.sched.n
     assert tl.span_us() > 0 and "Linear" in tl.summary() and len(tl.chrome_events()) > 0
+
+
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("rows,cols", [(1, 128256), (64, 128256), (3, 1000), (2, 8)])
+def test_argmax_rows(cuda, dtype, rows, cols):
+    g = torch.Generator(device=cuda).manual_seed(rows * 131 + cols)
+    x = torch.randn(rows, cols, generator=g, device=cuda, dtype=torch.float32).to(dtype)
+    # plant a unique maximum per row, and a tie whose lower index must win in row 0
+    want = torch.randint(0, cols, (rows,), generator=g, device=cuda)
+    x[torch.arange(rows, device=cuda), want] = 100.0
+    if cols > 8:
+        lo = int(want[0])
+        hi = min(cols - 1, lo + 5)
+        x[0, hi] = 100.0
+    got = mc.argmax(x)
+    assert got.dtype == torch.int64 and torch.equal(got, want)
+    # a view with a leading dimension larger than its width
+    wide = torch.zeros(rows, cols + 16, device=cuda, dtype=dtype)
+    wide[:, :cols] = x
+    assert torch.equal(mc.argmax(wide[:, :cols]), want)
