@@ -2,12 +2,15 @@
 //
 // One instruction = (sequence b, kv head j, split s of S).  The split owns a contiguous range of
 // the cached keys, computed on the device from pos so that any context length spreads evenly over
-// the S instructions.  Keys and values stream through a cp.async pipeline of 64-key tiles; the
-// G query heads of the kv head are held in registers.  With S > 1 every split writes an
-// unnormalised partial (O, running max, sum) and bumps an arrival count; the last split to arrive
-// merges the S partials and writes the output (no extra dependency hop).
-// Scores, probabilities and the rotated query stay fp32 (this path runs on CUDA cores, so the
-// reference's bf16 rounding of P and q before its tensor-core products is not needed); the
+// the S instructions.  Keys and values stream through a two-stage cp.async pipeline of 128-key
+// tiles (64 for head_dim 128).  S = Q K^T and O += P V run on tensor cores (mma.sync m16n8k16): the
+// G <= 8 query heads of the kv head are the rows of the A operand, every warp works on its own 16
+// keys of a tile with its own running max and sum, and the warps are merged once after the loop,
+// so a tile costs two CTA barriers.  With S > 1 every split writes an unnormalised partial (O,
+// running max, sum) and bumps an arrival count; the last split to arrive merges the S partials
+// and writes the output (no extra dependency hop).
+// q and P are each split into bf16 high + low parts (two MMAs) so scores and probabilities keep
+// ~16 mantissa bits where the reference rounds both to bf16 (megacute/ops/attention.py:293); the
 // appended k and v are rounded to the cache's bf16 and the new token is scored with those values.
 // Fused mode (rope_append folded in): q, k_new, v_new are the un-rotated columns of the QKV row;
 // the op rotates q and k at pos, the last split also attends the new token from registers and
@@ -18,25 +21,31 @@
 // args: 0 b, 1 kv head, 2 split
 #pragma once
 #include "mk_device.cuh"
+#include "mma.cuh"
 
 namespace mk {
 
-constexpr int kDecTileKeys = 64;
+template <int D>
+constexpr int kDecTileKeys = D <= 64 ? 128 : 64;     // keys per tile; 16 per computing warp
 constexpr int kMaxKvSplits = 32;          // config.py MAX_KV_SPLITS
 
 template <int D, int GMAX>
 __device__ __forceinline__ void decode_body(const Params& p, Ctrl* c, const mk_op_desc* op, int a0, int a1, int a2,
                                             uint8_t* work, int nwait, int wait_off, int seq) {
-    constexpr int DP = D / 8;                         // threads per key (8 dims each)
-    constexpr int KPP = kComputeThreads / DP;         // keys per pass
-    constexpr int PASSES = kDecTileKeys / KPP;
-    constexpr int TILE_BYTES = kDecTileKeys * D * 2;
-    constexpr int NST = (D == 64) ? 4 : 2;
-    constexpr int VPT = kDecTileKeys * DP / kComputeThreads;      // 16-byte vectors per thread per tile
+    constexpr int ROWB = D * 2 + 16;                   // padded tile row: conflict-free ldmatrix
+    constexpr int TK = kDecTileKeys<D>;                // keys per tile; warp w owns keys 16w .. 16w + 15 of a tile
+    constexpr int NW = TK / 16;                        // warps that compute
+    constexpr int TILE_BYTES = TK * ROWB;              // one K or V tile
+    constexpr int NST = 2;
+    constexpr int CPR = D / 8;                         // 16-byte chunks per row
+    constexpr int VPT = TK * CPR / kComputeThreads;    // chunks per thread per tile and tensor
+    constexpr int WROW = D + 2;                        // per (warp, head) record of the intra-CTA merge: O, m, l
     constexpr float NEG_INF = -__builtin_huge_valf();
+    static_assert(2 * NST * TILE_BYTES + 2 * 16 * ROWB + 4096 <= kWorkBytes, "decode tiles exceed the work area");
+    static_assert(kComputeWarps * GMAX * WROW * 4 <= 2 * NST * TILE_BYTES, "merge records reuse the tile buffers");
 
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
-    const int dp = t % DP, kg = t / DP;
+    const int dp = t % CPR;
     const int H = op->i[1], KVH = op->i[2], L = op->i[4], S = op->i[5], qdt = op->i[7];
     const bool fused = op->i[6] != 0;
     const int G = H / KVH;
@@ -45,18 +54,16 @@ __device__ __forceinline__ void decode_body(const Params& p, Ctrl* c, const mk_o
     const int n = fused ? pos : pos + 1;
     const int per = (n + S - 1) / S;
     const int k_begin = min(n, s * per), k_end = min(n, k_begin + per);
+    const int nk = k_end - k_begin;                                       // cached keys of this split
     const bool has_new = fused && s == S - 1;
     const int half = D / 2;
 
-    uint8_t* kst = work;                                         // NST K tiles then NST V tiles (64 KB)
+    uint8_t* kst = work;                                                  // NST K tiles then NST V tiles
     uint8_t* vst = work + NST * TILE_BYTES;
-    float* sS = reinterpret_cast<float*>(work + 2 * NST * TILE_BYTES);     // [GMAX][64]
-    float* sP = sS + GMAX * kDecTileKeys;                                 // [GMAX][64]
-    float* sM = sP + GMAX * kDecTileKeys;                                 // running max   [GMAX]
-    float* sL = sM + GMAX;                                                // running sum   [GMAX]
-    float* sA = sL + GMAX;                                                // rescale       [GMAX]
-    float* snew = sA + GMAX;                                              // new token: k [D], v [D]
-    float* ored = reinterpret_cast<float*>(work);                         // [KPP][G*D] after the loop
+    uint8_t* qs = work + 2 * NST * TILE_BYTES;                            // q high parts [16][ROWB], then low parts
+    float* sSc = reinterpret_cast<float*>(qs + 2 * 16 * ROWB);            // new token's score   [GMAX]
+    float* snew = sSc + GMAX;                                             // new token: k [D], v [D] (bf16 values)
+    float* wred = reinterpret_cast<float*>(work);                         // [8 warps][GMAX][WROW] after the loop
 
     const __nv_bfloat16* kc = reinterpret_cast<const __nv_bfloat16*>(op->ptr[1]);
     const __nv_bfloat16* vc = reinterpret_cast<const __nv_bfloat16*>(op->ptr[2]);
@@ -64,233 +71,236 @@ __device__ __forceinline__ void decode_body(const Params& p, Ctrl* c, const mk_o
     const long long row0 = (long long)b * L;
 
     auto issue_tile = [&](int tile) {
-        const int key0 = k_begin + tile * kDecTileKeys;
+        const int key0 = tile * TK;
         const int st = tile % NST;
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
             const int v = t + i * kComputeThreads;
-            const int key = key0 + v / DP, ch = v % DP;
-            const bool valid = key < k_end;
-            const long long r = row0 + (valid ? key : k_begin);
-            cp_async16(kst + st * TILE_BYTES + v * 16, kc + r * ldk + kvh * D + ch * 8, valid);
-            cp_async16(vst + st * TILE_BYTES + v * 16, vc + r * ldv + kvh * D + ch * 8, valid);
+            const int key = key0 + v / CPR, ch = v % CPR;
+            const bool valid = key < nk;
+            const long long r = row0 + k_begin + (valid ? key : 0);
+            cp_async16(kst + st * TILE_BYTES + (v / CPR) * ROWB + ch * 16, kc + r * ldk + kvh * D + ch * 8, valid);
+            cp_async16(vst + st * TILE_BYTES + (v / CPR) * ROWB + ch * 16, vc + r * ldv + kvh * D + ch * 8, valid);
         }
     };
 
-    const int ntiles = (k_end - k_begin + kDecTileKeys - 1) / kDecTileKeys;
+    const int ntiles = (nk + TK - 1) / TK;
     // Fused mode reads only cache rows below pos, which nothing in this launch writes: the first
-    // tiles and the rope table row are requested before the dependency wait (the op waits for its
+    // tile and the rope table row are requested before the dependency wait (the op waits for its
     // own dependencies).  Unfused mode may read the row a RopeAppend of this launch wrote, so it
     // waits first.
     if (!fused && wait_deps(p, c, nwait, wait_off, seq)) return;
-#pragma unroll
-    for (int i = 0; i < NST - 1; ++i) {
-        if (i < ntiles) issue_tile(i);
-        cp_async_commit();
-    }
-    const int pd = dp < DP / 2 ? dp * 8 + half : dp * 8 - half;     // partner chunk of the rotation
-    const float sign = dp < DP / 2 ? -1.f : 1.f;
+    if (ntiles > 0) issue_tile(0);
+    cp_async_commit();
+    const int pd = dp < CPR / 2 ? dp * 8 + half : dp * 8 - half;         // partner chunk of the rotation
+    const float sign = dp < CPR / 2 ? -1.f : 1.f;
     float cs[8], sn[8];
     if (fused) {
         load8(reinterpret_cast<const __nv_bfloat16*>(op->ptr[7]) + (long long)pos * op->ld[7], dp * 8, 0, cs);
         load8(reinterpret_cast<const __nv_bfloat16*>(op->ptr[8]) + (long long)pos * op->ld[8], dp * 8, 0, sn);
     }
-    if (t < GMAX) { sM[t] = NEG_INF; sL[t] = 0.f; }
+    for (int v = t; v < 2 * 16 * ROWB / 16; v += kComputeThreads) reinterpret_cast<uint4*>(qs)[v] = make_uint4(0u, 0u, 0u, 0u);
     if (fused && wait_deps(p, c, nwait, wait_off, seq)) {
         cp_async_wait<0>();
         return;
     }
+    if (!fused) compute_sync();                                           // the zero fill of qs, before the rows below land
     if (t == 0 && p.trace_cap > 0) c->t_dep = (long long)globaltimer();
 
-    // ---- query heads into registers (rotated when fused), pre-scaled to the log2 domain.  All
-    // loads of a batch of four heads are issued before any is used: one L2 round trip per batch. ----
-    float qf[GMAX][8];
-    const float qscale = op->f[0] * kLog2e;
+    // ---- q (rotated when fused, pre-scaled to the log2 domain) as MMA A operand: rows = the G query
+    // heads of this kv head, split into bf16 high and low parts so the scores keep ~16 mantissa bits.
+    // One thread per 8-wide chunk; the new token's k and v take two more chunk rows. ----
     {
-        const void* q = reinterpret_cast<const void*>(op->ptr[0]);
-        float kn[8], ko[8], vn[8];
-        if (has_new && kg == 0) {          // only the first key slot's threads use the new token's k and v
-            const long long ek = (long long)b * op->ld[5] + kvh * D, ev = (long long)b * op->ld[6] + kvh * D;
-            load8(reinterpret_cast<const void*>(op->ptr[5]), ek + dp * 8, qdt, kn);
-            load8(reinterpret_cast<const void*>(op->ptr[5]), ek + pd, qdt, ko);
-            load8(reinterpret_cast<const void*>(op->ptr[6]), ev + dp * 8, qdt, vn);
-        }
+        const float qscale = op->f[0] * kLog2e;
+        const int chunk = t / CPR;                                        // 0..G-1 q heads, G k_new, G+1 v_new
+        if (chunk < G || (has_new && chunk < G + 2)) {
+            const int which = chunk - G;                                  // < 0: q
+            const void* src = reinterpret_cast<const void*>(which < 0 ? op->ptr[0] : op->ptr[5 + which]);
+            const long long e0 = which < 0 ? (long long)b * op->ld[0] + (kvh * G + chunk) * D
+                                           : (long long)b * op->ld[5 + which] + kvh * D;
+            float a[8], o[8];
+            load8(src, e0 + dp * 8, qdt, a);
+            const bool rot = fused && which != 1;                         // v is not rotated
+            if (rot) load8(src, e0 + pd, qdt, o);
+            float y[8];
 #pragma unroll
-        for (int gb = 0; gb < GMAX; gb += 4) {
-            float a[4][8], o[4][8];
+            for (int e = 0; e < 8; ++e) y[e] = rot ? a[e] * cs[e] + sign * o[e] * sn[e] : a[e];
+            if (which < 0) {
+                uint32_t hi[4], lo[4];
 #pragma unroll
-            for (int g4 = 0; g4 < 4; ++g4) {
-                const int g = gb + g4;
-                if (g < G) {
-                    const long long e0 = (long long)b * op->ld[0] + (kvh * G + g) * D;
-                    load8(q, e0 + dp * 8, qdt, a[g4]);
-                    if (fused) load8(q, e0 + pd, qdt, o[g4]);
+                for (int j = 0; j < 4; ++j) {
+                    const float y0 = y[2 * j] * qscale, y1 = y[2 * j + 1] * qscale;
+                    const float h0 = round_bf16(y0), h1 = round_bf16(y1);
+                    hi[j] = pack2(h0, h1);
+                    lo[j] = pack2(y0 - h0, y1 - h1);
                 }
-            }
+                *reinterpret_cast<uint4*>(qs + chunk * ROWB + dp * 16) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                *reinterpret_cast<uint4*>(qs + (16 + chunk) * ROWB + dp * 16) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+            } else {
 #pragma unroll
-            for (int g4 = 0; g4 < 4; ++g4) {
-                const int g = gb + g4;
-#pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    float v = 0.f;
-                    if (g < G) v = fused ? a[g4][e] * cs[e] + sign * o[g4][e] * sn[e] : a[g4][e];
-                    qf[g][e] = v * qscale;
-                }
-            }
-        }
-        if (has_new && kg == 0) {          // new token's rotated k and its v wait in shared memory
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                snew[dp * 8 + e] = round_bf16(kn[e] * cs[e] + sign * ko[e] * sn[e]);
-                snew[D + dp * 8 + e] = round_bf16(vn[e]);
+                for (int e = 0; e < 8; ++e) snew[which * D + dp * 8 + e] = round_bf16(y[e]);     // the cache holds bf16
             }
         }
     }
 
-    float oacc[GMAX][8];
+    // ---- main loop: S = Q K^T and O += P V on tensor cores, every warp on its own 16 keys of the
+    // tile with its own running max and sum (no barrier inside a tile) ----
+    float oacc[D / 8][4];
 #pragma unroll
-    for (int g = 0; g < GMAX; ++g)
+    for (int j = 0; j < D / 8; ++j)
 #pragma unroll
-        for (int e = 0; e < 8; ++e) oacc[g][e] = 0.f;
+        for (int e = 0; e < 4; ++e) oacc[j][e] = 0.f;
+    float mrow = NEG_INF, lrow = 0.f;                                     // row lane >> 2 (rows 8.. are padding)
+    const uint32_t q_hi = smem_u32(qs) + (lane & 15) * ROWB + (lane >> 4) * 16;
+    const uint32_t q_lo = q_hi + 16 * ROWB;
 
 #pragma unroll 1
     for (int tile = 0; tile < ntiles; ++tile) {
-        if (tile + NST - 1 < ntiles) issue_tile(tile + NST - 1);
+        if (tile + 1 < ntiles) issue_tile(tile + 1);
         cp_async_commit();
-        cp_async_wait<NST - 1>();
-        compute_sync();
-        const int st = tile % NST;
-        const int key0 = k_begin + tile * kDecTileKeys;
-        // ---- scores ----
+        cp_async_wait<1>();
+        compute_sync();                                                   // tile (and, first time, q) visible to all
+        const int kb0 = tile * TK + 16 * warp;                            // first key of this warp, relative to the split
+        if (warp < NW && kb0 < nk) {
+            const uint32_t kb = smem_u32(kst + (tile % NST) * TILE_BYTES) + 16 * warp * ROWB;
+            const uint32_t vb = smem_u32(vst + (tile % NST) * TILE_BYTES) + 16 * warp * ROWB;
+            float sc[2][4];
 #pragma unroll
-        for (int ps = 0; ps < PASSES; ++ps) {
-            const int key = ps * KPP + kg;
-            float kf[8];
-            unpack8(*reinterpret_cast<const uint4*>(kst + st * TILE_BYTES + (key * DP + dp) * 16), kf);
-            float sc[GMAX];
+            for (int j = 0; j < 2; ++j)
 #pragma unroll
-            for (int g = 0; g < GMAX; ++g) {
-                float a = 0.f;
+                for (int e = 0; e < 4; ++e) sc[j][e] = 0.f;
 #pragma unroll
-                for (int e = 0; e < 8; ++e) a = fmaf(qf[g][e], kf[e], a);
-#pragma unroll
-                for (int o = 1; o < DP; o <<= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
-                sc[g] = a;
+            for (int kk = 0; kk < D / 16; ++kk) {
+                uint32_t ah[4], al[4], b0, b1, b2, b3;
+                ldmatrix_x4(q_hi + kk * 32, ah[0], ah[1], ah[2], ah[3]);
+                ldmatrix_x4(q_lo + kk * 32, al[0], al[1], al[2], al[3]);
+                ldmatrix_x4(kb + ((lane & 7) + (lane >> 4) * 8) * ROWB + (kk * 16 + ((lane >> 3) & 1) * 8) * 2, b0, b1, b2, b3);
+                mma_bf16(sc[0], ah, b0, b1);
+                mma_bf16(sc[1], ah, b2, b3);
+                mma_bf16(sc[0], al, b0, b1);
+                mma_bf16(sc[1], al, b2, b3);
             }
-            const bool in_range = key0 + key < k_end;
+            // mask keys past the end of the split; only row lane >> 2 matters (rows 8.. are padding)
+            float mx = NEG_INF;
 #pragma unroll
-            for (int g = 0; g < GMAX; ++g)
-                if (dp == g && g < G) sS[g * kDecTileKeys + key] = in_range ? sc[g] : NEG_INF;
-        }
-        compute_sync();
-        // ---- online softmax: warp g owns query head g ----
-        if (warp < G) {
-            const float s0 = sS[warp * kDecTileKeys + lane], s1 = sS[warp * kDecTileKeys + lane + 32];
-            const float mo = sM[warp];
-            const float mn = fmaxf(mo, warp_max(fmaxf(s0, s1)));
-            const float p0 = s0 == NEG_INF ? 0.f : ex2(s0 - mn);
-            const float p1 = s1 == NEG_INF ? 0.f : ex2(s1 - mn);
-            sP[warp * kDecTileKeys + lane] = p0;
-            sP[warp * kDecTileKeys + lane + 32] = p1;
-            const float sum = warp_sum(p0 + p1);
-            if (lane == 0) {
-                const float al = mo == NEG_INF ? 0.f : ex2(mo - mn);
-                sA[warp] = al;
-                sL[warp] = sL[warp] * al + sum;
-                sM[warp] = mn;
-            }
-        }
-        compute_sync();
-        // ---- O += P V ----
+            for (int j = 0; j < 2; ++j)
 #pragma unroll
-        for (int g = 0; g < GMAX; ++g) {
-            if (g < G) {
-                const float al = sA[g];
-#pragma unroll
-                for (int e = 0; e < 8; ++e) oacc[g][e] *= al;
-            }
-        }
-#pragma unroll
-        for (int ps = 0; ps < PASSES; ++ps) {
-            const int key = ps * KPP + kg;
-            float vf[8];
-            unpack8(*reinterpret_cast<const uint4*>(vst + st * TILE_BYTES + (key * DP + dp) * 16), vf);
-#pragma unroll
-            for (int g = 0; g < GMAX; ++g) {
-                if (g < G) {
-                    const float pg = sP[g * kDecTileKeys + key];
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) oacc[g][e] = fmaf(pg, vf[e], oacc[g][e]);
+                for (int e = 0; e < 2; ++e) {
+                    const int key = kb0 + j * 8 + (lane & 3) * 2 + e;
+                    if (key >= nk) sc[j][e] = NEG_INF;
+                    mx = fmaxf(mx, sc[j][e]);
                 }
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            const float mnew = fmaxf(mrow, mx);                           // finite: the warp has at least one key
+            const float alpha = mrow == NEG_INF ? 0.f : ex2(mrow - mnew);
+            mrow = mnew;
+            uint32_t ph[4], pl[4];
+            float sum = 0.f;
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const float p0 = sc[j][0] == NEG_INF ? 0.f : ex2(sc[j][0] - mnew);
+                const float p1 = sc[j][1] == NEG_INF ? 0.f : ex2(sc[j][1] - mnew);
+                sum += p0 + p1;
+                const float h0 = round_bf16(p0), h1 = round_bf16(p1);
+                ph[j * 2] = pack2(h0, h1);                                // row lane >> 2, keys j * 8 + ...
+                pl[j * 2] = pack2(p0 - h0, p1 - h1);
+                ph[j * 2 + 1] = 0u;                                       // rows 8..15: padding
+                pl[j * 2 + 1] = 0u;
+            }
+            lrow = lrow * alpha + sum;
+#pragma unroll
+            for (int j = 0; j < D / 8; ++j) { oacc[j][0] *= alpha; oacc[j][1] *= alpha; }
+#pragma unroll
+            for (int jp = 0; jp < D / 16; ++jp) {
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4_trans(vb + ((lane & 7) + ((lane >> 3) & 1) * 8) * ROWB + (jp * 16 + (lane >> 4) * 8) * 2, b0, b1, b2, b3);
+                mma_bf16(oacc[jp * 2], ph, b0, b1);
+                mma_bf16(oacc[jp * 2 + 1], ph, b2, b3);
+                mma_bf16(oacc[jp * 2], pl, b0, b1);
+                mma_bf16(oacc[jp * 2 + 1], pl, b2, b3);
             }
         }
-        compute_sync();
+        compute_sync();                                                   // the stage is overwritten by the next issue
     }
     cp_async_wait<0>();
+    if (ntiles == 0) compute_sync();                                      // q and snew visible without the loop's barriers
     phase_mark(p, c, 0);
 
-    // ---- the new token (fused mode, last split): attend it from registers and append it ----
-    if (ntiles == 0) compute_sync();     // no tile loop ran: its barriers are what orders snew otherwise
+    // ---- the new token (fused mode, last split): its score per head from the q parts in shared
+    // memory, and its k, v appended to the cache ----
     if (has_new) {
-        float kn[8], vn[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) { kn[e] = snew[dp * 8 + e]; vn[e] = snew[D + dp * 8 + e]; }
-        if (kg == 0) {
-#pragma unroll
-            for (int g = 0; g < GMAX; ++g) {
-                float a = 0.f;
-#pragma unroll
-                for (int e = 0; e < 8; ++e) a = fmaf(qf[g][e], kn[e], a);
-#pragma unroll
-                for (int o = 1; o < DP; o <<= 1) a += __shfl_xor_sync((1u << DP) - 1u, a, o);
-                if (dp == g && g < G) {
-                    const float mo = sM[g];
-                    const float mn = fmaxf(mo, a);
-                    const float al = mo == NEG_INF ? 0.f : ex2(mo - mn);
-                    const float pn = ex2(a - mn);
-                    sA[g] = al;
-                    sP[g * kDecTileKeys] = pn;
-                    sL[g] = sL[g] * al + pn;
-                    sM[g] = mn;
-                }
+        if (warp < G) {
+            float a = 0.f;
+            for (int d = lane; d < D; d += 32) {
+                const float qv = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(qs + warp * ROWB + d * 2)) +
+                                 __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(qs + (16 + warp) * ROWB + d * 2));
+                a = fmaf(qv, snew[d], a);
             }
-            const long long row = row0 + pos;
-            store8(const_cast<__nv_bfloat16*>(kc), row * ldk + kvh * D + dp * 8, 0, kn);
-            store8(const_cast<__nv_bfloat16*>(vc), row * ldv + kvh * D + dp * 8, 0, vn);
+            a = warp_sum(a);
+            if (lane == 0) sSc[warp] = a;
         }
-        compute_sync();
+        if (t < CPR) {
+            float kn[8], vn[8];
 #pragma unroll
-        for (int g = 0; g < GMAX; ++g) {
-            if (g < G) {
-                const float al = sA[g];
-                const float pn = kg == 0 ? sP[g * kDecTileKeys] : 0.f;
-#pragma unroll
-                for (int e = 0; e < 8; ++e) oacc[g][e] = fmaf(pn, vn[e], oacc[g][e] * al);
-            }
+            for (int e = 0; e < 8; ++e) { kn[e] = snew[t * 8 + e]; vn[e] = snew[D + t * 8 + e]; }
+            const long long row = row0 + pos;
+            store8(const_cast<__nv_bfloat16*>(kc), row * ldk + kvh * D + t * 8, 0, kn);
+            store8(const_cast<__nv_bfloat16*>(vc), row * ldv + kvh * D + t * 8, 0, vn);
         }
     }
-    compute_sync();          // every tile has been consumed: the tile buffers can be reused
-
-    // ---- reduce O over the KPP key slots ----
-    const int GD = G * D;
-#pragma unroll
-    for (int g = 0; g < GMAX; ++g) {
+    // ---- per-warp results to shared memory (the tile buffers are free: every warp passed the
+    // loop's last barrier) ----
+    lrow += __shfl_xor_sync(0xffffffffu, lrow, 1);
+    lrow += __shfl_xor_sync(0xffffffffu, lrow, 2);
+    {
+        const int g = lane >> 2;
         if (g < G) {
-            float4* d = reinterpret_cast<float4*>(ored + kg * GD + g * D + dp * 8);
-            d[0] = make_float4(oacc[g][0], oacc[g][1], oacc[g][2], oacc[g][3]);
-            d[1] = make_float4(oacc[g][4], oacc[g][5], oacc[g][6], oacc[g][7]);
+            float* rec = wred + (warp * GMAX + g) * WROW;
+#pragma unroll
+            for (int j = 0; j < D / 8; ++j) {
+                rec[j * 8 + (lane & 3) * 2] = oacc[j][0];
+                rec[j * 8 + (lane & 3) * 2 + 1] = oacc[j][1];
+            }
+            if ((lane & 3) == 0) { rec[D] = mrow; rec[D + 1] = lrow; }
         }
     }
     compute_sync();
+
+    // ---- merge the warps (and the new token) per output element: `acc` is this split's
+    // unnormalised O, with its running max and sum ----
+    const int GD = G * D;
+    auto merged = [&](int idx, float& mx_out, float& l_out) {
+        const int g = idx / D, d = idx % D;
+        float mx = has_new ? sSc[g] : NEG_INF;
+#pragma unroll
+        for (int w = 0; w < kComputeWarps; ++w) mx = fmaxf(mx, wred[(w * GMAX + g) * WROW + D]);
+        float a = 0.f, l = 0.f;
+        if (mx != NEG_INF) {
+#pragma unroll
+            for (int w = 0; w < kComputeWarps; ++w) {
+                const float* rec = wred + (w * GMAX + g) * WROW;
+                const float wgt = rec[D] == NEG_INF ? 0.f : ex2(rec[D] - mx);
+                a = fmaf(wgt, rec[d], a);
+                l = fmaf(wgt, rec[D + 1], l);
+            }
+            if (has_new) {
+                const float pn = ex2(sSc[g] - mx);
+                a = fmaf(pn, snew[D + d], a);
+                l += pn;
+            }
+        }
+        mx_out = mx;
+        l_out = l;
+        return a;
+    };
     const int pair = b * KVH + kvh;
     void* outp = reinterpret_cast<void*>(op->ptr[4]);
     const int odt = op->i[8];
     if (S == 1) {
         for (int idx = t; idx < GD; idx += kComputeThreads) {
-            float a = 0.f;
-#pragma unroll 8
-            for (int k = 0; k < KPP; ++k) a += ored[k * GD + idx];
-            const float l = sL[idx / D];
+            float mx, l;
+            const float a = merged(idx, mx, l);
             store1(outp, (long long)b * op->ld[4] + kvh * GD + idx, odt, l == 0.f ? 0.f : a * rcp(l));
         }
         return;
@@ -300,12 +310,10 @@ __device__ __forceinline__ void decode_body(const Params& p, Ctrl* c, const mk_o
     {
         float* mine = part + ((long long)pair * S + s) * ldp;
         for (int idx = t; idx < GD; idx += kComputeThreads) {
-            float a = 0.f;
-#pragma unroll 8
-            for (int k = 0; k < KPP; ++k) a += ored[k * GD + idx];
-            mine[idx] = a;
+            float mx, l;
+            mine[idx] = merged(idx, mx, l);
+            if (idx % D == 0) { mine[GD + idx / D] = mx; mine[GD + G + idx / D] = l; }
         }
-        if (t < G) { mine[GD + t] = sM[t]; mine[GD + G + t] = sL[t]; }
     }
     __threadfence();
     compute_sync();
