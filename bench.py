@@ -29,6 +29,9 @@ import torch
 ROOT = pathlib.Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
+# DRAM bytes of one megakernel launch of the default workload (batch 1, ctx 1024), from one ncu capture
+# (dram__bytes_read.sum + dram__bytes_write.sum; profiles/megakernel_llama1b_decode_b1_ctx1024.md)
+MEASURED_TRAFFIC_B1_CTX1024 = 2_506_381_000 + 9_379_328
 WEIGHT_BYTES = 2 * (16 * (3072 * 2048 + 2048 * 2048 + 16384 * 2048 + 2048 * 8192) + 128256 * 2048)   # 2 471 493 632
 KV_BYTES_PER_TOKEN = 16 * 2 * 512 * 2                                                               # 32 768
 
@@ -239,7 +242,8 @@ def main():
                      "d2h_bytes_per_step": a.batch * 8},
                 gpu_launches=a.steps, kernel_ms=kernel_ms, clocks=clocks,
                 roofline={"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                          "peak_kind": peak_kind, "traffic": None, "algorithmic_bytes": algo_bytes,
+                          "peak_kind": peak_kind,
+                          "traffic": MEASURED_TRAFFIC_B1_CTX1024 if (a.batch, a.ctx) == (1, 1024) else None, "algorithmic_bytes": algo_bytes,
                           "kernel": "mk::megakernel<false>"})
     if not a.no_cpu_baseline and world == 1:
         cpu_ms = cpu_oracle_ms(a.batch, a.ctx, 3)
