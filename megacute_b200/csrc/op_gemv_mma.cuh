@@ -34,6 +34,11 @@ __device__ __forceinline__ float4 lds_volatile4(const float4* p) {
 __device__ __forceinline__ void sts_volatile4(float4* p, float4 v) {
     asm volatile("st.volatile.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(smem_u32(p)), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
 }
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.b32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     uint4 v;
     asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
@@ -79,9 +84,15 @@ __device__ __forceinline__ void gemv_mma(const Params& p, Ctrl* c, uint8_t* ring
     const long long ldo = op->ld[2], ldr = op->ld[4];
     constexpr int kSlice = kSegElems / kComputeWarps;                         // 256: a warp's K slice of a segment
     const int kw = warp * kSlice;
-    const int bm = lane >> 2;                                                 // B-operand column = activation row
+    // B operand (16 k x 8 columns).  Up to 4 activation rows: columns 0..3 carry the high parts of
+    // rows 0..3 and columns 4..7 their low parts, so ONE MMA per k-step yields both products (they
+    // are added in the epilogue).  5 to 8 rows: a column per row, high and low parts in two MMAs.
+    const bool packed = M <= 4;
+    const int bn = lane >> 2;                                                 // this lane's B column
+    const int bm = packed ? (bn & 3) : bn;                                    // the activation row behind it
     const uint32_t a_lane = (uint32_t)((lane & 15) * kSegStride + ((lane >> 4) * 8) * 2 + kw * 2);
-    const uint32_t b_lane = smem_u32(xf) + (bm < M ? bm : 0) * xrow + (kw >> 4) * 64 + (lane & 3) * 16;
+    const uint32_t b_lane = smem_u32(xf) + (bm < M ? bm : 0) * xrow + (kw >> 4) * 64 + (lane & 3) * 16 +
+                            (packed ? (bn >> 2) * 8 : 0);
     const int xdt = op->i[4];
     const void* x = reinterpret_cast<const void*>(op->ptr[0]);
     const long long ldx = op->ld[0];
@@ -181,21 +192,35 @@ __device__ __forceinline__ void gemv_mma(const Params& p, Ctrl* c, uint8_t* ring
 #pragma unroll 1
                 for (int half = 0; half < kSlice / 128 && left > 0; ++half) {     // batches of 8 k-steps
                     uint32_t a[8][4];
-                    uint4 b[8];
+                    // lanes of absent activation rows feed zeros and stay out of the load: with one
+                    // row only a quarter of the warp touches shared memory
+                    if (packed) {
+                        uint2 b[8];
 #pragma unroll
-                    for (int ks = 0; ks < 8; ++ks) {
-                        if (ks * 16 < left) {
-                            ldmatrix_x4(a_base + ks * 32, a[ks][0], a[ks][1], a[ks][2], a[ks][3]);
-                            // lanes of absent activation rows feed zeros and stay out of the load:
-                            // with one row only a quarter of the warp touches shared memory
-                            b[ks] = bm < M ? lds128(b_base + ks * 64) : make_uint4(0u, 0u, 0u, 0u);
+                        for (int ks = 0; ks < 8; ++ks) {
+                            if (ks * 16 < left) {
+                                ldmatrix_x4(a_base + ks * 32, a[ks][0], a[ks][1], a[ks][2], a[ks][3]);
+                                b[ks] = bm < M ? lds64(b_base + ks * 64) : make_uint2(0u, 0u);
+                            }
                         }
-                    }
 #pragma unroll
-                    for (int ks = 0; ks < 8; ++ks) {
-                        if (ks * 16 < left) {
-                            mma_bf16(accs[(ks & 1) * 2], a[ks], b[ks].x, b[ks].y);
-                            mma_bf16(accs[(ks & 1) * 2 + 1], a[ks], b[ks].z, b[ks].w);
+                        for (int ks = 0; ks < 8; ++ks)
+                            if (ks * 16 < left) mma_bf16(accs[ks & 3], a[ks], b[ks].x, b[ks].y);
+                    } else {
+                        uint4 b[8];
+#pragma unroll
+                        for (int ks = 0; ks < 8; ++ks) {
+                            if (ks * 16 < left) {
+                                ldmatrix_x4(a_base + ks * 32, a[ks][0], a[ks][1], a[ks][2], a[ks][3]);
+                                b[ks] = bm < M ? lds128(b_base + ks * 64) : make_uint4(0u, 0u, 0u, 0u);
+                            }
+                        }
+#pragma unroll
+                        for (int ks = 0; ks < 8; ++ks) {
+                            if (ks * 16 < left) {
+                                mma_bf16(accs[(ks & 1) * 2], a[ks], b[ks].x, b[ks].y);
+                                mma_bf16(accs[(ks & 1) * 2 + 1], a[ks], b[ks].z, b[ks].w);
+                            }
                         }
                     }
                     a_base += 8 * 32;
@@ -226,7 +251,7 @@ __device__ __forceinline__ void gemv_mma(const Params& p, Ctrl* c, uint8_t* ring
             if (fin) cnt[sl] = 0;
             __threadfence_block();
         }
-        fin = __shfl_sync(0xffffffffu, fin, 0) && ok;
+        fin = __shfl_sync(0xffffffffu, fin, 0) && __all_sync(0xffffffffu, ok);      // uniform over the warp
         float v[4] = {0.f, 0.f, 0.f, 0.f};
         if (fin) {
 #pragma unroll
@@ -235,7 +260,13 @@ __device__ __forceinline__ void gemv_mma(const Params& p, Ctrl* c, uint8_t* ring
                 v[0] += q.x; v[1] += q.y; v[2] += q.z; v[3] += q.w;
             }
         }
-        if (fin) {
+        if (fin && packed) {
+            // columns 4..7 hold the low-part products of rows 0..3: add them to columns 0..3, which
+            // sit two lanes further down in the quad
+#pragma unroll
+            for (int e = 0; e < 4; ++e) v[e] += __shfl_xor_sync(0xffffffffu, v[e], 2);
+        }
+        if (fin && !(packed && (lane & 3) >= 2)) {
             // v[0], v[1]: row ob, activation rows m0, m0 + 1;  v[2], v[3]: row ob + 8
             if (swi && !(g & 1)) {
                 sts_volatile4(&gatebuf[lane], make_float4(v[0] * rs[0], v[1] * rs[1], v[2] * rs[0], v[3] * rs[1]));
