@@ -158,7 +158,8 @@ int mk_launch_noalloc(int device, const int32_t* d_insts, int n_insts, const int
  * dimension ld in elements; dtype 0 bf16 with ld % 8 == 0 and a 16-byte aligned base, 1 fp32), ties to
  * the lowest index, NaN never selected.  Asynchronous on `stream`; `out` is device memory of `rows`
  * int64.  Replaces the torch argmax of the reference's decode loop (examples/llama/llama1b.py:105),
- * which reduces a 128 256-wide row in a single 512-thread block. */
+ * which reduces a 128 256-wide row in a single 512-thread block.  Allocates nothing (its scratch is a
+ * static device array); two calls whose kernels may overlap on the GPU share it: serialise them. */
 int mk_argmax(const void* logits, int dtype, int rows, int cols, long long ld, long long* out, void* stream);
 
 #ifdef __cplusplus

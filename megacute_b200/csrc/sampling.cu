@@ -1,7 +1,9 @@
 // Greedy sampling: row-wise argmax of the logits, the last thing a decode step does before the
 // next token's embedding is gathered (the reference's loop calls torch's argmax there,
-// examples/llama/llama1b.py:105).  One CTA of 1024 threads per row: a row of 128 256 bf16 logits is
-// 250 KB, read once with 16-byte loads; ties go to the lowest index.
+// examples/llama/llama1b.py:105).  A row of 128 256 bf16 logits is 250 KB, read once with 16-byte
+// loads by kSplit CTAs of 1024 threads; each leaves its best (value, index) in a static device
+// array and the last CTA of a row to finish picks the winner (ties go to the lowest index).  Rows
+// beyond the static array's capacity are handled by one CTA each.  Nothing is allocated.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
@@ -19,13 +21,22 @@ __device__ __forceinline__ Best better(Best a, Best b) {        // NaN never win
     return (b.v > a.v || (b.v == a.v && b.i < a.i)) ? b : a;
 }
 
+constexpr int kSplit = 16;                 // CTAs per row
+constexpr int kMaxSplitRows = 4096;        // rows the static scratch covers (512 KB + 16 KB per GPU)
+__device__ float g_part_v[kMaxSplitRows * kSplit];
+__device__ int g_part_i[kMaxSplitRows * kSplit];
+__device__ int g_done[kMaxSplitRows];      // zero between launches: the last CTA of a row resets it
+
+// grid (rows, nsplit): CTA (r, s) scans every nsplit-th 16-byte vector group of row r
 __global__ void __launch_bounds__(1024) argmax_rows(const void* logits, int dtype, int cols, long long ld, long long* out) {
     const int t = threadIdx.x;
+    const int nsplit = gridDim.y, part = blockIdx.y;
+    const int stride = 1024 * nsplit, first = part * 1024 + t;
     Best best{-__builtin_huge_valf(), 0x7fffffff};
     if (dtype == 0) {
         const __nv_bfloat16* row = reinterpret_cast<const __nv_bfloat16*>(logits) + (long long)blockIdx.x * ld;
         const int nvec = cols >> 3;                                // rows start 16-byte aligned (ld % 8 == 0)
-        for (int v = t; v < nvec; v += 1024) {
+        for (int v = first; v < nvec; v += stride) {
             const uint4 q = __ldg(reinterpret_cast<const uint4*>(row) + v);
             const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
@@ -34,10 +45,10 @@ __global__ void __launch_bounds__(1024) argmax_rows(const void* logits, int dtyp
                 best = better(best, Best{x, v * 8 + e});
             }
         }
-        for (int c = (nvec << 3) + t; c < cols; c += 1024) best = better(best, Best{__bfloat162float(row[c]), c});
+        for (int c = (nvec << 3) + first; c < cols; c += stride) best = better(best, Best{__bfloat162float(row[c]), c});
     } else {
         const float* row = reinterpret_cast<const float*>(logits) + (long long)blockIdx.x * ld;
-        for (int c = t; c < cols; c += 1024) best = better(best, Best{row[c], c});
+        for (int c = first; c < cols; c += stride) best = better(best, Best{row[c], c});
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -55,7 +66,32 @@ __global__ void __launch_bounds__(1024) argmax_rows(const void* logits, int dtyp
             Best other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
             best = better(best, other);
         }
-        if (t == 0) out[blockIdx.x] = best.i == 0x7fffffff ? 0 : best.i;
+        if (nsplit == 1) {
+            if (t == 0) out[blockIdx.x] = best.i == 0x7fffffff ? 0 : best.i;
+            return;
+        }
+        // several CTAs per row: leave this CTA's best, and let the last one to arrive reduce them
+        __shared__ int last;
+        if (t == 0) {
+            g_part_v[blockIdx.x * kSplit + part] = best.v;
+            g_part_i[blockIdx.x * kSplit + part] = best.i;
+            __threadfence();
+            last = atomicAdd(&g_done[blockIdx.x], 1) == nsplit - 1;
+        }
+        __syncwarp();
+        if (!last) return;
+        __threadfence();
+        best = Best{-__builtin_huge_valf(), 0x7fffffff};
+        if (t < nsplit) best = Best{__ldcg(&g_part_v[blockIdx.x * kSplit + t]), __ldcg(&g_part_i[blockIdx.x * kSplit + t])};
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            Best other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+            best = better(best, other);
+        }
+        if (t == 0) {
+            out[blockIdx.x] = best.i == 0x7fffffff ? 0 : best.i;
+            g_done[blockIdx.x] = 0;
+        }
     }
 }
 
@@ -64,6 +100,8 @@ __global__ void __launch_bounds__(1024) argmax_rows(const void* logits, int dtyp
 extern "C" int mk_argmax(const void* logits, int dtype, int rows, int cols, long long ld, long long* out, void* stream) {
     if (!logits || !out || rows <= 0 || cols <= 0 || (dtype != 0 && dtype != 1) || ld < cols) return MK_E_ARG;
     if (dtype == 0 && ((ld & 7) != 0 || (reinterpret_cast<uintptr_t>(logits) & 15) != 0)) return MK_E_ARG;
-    argmax_rows<<<rows, 1024, 0, (cudaStream_t)stream>>>(logits, dtype, cols, ld, out);
+    // few long rows: several CTAs per row (calls that may overlap on the GPU share the scratch: serialise them)
+    const int nsplit = (rows <= 64 && rows <= kMaxSplitRows && cols >= 16 * 1024) ? kSplit : 1;
+    argmax_rows<<<dim3(rows, nsplit), 1024, 0, (cudaStream_t)stream>>>(logits, dtype, cols, ld, out);
     return cudaGetLastError() == cudaSuccess ? MK_OK : MK_E_CUDA;
 }
