@@ -9,8 +9,10 @@
 // so a tile costs two CTA barriers.  With S > 1 every split writes an unnormalised partial (O,
 // running max, sum) and bumps an arrival count; the last split to arrive merges the S partials
 // and writes the output (no extra dependency hop).
-// q and P are each split into bf16 high + low parts (two MMAs) so scores and probabilities keep
-// ~16 mantissa bits where the reference rounds both to bf16 (megacute/ops/attention.py:293); the
+// q and P are each split into bf16 high + low parts so scores and probabilities keep ~16 mantissa
+// bits where the reference rounds both to bf16 (megacute/ops/attention.py:293).  The low parts
+// ride in rows 8..15 of the same A operand (heads take rows 0..7), so they cost no extra MMA: the
+// two row halves of a result fragment are added in the lane that holds both.  The
 // appended k and v are rounded to the cache's bf16 and the new token is scored with those values.
 // Fused mode (rope_append folded in): q, k_new, v_new are the un-rotated columns of the QKV row;
 // the op rotates q and k at pos, the last split also attends the new token from registers and
@@ -41,7 +43,8 @@ __device__ __forceinline__ void decode_body(const Params& p, Ctrl* c, const mk_o
     constexpr int VPT = TK * CPR / kComputeThreads;    // chunks per thread per tile and tensor
     constexpr int WROW = D + 2;                        // per (warp, head) record of the intra-CTA merge: O, m, l
     constexpr float NEG_INF = -__builtin_huge_valf();
-    static_assert(2 * NST * TILE_BYTES + 2 * 16 * ROWB + 4096 <= kWorkBytes, "decode tiles exceed the work area");
+    static_assert(GMAX <= 8, "heads take rows 0..7 of the A operand, their low parts rows 8..15");
+    static_assert(2 * NST * TILE_BYTES + 16 * ROWB + 4096 <= kWorkBytes, "decode tiles exceed the work area");
     static_assert(kComputeWarps * GMAX * WROW * 4 <= 2 * NST * TILE_BYTES, "merge records reuse the tile buffers");
 
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
@@ -60,8 +63,8 @@ __device__ __forceinline__ void decode_body(const Params& p, Ctrl* c, const mk_o
 
     uint8_t* kst = work;                                                  // NST K tiles then NST V tiles
     uint8_t* vst = work + NST * TILE_BYTES;
-    uint8_t* qs = work + 2 * NST * TILE_BYTES;                            // q high parts [16][ROWB], then low parts
-    float* sSc = reinterpret_cast<float*>(qs + 2 * 16 * ROWB);            // new token's score   [GMAX]
+    uint8_t* qs = work + 2 * NST * TILE_BYTES;                            // q [16][ROWB]: rows 0..7 high parts, 8..15 low parts
+    float* sSc = reinterpret_cast<float*>(qs + 16 * ROWB);                // new token's score   [GMAX]
     float* snew = sSc + GMAX;                                             // new token: k [D], v [D] (bf16 values)
     float* wred = reinterpret_cast<float*>(work);                         // [8 warps][GMAX][WROW] after the loop
 
@@ -99,7 +102,7 @@ __device__ __forceinline__ void decode_body(const Params& p, Ctrl* c, const mk_o
         load8(reinterpret_cast<const __nv_bfloat16*>(op->ptr[7]) + (long long)pos * op->ld[7], dp * 8, 0, cs);
         load8(reinterpret_cast<const __nv_bfloat16*>(op->ptr[8]) + (long long)pos * op->ld[8], dp * 8, 0, sn);
     }
-    for (int v = t; v < 2 * 16 * ROWB / 16; v += kComputeThreads) reinterpret_cast<uint4*>(qs)[v] = make_uint4(0u, 0u, 0u, 0u);
+    for (int v = t; v < 16 * ROWB / 16; v += kComputeThreads) reinterpret_cast<uint4*>(qs)[v] = make_uint4(0u, 0u, 0u, 0u);
     if (fused && wait_deps(p, c, nwait, wait_off, seq)) {
         cp_async_wait<0>();
         return;
@@ -135,7 +138,7 @@ __device__ __forceinline__ void decode_body(const Params& p, Ctrl* c, const mk_o
                     lo[j] = pack2(y0 - h0, y1 - h1);
                 }
                 *reinterpret_cast<uint4*>(qs + chunk * ROWB + dp * 16) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-                *reinterpret_cast<uint4*>(qs + (16 + chunk) * ROWB + dp * 16) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                *reinterpret_cast<uint4*>(qs + (8 + chunk) * ROWB + dp * 16) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
             } else {
 #pragma unroll
                 for (int e = 0; e < 8; ++e) snew[which * D + dp * 8 + e] = round_bf16(y[e]);     // the cache holds bf16
@@ -150,9 +153,8 @@ __device__ __forceinline__ void decode_body(const Params& p, Ctrl* c, const mk_o
     for (int j = 0; j < D / 8; ++j)
 #pragma unroll
         for (int e = 0; e < 4; ++e) oacc[j][e] = 0.f;
-    float mrow = NEG_INF, lrow = 0.f;                                     // row lane >> 2 (rows 8.. are padding)
-    const uint32_t q_hi = smem_u32(qs) + (lane & 15) * ROWB + (lane >> 4) * 16;
-    const uint32_t q_lo = q_hi + 16 * ROWB;
+    float mrow = NEG_INF, lrow = 0.f;                                     // head lane >> 2
+    const uint32_t q_a = smem_u32(qs) + (lane & 15) * ROWB + (lane >> 4) * 16;
 
 #pragma unroll 1
     for (int tile = 0; tile < ntiles; ++tile) {
@@ -171,23 +173,20 @@ __device__ __forceinline__ void decode_body(const Params& p, Ctrl* c, const mk_o
                 for (int e = 0; e < 4; ++e) sc[j][e] = 0.f;
 #pragma unroll
             for (int kk = 0; kk < D / 16; ++kk) {
-                uint32_t ah[4], al[4], b0, b1, b2, b3;
-                ldmatrix_x4(q_hi + kk * 32, ah[0], ah[1], ah[2], ah[3]);
-                ldmatrix_x4(q_lo + kk * 32, al[0], al[1], al[2], al[3]);
+                uint32_t a[4], b0, b1, b2, b3;
+                ldmatrix_x4(q_a + kk * 32, a[0], a[1], a[2], a[3]);
                 ldmatrix_x4(kb + ((lane & 7) + (lane >> 4) * 8) * ROWB + (kk * 16 + ((lane >> 3) & 1) * 8) * 2, b0, b1, b2, b3);
-                mma_bf16(sc[0], ah, b0, b1);
-                mma_bf16(sc[1], ah, b2, b3);
-                mma_bf16(sc[0], al, b0, b1);
-                mma_bf16(sc[1], al, b2, b3);
+                mma_bf16(sc[0], a, b0, b1);
+                mma_bf16(sc[1], a, b2, b3);
             }
-            // mask keys past the end of the split; only row lane >> 2 matters (rows 8.. are padding)
+            // score of head lane >> 2 = high-part row + low-part row; mask keys past the end of the split
             float mx = NEG_INF;
 #pragma unroll
             for (int j = 0; j < 2; ++j)
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
                     const int key = kb0 + j * 8 + (lane & 3) * 2 + e;
-                    if (key >= nk) sc[j][e] = NEG_INF;
+                    sc[j][e] = key >= nk ? NEG_INF : sc[j][e] + sc[j][e + 2];
                     mx = fmaxf(mx, sc[j][e]);
                 }
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
@@ -195,7 +194,7 @@ __device__ __forceinline__ void decode_body(const Params& p, Ctrl* c, const mk_o
             const float mnew = fmaxf(mrow, mx);                           // finite: the warp has at least one key
             const float alpha = mrow == NEG_INF ? 0.f : ex2(mrow - mnew);
             mrow = mnew;
-            uint32_t ph[4], pl[4];
+            uint32_t pa[4];                                               // P as A operand: rows 0..7 high parts, 8..15 low parts
             float sum = 0.f;
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
@@ -203,22 +202,21 @@ __device__ __forceinline__ void decode_body(const Params& p, Ctrl* c, const mk_o
                 const float p1 = sc[j][1] == NEG_INF ? 0.f : ex2(sc[j][1] - mnew);
                 sum += p0 + p1;
                 const float h0 = round_bf16(p0), h1 = round_bf16(p1);
-                ph[j * 2] = pack2(h0, h1);                                // row lane >> 2, keys j * 8 + ...
-                pl[j * 2] = pack2(p0 - h0, p1 - h1);
-                ph[j * 2 + 1] = 0u;                                       // rows 8..15: padding
-                pl[j * 2 + 1] = 0u;
+                pa[j * 2] = pack2(h0, h1);                                // head lane >> 2, keys j * 8 + ...
+                pa[j * 2 + 1] = pack2(p0 - h0, p1 - h1);
             }
             lrow = lrow * alpha + sum;
 #pragma unroll
-            for (int j = 0; j < D / 8; ++j) { oacc[j][0] *= alpha; oacc[j][1] *= alpha; }
+            for (int j = 0; j < D / 8; ++j) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) oacc[j][e] *= alpha;
+            }
 #pragma unroll
             for (int jp = 0; jp < D / 16; ++jp) {
                 uint32_t b0, b1, b2, b3;
                 ldmatrix_x4_trans(vb + ((lane & 7) + ((lane >> 3) & 1) * 8) * ROWB + (jp * 16 + (lane >> 4) * 8) * 2, b0, b1, b2, b3);
-                mma_bf16(oacc[jp * 2], ph, b0, b1);
-                mma_bf16(oacc[jp * 2 + 1], ph, b2, b3);
-                mma_bf16(oacc[jp * 2], pl, b0, b1);
-                mma_bf16(oacc[jp * 2 + 1], pl, b2, b3);
+                mma_bf16(oacc[jp * 2], pa, b0, b1);
+                mma_bf16(oacc[jp * 2 + 1], pa, b2, b3);
             }
         }
         compute_sync();                                                   // the stage is overwritten by the next issue
@@ -234,7 +232,7 @@ __device__ __forceinline__ void decode_body(const Params& p, Ctrl* c, const mk_o
             float a = 0.f;
             for (int d = lane; d < D; d += 32) {
                 const float qv = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(qs + warp * ROWB + d * 2)) +
-                                 __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(qs + (16 + warp) * ROWB + d * 2));
+                                 __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(qs + (8 + warp) * ROWB + d * 2));
                 a = fmaf(qv, snew[d], a);
             }
             a = warp_sum(a);
@@ -258,9 +256,9 @@ __device__ __forceinline__ void decode_body(const Params& p, Ctrl* c, const mk_o
         if (g < G) {
             float* rec = wred + (warp * GMAX + g) * WROW;
 #pragma unroll
-            for (int j = 0; j < D / 8; ++j) {
-                rec[j * 8 + (lane & 3) * 2] = oacc[j][0];
-                rec[j * 8 + (lane & 3) * 2 + 1] = oacc[j][1];
+            for (int j = 0; j < D / 8; ++j) {                             // high-part rows + low-part rows
+                rec[j * 8 + (lane & 3) * 2] = oacc[j][0] + oacc[j][2];
+                rec[j * 8 + (lane & 3) * 2 + 1] = oacc[j][1] + oacc[j][3];
             }
             if ((lane & 3) == 0) { rec[D] = mrow; rec[D + 1] = lrow; }
         }
