@@ -1,10 +1,13 @@
 // MK_OP_GEMM: tiled linear for more than 8 activation rows.
 //   out[128 x 128 tile] = act(x @ w^T + bias) + residual        (one instruction per output tile)
 //   ws += x[:, Kj] @ w[:, Kj]^T                                  (split-K partial: reduce-add)
-// Operands stream through a 4-stage cp.async pipeline of 128 x 32 tiles; the math is warp-level
-// mma.sync m16n8k16 bf16 -> fp32 (8 warps as 2 x 4, warp tile 64 x 32).  This is the portable
-// first implementation of the tile path; the tcgen05 / TMEM version replaces the main loop and
-// keeps this epilogue.
+// Operands stream through a cp.async pipeline of 32-wide k-tiles; the math is warp-level mma.sync
+// m16n8k16 bf16 -> fp32 (8 warps as 2 x 4).  Two shapes: 128 activation rows per tile with 4 stages
+// (warp tile 64 x 32), and, when the op has at most 64 rows (batched decode, where the op is bound
+// by streaming the weights), 64 rows per tile with 6 stages (warp tile 32 x 32): no MMAs on
+// padding rows and 40 KB of weights in flight instead of 24 KB.  This is the portable first
+// implementation of the tile path; the tcgen05 / TMEM version replaces the main loop and keeps
+// this epilogue.
 //
 // ptr 0 x, 1 w, 2 out (or ws), 3 bias, 4 residual
 // i 0 M, 1 N (weight rows), 2 K, 3 act, 4 splits, 5 out dtype, 6 accumulate, 7 residual dtype,
@@ -16,11 +19,15 @@
 
 namespace mk {
 
-constexpr int kGemmBM = 128, kGemmBN = 128, kGemmBK = 32, kGemmStages = 4;
+constexpr int kGemmBM = 128, kGemmBN = 128, kGemmBK = 32;     // kGemmBM: rows per m tile in the schedule (config.py GEMM_BM)
 constexpr int kGemmRowBytes = kGemmBK * 2 + 16;                // padded: conflict-free ldmatrix
-constexpr int kGemmTileBytes = kGemmBM * kGemmRowBytes;        // 10 KB per operand per stage
 
+// BM: activation rows held per tile (128, or 64 when M <= 64); MI = 16-row fragments per warp.
+template <int BM, int kGemmStages>
 static __device__ __noinline__ void op_gemm(const mk_op_desc* op, int a0, int a1, int a2, uint8_t* work) {
+    constexpr int MI = BM / 32;
+    constexpr int kATileBytes = BM * kGemmRowBytes, kBTileBytes = kGemmBN * kGemmRowBytes;
+    static_assert(kGemmStages * (kATileBytes + kBTileBytes) <= kWorkBytes, "GEMM stages exceed the work area");
     const int M = op->i[0], N = op->i[1], K = op->i[2], act = op->i[3], splits = op->i[4];
     const int odt = op->i[5], accum = op->i[6], rdt = op->i[7], swi = op->i[8];
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
@@ -31,26 +38,29 @@ static __device__ __noinline__ void op_gemm(const mk_op_desc* op, int a0, int a1
     const __nv_bfloat16* Wt = reinterpret_cast<const __nv_bfloat16*>(op->ptr[1]);
     const long long ldx = op->ld[0], ldw = op->ld[1];
     uint8_t* sa = work;
-    uint8_t* sb = work + kGemmStages * kGemmTileBytes;
+    uint8_t* sb = work + kGemmStages * kATileBytes;
 
     auto issue = [&](int kt) {
         const int st = kt % kGemmStages;
         const int k0 = kbeg + kt * kGemmBK;
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
-            const int v = t + i * kComputeThreads;              // 512 chunks of 16 bytes per operand
+            const int v = t + i * kComputeThreads;              // 4 chunks of 16 bytes per row
             const int r = v >> 2, ch = v & 3;
-            const bool va = m0 + r < M, vb = n0 + r < N;
-            cp_async16(sa + st * kGemmTileBytes + r * kGemmRowBytes + ch * 16,
-                       X + (long long)(va ? m0 + r : m0) * ldx + k0 + ch * 8, va);
-            cp_async16(sb + st * kGemmTileBytes + r * kGemmRowBytes + ch * 16,
+            if (r < BM) {
+                const bool va = m0 + r < M;
+                cp_async16(sa + st * kATileBytes + r * kGemmRowBytes + ch * 16,
+                           X + (long long)(va ? m0 + r : m0) * ldx + k0 + ch * 8, va);
+            }
+            const bool vb = n0 + r < N;
+            cp_async16(sb + st * kBTileBytes + r * kGemmRowBytes + ch * 16,
                        Wt + (long long)(vb ? n0 + r : n0) * ldw + k0 + ch * 8, vb);
         }
     };
 
-    float acc[4][4][4];
+    float acc[MI][4][4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < MI; ++i)
 #pragma unroll
         for (int j = 0; j < 4; ++j)
 #pragma unroll
@@ -68,14 +78,14 @@ static __device__ __noinline__ void op_gemm(const mk_op_desc* op, int a0, int a1
         compute_sync();
         if (kt + kGemmStages - 1 < nk) issue(kt + kGemmStages - 1);
         cp_async_commit();
-        const uint32_t a_base = smem_u32(sa + (kt % kGemmStages) * kGemmTileBytes);
-        const uint32_t b_base = smem_u32(sb + (kt % kGemmStages) * kGemmTileBytes);
+        const uint32_t a_base = smem_u32(sa + (kt % kGemmStages) * kATileBytes);
+        const uint32_t b_base = smem_u32(sb + (kt % kGemmStages) * kBTileBytes);
 #pragma unroll
         for (int kk = 0; kk < kGemmBK / 16; ++kk) {
-            uint32_t af[4][4], bf[4][2];
+            uint32_t af[MI][4], bf[4][2];
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
-                ldmatrix_x4(a_base + (wm * 64 + i * 16 + (lane & 15)) * kGemmRowBytes + (kk * 16 + (lane >> 4) * 8) * 2,
+            for (int i = 0; i < MI; ++i)
+                ldmatrix_x4(a_base + (wm * (BM / 2) + i * 16 + (lane & 15)) * kGemmRowBytes + (kk * 16 + (lane >> 4) * 8) * 2,
                             af[i][0], af[i][1], af[i][2], af[i][3]);
 #pragma unroll
             for (int pr = 0; pr < 2; ++pr) {
@@ -84,7 +94,7 @@ static __device__ __noinline__ void op_gemm(const mk_op_desc* op, int a0, int a1
                             bf[pr * 2][1], bf[pr * 2 + 1][0], bf[pr * 2 + 1][1]);
             }
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
+            for (int i = 0; i < MI; ++i)
 #pragma unroll
                 for (int j = 0; j < 4; ++j) mma_bf16(acc[i][j], af[i], bf[j][0], bf[j][1]);
         }
@@ -97,10 +107,10 @@ static __device__ __noinline__ void op_gemm(const mk_op_desc* op, int a0, int a1
     void* O = reinterpret_cast<void*>(op->ptr[2]);
     const long long ldo = op->ld[2];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < MI; ++i) {
 #pragma unroll
         for (int hrow = 0; hrow < 2; ++hrow) {
-            const int r = m0 + wm * 64 + i * 16 + (lane >> 2) + hrow * 8;
+            const int r = m0 + wm * (BM / 2) + i * 16 + (lane >> 2) + hrow * 8;
             if (r >= M) continue;
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
