@@ -19,12 +19,13 @@
 
 namespace mk {
 
-constexpr int kGemmBM = 128, kGemmBN = 128, kGemmBK = 32;     // kGemmBM: rows per m tile in the schedule (config.py GEMM_BM)
-constexpr int kGemmRowBytes = kGemmBK * 2 + 16;                // padded: conflict-free ldmatrix
+constexpr int kGemmBM = 128, kGemmBN = 128;                    // kGemmBM: rows per m tile in the schedule (config.py GEMM_BM)
 
 // BM: activation rows held per tile (128, or 64 when M <= 64); MI = 16-row fragments per warp.
-template <int BM, int kGemmStages>
+template <int BM, int kGemmBK, int kGemmStages>
 static __device__ __noinline__ void op_gemm(const mk_op_desc* op, int a0, int a1, int a2, uint8_t* work) {
+    constexpr int kGemmRowBytes = kGemmBK * 2 + 16;            // padded: conflict-free ldmatrix
+    constexpr int CPRW = kGemmBK / 8;                          // 16-byte chunks per row
     constexpr int MI = BM / 32;
     constexpr int kATileBytes = BM * kGemmRowBytes, kBTileBytes = kGemmBN * kGemmRowBytes;
     static_assert(kGemmStages * (kATileBytes + kBTileBytes) <= kWorkBytes, "GEMM stages exceed the work area");
@@ -44,9 +45,9 @@ static __device__ __noinline__ void op_gemm(const mk_op_desc* op, int a0, int a1
         const int st = kt % kGemmStages;
         const int k0 = kbeg + kt * kGemmBK;
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            const int v = t + i * kComputeThreads;              // 4 chunks of 16 bytes per row
-            const int r = v >> 2, ch = v & 3;
+        for (int i = 0; i < kGemmBN * CPRW / kComputeThreads; ++i) {
+            const int v = t + i * kComputeThreads;
+            const int r = v / CPRW, ch = v % CPRW;
             if (r < BM) {
                 const bool va = m0 + r < M;
                 cp_async16(sa + st * kATileBytes + r * kGemmRowBytes + ch * 16,
