@@ -33,6 +33,8 @@ ATTN_BQ, ATTN_BK = 128, 64
 DECODE_KEYS_PER_TILE = 64
 MIN_SPLIT_KEYS = 64
 MAX_KV_SPLITS = 32
+# split-KV cost model (us): per instruction, extra when partials are written and merged, per cached key
+DEC_FIXED_US, DEC_MERGE_US, DEC_US_PER_KEY = 4.0, 1.5, 0.0086
 
 # ---- instruction word layout (16 x int32)
 IW = 16

@@ -83,20 +83,18 @@ def fuse_rope_attention(g: Graph) -> Graph:
 
 
 def kv_splits(pairs: int, max_seq: int, sm_count: int) -> int:
-    """Instructions per (sequence, kv head) pair.  Few pairs: one wave that covers the SMs.  Many
-    pairs: the smallest split count whose last wave is at least 90 % full, as long as a split
-    still has >= MIN_SPLIT_KEYS keys of room."""
-    cap = max(1, max_seq // C.MIN_SPLIT_KEYS)
-    if pairs <= sm_count:
-        return max(1, min(cap, sm_count // pairs, C.MAX_KV_SPLITS))
-    best, best_eff = 1, 0.0
-    for s in range(1, min(cap, 8) + 1):
-        n = pairs * s
-        eff = n / (-(-n // sm_count) * sm_count)
-        if eff > best_eff + 1e-9:
-            best, best_eff = s, eff
-        if eff >= 0.9:
-            break
+    """Instructions per (sequence, kv head) pair: the split count with the lowest modelled time
+    waves x (fixed cost per instruction [+ partial / merge cost when split] + keys per split x time per key),
+    with the constants measured on B200 (config.DEC_*).  Few pairs (batch 1) spread over one wave of
+    SMs; many pairs stay unsplit until the cache is long enough to pay for the partials.  A split
+    keeps at least MIN_SPLIT_KEYS keys of room."""
+    cap = max(1, min(max_seq // C.MIN_SPLIT_KEYS, C.MAX_KV_SPLITS))
+    best, best_cost = 1, float("inf")
+    for s in range(1, cap + 1):
+        waves = -(-(pairs * s) // sm_count)
+        cost = waves * (C.DEC_FIXED_US + (C.DEC_MERGE_US if s > 1 else 0.0) + (max_seq / s) * C.DEC_US_PER_KEY)
+        if cost < best_cost - 1e-9:
+            best, best_cost = s, cost
     return best
 
 
