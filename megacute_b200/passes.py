@@ -108,6 +108,10 @@ def split_kv(g: Graph, sm_count: int) -> Graph:
             if s > 1:
                 G, D = op.heads // op.kv_heads, op.head_dim
                 cols = -(-(G * D + 2 * G) // 4) * 4          # per split: O (G x D), running max (G), sum (G)
+                s = min(s, C.DECODE_MERGE_BYTES // (cols * 4))   # the merging split holds all partial rows in shared memory
+                if s < 2:
+                    ops.append(op)
+                    continue
                 part = out.workspace((pairs * s, cols), torch.float32)
                 count = out.workspace((pairs, 1), torch.int32)
                 op = op.clone(splits=s, part=part, count=count)

@@ -162,7 +162,8 @@ def test_streaming_linear_chain_and_counters(cuda):
 # ---------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("B,H,KVH,D,max_seq,ctx", [(1, 8, 2, 64, 256, 100), (3, 4, 4, 64, 128, 0), (2, 8, 1, 128, 256, 200),
                                                   (1, 32, 8, 64, 1152, 1024), (20, 8, 2, 64, 384, 300),
-                                                  (40, 16, 8, 64, 256, 129)])
+                                                  (40, 16, 8, 64, 256, 129), (160, 4, 1, 64, 128, 0), (50, 8, 4, 128, 256, 77),
+                                                  (150, 32, 8, 64, 128, 64)])
 @pytest.mark.parametrize("fused", [False, True])
 def test_decode_attention(cuda, B, H, KVH, D, max_seq, ctx, fused):
     """rope_append + decode_attention, kept separate (q_out is also an output) or fused by the pass."""
