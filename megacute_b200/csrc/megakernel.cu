@@ -33,6 +33,11 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
             mbar_init(&c->full[s], 1);
             mbar_init(&c->empty[s], kComputeWarps);
         }
+        for (int s = 0; s < 4; ++s) {
+            mbar_init(&c->slot_full[s], kComputeWarps);
+            mbar_init(&c->slot_free[s], 1);
+        }
+        mbar_init(&c->epi_done, 1);
         c->abort = 0;
         c->flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -42,6 +47,9 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
     if (warp == kProducerWarp) {
         // ---------------- producer warp ----------------
         producer_loop<TRACE>(p, c, ring);
+    } else if (warp == kFinisherWarp) {
+        // ---------------- finisher warp: epilogues of the streaming linear ----------------
+        mk_gemv_finisher(p);
     } else {
         // ---------------- compute warps ----------------
         // Instruction metadata runs one instruction ahead in shared memory (Meta): while instruction

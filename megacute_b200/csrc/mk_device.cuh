@@ -13,8 +13,9 @@ namespace mk {
 // ---- CTA shape (mirrors megacute_b200/config.py) --------------------------------------------
 constexpr int kComputeWarps = 8;
 constexpr int kComputeThreads = kComputeWarps * 32;
-constexpr int kThreads = kComputeThreads + 32;           // + one producer warp
+constexpr int kThreads = kComputeThreads + 64;           // + one producer warp + one finisher warp
 constexpr int kProducerWarp = kComputeWarps;
+constexpr int kFinisherWarp = kComputeWarps + 1;
 
 // ---- shared memory map -----------------------------------------------------------------------
 constexpr int kGemvRows = 8;                              // weight rows per ring stage
@@ -68,6 +69,9 @@ struct Ctrl {                     // lives in the last kCtrlBytes of shared memo
     Meta meta;
     unsigned long long full[kStages];
     unsigned long long empty[kStages];
+    unsigned long long slot_full[4];  // streaming linear: the 8 compute warps have deposited a row group's partial tiles
+    unsigned long long slot_free[4];  // ... the finisher warp has read them
+    unsigned long long epi_done;      // ... the finisher has stored the instruction's last outputs
     int abort;                    // set once a wait of this CTA gave up or saw the global abort
     int flag;                     // scratch broadcast word (split-KV last arriver)
     long long t_dep;              // tracing: when the dependencies of the current instruction were met
@@ -278,7 +282,7 @@ __device__ __forceinline__ void report(const Params& p, Ctrl* c, int code, int s
     }
 }
 
-enum { WHERE_RING_FULL = 1, WHERE_RING_EMPTY = 2, WHERE_DEP = 3, WHERE_DRAIN = 4 };
+enum { WHERE_RING_FULL = 1, WHERE_RING_EMPTY = 2, WHERE_DEP = 3, WHERE_DRAIN = 4, WHERE_COMBINE = 5 };
 
 __device__ __forceinline__ bool wait_barrier(const Params& p, Ctrl* c, unsigned long long* bar, uint32_t parity,
                                              int seq, int where) {

@@ -9,11 +9,17 @@ __device__ int mk_op_gemv_units(const Params& p, const mk_op_desc* op, int o0, i
     const SmemMap m = smem_map();
     RingPos pos;
     pos.stage = packed_pos & 0xff;
-    pos.phase = (uint32_t)(packed_pos >> 8);
+    pos.phase = (uint32_t)(packed_pos >> 8) & 1u;
+    pos.comb = (uint32_t)(packed_pos >> 16) & 0x1fu;
     gemv_mma(p, m.ctrl, m.ring, m.work, op, o0, o1, seq, pos, nwait, wait_off);
     // arrivals leave before the function epilogue restores callee-saved registers from local memory
     if (publish(p, m.ctrl, narrive, arrive_off)) return -1;
-    return pos.stage | ((int)pos.phase << 8);
+    return pos.stage | ((int)pos.phase << 8) | ((int)pos.comb << 16);
+}
+
+__device__ void mk_gemv_finisher(const Params& p) {
+    const SmemMap m = smem_map();
+    gemv_finisher(p, m.ctrl, m.work);
 }
 
 }  // namespace mk

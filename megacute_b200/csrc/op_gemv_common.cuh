@@ -30,6 +30,7 @@ constexpr int GEMV_F_UNITS = 4;
 struct RingPos {
     int stage = 0;
     uint32_t phase = 0;
+    uint32_t comb = 0;           // compute side only: parities of slot_free[0..3] (bits 0..3) and epi_done (bit 4)
     __device__ __forceinline__ void advance() {
         if (++stage == kStages) { stage = 0; phase ^= 1u; }
     }

@@ -13,8 +13,16 @@
 //            so a lane fetches its whole B operand of a k-step with one 128-bit load.  Rows are
 //            padded by 64 bytes so the 8 activation rows of a quarter-warp hit different banks.
 //   red      [4 slots][8 warps][32 lanes] float4: per-warp partial 16 x 8 tiles of a row group
-//   gatebuf  [32 lanes] float4: swiglu gate tile between the gate group and the up group
-//   cnt      [4 slots] arrivals of the combine;  rowstat [8 warps][8 rows] partial sums of x^2
+//   rowstat  [8 warps][8 rows] partial sums of x^2
+//
+// The eight compute warps only stream: each deposits its partial tile of a row group in a slot and
+// moves on to the next stage.  A ninth warp, the finisher (gemv_finisher below), adds the eight
+// partials and runs the epilogue (rstd, bias, activation, swiglu, residual, store).  With the
+// epilogue on a compute warp that warp is late for the next group by the epilogue's length, and
+// since every group needs every warp's K slice each group costs MMA + combine + epilogue; the ring
+// has only two stages, so a stage's period is (that + the refill latency) / 2.
+// Hand-over per slot: Ctrl::slot_full (8 arrivals, one per compute warp) and Ctrl::slot_free (the
+// finisher); Ctrl::epi_done tells the compute warps that the instruction's last store has left.
 #pragma once
 #include "mma.cuh"
 #include "op_gemv_common.cuh"
@@ -22,9 +30,7 @@
 namespace mk {
 
 constexpr int kMmaRedOff = 66 * 1024;                      // xf takes at most 64 KB + 512 B
-constexpr int kMmaGateOff = kMmaRedOff + 4 * 8 * 32 * 16;  // + 16 KB
-constexpr int kMmaCntOff = kMmaGateOff + 32 * 16;
-constexpr int kMmaStatOff = kMmaCntOff + 64;
+constexpr int kMmaStatOff = kMmaRedOff + 4 * 8 * 32 * 16;  // + 16 KB
 
 __device__ __forceinline__ float4 lds_volatile4(const float4* p) {
     float4 v;
@@ -50,14 +56,12 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
 __device__ __forceinline__ void gemv_mma(const Params& p, Ctrl* c, uint8_t* ring, uint8_t* work, const mk_op_desc* op,
                                          int o0, int o1, int seq, RingPos& pos, int nwait, int wait_off) {
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
-    const int M = op->i[0], K = op->i[2], act = op->i[3], odt = op->i[5], rdt = op->i[6];
+    const int M = op->i[0], K = op->i[2];
     const bool swi = op->flags & GEMV_F_SWIGLU, rms = op->flags & GEMV_F_RMS;
     const int S = (K + kSegElems - 1) / kSegElems;
     const int xrow = K * 4 + 64;                                              // bytes per activation row of xf
     uint8_t* xf = work;
     float4* red = reinterpret_cast<float4*>(work + kMmaRedOff);
-    float4* gatebuf = reinterpret_cast<float4*>(work + kMmaGateOff);
-    int* cnt = reinterpret_cast<int*>(work + kMmaCntOff);
     float* rowstat = reinterpret_cast<float*>(work + kMmaStatOff);
 
     // ---- before the dependency wait: the norm gain of this thread's first vectors ----
@@ -70,18 +74,11 @@ __device__ __forceinline__ void gemv_mma(const Params& p, Ctrl* c, uint8_t* ring
         const int v = t + i * kComputeThreads;
         g0[i] = (gain && v < nv) ? __ldg(gain + v) : ones;
     }
-    if (t < 4) cnt[t] = 0;
     // everything below that does not depend on the activations is also set up before the wait:
     // the op runs once per instruction, cold, and this code would otherwise sit between the
     // arrival of x and the first MMA
-    // this lane's output columns of a 16 x 8 accumulator tile are activation rows m0 and m0 + 1
-    const int m0 = 2 * (lane & 3);
     const int n = o1 - o0;
     const int ngroups = (swi ? 2 : 1) * ((n + 15) / 16);
-    const void* biasp = reinterpret_cast<const void*>(op->ptr[3]);
-    const void* resp = reinterpret_cast<const void*>(op->ptr[4]);
-    void* outp = reinterpret_cast<void*>(op->ptr[2]);
-    const long long ldo = op->ld[2], ldr = op->ld[4];
     constexpr int kSlice = kSegElems / kComputeWarps;                         // 256: a warp's K slice of a segment
     const int kw = warp * kSlice;
     // B operand (16 k x 8 columns).  Up to 4 activation rows: columns 0..3 carry the high parts of
@@ -96,7 +93,6 @@ __device__ __forceinline__ void gemv_mma(const Params& p, Ctrl* c, uint8_t* ring
     const int xdt = op->i[4];
     const void* x = reinterpret_cast<const void*>(op->ptr[0]);
     const long long ldx = op->ld[0];
-    const float eps = op->f[0];
     if (wait_deps(p, c, nwait, wait_off, seq)) return;
     if (t == 0 && p.trace_cap > 0) c->t_dep = (long long)globaltimer();
 
@@ -142,37 +138,8 @@ __device__ __forceinline__ void gemv_mma(const Params& p, Ctrl* c, uint8_t* ring
         compute_sync();
     }
     phase_mark(p, c, 0);
-    float rs[2] = {1.f, 1.f};
-    if (rms) {
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            if (m0 + j < M) {
-                float sq = 0.f;
-#pragma unroll
-                for (int w8 = 0; w8 < kComputeWarps; ++w8) sq += rowstat[w8 * 8 + m0 + j];
-                rs[j] = rsqrt_approx(sq / (float)K + eps);
-            }
-        }
-    }
-
 #pragma unroll 1
     for (int g = 0; g < ngroups; ++g) {
-        const int ob = o0 + (swi ? g >> 1 : g) * 16 + (lane >> 2);            // this lane's rows: ob, ob + 8
-        // epilogue operands are requested before the stage waits so their latency is hidden
-        float bias_v[2] = {0.f, 0.f}, res_v[4] = {0.f, 0.f, 0.f, 0.f};
-        if (!swi) {
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const int o = ob + h * 8;
-                if (o < o1) {
-                    if (biasp) bias_v[h] = load1(biasp, o, 0);
-                    if (resp) {
-                        if (m0 < M) res_v[h * 2] = load1(resp, (long long)m0 * ldr + o, rdt);
-                        if (m0 + 1 < M) res_v[h * 2 + 1] = load1(resp, (long long)(m0 + 1) * ldr + o, rdt);
-                    }
-                }
-            }
-        }
         // four independent accumulator tiles (even / odd k-step x high / low part of x) keep the
         // chain of dependent MMAs short; they are summed once per row group
         float accs[4][4];
@@ -233,63 +200,124 @@ __device__ __forceinline__ void gemv_mma(const Params& p, Ctrl* c, uint8_t* ring
             if (lane == 0) mbar_arrive(&c->empty[pos.stage]);
             pos.advance();
         }
-        // ---- combine the 8 warps' K slices: the last warp to arrive owns the epilogue.  Four
-        // partial slots used round-robin: a warp can be at most two row groups ahead of the
-        // slowest one (the ring has two stages and every group takes at least one). ----
-        static_assert(kStages <= 3, "four partial slots cover a run-ahead of at most kStages row groups");
+        // ---- hand the partial tile to the finisher.  Four slots round-robin; a slot is reused
+        // four groups later, once the finisher has freed it (it almost always has). ----
         const int sl = g & 3;
-        float4* slot = red + sl * (8 * 32);
-        sts_volatile4(&slot[warp * 32 + lane], make_float4((accs[0][0] + accs[1][0]) + (accs[2][0] + accs[3][0]),
-                                                           (accs[0][1] + accs[1][1]) + (accs[2][1] + accs[3][1]),
-                                                           (accs[0][2] + accs[1][2]) + (accs[2][2] + accs[3][2]),
-                                                           (accs[0][3] + accs[1][3]) + (accs[2][3] + accs[3][3])));
+        ok = wait_barrier(p, c, &c->slot_free[sl], ((pos.comb >> sl) & 1u) ^ 1u, seq, WHERE_COMBINE) && ok;
+        pos.comb ^= 1u << sl;
+        sts_volatile4(&red[sl * (8 * 32) + warp * 32 + lane],
+                      make_float4((accs[0][0] + accs[1][0]) + (accs[2][0] + accs[3][0]), (accs[0][1] + accs[1][1]) + (accs[2][1] + accs[3][1]),
+                                  (accs[0][2] + accs[1][2]) + (accs[2][2] + accs[3][2]), (accs[0][3] + accs[1][3]) + (accs[2][3] + accs[3][3])));
         __syncwarp();
-        int fin = 0;
-        if (lane == 0) {
-            __threadfence_block();
-            fin = atomicAdd(&cnt[sl], 1) == kComputeWarps - 1;
-            if (fin) cnt[sl] = 0;
-            __threadfence_block();
-        }
-        fin = __shfl_sync(0xffffffffu, fin, 0) && __all_sync(0xffffffffu, ok);      // uniform over the warp
-        float v[4] = {0.f, 0.f, 0.f, 0.f};
-        if (fin) {
+        if (lane == 0) mbar_arrive(&c->slot_full[sl]);                        // release: the warp's deposit
+    }
+    // the instruction's results are in memory when the finisher says so
+    wait_barrier(p, c, &c->epi_done, (pos.comb >> 4) & 1u, seq, WHERE_COMBINE);
+    pos.comb ^= 16u;
+    phase_mark(p, c, 2);
+}
+
+// The finisher warp: walks the CTA's instructions like the producer does and, for every streaming
+// linear of the tensor-core path, turns the deposited partial tiles into outputs.
+// Lane l holds rows ob = o0 + 16 * group + (l >> 2) and ob + 8, activation rows m0 = 2 * (l & 3), m0 + 1
+// (the MMA result layout); with packed activations (M <= 4) lanes l & 3 >= 2 hold low-part products.
+__device__ __forceinline__ void gemv_finisher(const Params& p, Ctrl* c, uint8_t* work) {
+    const int lane = threadIdx.x & 31;
+    const float4* red = reinterpret_cast<const float4*>(work + kMmaRedOff);
+    const float* rowstat = reinterpret_cast<const float*>(work + kMmaStatOff);
+    uint32_t fullpar = 0;                                                     // parities of slot_full[0..3]
+    for (int idx = blockIdx.x; idx < p.n_insts; idx += gridDim.x) {
+        const Inst in = fetch_inst(p, idx);
+        const int opi = in.opi - 1;
+        if (opi < 0 || opi >= p.n_ops) return;
+        const mk_op_desc* op = p.ops + opi;
+        if (op->kind != MK_OP_GEMV || !(op->flags & GEMV_F_UNITS)) continue;
+        const int M = op->i[0], K = op->i[2], act = op->i[3], odt = op->i[5], rdt = op->i[6];
+        const bool swi = op->flags & GEMV_F_SWIGLU, rms = op->flags & GEMV_F_RMS;
+        const int o0 = in.a0, o1 = in.a1, seq = in.seq;
+        const int ngroups = (swi ? 2 : 1) * ((o1 - o0 + 15) / 16);
+        const void* biasp = reinterpret_cast<const void*>(op->ptr[3]);
+        const void* resp = reinterpret_cast<const void*>(op->ptr[4]);
+        void* outp = reinterpret_cast<void*>(op->ptr[2]);
+        const long long ldo = op->ld[2], ldr = op->ld[4];
+        const float eps = op->f[0];
+        const bool packed = M <= 4;
+        const int m0 = 2 * (lane & 3);
+        const bool storer = !(packed && (lane & 3) >= 2);
+        float rs[2] = {1.f, 1.f};
+        float gate[4] = {0.f, 0.f, 0.f, 0.f};
+        bool ok = true;
+#pragma unroll 1
+        for (int g = 0; g < ngroups; ++g) {
+            const int sl = g & 3;
+            const int ob = o0 + (swi ? g >> 1 : g) * 16 + (lane >> 2);
+            // Epilogue operands.  For the first group they are read after the hand-over (the compute
+            // warps deposit only after the instruction's dependencies are met), later ones before it.
+            float bias_v[2] = {0.f, 0.f}, res_v[4] = {0.f, 0.f, 0.f, 0.f};
+            auto fetch_operands = [&]() {
+                if (swi || !storer) return;
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int o = ob + h * 8;
+                    if (o < o1) {
+                        if (biasp) bias_v[h] = load1(biasp, o, 0);
+                        if (resp) {
+                            if (m0 < M) res_v[h * 2] = load1(resp, (long long)m0 * ldr + o, rdt);
+                            if (m0 + 1 < M) res_v[h * 2 + 1] = load1(resp, (long long)(m0 + 1) * ldr + o, rdt);
+                        }
+                    }
+                }
+            };
+            if (g > 0) fetch_operands();
+            ok = wait_barrier(p, c, &c->slot_full[sl], (fullpar >> sl) & 1u, seq, WHERE_COMBINE) && ok;
+            fullpar ^= 1u << sl;
+            if (!ok) return;                                                  // the launch is failing
+            if (g == 0) {
+                fetch_operands();
+                if (rms && storer) {
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        if (m0 + j < M) {
+                            float sq = 0.f;
+#pragma unroll
+                            for (int w8 = 0; w8 < kComputeWarps; ++w8) sq += rowstat[w8 * 8 + m0 + j];
+                            rs[j] = rsqrt_approx(sq / (float)K + eps);
+                        }
+                    }
+                }
+            }
+            float v[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int w8 = 0; w8 < kComputeWarps; ++w8) {
-                const float4 q = lds_volatile4(&slot[w8 * 32 + lane]);
+                const float4 q = lds_volatile4(&red[sl * (8 * 32) + w8 * 32 + lane]);
                 v[0] += q.x; v[1] += q.y; v[2] += q.z; v[3] += q.w;
             }
-        }
-        if (fin && packed) {
-            // columns 4..7 hold the low-part products of rows 0..3: add them to columns 0..3, which
-            // sit two lanes further down in the quad
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&c->slot_free[sl]);                    // the slot has been read
+            if (packed) {
+                // columns 4..7 hold the low-part products of rows 0..3: add them to columns 0..3,
+                // which sit two lanes further down in the quad
 #pragma unroll
-            for (int e = 0; e < 4; ++e) v[e] += __shfl_xor_sync(0xffffffffu, v[e], 2);
-        }
-        if (fin && !(packed && (lane & 3) >= 2)) {
-            // v[0], v[1]: row ob, activation rows m0, m0 + 1;  v[2], v[3]: row ob + 8
-            if (swi && !(g & 1)) {
-                sts_volatile4(&gatebuf[lane], make_float4(v[0] * rs[0], v[1] * rs[1], v[2] * rs[0], v[3] * rs[1]));
-            } else {
-                float gt[4] = {0.f, 0.f, 0.f, 0.f};
-                if (swi) {
-                    const float4 q = lds_volatile4(&gatebuf[lane]);
-                    gt[0] = q.x; gt[1] = q.y; gt[2] = q.z; gt[3] = q.w;
-                }
+                for (int e = 0; e < 4; ++e) v[e] += __shfl_xor_sync(0xffffffffu, v[e], 2);
+            }
+            if (storer) {
+                // v[0], v[1]: row ob, activation rows m0, m0 + 1;  v[2], v[3]: row ob + 8
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int o = ob + (e >> 1) * 8, m = m0 + (e & 1);
-                    if (o < o1 && m < M) {
-                        float y = v[e] * rs[e & 1];
-                        if (swi) y = gt[e] * sigmoidf_(gt[e]) * y;
-                        else y = apply_act(act, y + bias_v[e >> 1]) + res_v[e];
-                        store1(outp, (long long)m * ldo + o, odt, y);
+                    const float y = v[e] * rs[e & 1];
+                    if (swi && !(g & 1)) {
+                        gate[e] = y;
+                    } else if (o < o1 && m < M) {
+                        store1(outp, (long long)m * ldo + o, odt,
+                               swi ? gate[e] * sigmoidf_(gate[e]) * y : apply_act(act, y + bias_v[e >> 1]) + res_v[e]);
                     }
                 }
             }
         }
+        __syncwarp();                                                         // every lane's stores before the arrival
+        if (lane == 0) mbar_arrive(&c->epi_done);
     }
-    phase_mark(p, c, 2);
 }
 
 }  // namespace mk
