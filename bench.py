@@ -31,7 +31,7 @@ sys.path.insert(0, str(ROOT))
 
 # DRAM bytes of one megakernel launch of the default workload (batch 1, ctx 1024), from one ncu capture
 # (dram__bytes_read.sum + dram__bytes_write.sum; profiles/megakernel_llama1b_decode_b1_ctx1024.md)
-MEASURED_TRAFFIC_B1_CTX1024 = 2_506_381_000 + 9_379_328
+MEASURED_TRAFFIC_B1_CTX1024 = 2_506_453_000 + 6_217_216
 WEIGHT_BYTES = 2 * (16 * (3072 * 2048 + 2048 * 2048 + 16384 * 2048 + 2048 * 8192) + 128256 * 2048)   # 2 471 493 632
 KV_BYTES_PER_TOKEN = 16 * 2 * 512 * 2                                                               # 32 768
 
