@@ -38,6 +38,7 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
             mbar_init(&c->slot_free[s], 1);
         }
         mbar_init(&c->epi_done, 1);
+        mbar_init(&c->deps_met, 1);
         c->abort = 0;
         c->flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");

@@ -71,7 +71,8 @@ struct Ctrl {                     // lives in the last kCtrlBytes of shared memo
     unsigned long long empty[kStages];
     unsigned long long slot_full[4];  // streaming linear: the 8 compute warps have deposited a row group's partial tiles
     unsigned long long slot_free[4];  // ... the finisher warp has read them
-    unsigned long long epi_done;      // ... the finisher has stored the instruction's last outputs
+    unsigned long long epi_done;      // ... the finisher has issued the instruction's last stores (its arrivals follow)
+    unsigned long long deps_met;      // ... the compute warps have seen the instruction's dependencies met
     int abort;                    // set once a wait of this CTA gave up or saw the global abort
     int flag;                     // scratch broadcast word (split-KV last arriver)
     long long t_dep;              // tracing: when the dependencies of the current instruction were met

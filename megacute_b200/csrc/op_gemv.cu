@@ -12,8 +12,10 @@ __device__ int mk_op_gemv_units(const Params& p, const mk_op_desc* op, int o0, i
     pos.phase = (uint32_t)(packed_pos >> 8) & 1u;
     pos.comb = (uint32_t)(packed_pos >> 16) & 0x1fu;
     gemv_mma(p, m.ctrl, m.ring, m.work, op, o0, o1, seq, pos, nwait, wait_off);
-    // arrivals leave before the function epilogue restores callee-saved registers from local memory
-    if (publish(p, m.ctrl, narrive, arrive_off)) return -1;
+    // The finisher warp has sent the first 32 arrivals (there are rarely more than two); what is left
+    // is the barrier that ends the instruction, and any further arrivals.
+    const int sent = narrive < 32 ? narrive : 32;
+    if (publish(p, m.ctrl, narrive - sent, arrive_off < 0 ? arrive_off : arrive_off + sent)) return -1;
     return pos.stage | ((int)pos.phase << 8) | ((int)pos.comb << 16);
 }
 

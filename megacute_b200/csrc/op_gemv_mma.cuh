@@ -94,7 +94,10 @@ __device__ __forceinline__ void gemv_mma(const Params& p, Ctrl* c, uint8_t* ring
     const void* x = reinterpret_cast<const void*>(op->ptr[0]);
     const long long ldx = op->ld[0];
     if (wait_deps(p, c, nwait, wait_off, seq)) return;
-    if (t == 0 && p.trace_cap > 0) c->t_dep = (long long)globaltimer();
+    if (t == 0) {
+        mbar_arrive(&c->deps_met);          // the finisher may now read the residual of the first row group
+        if (p.trace_cap > 0) c->t_dep = (long long)globaltimer();
+    }
 
     // ---- stage x * gain (high + low bf16 parts, fragment order); accumulate sum(x^2) per row ----
     {
@@ -225,7 +228,7 @@ __device__ __forceinline__ void gemv_finisher(const Params& p, Ctrl* c, uint8_t*
     const int lane = threadIdx.x & 31;
     const float4* red = reinterpret_cast<const float4*>(work + kMmaRedOff);
     const float* rowstat = reinterpret_cast<const float*>(work + kMmaStatOff);
-    uint32_t fullpar = 0;                                                     // parities of slot_full[0..3]
+    uint32_t fullpar = 0;                                                     // parities of slot_full[0..3], bit 4: deps_met
     for (int idx = blockIdx.x; idx < p.n_insts; idx += gridDim.x) {
         const Inst in = fetch_inst(p, idx);
         const int opi = in.opi - 1;
@@ -246,13 +249,18 @@ __device__ __forceinline__ void gemv_finisher(const Params& p, Ctrl* c, uint8_t*
         const bool storer = !(packed && (lane & 3) >= 2);
         float rs[2] = {1.f, 1.f};
         float gate[4] = {0.f, 0.f, 0.f, 0.f};
-        bool ok = true;
+        // this lane's arrival target, read now so that it is in a register when the last store has left
+        const int arrive_to = lane < in.narrive ? __ldg(p.arrives + in.arrive_off + lane) : -1;
+        // Operands of the epilogue may be results of earlier instructions: nothing is read before
+        // the compute warps have seen the instruction's dependencies met.
+        bool ok = wait_barrier(p, c, &c->deps_met, (fullpar >> 4) & 1u, seq, WHERE_COMBINE);
+        fullpar ^= 16u;
+        if (!ok) return;
 #pragma unroll 1
         for (int g = 0; g < ngroups; ++g) {
             const int sl = g & 3;
             const int ob = o0 + (swi ? g >> 1 : g) * 16 + (lane >> 2);
-            // Epilogue operands.  For the first group they are read after the hand-over (the compute
-            // warps deposit only after the instruction's dependencies are met), later ones before it.
+            // epilogue operands are requested before the hand-over wait so their latency is hidden
             float bias_v[2] = {0.f, 0.f}, res_v[4] = {0.f, 0.f, 0.f, 0.f};
             auto fetch_operands = [&]() {
                 if (swi || !storer) return;
@@ -268,12 +276,11 @@ __device__ __forceinline__ void gemv_finisher(const Params& p, Ctrl* c, uint8_t*
                     }
                 }
             };
-            if (g > 0) fetch_operands();
+            fetch_operands();
             ok = wait_barrier(p, c, &c->slot_full[sl], (fullpar >> sl) & 1u, seq, WHERE_COMBINE) && ok;
             fullpar ^= 1u << sl;
             if (!ok) return;                                                  // the launch is failing
             if (g == 0) {
-                fetch_operands();
                 if (rms && storer) {
 #pragma unroll
                     for (int j = 0; j < 2; ++j) {
@@ -315,8 +322,12 @@ __device__ __forceinline__ void gemv_finisher(const Params& p, Ctrl* c, uint8_t*
                 }
             }
         }
-        __syncwarp();                                                         // every lane's stores before the arrival
-        if (lane == 0) mbar_arrive(&c->epi_done);
+        // The instruction's arrivals leave from here, right behind its last store: __syncwarp orders
+        // every lane's stores before the arriving lanes' red.release.gpu, whose release is cumulative
+        // over them.  (More than 32 targets: the compute warps send the rest, see the wrapper.)
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&c->epi_done);                             // shared memory is free: the compute warps move on
+        if (arrive_to >= 0) red_release_add(p.counters + arrive_to, 1);
     }
 }
 
