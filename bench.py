@@ -56,7 +56,7 @@ class ClockSampler:
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+                                          "-lms", "25", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
             self.t = threading.Thread(target=lambda: self.rows.extend(self.proc.stdout), daemon=True)
             self.t.start()
         except OSError:
@@ -220,13 +220,13 @@ def main():
     run_steps(max(3, a.warmup))
     prog.check()
     reset_state()
-    with ClockSampler(local) as cs:
+    with ClockSampler(local) as cs:                  # clocks and throttle reasons over all three timed regions
         ms = timed(run_steps, a.steps)
+        reset_state()
+        kernel_ms = timed(run_kernel_only, a.steps)
+        reset_state()
+        e2e_ms = timed(run_e2e, a.steps)
     clocks = cs.summary()
-    reset_state()
-    kernel_ms = timed(run_kernel_only, a.steps)
-    reset_state()
-    e2e_ms = timed(run_e2e, a.steps)
     prog.check()
 
     if rank != 0:
