@@ -24,7 +24,6 @@ template <bool TRACE>
 __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant__ Params p) {
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* ring = smem;
-    uint8_t* work = smem + kRingBytes;
     Ctrl* c = reinterpret_cast<Ctrl*>(smem + kRingBytes + kWorkBytes);
     const int warp = threadIdx.x >> 5;
 
