@@ -34,8 +34,8 @@ DECODE_KEYS_PER_TILE = 64
 MIN_SPLIT_KEYS = 64
 MAX_KV_SPLITS = 32
 DECODE_MERGE_BYTES = 88 * 1024   # shared memory the merging split may fill with partial rows
-# split-KV cost model (us): per instruction, extra when partials are written and merged, per cached key
-DEC_FIXED_US, DEC_MERGE_US, DEC_US_PER_KEY = 4.0, 1.5, 0.0086
+# split-KV cost model (us): per instruction; partials + merge when split (base, per split); per key tile
+DEC_FIXED_US, DEC_MERGE_US, DEC_MERGE_US_PER_SPLIT, DEC_TILE_US = 4.0, 1.0, 0.05, 1.1
 
 # ---- instruction word layout (16 x int32)
 IW = 16

@@ -19,6 +19,8 @@ runtime's kernel:
 
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import config as C
@@ -82,17 +84,24 @@ def fuse_rope_attention(g: Graph) -> Graph:
     return out
 
 
-def kv_splits(pairs: int, max_seq: int, sm_count: int) -> int:
+def kv_splits(pairs: int, max_seq: int, sm_count: int, head_dim: int = 64) -> int:
     """Instructions per (sequence, kv head) pair: the split count with the lowest modelled time
-    waves x (fixed cost per instruction [+ partial / merge cost when split] + keys per split x time per key),
-    with the constants measured on B200 (config.DEC_*).  Few pairs (batch 1) spread over one wave of
-    SMs; many pairs stay unsplit until the cache is long enough to pay for the partials.  A split
-    keeps at least MIN_SPLIT_KEYS keys of room."""
+    waves x (fixed cost per instruction [+ partials and merge when split] + key tiles per split x time per tile),
+    with constants measured on B200 (config.DEC_*).  The kernel works in tiles of 128 keys (64 for
+    head_dim 128), so splitting below one tile buys nothing and only adds partials to merge.  Few
+    pairs (batch 1) spread over one wave of SMs; many pairs stay unsplit until the cache is long
+    enough to pay for the partials.  A split keeps at least MIN_SPLIT_KEYS keys of room.
+    MEGACUTE_B200_KV_SPLITS overrides the choice (experiments)."""
     cap = max(1, min(max_seq // C.MIN_SPLIT_KEYS, C.MAX_KV_SPLITS))
+    if os.environ.get("MEGACUTE_B200_KV_SPLITS"):
+        return max(1, min(cap, int(os.environ["MEGACUTE_B200_KV_SPLITS"])))
+    tile = 128 if head_dim <= 64 else 64
     best, best_cost = 1, float("inf")
     for s in range(1, cap + 1):
         waves = -(-(pairs * s) // sm_count)
-        cost = waves * (C.DEC_FIXED_US + (C.DEC_MERGE_US if s > 1 else 0.0) + (max_seq / s) * C.DEC_US_PER_KEY)
+        tiles = -(-(-(-max_seq // s)) // tile)
+        merge = C.DEC_MERGE_US + C.DEC_MERGE_US_PER_SPLIT * s if s > 1 else 0.0
+        cost = waves * (C.DEC_FIXED_US + merge + tiles * C.DEC_TILE_US)
         if cost < best_cost - 1e-9:
             best, best_cost = s, cost
     return best
@@ -104,7 +113,7 @@ def split_kv(g: Graph, sm_count: int) -> Graph:
     for op in g.ops:
         if op.kind == "DecodeAttention" and op.splits == 1:
             pairs = op.batch * op.kv_heads
-            s = kv_splits(pairs, op.max_seq, sm_count)
+            s = kv_splits(pairs, op.max_seq, sm_count, op.head_dim)
             if s > 1:
                 G, D = op.heads // op.kv_heads, op.head_dim
                 cols = -(-(G * D + 2 * G) // 4) * 4          # per split: O (G x D), running max (G), sum (G)

@@ -61,7 +61,7 @@ def test_passes_preserve_semantics_decode(B):
 
 
 def test_fold_and_fuse_conditions():
-    g, *_ = small_decode(B=1)
+    g, *_ = small_decode(B=1, max_seq=1024)            # long enough for the KV split to pay
     f = fold_norms(g)
     assert sum(o.kind == "Norm" for o in f.ops) == 0
     assert all(o.rms_eps is not None for o in f.ops if o.kind == "Linear" and o.norm_w is not None)
