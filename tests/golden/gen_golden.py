@@ -1,8 +1,9 @@
 """Generate the fixtures in this folder from the reference's own host code.
 
-Run in the build container, where the reference is mounted read-only:
+Run where a checkout of the reference is available (read-only is enough); MEGACUTE_REFERENCE names
+its root:
 
-    PYTHONPATH=/root/reference python tests/golden/gen_golden.py
+    MEGACUTE_REFERENCE=<reference checkout> python tests/golden/gen_golden.py
 
 What is recorded (the reference ships no tests or golden vectors of its own, and its device code
 cannot run without a Blackwell GPU and nvidia-cutlass-dsl 4.8.0, so these are what the reference
@@ -24,7 +25,9 @@ import torch
 HERE = pathlib.Path(__file__).resolve().parent
 ROOT = HERE.parent.parent
 sys.path.insert(0, str(ROOT))
-REF = pathlib.Path("/root/reference")
+import os
+
+REF = pathlib.Path(os.environ.get("MEGACUTE_REFERENCE", "/root/reference"))
 
 
 def load(path, name):
