@@ -240,7 +240,8 @@ def main():
     line = dict(base, value=ms, ms_per_step=ms, tokens_per_s=world * a.batch * 1e3 / ms,
                 e2e={"value": e2e_ms, "unit": "ms/step", "h2d_bytes_per_step": a.batch * 8,
                      "d2h_bytes_per_step": a.batch * 8},
-                gpu_launches=a.steps, kernel_ms=kernel_ms, clocks=clocks,
+                gpu_launches=2 * a.steps,        # per step: the megakernel and mk_argmax's kernel (+ torch's index_select)
+                kernel_ms=kernel_ms, clocks=clocks,
                 roofline={"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                           "peak_kind": peak_kind,
                           "traffic": MEASURED_TRAFFIC_B1_CTX1024 if (a.batch, a.ctx) == (1, 1024) else None, "algorithmic_bytes": algo_bytes,
