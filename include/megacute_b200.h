@@ -119,6 +119,10 @@ int mk_program_reset(mk_program* p, void* stream);
 
 /* Debug / test access to runtime-owned tables (synchronise the stream first). */
 int mk_program_epoch(mk_program* p);
+/* How many tile-GEMM ops of the last mk_program_set_ops() run on the tcgen05 tensor cores with
+ * bulk-tensor-copied operands (the others, if any, run the mma.sync body: K range per instruction
+ * not a multiple of 64, unaligned operands, or MEGACUTE_B200_NO_TCGEN05 set). */
+int mk_program_tcgen05_ops(mk_program* p);
 int mk_program_read_counters(mk_program* p, int32_t* out, int n);
 int mk_program_read_trace(mk_program* p, int64_t* out, size_t n_words);
 int mk_program_clear_trace(mk_program* p, void* stream);

@@ -9,6 +9,8 @@
 //              so HBM keeps streaming while the compute warps sit in a dependency hop.
 // This replaces the reference's JIT-traced kernel (megacute/kernel.py:251-571) and its per-op
 // role bodies (megacute/ops/*.py).
+#include <cuda.h>          // CUtensorMap and cuTensorMapEncodeTiled's signature (resolved at run time, libcuda is not linked)
+
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -38,6 +40,12 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
         }
         mbar_init(&c->epi_done, 1);
         mbar_init(&c->deps_met, 1);
+        for (int s = 0; s < kTcXStages; ++s) {
+            mbar_init(&c->x_full[s], 1);
+            mbar_init(&c->x_empty[s], 1);
+        }
+        mbar_init(&c->acc_full, 1);
+        c->x_loads = c->x_mmas = c->acc_uses = 0;
         c->abort = 0;
         c->flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -117,7 +125,10 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
                         npos = mk_op_gemv_general(p, op, in.a0, in.a1, in.seq, ppos);
                     }
                     break;
-                case MK_OP_GEMM: mk_op_gemm(op, in.a0, in.a1, in.a2); break;
+                case MK_OP_GEMM:
+                    npos = mk_op_gemm(p, op, in.a0, in.a1, in.a2, in.seq, ppos);
+                    aborting = npos < 0;
+                    break;
                 case MK_OP_ATTENTION: mk_op_attention(op, in.a0, in.a1, in.a2); break;
                 case MK_OP_DECODE_ATTN:
                     aborting = mk_op_decode_attn(p, op, in.a0, in.a1, in.a2, in.nwait, wait_off, in.seq, in.narrive, arrive_off);
@@ -128,7 +139,7 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
             if (!known && threadIdx.x == 0) report(p, c, MK_DEV_BAD_INST, in.seq, 1, op->kind, idx, 0);
             pos.stage = npos & 0xff;
             pos.phase = (uint32_t)(npos >> 8);
-            if (!self_wait) aborting = publish(p, c, in.narrive, arrive_off);
+            if (!self_wait) aborting = publish(p, c, in.narrive, arrive_off) || aborting;
             if (threadIdx.x == 0) {
                 trace_rec<TRACE>(p, 1, slot, in.seq, t0, t1, (long long)globaltimer());
                 if (TRACE && self_wait) trace_rec<TRACE>(p, 2, slot, in.seq, c->t_phase[0], c->t_phase[1], c->t_phase[2]);
@@ -171,12 +182,15 @@ struct mk_program {
     int32_t* d_counters = nullptr;
     mk_op_desc* d_ops = nullptr;
     mk_op_desc* h_ops = nullptr;     // pinned staging copy
+    uint8_t* d_tmaps = nullptr;      // per op: two 128-byte tensor maps (tile GEMM: activations, weights)
+    uint8_t* h_tmaps = nullptr;      // pinned staging copy
     int64_t* d_trace = nullptr;
     int32_t* d_status = nullptr;
     int32_t* h_status = nullptr;     // pinned
     int epoch = 0;
     int max_target = 1;
     unsigned long long timeout_ns = 2000000000ull;
+    int tcgen05_ops = 0;             // tile GEMMs bound to the tcgen05 body by the last set_ops
     int pf_stages = 0;               // L2 prefetch distance of the producer warp, in ring stages (0 = off)
 };
 
@@ -191,6 +205,54 @@ static int cuda_fail(cudaError_t e, const char* what) {
         cudaError_t e_ = (call);                             \
         if (e_ != cudaSuccess) return cuda_fail(e_, #call);  \
     } while (0)
+
+// Tensor map over a row-major bf16 matrix {cols, rows} with row pitch `ld` elements: boxes of 64
+// columns x 128 rows, stored with the 128-byte swizzle (the operand tile layout of the tcgen05 tile
+// GEMM), rows outside the matrix read as zero.  The driver entry point is looked up once; false
+// when it is missing or refuses the arguments (the kernel then runs its mma.sync body).
+static bool encode_tile_map(void* out, uint64_t base, long long rows, long long cols, long long ld, bool streamed) {
+    typedef CUresult (*encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static encode_fn fn = nullptr;
+    static bool looked = false;
+    if (!looked) {
+        looked = true;
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<encode_fn>(ptr);
+        (void)cudaGetLastError();
+    }
+    if (!fn || (base & 15) || (ld % 8) || rows <= 0 || cols < 64 || ld < cols) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    const cuuint32_t box[2] = {64, 128};
+    const cuuint32_t estr[2] = {1, 1};
+    alignas(64) CUtensorMap m;
+    if (fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, reinterpret_cast<void*>(base), dims, strides, box, estr,
+           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+           streamed ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;
+    memcpy(out, &m, sizeof(m));
+    return true;
+}
+
+// Can the tcgen05 body run this tile GEMM?  K range of an instruction in whole 64-element k-tiles,
+// and every operand the epilogue touches with 16-byte vectors aligned for them.
+static bool tile_gemm_on_tcgen05(const mk_op_desc& d) {
+    const int N = d.i[1], K = d.i[2], splits = d.i[4], odt = d.i[5], rdt = d.i[7], swi = d.i[8];
+    if (splits <= 0 || K % splits || (K / splits) % 64) return false;
+    const int n_out = swi ? N / 2 : N;
+    if (n_out % 8 || (swi && N % 128)) return false;
+    auto vec_ok = [](uint64_t ptr, int ld, int dt) { return !(ptr & 15) && ld % (dt == 1 ? 4 : 8) == 0; };
+    if (!vec_ok(d.ptr[2], d.ld[2], odt)) return false;
+    if (d.ptr[3] && (d.ptr[3] & 15)) return false;
+    if (d.ptr[4] && !vec_ok(d.ptr[4], d.ld[4], rdt)) return false;
+    return true;
+}
 
 extern "C" {
 
@@ -258,6 +320,8 @@ int mk_program_create(int device, const int32_t* insts, int n_insts, const int32
     MK_TRY(cudaMemset(p->d_counters, 0, (size_t)p->n_counters * 4));
     MK_TRY(cudaMalloc(&p->d_ops, (size_t)n_ops * sizeof(mk_op_desc)));
     MK_TRY(cudaMallocHost(&p->h_ops, (size_t)n_ops * sizeof(mk_op_desc)));
+    MK_TRY(cudaMalloc(&p->d_tmaps, (size_t)n_ops * 256));
+    MK_TRY(cudaMallocHost(&p->h_tmaps, (size_t)n_ops * 256));
     MK_TRY(cudaMalloc(&p->d_status, MK_ST_WORDS * 4));
     MK_TRY(cudaMemset(p->d_status, 0, MK_ST_WORDS * 4));
     MK_TRY(cudaMallocHost(&p->h_status, MK_ST_WORDS * 4));
@@ -280,6 +344,26 @@ int mk_program_set_ops(mk_program* p, const mk_op_desc* ops, int n_ops, void* st
     // the staging copy may still be in flight from an earlier rebind on this stream
     MK_CUDA(cudaStreamSynchronize(st));
     memcpy(p->h_ops, ops, (size_t)n_ops * sizeof(mk_op_desc));
+    // Tile GEMMs get tensor maps over their activations and weights (ptr 11): with them the kernel
+    // runs the tcgen05 body and streams the weight tiles through the producer warp's ring.
+    bool any_map = false;
+    int n_tc = 0;
+    const bool tc_off = getenv("MEGACUTE_B200_NO_TCGEN05") != nullptr;
+    for (int k = 0; k < n_ops; ++k) {
+        mk_op_desc& d = p->h_ops[k];
+        if (d.kind != MK_OP_GEMM) continue;
+        d.ptr[11] = 0;
+        if (tc_off || !tile_gemm_on_tcgen05(d)) continue;
+        uint8_t* maps = p->h_tmaps + (size_t)k * 256;
+        if (encode_tile_map(maps, d.ptr[0], d.i[0], d.i[2], d.ld[0], false) &&
+            encode_tile_map(maps + 128, d.ptr[1], d.i[1], d.i[2], d.ld[1], true)) {
+            d.ptr[11] = reinterpret_cast<uint64_t>(p->d_tmaps + (size_t)k * 256);
+            any_map = true;
+            ++n_tc;
+        }
+    }
+    p->tcgen05_ops = n_tc;
+    if (any_map) MK_CUDA(cudaMemcpyAsync(p->d_tmaps, p->h_tmaps, (size_t)n_ops * 256, cudaMemcpyHostToDevice, st));
     MK_CUDA(cudaMemcpyAsync(p->d_ops, p->h_ops, (size_t)n_ops * sizeof(mk_op_desc), cudaMemcpyHostToDevice, st));
     return MK_OK;
 }
@@ -343,6 +427,8 @@ int mk_program_reset(mk_program* p, void* stream) {
 
 int mk_program_epoch(mk_program* p) { return p ? p->epoch : MK_E_ARG; }
 
+int mk_program_tcgen05_ops(mk_program* p) { return p ? p->tcgen05_ops : MK_E_ARG; }
+
 int mk_program_read_counters(mk_program* p, int32_t* out, int n) {
     if (!p || !out || n < 0 || n > p->n_counters) return MK_E_ARG;
     MK_CUDA(cudaMemcpy(out, p->d_counters, (size_t)n * 4, cudaMemcpyDeviceToHost));
@@ -373,8 +459,9 @@ int mk_program_poke_wait(mk_program* p, int wait_index, int counter, int target)
 void mk_program_destroy(mk_program* p) {
     if (!p) return;
     cudaFree(p->d_insts); cudaFree(p->d_waits); cudaFree(p->d_arrives); cudaFree(p->d_counters);
-    cudaFree(p->d_ops); cudaFree(p->d_trace); cudaFree(p->d_status);
+    cudaFree(p->d_ops); cudaFree(p->d_trace); cudaFree(p->d_status); cudaFree(p->d_tmaps);
     if (p->h_ops) cudaFreeHost(p->h_ops);
+    if (p->h_tmaps) cudaFreeHost(p->h_tmaps);
     if (p->h_status) cudaFreeHost(p->h_status);
     delete p;
 }

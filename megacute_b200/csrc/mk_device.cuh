@@ -35,6 +35,18 @@ constexpr int kWorkBytes = 96 * 1024;                     // scratch of the inst
 constexpr int kXbufBytes = 64 * 1024;                     // GEMV: fp32 activation rows (front of work)
 constexpr int kCtrlBytes = 2048;                          // mbarriers, flags, staged instruction metadata
 constexpr int kSmemBytes = kRingBytes + kWorkBytes + kCtrlBytes;
+// tcgen05 tile GEMM (op_gemm_tc.cuh): operand tiles are 128 rows x 64 bf16 with the 128-byte swizzle
+// and must start on 1024-byte boundaries.  Weight tiles travel through the ring (slot 0 holds four,
+// slot 1 three: each lies inside the bytes the streaming linear uses for the same slot, so the two
+// kinds of instruction can follow one another); activation tiles use the work area.
+constexpr int kTcTileBytes = 128 * 128;
+constexpr int kTcXStages = 5;
+constexpr int kTcXOff = 512;                              // first 1024-aligned byte of the work area
+constexpr int kTcSlot1Off = 65 * 1024;
+static_assert((kRingBytes + kTcXOff) % 1024 == 0 && kTcXOff + kTcXStages * kTcTileBytes <= kWorkBytes, "activation tiles");
+static_assert(4 * kTcTileBytes <= kStageBytes && kTcSlot1Off >= kStageBytes && kTcSlot1Off + 3 * kTcTileBytes <= kRingBytes, "weight tiles");
+__host__ __device__ constexpr int tc_slot_off(int stage) { return stage == 0 ? 0 : kTcSlot1Off; }
+__host__ __device__ constexpr int tc_slot_tiles(int stage) { return stage == 0 ? 4 : 3; }
 
 struct Params {
     const int4* insts;            // [n_insts][4]
@@ -73,6 +85,12 @@ struct Ctrl {                     // lives in the last kCtrlBytes of shared memo
     unsigned long long slot_free[4];  // ... the finisher warp has read them
     unsigned long long epi_done;      // ... the finisher has issued the instruction's last stores (its arrivals follow)
     unsigned long long deps_met;      // ... the compute warps have seen the instruction's dependencies met
+    unsigned long long x_full[kTcXStages];   // tcgen05 tile GEMM: an activation k-tile has landed in the work area
+    unsigned long long x_empty[kTcXStages];  // ... the MMAs that read it have completed
+    unsigned long long acc_full;      // ... every MMA of the instruction has completed: the accumulator can be read
+    uint32_t tmem_base;               // ... tensor-memory address of the accumulator (written by tcgen05.alloc)
+    uint32_t x_loads, x_mmas;         // ... activation k-tiles requested / consumed since the launch began (ring positions)
+    uint32_t acc_uses;                // ... instructions that have used acc_full (its parity)
     int abort;                    // set once a wait of this CTA gave up or saw the global abort
     int flag;                     // scratch broadcast word (split-KV last arriver)
     long long t_dep;              // tracing: when the dependencies of the current instruction were met
@@ -131,6 +149,17 @@ __device__ __forceinline__ void bulk_g2s_hint(void* dst, const void* src, uint32
         "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(
             smem_u32(dst)),
         "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
+        : "memory");
+}
+// 2-D tiled bulk tensor copy global -> shared through a tensor map (no multicast), with an L2
+// eviction policy.  x is the innermost coordinate in elements; x times the element size must be a
+// multiple of 16 bytes.
+__device__ __forceinline__ void tma_load_2d(void* dst, const void* tmap, int x, int y, unsigned long long* bar,
+                                            unsigned long long policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;" ::"r"(
+            smem_u32(dst)),
+        "l"(tmap), "r"(x), "r"(y), "r"(smem_u32(bar)), "l"(policy)
         : "memory");
 }
 __device__ __forceinline__ void bulk_prefetch_l2(const void* src, uint32_t bytes) {

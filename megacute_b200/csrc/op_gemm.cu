@@ -1,15 +1,26 @@
 // Translation unit of MK_OP_GEMM.
 #include "op_gemm.cuh"
+#include "op_gemm_tc.cuh"
 #include "ops.cuh"
 
 namespace mk {
-__device__ void mk_op_gemm(const mk_op_desc* op, int a0, int a1, int a2) {
+__device__ int mk_op_gemm(const Params& p, const mk_op_desc* op, int a0, int a1, int a2, int seq, int packed_pos) {
+    const SmemMap m = smem_map();
+    if (op->ptr[11]) {
+        // the host library attached tensor maps: tcgen05 body, weights through the producer's ring
+        RingPos pos;
+        pos.stage = packed_pos & 0xff;
+        pos.phase = (uint32_t)(packed_pos >> 8) & 1u;
+        const int np = op_gemm_tc(p, m.ctrl, m.ring, m.work, op, a0, a1, a2, seq, pos);
+        return np < 0 ? -1 : np | (packed_pos & ~0x1ff);
+    }
     // ops with at most 64 activation rows have a single m tile: hold 64 rows and stream deeper
     if (op->i[0] <= 64) {
-        if ((op->i[2] / op->i[4]) % 64 == 0) op_gemm<64, 64, 3>(op, a0, a1, a2, smem_map().work);
-        else op_gemm<64, 32, 6>(op, a0, a1, a2, smem_map().work);
+        if ((op->i[2] / op->i[4]) % 64 == 0) op_gemm<64, 64, 3>(op, a0, a1, a2, m.work);
+        else op_gemm<64, 32, 6>(op, a0, a1, a2, m.work);
     } else {
-        op_gemm<128, 32, 4>(op, a0, a1, a2, smem_map().work);
+        op_gemm<128, 32, 4>(op, a0, a1, a2, m.work);
     }
+    return packed_pos;
 }
 }  // namespace mk

@@ -1,0 +1,241 @@
+// MK_OP_GEMM on the 5th-generation tensor cores (tcgen05 + tensor memory), compute-warp side.
+//   out[128 x 128 tile] = act(x @ w^T + bias) + residual        (one instruction per output tile)
+//   ws += x[:, Kj] @ w[:, Kj]^T                                  (split-K partial: reduce-add)
+// Same instructions, descriptor and epilogue semantics as the mma.sync body (op_gemm.cuh); the host
+// library selects this body by putting the address of two tensor maps in ptr 11 (activations, then
+// weights 128 bytes further: {K, rows} bf16, box {64, 128}, 128-byte swizzle, zero fill).
+//
+// Operands are K-major 128-row x 64-column tiles (16 KB).  The 128 activation rows of the m tile are
+// the MMA's M side, so an accumulator row (a tensor-memory lane) is an activation row and a thread of
+// the epilogue holds whole output rows: swiglu (gate columns 0..63, up columns 64..127 of the weight
+// tile) pairs values of one thread.  Rows beyond M are zero-filled by the copy and never stored.
+//   weights      producer warp -> ring slots (4 or 3 k-tiles per slot), across instruction boundaries:
+//                they depend on nothing in the launch, so the next instruction's first 112 KB are
+//                already on their way while this one waits for its dependencies
+//   activations  one compute thread -> kTcXStages single-tile stages in the work area, after the
+//                instruction's dependencies are met
+//   MMA          one compute thread: 4 x tcgen05.mma (128 x 128 x 16) per k-tile; tcgen05.commit
+//                returns the activation stage and the ring slot when the MMAs that read them are done
+//   epilogue     all 8 compute warps: warp w reads lanes 32 (w & 3) .. +31, column half w >> 2
+// Every wait is bounded (wait_barrier); tensor memory is allocated and freed inside the instruction,
+// on every path.
+#pragma once
+#include "mk_device.cuh"
+#include "op_gemv_common.cuh"
+
+namespace mk {
+
+constexpr int kTcCols = 128;                                // fp32 accumulator columns in tensor memory
+// instruction descriptor, kind::f16: D = f32, A = B = bf16, both K-major, N = 128, M = 128
+constexpr uint32_t kTcIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+
+// shared-memory matrix descriptor of a K-major tile with the 128-byte swizzle: start address,
+// leading byte offset 16 (unused by swizzled K-major layouts), 1024 bytes between 8-row groups,
+// descriptor version 1, layout type 2 (128-byte swizzle).  Advancing 16 K-elements inside the
+// swizzle atom adds 32 bytes to the start address.
+__device__ __forceinline__ uint64_t tc_smem_desc(uint32_t saddr) {
+    return (uint64_t)((saddr & 0x3ffffu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+    asm volatile(
+        "{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p; }" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(kTcIdesc), "r"(accumulate)
+        : "memory");
+}
+// arrives on the mbarrier once every tcgen05.mma this thread has issued so far has completed
+__device__ __forceinline__ void tc_commit(unsigned long long* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// 32 consecutive fp32 columns of this thread's lane (warp-wide, lanes 32 (warp & 3) .. +31)
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, float* v) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, "
+        "%18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n\t"
+        "tcgen05.wait::ld.sync.aligned;"          // in the same statement: no use of the registers can move above it
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+}
+
+// 32 consecutive output columns [col0, col0 + 32) of activation row r: bias, activation, residual,
+// store -- or, for a split-K partial, reduce-add into the workspace.
+__device__ __forceinline__ void tc_store32(const mk_op_desc* op, const float* v, int r, int col0, int n_out, bool plain) {
+    const int act = op->i[3], odt = op->i[5], accum = op->i[6], rdt = op->i[7];
+    void* O = reinterpret_cast<void*>(op->ptr[2]);
+    const void* bias = reinterpret_cast<const void*>(op->ptr[3]);
+    const void* R = reinterpret_cast<const void*>(op->ptr[4]);
+    const long long eo = (long long)r * op->ld[2], er = (long long)r * op->ld[4];
+#pragma unroll
+    for (int g8 = 0; g8 < 4; ++g8) {
+        const int col = col0 + g8 * 8;
+        if (col >= n_out) break;
+        float f[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] = v[g8 * 8 + j];
+        if (accum) {
+#pragma unroll
+            for (int j = 0; j < 8; j += 2) {
+                if (col + j >= n_out) break;
+                if (odt == 1) red_add_f32x2(reinterpret_cast<float*>(O) + eo + col + j, f[j], f[j + 1]);
+                else red_add_bf16x2(reinterpret_cast<__nv_bfloat16*>(O) + eo + col + j, f[j], f[j + 1]);
+            }
+            continue;
+        }
+        if (col + 8 <= n_out) {
+            if (plain) {
+                if (bias) {
+                    float b[8];
+                    load8(bias, col, 0, b);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) f[j] += b[j];
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) f[j] = apply_act(act, f[j]);
+                if (R) {
+                    float q[8];
+                    load8(R, er + col, rdt, q);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) f[j] += q[j];
+                }
+            }
+            store8(O, eo + col, odt, f);
+        } else {
+            for (int j = 0; j < 8 && col + j < n_out; ++j) {
+                float y = f[j];
+                if (plain) {
+                    if (bias) y += load1(bias, col + j, 0);
+                    y = apply_act(act, y);
+                    if (R) y += load1(R, er + col + j, rdt);
+                }
+                store1(O, eo + col + j, odt, y);
+            }
+        }
+    }
+}
+
+// All compute threads call this after the instruction's dependencies are met.  Returns the ring
+// position behind the instruction's last slot (stage | phase << 8), or -1 when the CTA is aborting.
+__device__ __forceinline__ int op_gemm_tc(const Params& p, Ctrl* c, uint8_t* ring, uint8_t* work, const mk_op_desc* op, int a0,
+                                          int a1, int a2, int seq, RingPos pos) {
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const int M = op->i[0], N = op->i[1], K = op->i[2], splits = op->i[4];
+    const int accum = op->i[6], swi = op->i[8];
+    const int m0 = a0 * 128, n0 = a1 * 128;
+    const int kc = K / splits, kbeg = a2 * kc, nk = kc / 64;
+    const uint8_t* tmaps = reinterpret_cast<const uint8_t*>(op->ptr[11]);
+    uint8_t* xs = work + kTcXOff;
+
+    // earlier instructions wrote the work area through the generic proxy; the bulk copies below
+    // write it through the asynchronous one (and read activations other SMs stored with plain stores)
+    asm volatile("fence.proxy.async;" ::: "memory");
+    // (the permit to allocate is never relinquished: every tile GEMM instruction of the CTA allocates again)
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&c->tmem_base)), "r"(kTcCols)
+                     : "memory");
+    }
+    tc_fence_before();
+    compute_sync();
+    tc_fence_after();
+    const uint32_t tmem = *(volatile uint32_t*)&c->tmem_base;
+    const uint32_t apar = *(volatile uint32_t*)&c->acc_uses & 1u;
+
+    // where the ring stands after this instruction: the same walk the producer and the MMA thread do
+    RingPos end = pos;
+    for (int kt = 0; kt < nk; end.advance()) kt += min(tc_slot_tiles(end.stage), nk - kt);
+
+    if (warp == 2 && lane == 0) {
+        // ---- activation tiles: {64 K-elements, 128 rows} at (kbeg + 64 kt, m0) ----
+        unsigned long long keep;
+        asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(keep));
+        uint32_t n = c->x_loads;
+        for (int kt = 0; kt < nk; ++kt, ++n) {
+            const int s = n % kTcXStages;
+            const uint32_t par = (n / kTcXStages) & 1u;
+            if (!wait_barrier(p, c, &c->x_empty[s], par ^ 1u, seq, WHERE_RING_EMPTY)) break;
+            mbar_arrive_expect_tx(&c->x_full[s], kTcTileBytes);
+            tma_load_2d(xs + s * kTcTileBytes, tmaps, kbeg + kt * 64, m0, &c->x_full[s], keep);
+        }
+        c->x_loads = n;
+    } else if (warp == 3 && lane == 0) {
+        // ---- MMAs: accumulator[128 activation rows][128 weight rows] += x tile . w tile^T ----
+        uint32_t n = c->x_mmas, acc = 0;
+        bool ok = true;
+        RingPos q = pos;
+        for (int kt = 0; kt < nk && ok; q.advance()) {
+            const int cnt = min(tc_slot_tiles(q.stage), nk - kt);
+            ok = wait_barrier(p, c, &c->full[q.stage], q.phase, seq, WHERE_RING_FULL);
+            const uint32_t wbase = smem_u32(ring + tc_slot_off(q.stage));
+            for (int j = 0; j < cnt && ok; ++j, ++n) {
+                const int s = n % kTcXStages;
+                ok = wait_barrier(p, c, &c->x_full[s], (n / kTcXStages) & 1u, seq, WHERE_RING_FULL);
+                if (!ok) break;
+                tc_fence_after();
+                const uint64_t ad = tc_smem_desc(smem_u32(xs + s * kTcTileBytes)), bd = tc_smem_desc(wbase + j * kTcTileBytes);
+#pragma unroll
+                for (int k16 = 0; k16 < 4; ++k16) {
+                    tc_mma(tmem, ad + 2 * k16, bd + 2 * k16, acc);
+                    acc = 1;
+                }
+                tc_commit(&c->x_empty[s]);
+            }
+            if (ok) {
+                // the slot's barrier counts one arrival per compute warp (the streaming linear's
+                // convention): seven plain ones now, the eighth when the MMAs have read the slot
+#pragma unroll
+                for (int w = 0; w < kComputeWarps - 1; ++w) mbar_arrive(&c->empty[q.stage]);
+                tc_commit(&c->empty[q.stage]);
+            }
+            kt += cnt;
+        }
+        c->x_mmas = n;
+        tc_commit(&c->acc_full);
+    }
+    __syncwarp();
+
+    // ---- epilogue: warp w owns lanes 32 (w & 3) .. +31 (activation rows) and column half w >> 2 ----
+    int ok = 1;
+    if (lane == 0) ok = wait_barrier(p, c, &c->acc_full, apar, seq, WHERE_COMBINE) ? 1 : 0;
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    tc_fence_after();
+    const int qd = warp & 3, h = warp >> 2;
+    const int r = m0 + qd * 32 + lane;
+    if (ok && m0 + qd * 32 < M) {
+        const uint32_t tl = tmem + ((uint32_t)(qd * 32) << 16);
+        float v[32];
+        if (swi) {
+            // gate columns 32 h .. +31 and the up columns 64 further of the same outputs
+            if (a1 * 64 + h * 32 < N / 2) {
+                float u[32];
+                tc_ld32(tl + h * 32, v);
+                tc_ld32(tl + 64 + h * 32, u);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = v[j] * sigmoidf_(v[j]) * u[j];
+                if (r < M) tc_store32(op, v, r, a1 * 64 + h * 32, N / 2, false);
+            }
+        } else {
+#pragma unroll 1
+            for (int ch = 0; ch < 2; ++ch) {
+                const int tcol = h * 64 + ch * 32;
+                if (n0 + tcol >= N) break;
+                tc_ld32(tl + tcol, v);
+                if (r < M) tc_store32(op, v, r, n0 + tcol, N, !accum);
+            }
+        }
+    }
+    tc_fence_before();
+    const bool aborting = compute_sync_or(!ok || *(volatile int*)&c->abort);
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTcCols) : "memory");
+    if (t == 0) c->acc_uses = c->acc_uses + 1;
+    if (aborting) return -1;
+    return end.stage | ((int)end.phase << 8);
+}
+
+}  // namespace mk

@@ -61,6 +61,11 @@ struct StageCursor {
     int o0, o1, K, flags;
     const __nv_bfloat16* w;
     long long ldw;
+    // tile GEMM on the tcgen05 path (op_gemm_tc.cuh): the weight k-tiles [kt, nk) of the instruction
+    // are still to be copied, through the tensor map `wmap`, from coordinates (kbeg + 64 kt, n0)
+    bool gemm;
+    int kt, nk, kbeg, n0;
+    const void* wmap;
 
     // position on the next streaming-linear instruction at or after `idx`
     __device__ __forceinline__ void seek(const Params& p) {
@@ -69,7 +74,15 @@ struct StageCursor {
             const int opi = in.opi - 1;
             if (opi < 0 || opi >= p.n_ops) { idx = p.n_insts; return; }
             const mk_op_desc* op = p.ops + opi;
+            if (op->kind == MK_OP_GEMM && op->ptr[11]) {
+                const int kc = op->i[2] / op->i[4];
+                gemm = true; seq = in.seq; kt = 0; nk = kc / 64; kbeg = in.a2 * kc; n0 = in.a1 * 128;
+                wmap = reinterpret_cast<const uint8_t*>(op->ptr[11]) + 128;
+                if (nk > 0) return;
+                continue;
+            }
             if (op->kind != MK_OP_GEMV) continue;
+            gemm = false;
             seq = in.seq; o0 = in.a0; o1 = in.a1; K = op->i[2]; flags = op->flags;
             w = reinterpret_cast<const __nv_bfloat16*>(op->ptr[1]);
             ldw = op->ld[1];
@@ -89,6 +102,11 @@ struct StageCursor {
     }
     __device__ __forceinline__ bool valid(const Params& p) const { return idx < p.n_insts; }
     __device__ __forceinline__ void advance(const Params& p) {
+        if (gemm) {                                   // (the L2 prefetch cursor: whole instruction at once)
+            idx += gridDim.x;
+            seek(p);
+            return;
+        }
         if (++seg < nseg) return;
         seg = 0;
         if (++g < ngroups) return;
@@ -99,6 +117,7 @@ struct StageCursor {
     __device__ __forceinline__ void piece(int lane, const __nv_bfloat16*& src, int& bytes, int& dst_off) const {
         const bool swi = flags & GEMV_F_SWIGLU;
         src = w; bytes = 0; dst_off = 0;
+        if (gemm) return;
         if (flags & GEMV_F_UNITS) {
             const int r = lane & 15;
             const int o = o0 + (swi ? g >> 1 : g) * 16 + r;
@@ -146,6 +165,23 @@ __device__ __forceinline__ void producer_loop(const Params& p, Ctrl* c, uint8_t*
             int ok = 1;
             if (lane == 0) ok = wait_barrier(p, c, &c->empty[pos.stage], pos.phase ^ 1u, rc.seq, WHERE_RING_EMPTY) ? 1 : 0;
             if (!__shfl_sync(0xffffffffu, ok, 0)) return;
+        }
+        if (rc.gemm) {
+            // tile GEMM: the slot takes the instruction's next 4 (slot 0) or 3 (slot 1) weight k-tiles,
+            // 128 rows x 64 K-elements each, one bulk tensor copy per tile
+            const int cnt = min(tc_slot_tiles(pos.stage), rc.nk - rc.kt);
+            if (lane == 0) {
+                mbar_arrive_expect_tx(&c->full[pos.stage], (uint32_t)(cnt * kTcTileBytes));
+                for (int j = 0; j < cnt; ++j)
+                    tma_load_2d(ring + tc_slot_off(pos.stage) + j * kTcTileBytes, rc.wmap, rc.kbeg + (rc.kt + j) * 64, rc.n0,
+                                &c->full[pos.stage], stream_policy);
+            }
+            __syncwarp();
+            rc.kt += cnt;
+            pos.advance();
+            if (rc.kt >= rc.nk) { rc.idx += gridDim.x; rc.seek(p); }
+            if (ahead > 0) --ahead;
+            continue;
         }
         const __nv_bfloat16* src; int bytes, off;
         rc.piece(lane, src, bytes, off);

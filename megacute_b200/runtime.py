@@ -151,6 +151,12 @@ class Program:
         return outs[0] if len(outs) == 1 else tuple(outs)
 
     # ---- status, recovery, introspection
+    @property
+    def tcgen05_ops(self) -> int:
+        """Tile-GEMM ops the library bound to its tcgen05 / bulk-tensor-copy body at the last launch
+        (the rest run the mma.sync body)."""
+        return int(_lib.load().mk_program_tcgen05_ops(self._handle)) if self._handle is not None else 0
+
     def check(self):
         """Synchronise and raise if the kernel reported an error (bounded wait gave up, bad table)."""
         st = (ctypes.c_int32 * _lib.ST_WORDS)()

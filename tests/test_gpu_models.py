@@ -39,6 +39,26 @@ def test_tile_linear(cuda, M, K, N, act, bias, res):
         t["r"] = rnd((M, n_out), 1.0, 5)
     outs, ref, _, _, prog = run_both(g, t, cuda, steps=2)      # twice: split-K workspaces are re-zeroed
     assert_close(outs, ref)
+    # every one of these shapes has whole 64-element k-tiles per instruction and aligned operands:
+    # the library must have bound the tile GEMM ops to its tcgen05 body, not the mma.sync one
+    n_gemm = sum(o.kind in ("Linear", "LinearSplit") for o in prog.g.ops)
+    assert prog.tcgen05_ops == n_gemm >= 1
+
+
+def test_tile_linear_both_bodies_agree(cuda, monkeypatch):
+    """The mma.sync body (MEGACUTE_B200_NO_TCGEN05) and the tcgen05 body give the same result up to
+    the order of fp32 accumulation."""
+    g = mc.Graph()
+    y = g.linear(g.input("x", (96, 1024)), g.param("w", (640, 1024)), act="gelu_tanh")
+    g.output(y)
+    t = {"x": rnd((96, 1024), 1.0, 1), "w": rnd((640, 1024), 0.03, 2)}
+    outs_tc, ref, _, _, prog_tc = run_both(g, t, cuda)
+    monkeypatch.setenv("MEGACUTE_B200_NO_TCGEN05", "1")
+    outs_mma, _, _, _, prog_mma = run_both(g, t, cuda)
+    assert prog_tc.tcgen05_ops == 1 and prog_mma.tcgen05_ops == 0
+    assert_close(outs_tc, ref)
+    assert_close(outs_mma, ref)
+    assert rel_l2(outs_tc[0], outs_mma[0]) < 2e-3
 
 
 def test_split_k_in_place_residual(cuda):
