@@ -123,6 +123,11 @@ int mk_program_epoch(mk_program* p);
  * bulk-tensor-copied operands (the others, if any, run the mma.sync body: K range per instruction
  * not a multiple of 64, unaligned operands, or MEGACUTE_B200_NO_TCGEN05 set). */
 int mk_program_tcgen05_ops(mk_program* p);
+/* Device memory the program holds for tile-image copies of the weights of those ops (made by
+ * mk_program_set_ops unless MEGACUTE_B200_NO_WEIGHT_PACK is set, freed when another set of
+ * addresses is bound or the program is destroyed).  The copies are snapshots: after changing
+ * weights in place, call mk_program_set_ops again. */
+long long mk_program_packed_bytes(mk_program* p);
 int mk_program_read_counters(mk_program* p, int32_t* out, int n);
 int mk_program_read_trace(mk_program* p, int64_t* out, size_t n_words);
 int mk_program_clear_trace(mk_program* p, void* stream);

@@ -26,6 +26,7 @@ INST_US, SM_GBPS = 2.0, 40.0    # split-K cost model: fixed us per instruction, 
 
 # ---- pointwise / norm / attention tiling
 EW_ROWS, EW_COLS = 32, 512
+FINALIZE_MIN_ROWS, FINALIZE_MIN_INSTS = 4, 96     # SplitFinalize: shorter tiles until the op has this many instructions
 NORM_ROWS = COMPUTE_WARPS       # rows per norm instruction (one per warp); 1 when the op has few rows
 WIDE_NORM_ROWS = 256
 ROPE_APPEND_ROWS = COMPUTE_WARPS

@@ -15,6 +15,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <new>
+#include <vector>
 
 #include "mk_device.cuh"
 #include "op_gemv_common.cuh"
@@ -40,12 +41,14 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
         }
         mbar_init(&c->epi_done, 1);
         mbar_init(&c->deps_met, 1);
-        for (int s = 0; s < kTcXStages; ++s) {
+        for (int s = 0; s < 2 * kTcXStages; ++s) {
             mbar_init(&c->x_full[s], 1);
             mbar_init(&c->x_empty[s], 1);
+            c->x_use_load[s] = c->x_use_mma[s] = 0;
         }
         mbar_init(&c->acc_full, 1);
-        c->x_loads = c->x_mmas = c->acc_uses = 0;
+        c->acc_uses = 0;
+        c->tmem_base = kTcNoTmem;
         c->abort = 0;
         c->flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -142,7 +145,7 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
             if (!self_wait) aborting = publish(p, c, in.narrive, arrive_off) || aborting;
             if (threadIdx.x == 0) {
                 trace_rec<TRACE>(p, 1, slot, in.seq, t0, t1, (long long)globaltimer());
-                if (TRACE && self_wait) trace_rec<TRACE>(p, 2, slot, in.seq, c->t_phase[0], c->t_phase[1], c->t_phase[2]);
+                if (TRACE && (self_wait || op->kind == MK_OP_GEMM)) trace_rec<TRACE>(p, 2, slot, in.seq, c->t_phase[0], c->t_phase[1], c->t_phase[2]);
             }
             if (aborting) break;
         }
@@ -164,6 +167,28 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
         while (globaltimer() - t0 < 200000ull) {}                  // let in-flight copies retire
     }
     __syncthreads();
+    // tensor memory of the tile GEMM (allocated by the CTA's first such instruction) goes back here
+    if (warp == 0 && c->tmem_base != kTcNoTmem)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(c->tmem_base), "r"(kTcCols) : "memory");
+}
+
+// Weight packing for the tcgen05 tile GEMM.  A bulk tensor copy of a 128-row x 64-column tile is 128
+// row requests of 128 bytes, and the copy engine of an SM sustains only ~28 GB/s of such rows
+// (measured: ~4 TB/s over the chip, whatever the depth of the pipeline), where one plain bulk copy of
+// the same bytes runs at the HBM rate.  So the library keeps, per weight matrix, a copy laid out as
+// the shared-memory images of its tiles: tile (n tile j, k tile t) is the 16 KB block j * K/64 + t,
+// row r's 16-byte chunk c at r * 128 + ((c ^ (r & 7)) << 4) -- the 128-byte swizzle a bulk tensor
+// copy would have applied.  Rows beyond N are zero.  One thread moves one 16-byte chunk.
+__global__ void pack_weight_tiles(const __nv_bfloat16* __restrict__ w, long long ld, int N, int K, uint4* __restrict__ out,
+                                  long long chunks) {
+    const int kchunks = K / 8, ktiles = K / 64;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < chunks; i += (long long)gridDim.x * blockDim.x) {
+        const int row = (int)(i / kchunks), kc = (int)(i % kchunks);
+        const int j = row >> 7, r = row & 127, t = kc >> 3, c = kc & 7;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (row < N) v = __ldg(reinterpret_cast<const uint4*>(w + (long long)row * ld + (long long)kc * 8));
+        out[((long long)j * ktiles + t) * (kTcTileBytes / 16) + r * 8 + (c ^ (r & 7))] = v;
+    }
 }
 
 }  // namespace mk
@@ -184,6 +209,11 @@ struct mk_program {
     mk_op_desc* h_ops = nullptr;     // pinned staging copy
     uint8_t* d_tmaps = nullptr;      // per op: two 128-byte tensor maps (tile GEMM: activations, weights)
     uint8_t* h_tmaps = nullptr;      // pinned staging copy
+    struct Packed {                  // tile-image copy of one weight matrix (see pack_weight_tiles)
+        uint64_t src; int N, K, ld;
+        uint8_t* buf; size_t bytes; bool used;
+    };
+    std::vector<Packed> packed;
     int64_t* d_trace = nullptr;
     int32_t* d_status = nullptr;
     int32_t* h_status = nullptr;     // pinned
@@ -207,10 +237,10 @@ static int cuda_fail(cudaError_t e, const char* what) {
     } while (0)
 
 // Tensor map over a row-major bf16 matrix {cols, rows} with row pitch `ld` elements: boxes of 64
-// columns x 128 rows, stored with the 128-byte swizzle (the operand tile layout of the tcgen05 tile
+// columns x `box_rows` rows, stored with the 128-byte swizzle (the operand tile layout of the tcgen05 tile
 // GEMM), rows outside the matrix read as zero.  The driver entry point is looked up once; false
 // when it is missing or refuses the arguments (the kernel then runs its mma.sync body).
-static bool encode_tile_map(void* out, uint64_t base, long long rows, long long cols, long long ld, bool streamed) {
+static bool encode_tile_map(void* out, uint64_t base, long long rows, long long cols, long long ld, int box_rows, bool streamed) {
     typedef CUresult (*encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -228,7 +258,7 @@ static bool encode_tile_map(void* out, uint64_t base, long long rows, long long 
     if (!fn || (base & 15) || (ld % 8) || rows <= 0 || cols < 64 || ld < cols) return false;
     const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
     const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    const cuuint32_t box[2] = {64, 128};
+    const cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
     const cuuint32_t estr[2] = {1, 1};
     alignas(64) CUtensorMap m;
     if (fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, reinterpret_cast<void*>(base), dims, strides, box, estr,
@@ -349,20 +379,58 @@ int mk_program_set_ops(mk_program* p, const mk_op_desc* ops, int n_ops, void* st
     bool any_map = false;
     int n_tc = 0;
     const bool tc_off = getenv("MEGACUTE_B200_NO_TCGEN05") != nullptr;
+    const bool pack_off = getenv("MEGACUTE_B200_NO_WEIGHT_PACK") != nullptr;
+    for (auto& e : p->packed) e.used = false;
     for (int k = 0; k < n_ops; ++k) {
         mk_op_desc& d = p->h_ops[k];
         if (d.kind != MK_OP_GEMM) continue;
         d.ptr[11] = 0;
         if (tc_off || !tile_gemm_on_tcgen05(d)) continue;
         uint8_t* maps = p->h_tmaps + (size_t)k * 256;
-        if (encode_tile_map(maps, d.ptr[0], d.i[0], d.i[2], d.ld[0], false) &&
-            encode_tile_map(maps + 128, d.ptr[1], d.i[1], d.i[2], d.ld[1], true)) {
+        d.ptr[10] = 0;
+        if (!encode_tile_map(maps, d.ptr[0], d.i[0], d.i[2], d.ld[0], d.i[0] <= 64 ? 64 : 128, false)) continue;
+        // weights: the packed copy (taken again at every call of this function: the snapshot follows
+        // a rebind; weights changed in place need another call), else a tensor map over the matrix
+        if (!pack_off && !(d.ptr[1] & 15) && d.ld[1] % 8 == 0) {
+            mk_program::Packed* hit = nullptr;
+            for (auto& e : p->packed)
+                if (e.src == d.ptr[1] && e.N == d.i[1] && e.K == d.i[2] && e.ld == d.ld[1]) hit = &e;
+            if (!hit) {
+                mk_program::Packed e{d.ptr[1], d.i[1], d.i[2], d.ld[1], nullptr, 0, false};
+                e.bytes = (size_t)((d.i[1] + 127) / 128) * 128 * (size_t)d.i[2] * 2;
+                if (cudaMalloc(&e.buf, e.bytes) == cudaSuccess) {
+                    p->packed.push_back(e);
+                    hit = &p->packed.back();
+                } else {
+                    (void)cudaGetLastError();
+                }
+            }
+            if (hit) {
+                if (!hit->used) {
+                    const long long chunks = (long long)(hit->bytes / 16);
+                    const int blocks = (int)((chunks + 255) / 256 < 4096 ? (chunks + 255) / 256 : 4096);
+                    mk::pack_weight_tiles<<<blocks, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(hit->src), hit->ld, hit->N,
+                                                                  hit->K, reinterpret_cast<uint4*>(hit->buf), chunks);
+                    MK_CUDA(cudaGetLastError());
+                    hit->used = true;
+                }
+                d.ptr[10] = reinterpret_cast<uint64_t>(hit->buf);
+            }
+        }
+        if (d.ptr[10] || encode_tile_map(maps + 128, d.ptr[1], d.i[1], d.i[2], d.ld[1], 128, true)) {
             d.ptr[11] = reinterpret_cast<uint64_t>(p->d_tmaps + (size_t)k * 256);
             any_map = true;
             ++n_tc;
         }
     }
     p->tcgen05_ops = n_tc;
+    // packed copies of matrices that are no longer bound (the stream was synchronised above, so no
+    // launch is still reading them)
+    for (size_t e = 0; e < p->packed.size();) {
+        if (p->packed[e].used) { ++e; continue; }
+        cudaFree(p->packed[e].buf);
+        p->packed.erase(p->packed.begin() + e);
+    }
     if (any_map) MK_CUDA(cudaMemcpyAsync(p->d_tmaps, p->h_tmaps, (size_t)n_ops * 256, cudaMemcpyHostToDevice, st));
     MK_CUDA(cudaMemcpyAsync(p->d_ops, p->h_ops, (size_t)n_ops * sizeof(mk_op_desc), cudaMemcpyHostToDevice, st));
     return MK_OK;
@@ -429,6 +497,13 @@ int mk_program_epoch(mk_program* p) { return p ? p->epoch : MK_E_ARG; }
 
 int mk_program_tcgen05_ops(mk_program* p) { return p ? p->tcgen05_ops : MK_E_ARG; }
 
+long long mk_program_packed_bytes(mk_program* p) {
+    if (!p) return MK_E_ARG;
+    long long total = 0;
+    for (auto& e : p->packed) total += (long long)e.bytes;
+    return total;
+}
+
 int mk_program_read_counters(mk_program* p, int32_t* out, int n) {
     if (!p || !out || n < 0 || n > p->n_counters) return MK_E_ARG;
     MK_CUDA(cudaMemcpy(out, p->d_counters, (size_t)n * 4, cudaMemcpyDeviceToHost));
@@ -460,6 +535,7 @@ void mk_program_destroy(mk_program* p) {
     if (!p) return;
     cudaFree(p->d_insts); cudaFree(p->d_waits); cudaFree(p->d_arrives); cudaFree(p->d_counters);
     cudaFree(p->d_ops); cudaFree(p->d_trace); cudaFree(p->d_status); cudaFree(p->d_tmaps);
+    for (auto& e : p->packed) cudaFree(e.buf);
     if (p->h_ops) cudaFreeHost(p->h_ops);
     if (p->h_tmaps) cudaFreeHost(p->h_tmaps);
     if (p->h_status) cudaFreeHost(p->h_status);

@@ -43,7 +43,9 @@ constexpr int kTcTileBytes = 128 * 128;
 constexpr int kTcXStages = 5;
 constexpr int kTcXOff = 512;                              // first 1024-aligned byte of the work area
 constexpr int kTcSlot1Off = 65 * 1024;
-static_assert((kRingBytes + kTcXOff) % 1024 == 0 && kTcXOff + kTcXStages * kTcTileBytes <= kWorkBytes, "activation tiles");
+constexpr int kTcCols = 128;                              // fp32 accumulator columns in tensor memory
+constexpr uint32_t kTcNoTmem = 0xffffffffu;               // Ctrl::tmem_base before the CTA's first allocation
+static_assert((kRingBytes + kTcXOff) % 1024 == 0 && kTcXOff + kTcXStages * kTcTileBytes + kTcTileBytes / 2 <= kWorkBytes, "activation tiles");
 static_assert(4 * kTcTileBytes <= kStageBytes && kTcSlot1Off >= kStageBytes && kTcSlot1Off + 3 * kTcTileBytes <= kRingBytes, "weight tiles");
 __host__ __device__ constexpr int tc_slot_off(int stage) { return stage == 0 ? 0 : kTcSlot1Off; }
 __host__ __device__ constexpr int tc_slot_tiles(int stage) { return stage == 0 ? 4 : 3; }
@@ -85,17 +87,19 @@ struct Ctrl {                     // lives in the last kCtrlBytes of shared memo
     unsigned long long slot_free[4];  // ... the finisher warp has read them
     unsigned long long epi_done;      // ... the finisher has issued the instruction's last stores (its arrivals follow)
     unsigned long long deps_met;      // ... the compute warps have seen the instruction's dependencies met
-    unsigned long long x_full[kTcXStages];   // tcgen05 tile GEMM: an activation k-tile has landed in the work area
-    unsigned long long x_empty[kTcXStages];  // ... the MMAs that read it have completed
+    unsigned long long x_full[2 * kTcXStages];   // tcgen05 tile GEMM: an activation k-tile has landed in the work area
+    unsigned long long x_empty[2 * kTcXStages];  // ... the MMAs that read it have completed
     unsigned long long acc_full;      // ... every MMA of the instruction has completed: the accumulator can be read
     uint32_t tmem_base;               // ... tensor-memory address of the accumulator (written by tcgen05.alloc)
-    uint32_t x_loads, x_mmas;         // ... activation k-tiles requested / consumed since the launch began (ring positions)
+    uint8_t x_use_load[2 * kTcXStages];   // ... how often each stage has been filled / consumed since the launch
+    uint8_t x_use_mma[2 * kTcXStages];    //     began (the parities of x_empty / x_full)
     uint32_t acc_uses;                // ... instructions that have used acc_full (its parity)
     int abort;                    // set once a wait of this CTA gave up or saw the global abort
     int flag;                     // scratch broadcast word (split-KV last arriver)
     long long t_dep;              // tracing: when the dependencies of the current instruction were met
     long long t_phase[3];         // tracing: op-internal phase marks (role 2 records)
 };
+static_assert(sizeof(Ctrl) <= kCtrlBytes, "Ctrl outgrew its shared-memory slot");
 constexpr int kTraceRoles = 3;    // 0 producer, 1 compute, 2 op-internal phases
 __device__ __forceinline__ void phase_mark(const Params& p, Ctrl* c, int k);
 

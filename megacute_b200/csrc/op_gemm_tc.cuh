@@ -3,7 +3,9 @@
 //   ws += x[:, Kj] @ w[:, Kj]^T                                  (split-K partial: reduce-add)
 // Same instructions, descriptor and epilogue semantics as the mma.sync body (op_gemm.cuh); the host
 // library selects this body by putting the address of two tensor maps in ptr 11 (activations, then
-// weights 128 bytes further: {K, rows} bf16, box {64, 128}, 128-byte swizzle, zero fill).
+// weights 128 bytes further: {K, rows} bf16, 128-byte swizzle, zero fill; boxes of 64 columns x 128
+// rows, or x 64 rows for the activations of an op with at most 64 of them) and, when it has packed
+// the weights into tile images, the packed array in ptr 10.
 //
 // Operands are K-major 128-row x 64-column tiles (16 KB).  The 128 activation rows of the m tile are
 // the MMA's M side, so an accumulator row (a tensor-memory lane) is an activation row and a thread of
@@ -12,20 +14,20 @@
 //   weights      producer warp -> ring slots (4 or 3 k-tiles per slot), across instruction boundaries:
 //                they depend on nothing in the launch, so the next instruction's first 112 KB are
 //                already on their way while this one waits for its dependencies
-//   activations  one compute thread -> kTcXStages single-tile stages in the work area, after the
-//                instruction's dependencies are met
+//   activations  one compute thread -> single-tile stages in the work area, after the instruction's
+//                dependencies are met: 5 stages of 128 rows, or 10 of 64 rows when the op has at most
+//                64 (the MMA still reads 128 rows: the upper 64 accumulator rows are never looked at)
 //   MMA          one compute thread: 4 x tcgen05.mma (128 x 128 x 16) per k-tile; tcgen05.commit
 //                returns the activation stage and the ring slot when the MMAs that read them are done
 //   epilogue     all 8 compute warps: warp w reads lanes 32 (w & 3) .. +31, column half w >> 2
-// Every wait is bounded (wait_barrier); tensor memory is allocated and freed inside the instruction,
-// on every path.
+// Every wait is bounded (wait_barrier); tensor memory is allocated by the first such instruction of a
+// CTA and freed by the kernel before it exits, on every path.
 #pragma once
 #include "mk_device.cuh"
 #include "op_gemv_common.cuh"
 
 namespace mk {
 
-constexpr int kTcCols = 128;                                // fp32 accumulator columns in tensor memory
 // instruction descriptor, kind::f16: D = f32, A = B = bf16, both K-major, N = 128, M = 128
 constexpr uint32_t kTcIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
 
@@ -132,41 +134,50 @@ __device__ __forceinline__ int op_gemm_tc(const Params& p, Ctrl* c, uint8_t* rin
     const int kc = K / splits, kbeg = a2 * kc, nk = kc / 64;
     const uint8_t* tmaps = reinterpret_cast<const uint8_t*>(op->ptr[11]);
     uint8_t* xs = work + kTcXOff;
+    // activation stages: whole 128-row tiles, or twice as many 64-row half tiles
+    const int xbytes = M <= 64 ? kTcTileBytes / 2 : kTcTileBytes;
+    const uint32_t xstages = M <= 64 ? 2 * kTcXStages : kTcXStages;
 
-    // earlier instructions wrote the work area through the generic proxy; the bulk copies below
-    // write it through the asynchronous one (and read activations other SMs stored with plain stores)
-    asm volatile("fence.proxy.async;" ::: "memory");
-    // (the permit to allocate is never relinquished: every tile GEMM instruction of the CTA allocates again)
-    if (warp == 0) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&c->tmem_base)), "r"(kTcCols)
-                     : "memory");
+    // Tensor memory is allocated by the CTA's first tile GEMM instruction and kept until the kernel
+    // ends (the kernel frees it on every path); the permit to allocate is never relinquished.
+    // (the test is on a word that only changes behind a barrier, so every thread takes the same branch)
+    const uint32_t uses = *(volatile uint32_t*)&c->acc_uses;
+    if (uses == 0) {
+        if (warp == 0)
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&c->tmem_base)), "r"(kTcCols)
+                         : "memory");
+        tc_fence_before();
+        compute_sync();
+        tc_fence_after();
     }
-    tc_fence_before();
-    compute_sync();
-    tc_fence_after();
     const uint32_t tmem = *(volatile uint32_t*)&c->tmem_base;
-    const uint32_t apar = *(volatile uint32_t*)&c->acc_uses & 1u;
+    const uint32_t apar = uses & 1u;
 
+    phase_mark(p, c, 0);
     // where the ring stands after this instruction: the same walk the producer and the MMA thread do
     RingPos end = pos;
     for (int kt = 0; kt < nk; end.advance()) kt += min(tc_slot_tiles(end.stage), nk - kt);
 
     if (warp == 2 && lane == 0) {
         // ---- activation tiles: {64 K-elements, 128 rows} at (kbeg + 64 kt, m0) ----
+        // earlier instructions wrote the work area through the generic proxy (all of that is behind
+        // the barrier that ended the dependency wait); the bulk copies below write it through the
+        // asynchronous one, and read activations other SMs stored with plain stores
+        asm volatile("fence.proxy.async;" ::: "memory");
         unsigned long long keep;
         asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(keep));
-        uint32_t n = c->x_loads;
-        for (int kt = 0; kt < nk; ++kt, ++n) {
-            const int s = n % kTcXStages;
-            const uint32_t par = (n / kTcXStages) & 1u;
+        // stage of k-tile kt: kt mod the number of stages; a barrier's parity follows from how often
+        // the stage has been used since the launch began (ops with 5 and with 10 stages may alternate)
+        for (int kt = 0; kt < nk; ++kt) {
+            const int s = kt % xstages;
+            const uint32_t par = c->x_use_load[s]++ & 1u;
             if (!wait_barrier(p, c, &c->x_empty[s], par ^ 1u, seq, WHERE_RING_EMPTY)) break;
-            mbar_arrive_expect_tx(&c->x_full[s], kTcTileBytes);
-            tma_load_2d(xs + s * kTcTileBytes, tmaps, kbeg + kt * 64, m0, &c->x_full[s], keep);
+            mbar_arrive_expect_tx(&c->x_full[s], (uint32_t)xbytes);
+            tma_load_2d(xs + s * xbytes, tmaps, kbeg + kt * 64, m0, &c->x_full[s], keep);
         }
-        c->x_loads = n;
     } else if (warp == 3 && lane == 0) {
         // ---- MMAs: accumulator[128 activation rows][128 weight rows] += x tile . w tile^T ----
-        uint32_t n = c->x_mmas, acc = 0;
+        uint32_t n = 0, acc = 0;
         bool ok = true;
         RingPos q = pos;
         for (int kt = 0; kt < nk && ok; q.advance()) {
@@ -174,11 +185,11 @@ __device__ __forceinline__ int op_gemm_tc(const Params& p, Ctrl* c, uint8_t* rin
             ok = wait_barrier(p, c, &c->full[q.stage], q.phase, seq, WHERE_RING_FULL);
             const uint32_t wbase = smem_u32(ring + tc_slot_off(q.stage));
             for (int j = 0; j < cnt && ok; ++j, ++n) {
-                const int s = n % kTcXStages;
-                ok = wait_barrier(p, c, &c->x_full[s], (n / kTcXStages) & 1u, seq, WHERE_RING_FULL);
+                const int s = n % xstages;
+                ok = wait_barrier(p, c, &c->x_full[s], c->x_use_mma[s]++ & 1u, seq, WHERE_RING_FULL);
                 if (!ok) break;
                 tc_fence_after();
-                const uint64_t ad = tc_smem_desc(smem_u32(xs + s * kTcTileBytes)), bd = tc_smem_desc(wbase + j * kTcTileBytes);
+                const uint64_t ad = tc_smem_desc(smem_u32(xs + s * xbytes)), bd = tc_smem_desc(wbase + j * kTcTileBytes);
 #pragma unroll
                 for (int k16 = 0; k16 < 4; ++k16) {
                     tc_mma(tmem, ad + 2 * k16, bd + 2 * k16, acc);
@@ -195,8 +206,8 @@ __device__ __forceinline__ int op_gemm_tc(const Params& p, Ctrl* c, uint8_t* rin
             }
             kt += cnt;
         }
-        c->x_mmas = n;
         tc_commit(&c->acc_full);
+        if (p.trace_cap > 0) c->t_phase[1] = (long long)globaltimer();     // last MMA issued
     }
     __syncwarp();
 
@@ -205,6 +216,7 @@ __device__ __forceinline__ int op_gemm_tc(const Params& p, Ctrl* c, uint8_t* rin
     if (lane == 0) ok = wait_barrier(p, c, &c->acc_full, apar, seq, WHERE_COMBINE) ? 1 : 0;
     ok = __shfl_sync(0xffffffffu, ok, 0);
     tc_fence_after();
+    phase_mark(p, c, 2);                                                    // accumulator complete
     const int qd = warp & 3, h = warp >> 2;
     const int r = m0 + qd * 32 + lane;
     if (ok && m0 + qd * 32 < M) {
@@ -232,8 +244,7 @@ __device__ __forceinline__ int op_gemm_tc(const Params& p, Ctrl* c, uint8_t* rin
     }
     tc_fence_before();
     const bool aborting = compute_sync_or(!ok || *(volatile int*)&c->abort);
-    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTcCols) : "memory");
-    if (t == 0) c->acc_uses = c->acc_uses + 1;
+    if (t == 0) c->acc_uses = uses + 1;
     if (aborting) return -1;
     return end.stage | ((int)end.phase << 8);
 }

@@ -66,6 +66,10 @@ struct StageCursor {
     bool gemm;
     int kt, nk, kbeg, n0;
     const void* wmap;
+    // ... or, when the host library has packed the weights into tile images (ptr 10), k-tile
+    // `wtile0 + kt` onwards of that array: consecutive k-tiles of an n tile are consecutive 16 KB blocks
+    const uint8_t* wpack;
+    long long wtile0;
 
     // position on the next streaming-linear instruction at or after `idx`
     __device__ __forceinline__ void seek(const Params& p) {
@@ -78,6 +82,8 @@ struct StageCursor {
                 const int kc = op->i[2] / op->i[4];
                 gemm = true; seq = in.seq; kt = 0; nk = kc / 64; kbeg = in.a2 * kc; n0 = in.a1 * 128;
                 wmap = reinterpret_cast<const uint8_t*>(op->ptr[11]) + 128;
+                wpack = reinterpret_cast<const uint8_t*>(op->ptr[10]);
+                wtile0 = (long long)in.a1 * (op->i[2] / 64) + kbeg / 64;
                 if (nk > 0) return;
                 continue;
             }
@@ -168,11 +174,15 @@ __device__ __forceinline__ void producer_loop(const Params& p, Ctrl* c, uint8_t*
         }
         if (rc.gemm) {
             // tile GEMM: the slot takes the instruction's next 4 (slot 0) or 3 (slot 1) weight k-tiles,
-            // 128 rows x 64 K-elements each, one bulk tensor copy per tile
+            // 128 rows x 64 K-elements each: one bulk tensor copy per tile, or one plain bulk copy
+            // for all of them when the weights are packed
             const int cnt = min(tc_slot_tiles(pos.stage), rc.nk - rc.kt);
             if (lane == 0) {
                 mbar_arrive_expect_tx(&c->full[pos.stage], (uint32_t)(cnt * kTcTileBytes));
-                for (int j = 0; j < cnt; ++j)
+                if (rc.wpack)       // packed weights: the slot's k-tiles are one contiguous block
+                    bulk_g2s_hint(ring + tc_slot_off(pos.stage), rc.wpack + (rc.wtile0 + rc.kt) * kTcTileBytes,
+                                  (uint32_t)(cnt * kTcTileBytes), &c->full[pos.stage], stream_policy);
+                for (int j = 0; j < cnt && !rc.wpack; ++j)
                     tma_load_2d(ring + tc_slot_off(pos.stage) + j * kTcTileBytes, rc.wmap, rc.kbeg + (rc.kt + j) * 64, rc.n0,
                                 &c->full[pos.stage], stream_policy);
             }

@@ -20,12 +20,14 @@ __device__ __forceinline__ float apply_bin(int fn, float a, float b) {
 }
 
 // MK_OP_FINALIZE: out = act(ws + bias) + residual; ws = 0.
-// ptr 0 ws (fp32), 1 out, 2 bias, 3 residual; i 0 R, 1 C, 2 act, 3 out dtype, 4 residual dtype
-// args: 0 row tile, 1 col tile (kEwRows x kEwCols)
+// ptr 0 ws (fp32), 1 out, 2 bias, 3 residual; i 0 R, 1 C, 2 act, 3 out dtype, 4 residual dtype,
+// 5 rows per instruction (schedule.py finalize_rows; 0 = kEwRows)
+// args: 0 row tile, 1 col tile (i5 x kEwCols)
 static __device__ __noinline__ void op_finalize(const mk_op_desc* op, int a0, int a1) {
     const int R = op->i[0], Cc = op->i[1], act = op->i[2];
-    const int r0 = a0 * kEwRows, c0 = a1 * kEwCols;
-    const int rows = min(kEwRows, R - r0), cols = min(kEwCols, Cc - c0);
+    const int tr = op->i[5] > 0 ? op->i[5] : kEwRows;
+    const int r0 = a0 * tr, c0 = a1 * kEwCols;
+    const int rows = min(tr, R - r0), cols = min(kEwCols, Cc - c0);
     const int vpr = cols >> 3;
     float* ws = reinterpret_cast<float*>(op->ptr[0]);
     for (int v = threadIdx.x; v < rows * vpr; v += kComputeThreads) {

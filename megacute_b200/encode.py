@@ -28,7 +28,7 @@ import torch
 
 from . import config as C
 from .graph import DTYPE_CODE, ELEM_BYTES, Op, View
-from .schedule import is_gemv, norm_rows
+from .schedule import finalize_rows, is_gemv, norm_rows
 
 BF16 = torch.bfloat16
 
@@ -96,7 +96,7 @@ def fill(d, op: Op, addr) -> None:
     elif k == "SplitFinalize":
         d.kind = C.OP_FINALIZE
         ptrs = [op.ws, op.out, op.bias, op.residual]
-        ints = [op.out.rows, op.out.cols, C.ACT_CODE[op.act], dt(op.out), dt(op.residual)]
+        ints = [op.out.rows, op.out.cols, C.ACT_CODE[op.act], dt(op.out), dt(op.residual), finalize_rows(op.out.rows, op.out.cols)]
     elif k in ("Unary", "Binary", "SwiGLU", "Modulate", "Rope"):
         d.kind = C.OP_ELTWISE
         R, Cc = op.out.shape

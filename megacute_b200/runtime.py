@@ -157,6 +157,12 @@ class Program:
         (the rest run the mma.sync body)."""
         return int(_lib.load().mk_program_tcgen05_ops(self._handle)) if self._handle is not None else 0
 
+    @property
+    def packed_weight_bytes(self) -> int:
+        """Device memory held for tile-image copies of tile-GEMM weights (snapshots taken when the
+        operand addresses are bound; rebind after changing weights in place)."""
+        return int(_lib.load().mk_program_packed_bytes(self._handle)) if self._handle is not None else 0
+
     def check(self):
         """Synchronise and raise if the kernel reported an error (bounded wait gave up, bad table)."""
         st = (ctypes.c_int32 * _lib.ST_WORDS)()

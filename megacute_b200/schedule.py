@@ -146,6 +146,8 @@ def tile_op(op: Op, sm_count: int) -> Tiled:
     if k in ("SplitFinalize", "Unary", "Binary", "SwiGLU", "Modulate", "Rope"):
         R, Cc = op.out.shape
         TR, TC = C.EW_ROWS, C.EW_COLS
+        if k == "SplitFinalize":
+            TR = finalize_rows(R, Cc)
         if k == "Rope":
             assert TC % op.head_dim == 0, "rope: head_dim must divide the pointwise tile width"
         rt, ct = np.divmod(np.arange(_ceil(R, TR) * _ceil(Cc, TC)), _ceil(Cc, TC))
@@ -227,6 +229,17 @@ def tile_op(op: Op, sm_count: int) -> Tiled:
     if k == "Increment":
         return Tiled(_args(1), [_acc(op.pos, WRITE, n=1)])
     raise NotImplementedError(k)
+
+
+def finalize_rows(rows: int, cols: int) -> int:
+    """Rows per SplitFinalize instruction.  The op sits between two dependent linears; with few
+    rows (batched decode) whole pointwise tiles would leave it a dozen instructions of eight
+    dependent round trips each, so the tile is shortened until the op has about one instruction
+    per SM."""
+    tr = C.EW_ROWS
+    while tr > C.FINALIZE_MIN_ROWS and _ceil(rows, tr) * _ceil(cols, C.EW_COLS) < C.FINALIZE_MIN_INSTS:
+        tr //= 2
+    return tr
 
 
 def norm_rows(rows: int) -> int:
