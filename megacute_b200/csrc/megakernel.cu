@@ -46,6 +46,11 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
             mbar_init(&c->x_empty[s], 1);
             c->x_use_load[s] = c->x_use_mma[s] = 0;
         }
+        for (int s = 0; s < kTcWSlots; ++s) {
+            mbar_init(&c->w_full[s], 1);
+            mbar_init(&c->w_empty[s], 1);
+        }
+        c->w_slot = c->w_phase = 0;
         mbar_init(&c->acc_full, 1);
         c->acc_uses = 0;
         c->tmem_base = kTcNoTmem;
@@ -161,6 +166,12 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
             // the role that knew the parity has already left its loop
             while (!(mbar_try_wait(&c->full[s], 0) || mbar_try_wait(&c->full[s], 1))) {
                 if (globaltimer() - t0 > 20000000ull) break;      // 20 ms
+            }
+        }
+        for (int s = 0; s < kTcWSlots; ++s) {
+            unsigned long long t0 = globaltimer();
+            while (!(mbar_try_wait(&c->w_full[s], 0) || mbar_try_wait(&c->w_full[s], 1))) {
+                if (globaltimer() - t0 > 20000000ull) break;
             }
         }
         unsigned long long t0 = globaltimer();

@@ -36,9 +36,10 @@ constexpr int kXbufBytes = 64 * 1024;                     // GEMV: fp32 activati
 constexpr int kCtrlBytes = 2048;                          // mbarriers, flags, staged instruction metadata
 constexpr int kSmemBytes = kRingBytes + kWorkBytes + kCtrlBytes;
 // tcgen05 tile GEMM (op_gemm_tc.cuh): operand tiles are 128 rows x 64 bf16 with the 128-byte swizzle
-// and must start on 1024-byte boundaries.  Weight tiles travel through the ring (slot 0 holds four,
-// slot 1 three: each lies inside the bytes the streaming linear uses for the same slot, so the two
-// kinds of instruction can follow one another); activation tiles use the work area.
+// and must start on 1024-byte boundaries.  Weight tiles travel through the ring's memory as seven
+// single-tile slots with barriers of their own (four in the bytes of the streaming linear's stage 0,
+// three in those of stage 1; the producer drains one kind of slot before it fills the other kind);
+// activation tiles use the work area.
 constexpr int kTcTileBytes = 128 * 128;
 constexpr int kTcXStages = 5;
 constexpr int kTcXOff = 512;                              // first 1024-aligned byte of the work area
@@ -47,8 +48,8 @@ constexpr int kTcCols = 128;                              // fp32 accumulator co
 constexpr uint32_t kTcNoTmem = 0xffffffffu;               // Ctrl::tmem_base before the CTA's first allocation
 static_assert((kRingBytes + kTcXOff) % 1024 == 0 && kTcXOff + kTcXStages * kTcTileBytes + kTcTileBytes / 2 <= kWorkBytes, "activation tiles");
 static_assert(4 * kTcTileBytes <= kStageBytes && kTcSlot1Off >= kStageBytes && kTcSlot1Off + 3 * kTcTileBytes <= kRingBytes, "weight tiles");
-__host__ __device__ constexpr int tc_slot_off(int stage) { return stage == 0 ? 0 : kTcSlot1Off; }
-__host__ __device__ constexpr int tc_slot_tiles(int stage) { return stage == 0 ? 4 : 3; }
+constexpr int kTcWSlots = 7;
+__host__ __device__ constexpr int tc_wslot_off(int slot) { return slot < 4 ? slot * kTcTileBytes : kTcSlot1Off + (slot - 4) * kTcTileBytes; }
 
 struct Params {
     const int4* insts;            // [n_insts][4]
@@ -89,10 +90,13 @@ struct Ctrl {                     // lives in the last kCtrlBytes of shared memo
     unsigned long long deps_met;      // ... the compute warps have seen the instruction's dependencies met
     unsigned long long x_full[2 * kTcXStages];   // tcgen05 tile GEMM: an activation k-tile has landed in the work area
     unsigned long long x_empty[2 * kTcXStages];  // ... the MMAs that read it have completed
+    unsigned long long w_full[kTcWSlots];    // ... a weight k-tile has landed in its slot of the ring
+    unsigned long long w_empty[kTcWSlots];   // ... the MMAs that read it have completed
     unsigned long long acc_full;      // ... every MMA of the instruction has completed: the accumulator can be read
     uint32_t tmem_base;               // ... tensor-memory address of the accumulator (written by tcgen05.alloc)
     uint8_t x_use_load[2 * kTcXStages];   // ... how often each stage has been filled / consumed since the launch
     uint8_t x_use_mma[2 * kTcXStages];    //     began (the parities of x_empty / x_full)
+    uint8_t w_slot, w_phase;              // ... the MMA thread's position in the weight slots
     uint32_t acc_uses;                // ... instructions that have used acc_full (its parity)
     int abort;                    // set once a wait of this CTA gave up or saw the global abort
     int flag;                     // scratch broadcast word (split-KV last arriver)

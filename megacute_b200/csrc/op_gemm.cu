@@ -8,11 +8,8 @@ __device__ int mk_op_gemm(const Params& p, const mk_op_desc* op, int a0, int a1,
     const SmemMap m = smem_map();
     if (op->ptr[11]) {
         // the host library attached tensor maps: tcgen05 body, weights through the producer's ring
-        RingPos pos;
-        pos.stage = packed_pos & 0xff;
-        pos.phase = (uint32_t)(packed_pos >> 8) & 1u;
-        const int np = op_gemm_tc(p, m.ctrl, m.ring, m.work, op, a0, a1, a2, seq, pos);
-        return np < 0 ? -1 : np | (packed_pos & ~0x1ff);
+        // (the weight tiles have slots and barriers of their own: the ring position is untouched)
+        return op_gemm_tc(p, m.ctrl, m.ring, m.work, op, a0, a1, a2, seq) < 0 ? -1 : packed_pos;
     }
     // ops with at most 64 activation rows have a single m tile: hold 64 rows and stream deeper
     if (op->i[0] <= 64) {

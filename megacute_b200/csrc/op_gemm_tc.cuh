@@ -11,9 +11,9 @@
 // the MMA's M side, so an accumulator row (a tensor-memory lane) is an activation row and a thread of
 // the epilogue holds whole output rows: swiglu (gate columns 0..63, up columns 64..127 of the weight
 // tile) pairs values of one thread.  Rows beyond M are zero-filled by the copy and never stored.
-//   weights      producer warp -> ring slots (4 or 3 k-tiles per slot), across instruction boundaries:
-//                they depend on nothing in the launch, so the next instruction's first 112 KB are
-//                already on their way while this one waits for its dependencies
+//   weights      producer warp -> seven single-tile slots in the ring's memory, across instruction
+//                boundaries: they depend on nothing in the launch, so the next instruction's first
+//                112 KB are already on their way while this one waits for its dependencies
 //   activations  one compute thread -> single-tile stages in the work area, after the instruction's
 //                dependencies are met: 5 stages of 128 rows, or 10 of 64 rows when the op has at most
 //                64 (the MMA still reads 128 rows: the upper 64 accumulator rows are never looked at)
@@ -123,10 +123,10 @@ __device__ __forceinline__ void tc_store32(const mk_op_desc* op, const float* v,
     }
 }
 
-// All compute threads call this after the instruction's dependencies are met.  Returns the ring
-// position behind the instruction's last slot (stage | phase << 8), or -1 when the CTA is aborting.
+// All compute threads call this after the instruction's dependencies are met.  Returns 0, or -1
+// when the CTA is aborting.
 __device__ __forceinline__ int op_gemm_tc(const Params& p, Ctrl* c, uint8_t* ring, uint8_t* work, const mk_op_desc* op, int a0,
-                                          int a1, int a2, int seq, RingPos pos) {
+                                          int a1, int a2, int seq) {
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     const int M = op->i[0], N = op->i[1], K = op->i[2], splits = op->i[4];
     const int accum = op->i[6], swi = op->i[8];
@@ -154,10 +154,6 @@ __device__ __forceinline__ int op_gemm_tc(const Params& p, Ctrl* c, uint8_t* rin
     const uint32_t apar = uses & 1u;
 
     phase_mark(p, c, 0);
-    // where the ring stands after this instruction: the same walk the producer and the MMA thread do
-    RingPos end = pos;
-    for (int kt = 0; kt < nk; end.advance()) kt += min(tc_slot_tiles(end.stage), nk - kt);
-
     if (warp == 2 && lane == 0) {
         // ---- activation tiles: {64 K-elements, 128 rows} at (kbeg + 64 kt, m0) ----
         // earlier instructions wrote the work area through the generic proxy (all of that is behind
@@ -179,33 +175,26 @@ __device__ __forceinline__ int op_gemm_tc(const Params& p, Ctrl* c, uint8_t* rin
         // ---- MMAs: accumulator[128 activation rows][128 weight rows] += x tile . w tile^T ----
         uint32_t n = 0, acc = 0;
         bool ok = true;
-        RingPos q = pos;
-        for (int kt = 0; kt < nk && ok; q.advance()) {
-            const int cnt = min(tc_slot_tiles(q.stage), nk - kt);
-            ok = wait_barrier(p, c, &c->full[q.stage], q.phase, seq, WHERE_RING_FULL);
-            const uint32_t wbase = smem_u32(ring + tc_slot_off(q.stage));
-            for (int j = 0; j < cnt && ok; ++j, ++n) {
-                const int s = n % xstages;
-                ok = wait_barrier(p, c, &c->x_full[s], c->x_use_mma[s]++ & 1u, seq, WHERE_RING_FULL);
-                if (!ok) break;
-                tc_fence_after();
-                const uint64_t ad = tc_smem_desc(smem_u32(xs + s * xbytes)), bd = tc_smem_desc(wbase + j * kTcTileBytes);
+        int ws = c->w_slot;
+        uint32_t wph = c->w_phase;
+        for (int kt = 0; kt < nk && ok; ++kt, ++n) {
+            const int s = n % xstages;
+            ok = wait_barrier(p, c, &c->w_full[ws], wph, seq, WHERE_RING_FULL) &&
+                 wait_barrier(p, c, &c->x_full[s], c->x_use_mma[s]++ & 1u, seq, WHERE_RING_FULL);
+            if (!ok) break;
+            tc_fence_after();
+            const uint64_t ad = tc_smem_desc(smem_u32(xs + s * xbytes)), bd = tc_smem_desc(smem_u32(ring + tc_wslot_off(ws)));
 #pragma unroll
-                for (int k16 = 0; k16 < 4; ++k16) {
-                    tc_mma(tmem, ad + 2 * k16, bd + 2 * k16, acc);
-                    acc = 1;
-                }
-                tc_commit(&c->x_empty[s]);
+            for (int k16 = 0; k16 < 4; ++k16) {
+                tc_mma(tmem, ad + 2 * k16, bd + 2 * k16, acc);
+                acc = 1;
             }
-            if (ok) {
-                // the slot's barrier counts one arrival per compute warp (the streaming linear's
-                // convention): seven plain ones now, the eighth when the MMAs have read the slot
-#pragma unroll
-                for (int w = 0; w < kComputeWarps - 1; ++w) mbar_arrive(&c->empty[q.stage]);
-                tc_commit(&c->empty[q.stage]);
-            }
-            kt += cnt;
+            tc_commit(&c->x_empty[s]);
+            tc_commit(&c->w_empty[ws]);
+            if (++ws == kTcWSlots) { ws = 0; wph ^= 1u; }
         }
+        c->w_slot = (uint8_t)ws;
+        c->w_phase = (uint8_t)wph;
         tc_commit(&c->acc_full);
         if (p.trace_cap > 0) c->t_phase[1] = (long long)globaltimer();     // last MMA issued
     }
@@ -246,7 +235,7 @@ __device__ __forceinline__ int op_gemm_tc(const Params& p, Ctrl* c, uint8_t* rin
     const bool aborting = compute_sync_or(!ok || *(volatile int*)&c->abort);
     if (t == 0) c->acc_uses = uses + 1;
     if (aborting) return -1;
-    return end.stage | ((int)end.phase << 8);
+    return 0;
 }
 
 }  // namespace mk

@@ -152,7 +152,57 @@ __device__ __forceinline__ void producer_loop(const Params& p, Ctrl* c, uint8_t*
     long long t_first = 0;
     int slot_first = 0;
     const unsigned long long stream_policy = l2_policy_evict_first();
+    // tile GEMM weight slots: position, and which kind of slot the ring's memory currently serves
+    int wslot = 0;
+    uint32_t wphase = 0;
+    bool gemm_mode = false;
+    // Wait until the compute side has released every slot of the kind used so far (slot s was last
+    // filled in the current round if s < position, else in the previous one).
+    auto drain = [&](bool tiles) -> bool {
+        int ok = 1;
+        if (lane == 0) {
+            if (tiles) {
+                for (int s = 0; s < kTcWSlots && ok; ++s)
+                    ok = wait_barrier(p, c, &c->w_empty[s], (wphase ^ (s < wslot ? 1u : 0u)) ^ 1u, rc.seq, WHERE_RING_EMPTY) ? 1 : 0;
+            } else {
+                for (int s = 0; s < kStages && ok; ++s)
+                    ok = wait_barrier(p, c, &c->empty[s], (pos.phase ^ (s < pos.stage ? 1u : 0u)) ^ 1u, rc.seq, WHERE_RING_EMPTY) ? 1 : 0;
+            }
+        }
+        return __shfl_sync(0xffffffffu, ok, 0) != 0;
+    };
     while (rc.valid(p)) {
+        if (rc.gemm) {
+            // tile GEMM: one weight k-tile (128 rows x 64 K-elements, 16 KB) per slot -- one plain bulk
+            // copy when the weights are packed, one bulk tensor copy otherwise.  Seven single-tile
+            // slots rather than two large ones: a slot is refilled the moment its tile has been
+            // consumed, so ~100 KB stay in flight (with 64 KB + 48 KB slots the refill of a slot
+            // waited for its last tile and the stream reached 33 GB/s per SM instead of 45).
+            if (!gemm_mode) {
+                if (!drain(false)) return;
+                gemm_mode = true;
+            }
+            int ok = 1;
+            if (lane == 0) {
+                ok = wait_barrier(p, c, &c->w_empty[wslot], wphase ^ 1u, rc.seq, WHERE_RING_EMPTY) ? 1 : 0;
+                if (ok) {
+                    uint8_t* dst = ring + tc_wslot_off(wslot);
+                    mbar_arrive_expect_tx(&c->w_full[wslot], (uint32_t)kTcTileBytes);
+                    if (rc.wpack)
+                        bulk_g2s_hint(dst, rc.wpack + (rc.wtile0 + rc.kt) * kTcTileBytes, (uint32_t)kTcTileBytes, &c->w_full[wslot], stream_policy);
+                    else
+                        tma_load_2d(dst, rc.wmap, rc.kbeg + rc.kt * 64, rc.n0, &c->w_full[wslot], stream_policy);
+                }
+            }
+            if (!__shfl_sync(0xffffffffu, ok, 0)) return;
+            if (++wslot == kTcWSlots) { wslot = 0; wphase ^= 1u; }
+            if (++rc.kt >= rc.nk) { rc.idx += gridDim.x; rc.seek(p); }
+            continue;
+        }
+        if (gemm_mode) {
+            if (!drain(true)) return;
+            gemm_mode = false;
+        }
         // one lane looks whether the ring has a free stage (non-blocking)
         int free_now = 0;
         if (lane == 0) free_now = mbar_try_wait(&c->empty[pos.stage], pos.phase ^ 1u) ? 1 : 0;
@@ -171,27 +221,6 @@ __device__ __forceinline__ void producer_loop(const Params& p, Ctrl* c, uint8_t*
             int ok = 1;
             if (lane == 0) ok = wait_barrier(p, c, &c->empty[pos.stage], pos.phase ^ 1u, rc.seq, WHERE_RING_EMPTY) ? 1 : 0;
             if (!__shfl_sync(0xffffffffu, ok, 0)) return;
-        }
-        if (rc.gemm) {
-            // tile GEMM: the slot takes the instruction's next 4 (slot 0) or 3 (slot 1) weight k-tiles,
-            // 128 rows x 64 K-elements each: one bulk tensor copy per tile, or one plain bulk copy
-            // for all of them when the weights are packed
-            const int cnt = min(tc_slot_tiles(pos.stage), rc.nk - rc.kt);
-            if (lane == 0) {
-                mbar_arrive_expect_tx(&c->full[pos.stage], (uint32_t)(cnt * kTcTileBytes));
-                if (rc.wpack)       // packed weights: the slot's k-tiles are one contiguous block
-                    bulk_g2s_hint(ring + tc_slot_off(pos.stage), rc.wpack + (rc.wtile0 + rc.kt) * kTcTileBytes,
-                                  (uint32_t)(cnt * kTcTileBytes), &c->full[pos.stage], stream_policy);
-                for (int j = 0; j < cnt && !rc.wpack; ++j)
-                    tma_load_2d(ring + tc_slot_off(pos.stage) + j * kTcTileBytes, rc.wmap, rc.kbeg + (rc.kt + j) * 64, rc.n0,
-                                &c->full[pos.stage], stream_policy);
-            }
-            __syncwarp();
-            rc.kt += cnt;
-            pos.advance();
-            if (rc.kt >= rc.nk) { rc.idx += gridDim.x; rc.seek(p); }
-            if (ahead > 0) --ahead;
-            continue;
         }
         const __nv_bfloat16* src; int bytes, off;
         rc.piece(lane, src, bytes, off);
