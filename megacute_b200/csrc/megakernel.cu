@@ -187,18 +187,21 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
 // row requests of 128 bytes, and the copy engine of an SM sustains only ~28 GB/s of such rows
 // (measured: ~4 TB/s over the chip, whatever the depth of the pipeline), where one plain bulk copy of
 // the same bytes runs at the HBM rate.  So the library keeps, per weight matrix, a copy laid out as
-// the shared-memory images of its tiles: tile (n tile j, k tile t) is the 16 KB block j * K/64 + t,
+// the shared-memory images of its tiles: tile (n tile j, k tile t) is the 16 KB block t * ceil(N/128) + j,
 // row r's 16-byte chunk c at r * 128 + ((c ^ (r & 7)) << 4) -- the 128-byte swizzle a bulk tensor
 // copy would have applied.  Rows beyond N are zero.  One thread moves one 16-byte chunk.
+// k-tile-major on purpose: the CTAs of an op walk K in step, each on its own n tile, so at any
+// moment they read neighbouring blocks (one sequential stream over the chip) instead of addresses a
+// large power of two apart.
 __global__ void pack_weight_tiles(const __nv_bfloat16* __restrict__ w, long long ld, int N, int K, uint4* __restrict__ out,
                                   long long chunks) {
-    const int kchunks = K / 8, ktiles = K / 64;
+    const int kchunks = K / 8, ntiles = (N + 127) / 128;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < chunks; i += (long long)gridDim.x * blockDim.x) {
         const int row = (int)(i / kchunks), kc = (int)(i % kchunks);
         const int j = row >> 7, r = row & 127, t = kc >> 3, c = kc & 7;
         uint4 v = make_uint4(0u, 0u, 0u, 0u);
         if (row < N) v = __ldg(reinterpret_cast<const uint4*>(w + (long long)row * ld + (long long)kc * 8));
-        out[((long long)j * ktiles + t) * (kTcTileBytes / 16) + r * 8 + (c ^ (r & 7))] = v;
+        out[((long long)t * ntiles + j) * (kTcTileBytes / 16) + r * 8 + (c ^ (r & 7))] = v;
     }
 }
 

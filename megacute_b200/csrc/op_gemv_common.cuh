@@ -66,10 +66,11 @@ struct StageCursor {
     bool gemm;
     int kt, nk, kbeg, n0;
     const void* wmap;
-    // ... or, when the host library has packed the weights into tile images (ptr 10), k-tile
-    // `wtile0 + kt` onwards of that array: consecutive k-tiles of an n tile are consecutive 16 KB blocks
+    // ... or, when the host library has packed the weights into tile images (ptr 10), the 16 KB
+    // block `wtile0 + kt * wstride` of that array (k-tile-major: wstride = number of n tiles)
     const uint8_t* wpack;
     long long wtile0;
+    int wstride;
 
     // position on the next streaming-linear instruction at or after `idx`
     __device__ __forceinline__ void seek(const Params& p) {
@@ -83,7 +84,8 @@ struct StageCursor {
                 gemm = true; seq = in.seq; kt = 0; nk = kc / 64; kbeg = in.a2 * kc; n0 = in.a1 * 128;
                 wmap = reinterpret_cast<const uint8_t*>(op->ptr[11]) + 128;
                 wpack = reinterpret_cast<const uint8_t*>(op->ptr[10]);
-                wtile0 = (long long)in.a1 * (op->i[2] / 64) + kbeg / 64;
+                wstride = (op->i[1] + 127) / 128;
+                wtile0 = (long long)(kbeg / 64) * wstride + in.a1;
                 if (nk > 0) return;
                 continue;
             }
@@ -189,7 +191,7 @@ __device__ __forceinline__ void producer_loop(const Params& p, Ctrl* c, uint8_t*
                     uint8_t* dst = ring + tc_wslot_off(wslot);
                     mbar_arrive_expect_tx(&c->w_full[wslot], (uint32_t)kTcTileBytes);
                     if (rc.wpack)
-                        bulk_g2s_hint(dst, rc.wpack + (rc.wtile0 + rc.kt) * kTcTileBytes, (uint32_t)kTcTileBytes, &c->w_full[wslot], stream_policy);
+                        bulk_g2s_hint(dst, rc.wpack + (rc.wtile0 + (long long)rc.kt * rc.wstride) * kTcTileBytes, (uint32_t)kTcTileBytes, &c->w_full[wslot], stream_policy);
                     else
                         tma_load_2d(dst, rc.wmap, rc.kbeg + rc.kt * 64, rc.n0, &c->w_full[wslot], stream_policy);
                 }
