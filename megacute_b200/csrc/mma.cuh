@@ -23,6 +23,15 @@ __device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b
 __device__ __forceinline__ void red_add_f32x2(float* p, float a, float b) {
     asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(p), "f"(a), "f"(b) : "memory");
 }
+// four consecutive fp32 (16-byte aligned) / eight consecutive bf16 (16-byte aligned) in one reduction
+__device__ __forceinline__ void red_add_f32x4(float* p, float a, float b, float c, float d) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+__device__ __forceinline__ void red_add_bf16x8(void* p, const float* f) {
+    asm volatile("red.global.add.noftz.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(pack2(f[0], f[1])), "r"(pack2(f[2], f[3])),
+                 "r"(pack2(f[4], f[5])), "r"(pack2(f[6], f[7]))
+                 : "memory");
+}
 __device__ __forceinline__ void red_add_bf16x2(void* p, float a, float b) {
     const uint32_t v = pack2(a, b);
     asm volatile("red.global.add.noftz.bf16x2 [%0], %1;" ::"l"(p), "r"(v) : "memory");

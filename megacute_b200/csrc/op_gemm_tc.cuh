@@ -24,6 +24,7 @@
 // CTA and freed by the kernel before it exits, on every path.
 #pragma once
 #include "mk_device.cuh"
+#include "mma.cuh"
 #include "op_gemv_common.cuh"
 
 namespace mk {
@@ -82,6 +83,16 @@ __device__ __forceinline__ void tc_store32(const mk_op_desc* op, const float* v,
         float f[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) f[j] = v[g8 * 8 + j];
+        if (accum && col + 8 <= n_out) {
+            // whole groups of eight columns: 16-byte vector reductions (the host checked the alignment)
+            if (odt == 1) {
+                red_add_f32x4(reinterpret_cast<float*>(O) + eo + col, f[0], f[1], f[2], f[3]);
+                red_add_f32x4(reinterpret_cast<float*>(O) + eo + col + 4, f[4], f[5], f[6], f[7]);
+            } else {
+                red_add_bf16x8(reinterpret_cast<__nv_bfloat16*>(O) + eo + col, f);
+            }
+            continue;
+        }
         if (accum) {
 #pragma unroll
             for (int j = 0; j < 8; j += 2) {
