@@ -61,6 +61,32 @@ def test_tile_linear_both_bodies_agree(cuda, monkeypatch):
     assert rel_l2(outs_tc[0], outs_mma[0]) < 2e-3
 
 
+def test_streaming_and_tile_linears_alternate(cuda):
+    """Streaming linears (<= 8 rows: two-stage weight ring) and tcgen05 tile linears (seven single-tile
+    weight slots in the same shared memory) alternate in one launch, several instructions of each
+    per CTA: the producer warp must drain one kind of slot before it fills the other."""
+    g = mc.Graph()
+    a = g.input("a", (4, 1024))
+    b = g.input("b", (96, 1024))
+    for i in range(3):
+        a = g.linear(a, g.param(f"ws{i}", (40 * 148, 1024)), act="gelu_tanh")      # 40 outputs per CTA and op
+        a = g.linear(a, g.param(f"wd{i}", (1024, 40 * 148)))
+        b = g.linear(b, g.param(f"wt{i}", (2 * 148 * 128, 1024)), act="relu")       # two tiles per CTA and op
+        b = g.linear(b, g.param(f"wu{i}", (1024, 2 * 148 * 128)))
+    g.output(a)
+    g.output(b)
+    t = {"a": rnd((4, 1024), 1.0, 1), "b": rnd((96, 1024), 1.0, 2)}
+    for i in range(3):
+        t[f"ws{i}"] = rnd((40 * 148, 1024), 0.03, 10 + i)
+        t[f"wd{i}"] = rnd((1024, 40 * 148), 0.03, 20 + i)
+        t[f"wt{i}"] = rnd((2 * 148 * 128, 1024), 0.03, 30 + i)
+        t[f"wu{i}"] = rnd((1024, 2 * 148 * 128), 0.01, 40 + i)
+    outs, ref, _, _, prog = run_both(g, t, cuda, steps=2)
+    kinds = {o.kind for o in prog.g.ops}
+    assert prog.tcgen05_ops >= 6 and prog.packed_weight_bytes > 0
+    assert_close(outs, ref)
+
+
 def test_split_k_in_place_residual(cuda):
     """A residual linear with few tiles reduce-adds its K splits straight into the residual stream."""
     g = mc.Graph()
