@@ -27,6 +27,9 @@ __device__ __forceinline__ void red_add_f32x2(float* p, float a, float b) {
 __device__ __forceinline__ void red_add_f32x4(float* p, float a, float b, float c, float d) {
     asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
+__device__ __forceinline__ void red_add_bf16x4(void* p, const float* f) {
+    asm volatile("red.global.add.noftz.v2.bf16x2 [%0], {%1, %2};" ::"l"(p), "r"(pack2(f[0], f[1])), "r"(pack2(f[2], f[3])) : "memory");
+}
 __device__ __forceinline__ void red_add_bf16x8(void* p, const float* f) {
     asm volatile("red.global.add.noftz.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(pack2(f[0], f[1])), "r"(pack2(f[2], f[3])),
                  "r"(pack2(f[4], f[5])), "r"(pack2(f[6], f[7]))

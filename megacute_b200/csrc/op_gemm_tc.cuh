@@ -19,7 +19,8 @@
 //                64 (the MMA still reads 128 rows: the upper 64 accumulator rows are never looked at)
 //   MMA          one compute thread: 4 x tcgen05.mma (128 x 128 x 16) per k-tile; tcgen05.commit
 //                returns the activation stage and the ring slot when the MMAs that read them are done
-//   epilogue     all 8 compute warps: warp w reads lanes 32 (w & 3) .. +31, column half w >> 2
+//   epilogue     all 8 compute warps: tensor memory -> shared memory (warp w reads lanes 32 (w & 3) .. +31,
+//                column half w >> 2), then row-contiguous global stores / reductions from there
 // Every wait is bounded (wait_barrier); tensor memory is allocated by the first such instruction of a
 // CTA and freed by the kernel before it exits, on every path.
 #pragma once
@@ -68,69 +69,57 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, float* v) {
     for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
 }
 
-// 32 consecutive output columns [col0, col0 + 32) of activation row r: bias, activation, residual,
-// store -- or, for a split-K partial, reduce-add into the workspace.
-__device__ __forceinline__ void tc_store32(const mk_op_desc* op, const float* v, int r, int col0, int n_out, bool plain) {
+// Epilogue, second half.  The accumulator tile has been copied to shared memory (fp32, row pitch
+// kTcStagePitch words); here a warp instruction covers one output row (or two half rows), four
+// consecutive columns per lane, so every global access of the epilogue -- bias, residual, store or
+// reduce-add -- is a contiguous 256 or 512 bytes.  Straight from tensor memory a lane holds a row,
+// and a warp store touched 32 rows: measured on the lm_head tiles of batch-64 decode (rows 256 KB
+// apart, lines not in L2) the stores of one tile took 9.5 us to issue.
+constexpr int kTcStagePitch = 132;                          // words: conflict-free 16-byte writes by row, reads by column
+static_assert(kTcXOff + 128 * kTcStagePitch * 4 <= kWorkBytes, "epilogue staging tile");
+__device__ __forceinline__ void tc_write_rows(const mk_op_desc* op, const float* stage, int m0, int rows, int ncols, int col0,
+                                              int n_out) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int act = op->i[3], odt = op->i[5], accum = op->i[6], rdt = op->i[7];
-    void* O = reinterpret_cast<void*>(op->ptr[2]);
-    const void* bias = reinterpret_cast<const void*>(op->ptr[3]);
-    const void* R = reinterpret_cast<const void*>(op->ptr[4]);
-    const long long eo = (long long)r * op->ld[2], er = (long long)r * op->ld[4];
-#pragma unroll
-    for (int g8 = 0; g8 < 4; ++g8) {
-        const int col = col0 + g8 * 8;
-        if (col >= n_out) break;
-        float f[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) f[j] = v[g8 * 8 + j];
-        if (accum && col + 8 <= n_out) {
-            // whole groups of eight columns: 16-byte vector reductions (the host checked the alignment)
-            if (odt == 1) {
-                red_add_f32x4(reinterpret_cast<float*>(O) + eo + col, f[0], f[1], f[2], f[3]);
-                red_add_f32x4(reinterpret_cast<float*>(O) + eo + col + 4, f[4], f[5], f[6], f[7]);
-            } else {
-                red_add_bf16x8(reinterpret_cast<__nv_bfloat16*>(O) + eo + col, f);
-            }
-            continue;
-        }
+    const bool plain = !accum && !op->i[8];
+    uint8_t* O = reinterpret_cast<uint8_t*>(op->ptr[2]);
+    const uint8_t* bias = reinterpret_cast<const uint8_t*>(op->ptr[3]);
+    const uint8_t* R = reinterpret_cast<const uint8_t*>(op->ptr[4]);
+    const int lpr = ncols >> 2;                                // lanes per row: 32, or 16 (swiglu: two rows per pass)
+    const int sub = lane / lpr, c4 = (lane % lpr) * 4, col = col0 + c4;
+    if (col >= n_out) return;
+    float b4[4] = {0.f, 0.f, 0.f, 0.f};
+    if (plain && bias) {
+        const uint2 w = __ldg(reinterpret_cast<const uint2*>(bias + (long long)col * 2));
+        b4[0] = bf16_lo(w.x); b4[1] = bf16_hi(w.x); b4[2] = bf16_lo(w.y); b4[3] = bf16_hi(w.y);
+    }
+    const int step = kComputeWarps * (32 / lpr);
+#pragma unroll 2
+    for (int row = warp * (32 / lpr) + sub; row < rows; row += step) {
+        const float4 q = *reinterpret_cast<const float4*>(stage + row * kTcStagePitch + c4);
+        float f[4] = {q.x, q.y, q.z, q.w};
+        const long long eo = (long long)(m0 + row) * op->ld[2] + col;
         if (accum) {
-#pragma unroll
-            for (int j = 0; j < 8; j += 2) {
-                if (col + j >= n_out) break;
-                if (odt == 1) red_add_f32x2(reinterpret_cast<float*>(O) + eo + col + j, f[j], f[j + 1]);
-                else red_add_bf16x2(reinterpret_cast<__nv_bfloat16*>(O) + eo + col + j, f[j], f[j + 1]);
-            }
+            if (odt == 1) red_add_f32x4(reinterpret_cast<float*>(O) + eo, f[0], f[1], f[2], f[3]);
+            else red_add_bf16x4(O + eo * 2, f);
             continue;
         }
-        if (col + 8 <= n_out) {
-            if (plain) {
-                if (bias) {
-                    float b[8];
-                    load8(bias, col, 0, b);
+        if (plain) {
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) f[j] += b[j];
+            for (int j = 0; j < 4; ++j) f[j] = apply_act(act, f[j] + b4[j]);
+            if (R) {
+                const long long er = (long long)(m0 + row) * op->ld[4] + col;
+                if (rdt == 1) {
+                    const float4 x = __ldcg(reinterpret_cast<const float4*>(R + er * 4));
+                    f[0] += x.x; f[1] += x.y; f[2] += x.z; f[3] += x.w;
+                } else {
+                    const uint2 w = __ldcg(reinterpret_cast<const uint2*>(R + er * 2));
+                    f[0] += bf16_lo(w.x); f[1] += bf16_hi(w.x); f[2] += bf16_lo(w.y); f[3] += bf16_hi(w.y);
                 }
-#pragma unroll
-                for (int j = 0; j < 8; ++j) f[j] = apply_act(act, f[j]);
-                if (R) {
-                    float q[8];
-                    load8(R, er + col, rdt, q);
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) f[j] += q[j];
-                }
-            }
-            store8(O, eo + col, odt, f);
-        } else {
-            for (int j = 0; j < 8 && col + j < n_out; ++j) {
-                float y = f[j];
-                if (plain) {
-                    if (bias) y += load1(bias, col + j, 0);
-                    y = apply_act(act, y);
-                    if (R) y += load1(R, er + col + j, rdt);
-                }
-                store1(O, eo + col + j, odt, y);
             }
         }
+        if (odt == 1) *reinterpret_cast<float4*>(O + eo * 4) = make_float4(f[0], f[1], f[2], f[3]);
+        else *reinterpret_cast<uint2*>(O + eo * 2) = make_uint2(pack2(f[0], f[1]), pack2(f[2], f[3]));
     }
 }
 
@@ -140,7 +129,7 @@ __device__ __forceinline__ int op_gemm_tc(const Params& p, Ctrl* c, uint8_t* rin
                                           int a1, int a2, int seq) {
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     const int M = op->i[0], N = op->i[1], K = op->i[2], splits = op->i[4];
-    const int accum = op->i[6], swi = op->i[8];
+    const int swi = op->i[8];
     const int m0 = a0 * 128, n0 = a1 * 128;
     const int kc = K / splits, kbeg = a2 * kc, nk = kc / 64;
     const uint8_t* tmaps = reinterpret_cast<const uint8_t*>(op->ptr[11]);
@@ -217,30 +206,41 @@ __device__ __forceinline__ int op_gemm_tc(const Params& p, Ctrl* c, uint8_t* rin
     ok = __shfl_sync(0xffffffffu, ok, 0);
     tc_fence_after();
     phase_mark(p, c, 2);                                                    // accumulator complete
+    // first half: tensor memory -> shared memory.  Warp w reads lanes 32 (w & 3) .. +31 (activation
+    // rows) and column half w >> 2; the activation stages are free now (every MMA has completed).
     const int qd = warp & 3, h = warp >> 2;
-    const int r = m0 + qd * 32 + lane;
-    if (ok && m0 + qd * 32 < M) {
+    float* stage = reinterpret_cast<float*>(work + kTcXOff);
+    const int rows = min(128, M - m0);
+    if (ok && qd * 32 < rows) {
         const uint32_t tl = tmem + ((uint32_t)(qd * 32) << 16);
+        float* srow = stage + (qd * 32 + lane) * kTcStagePitch;
         float v[32];
         if (swi) {
             // gate columns 32 h .. +31 and the up columns 64 further of the same outputs
-            if (a1 * 64 + h * 32 < N / 2) {
-                float u[32];
-                tc_ld32(tl + h * 32, v);
-                tc_ld32(tl + 64 + h * 32, u);
+            float u[32];
+            tc_ld32(tl + h * 32, v);
+            tc_ld32(tl + 64 + h * 32, u);
 #pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] = v[j] * sigmoidf_(v[j]) * u[j];
-                if (r < M) tc_store32(op, v, r, a1 * 64 + h * 32, N / 2, false);
-            }
+            for (int j = 0; j < 32; j += 4)
+                *reinterpret_cast<float4*>(srow + h * 32 + j) =
+                    make_float4(v[j] * sigmoidf_(v[j]) * u[j], v[j + 1] * sigmoidf_(v[j + 1]) * u[j + 1],
+                                v[j + 2] * sigmoidf_(v[j + 2]) * u[j + 2], v[j + 3] * sigmoidf_(v[j + 3]) * u[j + 3]);
         } else {
 #pragma unroll 1
             for (int ch = 0; ch < 2; ++ch) {
                 const int tcol = h * 64 + ch * 32;
                 if (n0 + tcol >= N) break;
                 tc_ld32(tl + tcol, v);
-                if (r < M) tc_store32(op, v, r, n0 + tcol, N, !accum);
+#pragma unroll
+                for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(srow + tcol + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
             }
         }
+    }
+    tc_fence_before();
+    compute_sync();
+    if (ok) {
+        if (swi) tc_write_rows(op, stage, m0, rows, 64, a1 * 64, N / 2);
+        else tc_write_rows(op, stage, m0, rows, 128, n0, N);
     }
     tc_fence_before();
     const bool aborting = compute_sync_or(!ok || *(volatile int*)&c->abort);
