@@ -36,20 +36,19 @@ constexpr int kXbufBytes = 64 * 1024;                     // GEMV: fp32 activati
 constexpr int kCtrlBytes = 2048;                          // mbarriers, flags, staged instruction metadata
 constexpr int kSmemBytes = kRingBytes + kWorkBytes + kCtrlBytes;
 // tcgen05 tile GEMM (op_gemm_tc.cuh): operand tiles are 128 rows x 64 bf16 with the 128-byte swizzle
-// and must start on 1024-byte boundaries.  Weight tiles travel through the ring's memory as seven
-// single-tile slots with barriers of their own (four in the bytes of the streaming linear's stage 0,
-// three in those of stage 1; the producer drains one kind of slot before it fills the other kind);
-// activation tiles use the work area.
+// and must start on 1024-byte boundaries.  Weight tiles travel through the ring's memory as eight
+// single-tile slots with barriers of their own (the producer drains one kind of slot -- these, or
+// the streaming linear's two stages -- before it fills the other kind); activation tiles use the
+// work area.
 constexpr int kTcTileBytes = 128 * 128;
 constexpr int kTcXStages = 5;
 constexpr int kTcXOff = 512;                              // first 1024-aligned byte of the work area
-constexpr int kTcSlot1Off = 65 * 1024;
 constexpr int kTcCols = 128;                              // fp32 accumulator columns in tensor memory
 constexpr uint32_t kTcNoTmem = 0xffffffffu;               // Ctrl::tmem_base before the CTA's first allocation
 static_assert((kRingBytes + kTcXOff) % 1024 == 0 && kTcXOff + kTcXStages * kTcTileBytes + kTcTileBytes / 2 <= kWorkBytes, "activation tiles");
-static_assert(4 * kTcTileBytes <= kStageBytes && kTcSlot1Off >= kStageBytes && kTcSlot1Off + 3 * kTcTileBytes <= kRingBytes, "weight tiles");
-constexpr int kTcWSlots = 7;
-__host__ __device__ constexpr int tc_wslot_off(int slot) { return slot < 4 ? slot * kTcTileBytes : kTcSlot1Off + (slot - 4) * kTcTileBytes; }
+constexpr int kTcWSlots = 8;
+__host__ __device__ constexpr int tc_wslot_off(int slot) { return slot * kTcTileBytes; }
+static_assert(kTcWSlots * kTcTileBytes <= kRingBytes, "weight slots");
 
 struct Params {
     const int4* insts;            // [n_insts][4]

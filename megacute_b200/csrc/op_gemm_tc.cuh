@@ -11,9 +11,9 @@
 // the MMA's M side, so an accumulator row (a tensor-memory lane) is an activation row and a thread of
 // the epilogue holds whole output rows: swiglu (gate columns 0..63, up columns 64..127 of the weight
 // tile) pairs values of one thread.  Rows beyond M are zero-filled by the copy and never stored.
-//   weights      producer warp -> seven single-tile slots in the ring's memory, across instruction
+//   weights      producer warp -> eight single-tile slots in the ring's memory, across instruction
 //                boundaries: they depend on nothing in the launch, so the next instruction's first
-//                112 KB are already on their way while this one waits for its dependencies
+//                128 KB are already on their way while this one waits for its dependencies
 //   activations  one compute thread -> single-tile stages in the work area, after the instruction's
 //                dependencies are met: 5 stages of 128 rows, or 10 of 64 rows when the op has at most
 //                64 (the MMA still reads 128 rows: the upper 64 accumulator rows are never looked at)

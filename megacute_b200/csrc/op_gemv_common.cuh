@@ -176,7 +176,7 @@ __device__ __forceinline__ void producer_loop(const Params& p, Ctrl* c, uint8_t*
     while (rc.valid(p)) {
         if (rc.gemm) {
             // tile GEMM: one weight k-tile (128 rows x 64 K-elements, 16 KB) per slot -- one plain bulk
-            // copy when the weights are packed, one bulk tensor copy otherwise.  Seven single-tile
+            // copy when the weights are packed, one bulk tensor copy otherwise.  Eight single-tile
             // slots rather than two large ones: a slot is refilled the moment its tile has been
             // consumed, so ~100 KB stay in flight (with 64 KB + 48 KB slots the refill of a slot
             // waited for its last tile and the stream reached 33 GB/s per SM instead of 45).
