@@ -61,6 +61,57 @@ def test_tile_linear_both_bodies_agree(cuda, monkeypatch):
     assert rel_l2(outs_tc[0], outs_mma[0]) < 2e-3
 
 
+def test_tile_linear_weight_sources_and_rebind(cuda, monkeypatch):
+    """Packed weight tiles (default) and bulk tensor copies over the caller's matrix
+    (MEGACUTE_B200_NO_WEIGHT_PACK) give the same result; binding another weight tensor re-packs."""
+    g = mc.Graph()
+    g.output(g.linear(g.input("x", (64, 2048)), g.param("w", (1536, 2048)), residual=g.input("r", (64, 1536))))
+    t = {"x": rnd((64, 2048), 1.0, 1), "w": rnd((1536, 2048), 0.03, 2), "r": rnd((64, 1536), 1.0, 3)}
+    outs_p, ref, _, _, prog_p = run_both(g, t, cuda)
+    assert prog_p.tcgen05_ops >= 1 and prog_p.packed_weight_bytes == 1536 * 2048 * 2
+    assert_close(outs_p, ref)
+    # the same program with another weight tensor: the snapshot follows the rebind
+    t2 = dict(t, w=rnd((1536, 2048), 0.03, 7))
+    dev2 = {k: v.to(cuda).contiguous() for k, v in t2.items()}
+    out2 = prog_p(**dev2)
+    prog_p.check()
+    ref2, _ = evaluate(g, t2)
+    assert rel_l2(out2.float().cpu(), ref2[0]) < TOL
+    assert prog_p.packed_weight_bytes == 1536 * 2048 * 2            # the first copy was freed
+    monkeypatch.setenv("MEGACUTE_B200_NO_WEIGHT_PACK", "1")
+    outs_t, _, _, _, prog_t = run_both(g, t, cuda)
+    assert prog_t.tcgen05_ops >= 1 and prog_t.packed_weight_bytes == 0
+    assert_close(outs_t, ref)
+    assert rel_l2(outs_t[0], outs_p[0]) < 1e-3
+
+
+def test_tile_linear_timeout_is_reported_not_hung(cuda):
+    """Host-made fault in a launch of tcgen05 tile linears: a wait target no arrival can satisfy.
+    The launch ends with an error status (bounded waits; weight tiles already requested are waited
+    for, tensor memory is given back) and the program works again after reset()."""
+    g = mc.Graph()
+    h = g.linear(g.input("x", (96, 512)), g.param("w1", (1024, 512)), act="relu")
+    g.output(g.linear(h, g.param("w2", (512, 1024))))
+    t = {"x": rnd((96, 512), 1, 1).to(cuda), "w1": rnd((1024, 512), 0.04, 2).to(cuda), "w2": rnd((512, 1024), 0.04, 3).to(cuda)}
+    prog = mc.compile(g)
+    good = prog(**t).float().cpu().clone()
+    prog.check()
+    assert prog.tcgen05_ops >= 2
+    from megacute_b200 import _lib
+    prog.set_timeout(0.05)
+    s = prog.sched
+    _lib.check(_lib.load().mk_program_poke_wait(prog._handle, 0, int(s.wait_cnt[0]), int(s.wait_tgt[0]) + 1000))
+    prog(**t)
+    with pytest.raises(_lib.MegakernelTimeout):
+        prog.check()
+    _lib.check(_lib.load().mk_program_poke_wait(prog._handle, 0, int(s.wait_cnt[0]), int(s.wait_tgt[0])))
+    prog.reset()
+    again = prog(**t).float().cpu()
+    prog.check()
+    # (split-K partial sums are reduce-added in whatever order the CTAs arrive: equal up to fp32 rounding)
+    assert rel_l2(again, good) < 1e-3
+
+
 def test_streaming_and_tile_linears_alternate(cuda):
     """Streaming linears (<= 8 rows: two-stage weight ring) and tcgen05 tile linears (seven single-tile
     weight slots in the same shared memory) alternate in one launch, several instructions of each
