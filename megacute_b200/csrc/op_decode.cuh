@@ -19,7 +19,9 @@
 // appends k, v to cache row b * max_seq + pos (reference semantics: graph.py:412-418).
 //
 // ptr 0 q, 1 k_cache, 2 v_cache, 3 pos, 4 out, 5 k_new, 6 v_new, 7 cos, 8 sin, 9 part, 10 count
-// i 0 B, 1 H, 2 KVH, 3 D, 4 max_seq, 5 splits, 6 fused, 7 dtype of q / k_new / v_new, 8 out dtype;  f 0 scale
+// i 0 B, 1 H, 2 KVH, 3 D, 4 max_seq, 5 splits, 6 fused, 7 dtype of q / k_new / v_new, 8 out dtype,
+//   9 zero q / k_new / v_new after use (they are fp32 columns of a split-K workspace: the instruction that
+//     writes the pair's output hands them back zeroed, as the SplitFinalize it replaces would);  f 0 scale
 // args: 0 b, 1 kv head, 2 split
 #pragma once
 #include "mk_device.cuh"
@@ -293,6 +295,17 @@ __device__ __forceinline__ void decode_body(const Params& p, Ctrl* c, const mk_o
         return a;
     };
     const int pair = b * KVH + kvh;
+    // every instruction of the pair has read q (and the one with the new token k_new, v_new) by the
+    // time one of them writes the pair's output
+    auto zero_inputs = [&]() {
+        if (!op->i[9]) return;
+        float* q = reinterpret_cast<float*>(op->ptr[0]) + (long long)b * op->ld[0] + kvh * GD;
+        for (int idx = t; idx < GD; idx += kComputeThreads) q[idx] = 0.f;
+        if (t < 2 * D) {
+            const int which = t / D;
+            reinterpret_cast<float*>(op->ptr[5 + which])[(long long)b * op->ld[5 + which] + kvh * D + t % D] = 0.f;
+        }
+    };
     void* outp = reinterpret_cast<void*>(op->ptr[4]);
     const int odt = op->i[8];
     if (S == 1) {
@@ -301,6 +314,7 @@ __device__ __forceinline__ void decode_body(const Params& p, Ctrl* c, const mk_o
             const float a = merged(idx, mx, l);
             store1(outp, (long long)b * op->ld[4] + kvh * GD + idx, odt, l == 0.f ? 0.f : a * rcp(l));
         }
+        zero_inputs();
         return;
     }
     float* part = reinterpret_cast<float*>(op->ptr[9]);
@@ -352,6 +366,7 @@ __device__ __forceinline__ void decode_body(const Params& p, Ctrl* c, const mk_o
         }
         store1(outp, (long long)b * op->ld[4] + kvh * GD + idx, odt, l == 0.f ? 0.f : a * rcp(l));
     }
+    zero_inputs();
 }
 
 // The op waits for its own dependencies (see decode_body) and publishes its own arrivals, so the

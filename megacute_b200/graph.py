@@ -119,7 +119,7 @@ OP_TABLE = {
                         ("heads", "kv_heads", "head_dim", "max_seq")),
     "DecodeAttention": (("q", "k_cache", "v_cache", "pos", "k_new", "v_new", "cos", "sin", "part", "count"),
                         ("out", "part", "count"),
-                        ("batch", "heads", "kv_heads", "head_dim", "max_seq", "scale", "splits")),
+                        ("batch", "heads", "kv_heads", "head_dim", "max_seq", "scale", "splits", "zero_inputs")),
     "Increment":       ((), ("pos",), ()),
 }
 

@@ -221,6 +221,10 @@ def tile_op(op: Op, sm_count: int) -> Tiled:
                     _acc(op.v_new, READ, b, b + 1, h * D, (h + 1) * D, n=n, covers=S == 1),
                     _acc(op.cos, READ, n=n, covers=False), _acc(op.sin, READ, n=n, covers=False),
                     cache(op.k_cache, WRITE), cache(op.v_cache, WRITE)]
+        if op.zero_inputs:      # q, k_new, v_new are a split-K workspace, zeroed by the pair's last instruction
+            acc += [_acc(op.q, WRITE, b, b + 1, *qcols, n=n, covers=S == 1),
+                    _acc(op.k_new, WRITE, b, b + 1, h * D, (h + 1) * D, n=n, covers=S == 1),
+                    _acc(op.v_new, WRITE, b, b + 1, h * D, (h + 1) * D, n=n, covers=S == 1)]
         if S > 1:
             r = b * op.kv_heads + h
             acc += [_acc(op.part, WRITE, r * S, (r + 1) * S, n=n, covers=False),

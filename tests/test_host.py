@@ -155,6 +155,25 @@ def _simulate(s, g, order_seed):
                         assert rank[j] < rank[i], (j, i)
 
 
+def test_finalize_fused_into_decode_attention():
+    """Batched decode: the split-K QKV projection's SplitFinalize (a plain fp32 copy) is dropped, the
+    fused attention reads the workspace and zeroes it; every hazard on the workspace stays ordered."""
+    g, *_ = small_decode(B=16, n=2, E=2048, H=32, KVH=8, F=1024, vocab=512, max_seq=128, ctx=10)
+    g2 = run_all(g, 148)
+    att = [o for o in g2.ops if o.kind == "DecodeAttention"]
+    assert att and all(o.zero_inputs and o.q.buf.kind == "workspace" and o.q.buf is o.k_new.buf is o.v_new.buf for o in att)
+    fins = [o for o in g2.ops if o.kind == "SplitFinalize"]
+    assert not any(o.out.buf is a.q.buf for o in fins for a in att)
+    for a in att:                                                     # a split-K QKV projection accumulates there
+        assert any(o.kind == "LinearSplit" and o.ws.buf is a.q.buf for o in g2.ops)
+    s = schedule(g2, 148)
+    _check_schedule(s, g2)
+    for seed in range(3):
+        _simulate(s, g2, seed)
+    g1, *_ = small_decode(B=1)
+    assert not any(o.zero_inputs for o in run_all(g1, 148).ops if o.kind == "DecodeAttention")
+
+
 def test_schedule_invariants_decode():
     for B, sm in ((1, 148), (16, 148), (2, 8)):
         g, *_ = small_decode(B=B)
