@@ -2,7 +2,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B] [--ctx C] [--impl reference]
 
-Workload (BASELINE.json configs[1]): 16 layers, hidden 2048, 32 q / 8 kv heads, head_dim 64,
+Workload (the reference's batch-1 decode benchmark): 16 layers, hidden 2048, 32 q / 8 kv heads, head_dim 64,
 SwiGLU 8192, vocab 128256 tied, bf16 random-init weights, batch 1, KV caches prefilled to context
 1024, greedy decode.  A step is what the reference times in examples/llama/llama1b.py:103-121:
 embedding gather + copy into x, one megakernel launch, argmax.  With N > 1 every rank runs its own
@@ -30,7 +30,7 @@ ROOT = pathlib.Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 # DRAM bytes of one megakernel launch of the default workload (batch 1, ctx 1024), from one ncu capture
-# (dram__bytes_read.sum + dram__bytes_write.sum; profiles/megakernel_llama1b_decode_b1_ctx1024.md)
+# (dram__bytes_read.sum + dram__bytes_write.sum of the megakernel launch)
 MEASURED_TRAFFIC_B1_CTX1024 = 2_506_453_000 + 6_217_216
 WEIGHT_BYTES = 2 * (16 * (3072 * 2048 + 2048 * 2048 + 16384 * 2048 + 2048 * 8192) + 128256 * 2048)   # 2 471 493 632
 KV_BYTES_PER_TOKEN = 16 * 2 * 512 * 2                                                               # 32 768

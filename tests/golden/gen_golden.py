@@ -27,7 +27,7 @@ ROOT = HERE.parent.parent
 sys.path.insert(0, str(ROOT))
 import os
 
-REF = pathlib.Path(os.environ.get("MEGACUTE_REFERENCE", "/root/reference"))
+REF = pathlib.Path(os.environ.get("MEGACUTE_REFERENCE") or pathlib.Path(__file__).resolve().parents[3] / "reference")
 
 
 def load(path, name):

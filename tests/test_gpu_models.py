@@ -154,7 +154,7 @@ def test_split_k_in_place_residual(cuda):
 
 
 def test_mlp_block_config(cuda):
-    """BASELINE config 1: y = linear(linear(rms_norm(x, nw), w1, swiglu), w2, residual=x), M = 256."""
+    """The single MLP block of the benchmark configurations: y = linear(linear(rms_norm(x, nw), w1, swiglu), w2, residual=x), M = 256."""
     g = mlp_block(256)
     t = {k: v.cpu() for k, v in W.mlp_block_inputs(256, device="cpu").items()}
     outs, ref, _, _, prog = run_both(g, t, cuda, steps=2)
@@ -220,7 +220,7 @@ def test_batched_decode_small(cuda, B):
 
 
 def test_llama_1b_decode_32_greedy_steps(cuda):
-    """BASELINE config 2 at full size: 32 greedy steps, tokens identical to the fp32 evaluation
+    """The headline decode configuration at full size: 32 greedy steps, tokens identical to the fp32 evaluation
     (run on the same GPU in fp32 torch so that it finishes in seconds), logits within tolerance,
     pos and the appended cache rows exact."""
     c = W.LLAMA_1B
