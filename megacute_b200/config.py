@@ -37,6 +37,8 @@ MAX_KV_SPLITS = 32
 DECODE_MERGE_BYTES = 88 * 1024   # shared memory the merging split may fill with partial rows
 # split-KV cost model (us): per instruction; partials + merge when split (base, per split); per key tile
 DEC_FIXED_US, DEC_MERGE_US, DEC_MERGE_US_PER_SPLIT, DEC_TILE_US = 4.0, 1.0, 0.05, 1.1
+# of the fixed cost, the part an instruction pays once however many kv heads it handles (fetch, dependency wait, arrival)
+DEC_SHARED_US = 2.5
 
 # ---- instruction word layout (16 x int32)
 IW = 16

@@ -21,7 +21,8 @@
 // ptr 0 q, 1 k_cache, 2 v_cache, 3 pos, 4 out, 5 k_new, 6 v_new, 7 cos, 8 sin, 9 part, 10 count
 // i 0 B, 1 H, 2 KVH, 3 D, 4 max_seq, 5 splits, 6 fused, 7 dtype of q / k_new / v_new, 8 out dtype,
 //   9 zero q / k_new / v_new after use (they are fp32 columns of a split-K workspace: the instruction that
-//     writes the pair's output hands them back zeroed, as the SplitFinalize it replaces would);  f 0 scale
+//     writes the pair's output hands them back zeroed, as the SplitFinalize it replaces would),
+//   10 kv heads per instruction;  f 0 scale
 // args: 0 b, 1 kv head, 2 split
 #pragma once
 #include "mk_device.cuh"
@@ -376,7 +377,14 @@ template <int D, int GMAX>
 static __device__ __noinline__ bool op_decode_attn(const Params& p, Ctrl* c, const mk_op_desc* op, int a0, int a1, int a2,
                                                    uint8_t* work, int nwait, int wait_off, int seq, int narrive,
                                                    int arrive_off) {
-    decode_body<D, GMAX>(p, c, op, a0, a1, a2, work, nwait, wait_off, seq);
+    // i 10 kv heads per instruction (unsplit batched decode: kv heads a1 .. a1 + i10 - 1 one after the
+    // other; fetch, dependency wait and arrival are paid once)
+    const int hp = op->i[10] > 1 ? op->i[10] : 1;
+    for (int j = 0; j < hp; ++j) {
+        if (j) compute_sync();                                  // the previous head's merge reads the tile buffers
+        decode_body<D, GMAX>(p, c, op, a0, a1 + j, a2, work, j ? 0 : nwait, wait_off, seq);
+        if (*(volatile int*)&c->abort) break;
+    }
     return publish(p, c, narrive, arrive_off);
 }
 

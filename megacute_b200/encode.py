@@ -128,7 +128,7 @@ def fill(d, op: Op, addr) -> None:
         d.kind = C.OP_DECODE_ATTN
         ptrs = [op.q, op.k_cache, op.v_cache, op.pos, op.out, op.k_new, op.v_new, op.cos, op.sin, op.part, op.count]
         ints = [op.batch, op.heads, op.kv_heads, op.head_dim, op.max_seq, op.splits, int(op.k_new is not None),
-                dt(op.q), dt(op.out), int(bool(op.zero_inputs))]
+                dt(op.q), dt(op.out), int(bool(op.zero_inputs)), int(op.heads_per_inst or 1)]
         assert not op.zero_inputs or dt(op.q) == 1
         assert op.k_new is None or dt(op.k_new) == dt(op.v_new) == dt(op.q)
         assert op.splits <= C.MAX_KV_SPLITS

@@ -119,7 +119,7 @@ OP_TABLE = {
                         ("heads", "kv_heads", "head_dim", "max_seq")),
     "DecodeAttention": (("q", "k_cache", "v_cache", "pos", "k_new", "v_new", "cos", "sin", "part", "count"),
                         ("out", "part", "count"),
-                        ("batch", "heads", "kv_heads", "head_dim", "max_seq", "scale", "splits", "zero_inputs")),
+                        ("batch", "heads", "kv_heads", "head_dim", "max_seq", "scale", "splits", "zero_inputs", "heads_per_inst")),
     "Increment":       ((), ("pos",), ()),
 }
 
@@ -271,6 +271,8 @@ def _chk_rope_append(o):
 def _chk_decode_attention(o):
     D = o.head_dim
     o.splits = o.splits or 1
+    o.heads_per_inst = o.heads_per_inst or 1
+    assert o.kv_heads % o.heads_per_inst == 0 and (o.heads_per_inst == 1 or o.splits == 1)
     assert o.heads % o.kv_heads == 0 and o.heads // o.kv_heads <= 8, "decode attention: GQA group <= 8"
     assert D in (64, 128) and o.max_seq % 128 == 0
     assert o.q.shape == o.out.shape == (o.batch, o.heads * D)

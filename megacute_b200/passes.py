@@ -107,6 +107,27 @@ def kv_splits(pairs: int, max_seq: int, sm_count: int, head_dim: int = 64) -> in
     return best
 
 
+def kv_heads_per_instruction(pairs: int, kv_heads: int, max_seq: int, sm_count: int, head_dim: int = 64) -> int:
+    """Unsplit decode attention with more (sequence, kv head) pairs than SMs (batched decode): how many
+    kv heads of a sequence one instruction handles, one after the other.  An instruction's fetch,
+    dependency wait and arrival are paid once, so fewer and longer instructions win as long as they
+    still fill the SMs evenly: waves x (shared cost + heads x (per-head cost + tiles x time per tile)).
+    MEGACUTE_B200_ATT_HEADS overrides the choice (experiments)."""
+    if os.environ.get("MEGACUTE_B200_ATT_HEADS"):
+        h = int(os.environ["MEGACUTE_B200_ATT_HEADS"])
+        return h if h >= 1 and kv_heads % h == 0 else 1
+    tiles = -(-max_seq // (128 if head_dim <= 64 else 64))
+    best, best_cost = 1, float("inf")
+    for h in (1, 2, 4, 8):
+        if kv_heads % h:
+            continue
+        waves = -(-(pairs // h) // sm_count)
+        cost = waves * (C.DEC_SHARED_US + h * (C.DEC_FIXED_US - C.DEC_SHARED_US + tiles * C.DEC_TILE_US))
+        if cost < best_cost - 1e-9:
+            best, best_cost = h, cost
+    return best
+
+
 def split_kv(g: Graph, sm_count: int) -> Graph:
     out = g.derive()
     ops = []
@@ -114,6 +135,10 @@ def split_kv(g: Graph, sm_count: int) -> Graph:
         if op.kind == "DecodeAttention" and op.splits == 1:
             pairs = op.batch * op.kv_heads
             s = kv_splits(pairs, op.max_seq, sm_count, op.head_dim)
+            if s == 1 and (pairs > sm_count or os.environ.get("MEGACUTE_B200_ATT_HEADS")):
+                hpi = kv_heads_per_instruction(pairs, op.kv_heads, op.max_seq, sm_count, op.head_dim)
+                if hpi > 1:
+                    op = op.clone(heads_per_inst=hpi)
             if s > 1:
                 G, D = op.heads // op.kv_heads, op.head_dim
                 cols = -(-(G * D + 2 * G) // 4) * 4          # per split: O (G x D), running max (G), sum (G)

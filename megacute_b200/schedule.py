@@ -208,23 +208,24 @@ def tile_op(op: Op, sm_count: int) -> Tiled:
         return Tiled(_args(n, rt), acc)
     if k == "DecodeAttention":
         D, G, L, S = op.head_dim, op.heads // op.kv_heads, op.max_seq, op.splits
-        b, h, s = (a.ravel() for a in np.meshgrid(np.arange(op.batch), np.arange(op.kv_heads), np.arange(S),
+        hp = op.heads_per_inst or 1          # kv heads h .. h + hp - 1 per instruction (unsplit batched decode)
+        b, h, s = (a.ravel() for a in np.meshgrid(np.arange(op.batch), np.arange(0, op.kv_heads, hp), np.arange(S),
                                                   indexing="ij"))
         n = len(b)
-        cache = lambda v, kind: _acc(v, kind, b * L, (b + 1) * L, h * D, (h + 1) * D, n=n, covers=False)
-        qcols = (h * G * D, (h + 1) * G * D)
+        cache = lambda v, kind: _acc(v, kind, b * L, (b + 1) * L, h * D, (h + hp) * D, n=n, covers=False)
+        qcols = (h * G * D, (h + hp) * G * D)
         acc = [_acc(op.q, READ, b, b + 1, *qcols, n=n, covers=S == 1), _acc(op.pos, READ, n=n),
                cache(op.k_cache, READ), cache(op.v_cache, READ),
                _acc(op.out, WRITE, b, b + 1, *qcols, n=n, covers=S == 1)]
         if op.k_new is not None:
-            acc += [_acc(op.k_new, READ, b, b + 1, h * D, (h + 1) * D, n=n, covers=S == 1),
-                    _acc(op.v_new, READ, b, b + 1, h * D, (h + 1) * D, n=n, covers=S == 1),
+            acc += [_acc(op.k_new, READ, b, b + 1, h * D, (h + hp) * D, n=n, covers=S == 1),
+                    _acc(op.v_new, READ, b, b + 1, h * D, (h + hp) * D, n=n, covers=S == 1),
                     _acc(op.cos, READ, n=n, covers=False), _acc(op.sin, READ, n=n, covers=False),
                     cache(op.k_cache, WRITE), cache(op.v_cache, WRITE)]
         if op.zero_inputs:      # q, k_new, v_new are a split-K workspace, zeroed by the pair's last instruction
             acc += [_acc(op.q, WRITE, b, b + 1, *qcols, n=n, covers=S == 1),
-                    _acc(op.k_new, WRITE, b, b + 1, h * D, (h + 1) * D, n=n, covers=S == 1),
-                    _acc(op.v_new, WRITE, b, b + 1, h * D, (h + 1) * D, n=n, covers=S == 1)]
+                    _acc(op.k_new, WRITE, b, b + 1, h * D, (h + hp) * D, n=n, covers=S == 1),
+                    _acc(op.v_new, WRITE, b, b + 1, h * D, (h + hp) * D, n=n, covers=S == 1)]
         if S > 1:
             r = b * op.kv_heads + h
             acc += [_acc(op.part, WRITE, r * S, (r + 1) * S, n=n, covers=False),

@@ -197,11 +197,16 @@ def test_small_dit_stack(cuda):
     assert_close(outs, ref)
 
 
-@pytest.mark.parametrize("B", [16, 64])
-def test_batched_decode_small(cuda, B):
-    """More than 8 sequences: unfolded norms, tile GEMMs with split-K, many-pair decode attention."""
+@pytest.mark.parametrize("B,att_heads", [(16, None), (64, None), (64, "2")])
+def test_batched_decode_small(cuda, monkeypatch, B, att_heads):
+    """More than 8 sequences: unfolded norms, tile GEMMs with split-K, many-pair decode attention --
+    one kv head per instruction, or (forced here; chosen when there are more pairs than SMs) several."""
+    if att_heads:
+        monkeypatch.setenv("MEGACUTE_B200_ATT_HEADS", att_heads)
     g, params, st, ids = small_decode(B=B, E=256, H=4, KVH=2, F=512, n=2, max_seq=256, ctx=120, vocab=1000)
     prog = mc.compile(g)
+    hp = {o.heads_per_inst for o in prog.g.ops if o.kind == "DecodeAttention"}
+    assert hp == ({2} if att_heads else {1})
     dp = {k: v.to(cuda) for k, v in params.items()}
     ds = {k: v.to(cuda) for k, v in st.items()}
     rs = {k: v.clone() for k, v in st.items()}

@@ -174,6 +174,22 @@ def test_finalize_fused_into_decode_attention():
     assert not any(o.zero_inputs for o in run_all(g1, 148).ops if o.kind == "DecodeAttention")
 
 
+def test_kv_heads_per_instruction_choice_and_schedule():
+    """More (sequence, kv head) pairs than SMs: several kv heads per attention instruction; the
+    schedule of such a graph still orders every hazard."""
+    from megacute_b200.passes import kv_heads_per_instruction
+    assert kv_heads_per_instruction(512, 8, 1280, 148) == 4            # batch 64 of the 1B shape: one wave of 128
+    assert kv_heads_per_instruction(128, 8, 1280, 148) == 1            # fewer pairs than SMs: nothing to amortise over
+    g, *_ = small_decode(B=40, n=1, E=512, H=8, KVH=8, F=512, vocab=512, max_seq=128, ctx=10)
+    g2 = run_all(g, 148)
+    att = [o for o in g2.ops if o.kind == "DecodeAttention"]
+    assert att and all(o.heads_per_inst > 1 and o.splits == 1 for o in att)
+    s = schedule(g2, 148)
+    _check_schedule(s, g2)
+    for seed in range(3):
+        _simulate(s, g2, seed)
+
+
 def test_schedule_invariants_decode():
     for B, sm in ((1, 148), (16, 148), (2, 8)):
         g, *_ = small_decode(B=B)
