@@ -41,7 +41,10 @@ enum {
 /* One graph op as the kernel sees it.  `ptr[k]` is the device byte address of the first element
  * of operand k's view (0 when absent), `ld[k]` its row stride in elements.  The meaning of
  * ptr/i/f per kind is listed in megacute_b200/encode.py next to the code that fills them and in
- * csrc/megakernel.cu next to the code that reads them.  sizeof == 256. */
+ * csrc/megakernel.cu next to the code that reads them.  sizeof == 256.
+ * For MK_OP_GEMM, ptr[10] and ptr[11] belong to the library: mk_program_set_ops overwrites them
+ * (packed weight tiles, tensor maps) when it binds the op to its tcgen05 body; callers that hand
+ * descriptors straight to the kernel (mk_launch_noalloc) leave them 0. */
 typedef struct mk_op_desc {
     int32_t  kind;
     int32_t  flags;

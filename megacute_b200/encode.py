@@ -11,8 +11,9 @@ view's first element.  Field meaning per kind (the kernel side repeats it next t
   GEMV         ptr x, w, out, bias, residual, norm gain; i M, N_out, K, act, x dtype, out dtype,
                residual dtype; f eps; flags 1 = swiglu, 2 = rms-normalise x, 4 = tensor-core streaming path
   GEMM         ptr x, w, out, bias, residual; i M, N (weight rows), K, act, splits, out dtype,
-               accumulate, residual dtype, swiglu
-  FINALIZE     ptr ws, out, bias, residual; i R, C, act, out dtype, residual dtype
+               accumulate, residual dtype, swiglu  (ptr 10, 11: set by the C library when it binds
+               the op to its tcgen05 body: packed weight tiles, tensor maps)
+  FINALIZE     ptr ws, out, bias, residual; i R, C, act, out dtype, residual dtype, rows per instruction
   ELTWISE      ptr a, b, c, out; i R, C, mode, fn, group, head_dim
   NORM         ptr x, out, weight, bias; i R, C, rms, rows per instruction, x dtype; f eps
   ATTENTION    ptr q, k, v, out; i batch, seq_q, seq_k, heads, kv_heads, head_dim, causal; f scale
