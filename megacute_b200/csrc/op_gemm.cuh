@@ -1,13 +1,14 @@
-// MK_OP_GEMM: tiled linear for more than 8 activation rows.
+// MK_OP_GEMM, warp-level mma.sync body: tiled linear for more than 8 activation rows.
 //   out[128 x 128 tile] = act(x @ w^T + bias) + residual        (one instruction per output tile)
 //   ws += x[:, Kj] @ w[:, Kj]^T                                  (split-K partial: reduce-add)
-// Operands stream through a cp.async pipeline of 32-wide k-tiles; the math is warp-level mma.sync
+// The tcgen05 body (op_gemm_tc.cuh) runs the ops the host library binds to it; this one takes the
+// rest: a K range per instruction that is not a multiple of 64, operands not aligned for 16-byte
+// accesses, launches whose descriptors the library never saw (mk_launch_noalloc).
+// Operands stream through a cp.async pipeline of 32- or 64-wide k-tiles; the math is mma.sync
 // m16n8k16 bf16 -> fp32 (8 warps as 2 x 4).  Two shapes: 128 activation rows per tile with 4 stages
 // (warp tile 64 x 32), and, when the op has at most 64 rows (batched decode, where the op is bound
-// by streaming the weights), 64 rows per tile with 6 stages (warp tile 32 x 32): no MMAs on
-// padding rows and 40 KB of weights in flight instead of 24 KB.  This is the portable first
-// implementation of the tile path; the tcgen05 / TMEM version replaces the main loop and keeps
-// this epilogue.
+// by streaming the weights), 64 rows per tile (warp tile 32 x 32): no MMAs on padding rows and more
+// weight bytes in flight.
 //
 // ptr 0 x, 1 w, 2 out (or ws), 3 bias, 4 residual
 // i 0 M, 1 N (weight rows), 2 K, 3 act, 4 splits, 5 out dtype, 6 accumulate, 7 residual dtype,
