@@ -377,12 +377,27 @@ template <int D, int GMAX>
 static __device__ __noinline__ bool op_decode_attn(const Params& p, Ctrl* c, const mk_op_desc* op, int a0, int a1, int a2,
                                                    uint8_t* work, int nwait, int wait_off, int seq, int narrive,
                                                    int arrive_off) {
-    // i 10 kv heads per instruction (unsplit batched decode: kv heads a1 .. a1 + i10 - 1 one after the
-    // other; fetch, dependency wait and arrival are paid once)
-    const int hp = op->i[10] > 1 ? op->i[10] : 1;
+    decode_body<D, GMAX>(p, c, op, a0, a1, a2, work, nwait, wait_off, seq);
+    return publish(p, c, narrive, arrive_off);
+}
+
+// i 10 > 1 (unsplit batched decode): kv heads a1 .. a1 + i10 - 1 of the sequence, one after the other;
+// fetch, dependency wait and arrival are paid once per instruction.  A function of its own: in the
+// single-head function the loop's extra live state costs registers (spills are L2 round trips here).
+template <int D, int GMAX>
+static __device__ __noinline__ void decode_one_head(const Params& p, Ctrl* c, const mk_op_desc* op, int a0, int a1, int a2,
+                                                    uint8_t* work, int nwait, int wait_off, int seq) {
+    decode_body<D, GMAX>(p, c, op, a0, a1, a2, work, nwait, wait_off, seq);
+}
+template <int D, int GMAX>
+static __device__ __noinline__ bool op_decode_attn_heads(const Params& p, Ctrl* c, const mk_op_desc* op, int a0, int a1, int a2,
+                                                         uint8_t* work, int nwait, int wait_off, int seq, int narrive,
+                                                         int arrive_off) {
+    const int hp = op->i[10];
+#pragma unroll 1
     for (int j = 0; j < hp; ++j) {
         if (j) compute_sync();                                  // the previous head's merge reads the tile buffers
-        decode_body<D, GMAX>(p, c, op, a0, a1 + j, a2, work, j ? 0 : nwait, wait_off, seq);
+        decode_one_head<D, GMAX>(p, c, op, a0, a1 + j, a2, work, j ? 0 : nwait, wait_off, seq);
         if (*(volatile int*)&c->abort) break;
     }
     return publish(p, c, narrive, arrive_off);
