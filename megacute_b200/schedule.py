@@ -386,14 +386,18 @@ def schedule(g: Graph, sm_count: int = 148) -> Schedule:
         for ka, o in sorted(dep.items()):
             a0 = node_ranges[ka][0]
             packed = np.packbits(o, axis=1)
-            uniq, inv = np.unique(packed, axis=0, return_inverse=True)
-            inv = inv.reshape(-1)
-            for u in range(len(uniq)):
-                rows = np.nonzero(inv == u)[0]
+            # consumers with the same producer set share a counter: group the packed rows (a dict on
+            # the rows' bytes, visited in lexicographic order as np.unique(axis=0) would return them;
+            # its structured-dtype sort took most of the scheduling time of a prefill graph)
+            groups: dict[bytes, list[int]] = {}
+            for i, row in enumerate(packed):
+                groups.setdefault(row.tobytes(), []).append(i)
+            for row_bytes in sorted(groups):
+                rows = groups[row_bytes]
                 members = np.nonzero(o[rows[0]])[0]
                 if len(members) == 0:
                     continue
-                key = (ka, uniq[u].tobytes())
+                key = (ka, row_bytes)
                 c = counter_key.get(key)
                 if c is None:
                     c = counter_key[key] = len(counter_members)
