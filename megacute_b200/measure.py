@@ -1,0 +1,90 @@
+"""Kernel-time measurements of the tensor-bound benchmark configurations (the decode step has its own
+driver, ``bench.py``):
+
+    python -m megacute_b200.measure [mlp_block] [dit] [prefill]
+
+* ``mlp_block``: RMS norm -> gate/up + swiglu -> down + residual, 256 rows, 2048 -> 2 x 5632 -> 2048
+* ``dit``: 28 DiT blocks, 32 images x 256 tokens, width 1024, 16 heads, MLP 4096
+* ``prefill``: Llama-3.2-1B shape, 4 sequences x 4096 tokens, 16 layers + lm_head
+
+Synthetic bf16 inputs and weights of those shapes; each configuration is compiled once, warmed up
+twice, then timed over a few launches with CUDA events on the launching stream.  Prints one line
+per configuration: time per launch and TFLOP/s against the configuration's algorithmic flops.
+"""
+
+from __future__ import annotations
+
+import sys
+import time
+
+import torch
+
+import megacute_b200 as mc
+from megacute_b200 import workloads as W
+from megacute_b200.builders import dit_stack, llama_stack, mlp_block
+
+
+def _time(prog, args, launches):
+    for _ in range(2):
+        prog(**args)
+    prog.check()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(launches):
+        prog(**args)
+    e1.record()
+    torch.cuda.synchronize()
+    prog.check()
+    return e0.elapsed_time(e1) / launches
+
+
+def measure_mlp_block(dev):
+    g = mlp_block(256)
+    prog = mc.compile(g)
+    ms = _time(prog, W.mlp_block_inputs(device=dev), 20)
+    flop = 2 * 256 * 2048 * 11264 + 2 * 256 * 5632 * 2048
+    return ms, flop, prog
+
+
+def measure_dit(dev):
+    g = dit_stack(32, 256, 1024, 16, 4096, 28)
+    prog = mc.compile(g)
+    ms = _time(prog, W.dit_inputs(32, 256, 1024, 4096, 28, 0, dev), 3)
+    return ms, 6.02e12, prog
+
+
+def measure_prefill(dev):
+    c = W.LLAMA_1B
+    g = llama_stack(4, 4096, c["E"], c["H"], c["KVH"], c["F"], c["n"], vocab=c["vocab"])
+    prog = mc.compile(g)
+    w = W.llama_weights(c["E"], c["H"], c["KVH"], c["F"], c["n"], c["vocab"], 0, dev)
+    x = torch.randn(4 * 4096, c["E"], device=dev, dtype=torch.bfloat16)
+    cos, sin = W.rope_tables(4096, c["E"] // c["H"], c["theta"], dev)
+    names = {b.name for b in prog.g.inputs + prog.g.params + prog.g.states}
+    args = {k: v for k, v in dict(x=x, cos=cos, sin=sin, **w).items() if k in names}
+    ms = _time(prog, args, 2)
+    return ms, 3.63e13, prog
+
+
+CONFIGS = {"mlp_block": measure_mlp_block, "dit": measure_dit, "prefill": measure_prefill}
+
+
+def main(argv):
+    names = argv or list(CONFIGS)
+    unknown = [n for n in names if n not in CONFIGS]
+    if unknown:
+        raise SystemExit(f"unknown configuration(s) {unknown}; choose from {list(CONFIGS)}")
+    if not torch.cuda.is_available():
+        raise SystemExit("a CUDA device (B200) is required: there is no CPU path")
+    dev = torch.device("cuda", 0)
+    for n in names:
+        t0 = time.time()
+        ms, flop, prog = CONFIGS[n](dev)
+        print(f"{n}: {ms * 1e3:.1f} us per launch, {flop / ms / 1e9:.0f} TFLOP/s, {prog.tcgen05_ops} tile-GEMM ops on tcgen05, "
+              f"{prog.packed_weight_bytes / 1e6:.0f} MB of packed weights, compiled and measured in {time.time() - t0:.1f} s")
+        del prog
+        torch.cuda.empty_cache()
+
+
+if __name__ == "__main__":
+    main(sys.argv[1:])
