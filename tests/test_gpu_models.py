@@ -224,6 +224,32 @@ def test_batched_decode_small(cuda, monkeypatch, B, att_heads):
     assert np.array_equal(prog.counters(), prog.sched.counter_target * 3)
 
 
+def test_batched_decode_workspace_inputs_with_kv_splits(cuda, monkeypatch):
+    """Split-K QKV projection feeding the fused decode attention straight from its fp32 workspace, with
+    the KV range split over several instructions: the pair's last instruction to arrive zeroes the
+    workspace columns, so three consecutive steps (which accumulate into the same workspace) stay
+    right."""
+    monkeypatch.setenv("MEGACUTE_B200_KV_SPLITS", "3")
+    g, params, st, ids = small_decode(B=16, E=2048, H=32, KVH=8, F=512, n=1, max_seq=512, ctx=300, vocab=512)
+    prog = mc.compile(g)
+    att = [o for o in prog.g.ops if o.kind == "DecodeAttention"]
+    assert att and all(o.zero_inputs and o.splits == 3 for o in att)
+    dp = {k: v.to(cuda) for k, v in params.items()}
+    ds = {k: v.to(cuda) for k, v in st.items()}
+    rs = {k: v.clone() for k, v in st.items()}
+    for step in range(3):
+        logits = prog(**dp, **ds).float().cpu()
+        ref, new = evaluate(g, {**params, **rs})
+        assert rel_l2(logits, ref[0]) < TOL, (step, rel_l2(logits, ref[0]))
+        for n_ in ("pos", "k_cache", "v_cache"):
+            rs[n_] = new[n_]
+        rs["x"] = params["lm_head"][ref[0].argmax(-1)].clone()
+        ds["x"].copy_(rs["x"].to(cuda))
+    prog.check()
+    # (split-K sums arrive in any order, so an appended key may differ from the oracle's by a bf16 ulp)
+    assert rel_l2(ds["k_cache"].float().cpu(), rs["k_cache"].float()) < 1e-3 and int(ds["pos"]) == 303
+
+
 def test_llama_1b_decode_32_greedy_steps(cuda):
     """The headline decode configuration at full size: 32 greedy steps, tokens identical to the fp32 evaluation
     (run on the same GPU in fp32 torch so that it finishes in seconds), logits within tolerance,
