@@ -127,10 +127,13 @@ int mk_program_epoch(mk_program* p);
  * not a multiple of 64, unaligned operands, or MEGACUTE_B200_NO_TCGEN05 set). */
 int mk_program_tcgen05_ops(mk_program* p);
 /* Device memory the program holds for tile-image copies of the weights of those ops (made by
- * mk_program_set_ops unless MEGACUTE_B200_NO_WEIGHT_PACK is set, freed when another set of
- * addresses is bound or the program is destroyed).  The copies are snapshots: after changing
- * weights in place, call mk_program_set_ops again. */
+ * mk_program_set_ops unless MEGACUTE_B200_NO_WEIGHT_PACK is set, when a weight matrix is bound
+ * for the first time; kept while that matrix stays bound, freed when it is no longer bound or the
+ * program is destroyed).  The copies are snapshots of the weights. */
 long long mk_program_packed_bytes(mk_program* p);
+/* After changing weights in place: drop the packed copies (synchronises `stream`); the next
+ * mk_program_set_ops packs again. */
+int mk_program_refresh_weights(mk_program* p, void* stream);
 int mk_program_read_counters(mk_program* p, int32_t* out, int n);
 int mk_program_read_trace(mk_program* p, int64_t* out, size_t n_words);
 int mk_program_clear_trace(mk_program* p, void* stream);

@@ -225,7 +225,7 @@ struct mk_program {
     uint8_t* h_tmaps = nullptr;      // pinned staging copy
     struct Packed {                  // tile-image copy of one weight matrix (see pack_weight_tiles)
         uint64_t src; int N, K, ld;
-        uint8_t* buf; size_t bytes; bool used;
+        uint8_t* buf; size_t bytes; bool used, fresh;
     };
     std::vector<Packed> packed;
     int64_t* d_trace = nullptr;
@@ -403,14 +403,16 @@ int mk_program_set_ops(mk_program* p, const mk_op_desc* ops, int n_ops, void* st
         uint8_t* maps = p->h_tmaps + (size_t)k * 256;
         d.ptr[10] = 0;
         if (!encode_tile_map(maps, d.ptr[0], d.i[0], d.i[2], d.ld[0], d.i[0] <= 64 ? 64 : 128, false)) continue;
-        // weights: the packed copy (taken again at every call of this function: the snapshot follows
-        // a rebind; weights changed in place need another call), else a tensor map over the matrix
+        // weights: the packed copy, made when a matrix (address, shape, pitch) is bound for the first
+        // time and kept while it stays bound -- rebinding other operands (a new input tensor every
+        // call) must not copy gigabytes of weights again; weights changed in place need
+        // mk_program_refresh_weights -- else a tensor map over the matrix
         if (!pack_off && !(d.ptr[1] & 15) && d.ld[1] % 8 == 0) {
             mk_program::Packed* hit = nullptr;
             for (auto& e : p->packed)
                 if (e.src == d.ptr[1] && e.N == d.i[1] && e.K == d.i[2] && e.ld == d.ld[1]) hit = &e;
             if (!hit) {
-                mk_program::Packed e{d.ptr[1], d.i[1], d.i[2], d.ld[1], nullptr, 0, false};
+                mk_program::Packed e{d.ptr[1], d.i[1], d.i[2], d.ld[1], nullptr, 0, false, true};
                 e.bytes = (size_t)((d.i[1] + 127) / 128) * 128 * (size_t)d.i[2] * 2;
                 if (cudaMalloc(&e.buf, e.bytes) == cudaSuccess) {
                     p->packed.push_back(e);
@@ -420,14 +422,15 @@ int mk_program_set_ops(mk_program* p, const mk_op_desc* ops, int n_ops, void* st
                 }
             }
             if (hit) {
-                if (!hit->used) {
+                if (hit->fresh) {       // a copy made by this call: fill it (once, however many ops share the matrix)
                     const long long chunks = (long long)(hit->bytes / 16);
                     const int blocks = (int)((chunks + 255) / 256 < 4096 ? (chunks + 255) / 256 : 4096);
                     mk::pack_weight_tiles<<<blocks, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(hit->src), hit->ld, hit->N,
                                                                   hit->K, reinterpret_cast<uint4*>(hit->buf), chunks);
                     MK_CUDA(cudaGetLastError());
-                    hit->used = true;
+                    hit->fresh = false;
                 }
+                hit->used = true;
                 d.ptr[10] = reinterpret_cast<uint64_t>(hit->buf);
             }
         }
@@ -510,6 +513,14 @@ int mk_program_reset(mk_program* p, void* stream) {
 int mk_program_epoch(mk_program* p) { return p ? p->epoch : MK_E_ARG; }
 
 int mk_program_tcgen05_ops(mk_program* p) { return p ? p->tcgen05_ops : MK_E_ARG; }
+
+int mk_program_refresh_weights(mk_program* p, void* stream) {
+    if (!p) return MK_E_ARG;
+    MK_CUDA(cudaStreamSynchronize((cudaStream_t)stream));       // no launch may still be reading the copies
+    for (auto& e : p->packed) cudaFree(e.buf);
+    p->packed.clear();
+    return MK_OK;
+}
 
 long long mk_program_packed_bytes(mk_program* p) {
     if (!p) return MK_E_ARG;

@@ -159,9 +159,18 @@ class Program:
 
     @property
     def packed_weight_bytes(self) -> int:
-        """Device memory held for tile-image copies of tile-GEMM weights (snapshots taken when the
-        operand addresses are bound; rebind after changing weights in place)."""
+        """Device memory held for tile-image copies of tile-GEMM weights (snapshots taken when a weight
+        tensor is first bound; `refresh_weights()` after changing weights in place)."""
         return int(_lib.load().mk_program_packed_bytes(self._handle)) if self._handle is not None else 0
+
+    def refresh_weights(self):
+        """Call after changing bound weights in place: the packed tile copies of tile-GEMM weights are
+        dropped and made again at the next launch."""
+        if self._handle is None:
+            return
+        stream = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+        _lib.check(_lib.load().mk_program_refresh_weights(self._handle, stream), "mk_program_refresh_weights")
+        self._desc_key = None
 
     def check(self):
         """Synchronise and raise if the kernel reported an error (bounded wait gave up, bad table)."""

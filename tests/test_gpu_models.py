@@ -78,6 +78,19 @@ def test_tile_linear_weight_sources_and_rebind(cuda, monkeypatch):
     ref2, _ = evaluate(g, t2)
     assert rel_l2(out2.float().cpu(), ref2[0]) < TOL
     assert prog_p.packed_weight_bytes == 1536 * 2048 * 2            # the first copy was freed
+    # weights changed in place: the snapshot is stale until refresh_weights()
+    dev2["w"].mul_(0.5)
+    t3 = dict(t2, w=(t2["w"].float() * 0.5).to(BF))
+    prog_p.refresh_weights()
+    out3 = prog_p(**dev2)
+    prog_p.check()
+    ref3, _ = evaluate(g, t3)
+    assert rel_l2(out3.float().cpu(), ref3[0]) < TOL
+    # another input tensor, same weights: bound again, not packed again
+    dev2["x"] = dev2["x"].clone()
+    out4 = prog_p(**dev2)
+    prog_p.check()
+    assert torch.equal(out4, out3) and prog_p.packed_weight_bytes == 1536 * 2048 * 2
     monkeypatch.setenv("MEGACUTE_B200_NO_WEIGHT_PACK", "1")
     outs_t, _, _, _, prog_t = run_both(g, t, cuda)
     assert prog_t.tcgen05_ops >= 1 and prog_t.packed_weight_bytes == 0
