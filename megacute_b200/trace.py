@@ -11,75 +11,97 @@ chrome_events, save_chrome).  This kernel has three record kinds per SM:
                      dependencies: streaming linear (x staged, first stage landed, last group
                      done) and decode attention (tiles done, partial written, merged)
 Times are globaltimer nanoseconds rebased to the earliest record.
+
+The records are kept as one structured numpy table (``Timeline.table``) and every report is a
+column operation on it; ``records`` is the same data as the reference's list of tuples.
 """
 
 from __future__ import annotations
 
 import json
-from collections import defaultdict
 
 import numpy as np
 
-ROLES = ("producer", "compute")
+ROLES = ("producer", "compute", "phases")
+_REC = np.dtype([("sm", np.int32), ("role", np.int32), ("seq", np.int64), ("t0", np.int64), ("t1", np.int64),
+                 ("t2", np.int64)])
 
 
 class Timeline:
     def __init__(self, prog, buf: np.ndarray):
         self.prog = prog
-        sms, roles, cap, _ = buf.shape
-        idx = np.argwhere(buf[..., 1] != 0)
-        self.records = [(int(sm), int(role), *(int(x) for x in buf[sm, role, ev])) for sm, role, ev in idx]
-        self.t_base = min((r[3] for r in self.records), default=0)
-        self.op_of = prog.sched.op_of
+        self.op_of = np.asarray(prog.sched.op_of)
+        sm, role, ev = np.nonzero(buf[..., 1])               # a record whose t0 is 0 was never written
+        tab = np.empty(len(sm), _REC)
+        tab["sm"], tab["role"] = sm, role
+        for k, name in enumerate(("seq", "t0", "t1", "t2")):
+            tab[name] = buf[sm, role, ev, k]
+        self.table = tab
+        self.t_base = int(tab["t0"].min()) if len(tab) else 0
+
+    @property
+    def records(self):
+        """[(sm, role, seq, t0, t1, t2)] with plain ints, in (sm, role, slot) order."""
+        return [tuple(int(x) for x in r) for r in self.table.tolist()]
+
+    def _us(self, t):
+        return (np.asarray(t, np.float64) - self.t_base) * 1e-3
 
     def span_us(self) -> float:
-        if not self.records:
-            return 0.0
-        return (max(r[5] for r in self.records) - self.t_base) / 1e3
+        return float(self._us(self.table["t2"].max())) if len(self.table) else 0.0
 
-    def _label(self, seq):
-        k = int(self.op_of[seq])
+    def _label(self, seq) -> str:
+        k = int(self.op_of[int(seq)])
         return f"{k}:{self.prog.g.ops[k].kind}"
+
+    def node_table(self) -> np.ndarray:
+        """One row per node that ran: node, instructions, first fetch, last publish, mean wait for
+        dependencies and mean busy time per instruction (us), from the compute-role records."""
+        c = self.table[self.table["role"] == 1]
+        node = np.array([self.prog.node_of[int(k)][0] for k in self.op_of[c["seq"]]], np.int64)
+        ids, inv, n = np.unique(node, return_inverse=True, return_counts=True)
+        out = np.zeros(len(ids), [("node", np.int64), ("insts", np.int64), ("start", np.float64), ("end", np.float64),
+                                  ("dep", np.float64), ("busy", np.float64)])
+        out["node"], out["insts"] = ids, n
+        first = np.full(len(ids), np.inf)
+        last = np.full(len(ids), -np.inf)
+        np.minimum.at(first, inv, self._us(c["t0"]))
+        np.maximum.at(last, inv, self._us(c["t2"]))
+        out["start"], out["end"] = first, last
+        out["dep"] = np.bincount(inv, (c["t1"] - c["t0"]) * 1e-3, len(ids)) / n
+        out["busy"] = np.bincount(inv, (c["t2"] - c["t1"]) * 1e-3, len(ids)) / n
+        return out
 
     def summary(self) -> str:
         """Per node: instructions, first start, last end, mean dependency wait, mean busy time (us)."""
-        agg = defaultdict(lambda: {"n": 0, "dep": 0.0, "busy": 0.0, "first": 1e30, "last": 0.0})
-        for sm, role, seq, t0, t1, t2 in self.records:
-            if role != 1:
-                continue
-            a = agg[self.prog.node_of[int(self.op_of[seq])][0]]
-            a["n"] += 1
-            a["dep"] += (t1 - t0) / 1e3
-            a["busy"] += (t2 - t1) / 1e3
-            a["first"] = min(a["first"], (t0 - self.t_base) / 1e3)
-            a["last"] = max(a["last"], (t2 - self.t_base) / 1e3)
-        lines = [f"launch span {self.span_us():.1f} us over {len({r[0] for r in self.records})} SMs; "
-                 f"{sum(1 for r in self.records if r[1] == 1)} instructions traced",
-                 f"{'node':<24}{'insts':>7}{'start':>9}{'end':>9}{'dep-wait/inst':>15}{'busy/inst':>12}"]
-        for n in sorted(agg):
-            a = agg[n]
-            kind = self.prog.nodes[n][0].kind
-            lines.append(f"{n:>3} {kind:<20}{a['n']:>7}{a['first']:>9.1f}{a['last']:>9.1f}"
-                         f"{a['dep'] / a['n']:>15.2f}{a['busy'] / a['n']:>12.2f}")
-        return "\n".join(lines)
+        tab = self.table
+        head = (f"launch span {self.span_us():.1f} us over {len(np.unique(tab['sm']))} SMs; "
+                f"{int((tab['role'] == 1).sum())} instructions traced")
+        cols = f"{'node':<24}{'insts':>7}{'start':>9}{'end':>9}{'dep-wait/inst':>15}{'busy/inst':>12}"
+        rows = [f"{int(r['node']):>3} {self.prog.nodes[int(r['node'])][0].kind:<20}{int(r['insts']):>7}{r['start']:>9.1f}"
+                f"{r['end']:>9.1f}{r['dep']:>15.2f}{r['busy']:>12.2f}" for r in self.node_table()]
+        return "\n".join([head, cols, *rows])
 
     def chrome_events(self):
-        ev = []
-        us = lambda t: (t - self.t_base) / 1e3
-        for sm, role, seq, t0, t1, t2 in self.records:
-            name = self._label(seq)
-            if role == 0:
-                ev.append({"name": "stream " + name, "ph": "X", "pid": sm, "tid": ROLES[0], "ts": us(t0),
-                           "dur": max(0.0, (t2 - t0) / 1e3), "args": {"inst": seq}})
-            else:
-                if t1 > t0:
-                    ev.append({"name": "wait " + name, "ph": "X", "pid": sm, "tid": ROLES[1], "ts": us(t0),
-                               "dur": (t1 - t0) / 1e3, "args": {"inst": seq}})
-                ev.append({"name": name, "ph": "X", "pid": sm, "tid": ROLES[1], "ts": us(t1),
-                           "dur": max(0.0, (t2 - t1) / 1e3), "args": {"inst": seq}})
-        return ev
+        """Complete ("X") events, one process per SM and one thread per role: the producer's streaming
+        span, and per instruction its dependency wait (when it had one) and its busy span."""
+        tab = self.table
+        out = []
+
+        def emit(rows, prefix, tid, a, b):
+            ts, dur = self._us(rows[a]), np.maximum(0.0, (rows[b] - rows[a]) * 1e-3)
+            for r, t, d in zip(rows, ts.tolist(), dur.tolist()):
+                out.append({"name": prefix + self._label(r["seq"]), "ph": "X", "pid": int(r["sm"]), "tid": tid, "ts": t,
+                            "dur": d, "args": {"inst": int(r["seq"])}})
+
+        emit(tab[tab["role"] == 0], "stream ", ROLES[0], "t0", "t2")
+        comp = tab[tab["role"] == 1]
+        emit(comp[comp["t1"] > comp["t0"]], "wait ", ROLES[1], "t0", "t1")
+        emit(comp, "", ROLES[1], "t1", "t2")
+        return out
 
     def save_chrome(self, path):
+        doc = {"traceEvents": self.chrome_events(), "displayTimeUnit": "ns"}
         with open(path, "w") as f:
-            json.dump({"traceEvents": self.chrome_events(), "displayTimeUnit": "ns"}, f)
+            json.dump(doc, f)
         return path

@@ -14,6 +14,12 @@ cannot run without a Blackwell GPU and nvidia-cutlass-dsl 4.8.0, so these are wh
   oracle_small.pt    seeded inputs of two small graphs built by the REFERENCE's builders and the
                      fp32 oracle's outputs on them (ties the oracle's duck-typed reading of the
                      reference's op dataclasses to this repository's graphs)
+  ref_passes.pt      for graphs built by the reference's builders: the oracle's result on the graph as
+                     built, and on the graph rewritten by the REFERENCE's own passes
+                     (megacute/runtime.py:44-199: fold_norms, split_k, fuse_rope_attention, split_kv).
+                     Both must agree, which pins the oracle's reading of LinearSplit, SplitFinalize,
+                     folded rms_eps over a derived weight and the fused DecodeAttention against the
+                     reference's own rewrites
 """
 import importlib.util
 import json
@@ -64,6 +70,70 @@ CONFIGS = {
 }
 
 
+PASS_CASES = {
+    # name: (builder, kwargs, context length of the caches)
+    "decode_b1_splitkv": ("llama_decode", dict(B=1, E=256, H=4, KVH=2, F=512, n=2, max_seq=1024, vocab=1000, eps=1e-5), 700),
+    "decode_b2_fold": ("llama_decode", dict(B=2, E=256, H=4, KVH=2, F=512, n=2, max_seq=256, vocab=1000, eps=1e-5), 40),
+    "decode_b16_splitk": ("llama_decode", dict(B=16, E=256, H=4, KVH=2, F=512, n=2, max_seq=256, vocab=1000, eps=1e-5), 90),
+    "decode_b40_head_parallel": ("llama_decode", dict(B=40, E=512, H=8, KVH=8, F=512, n=1, max_seq=128, vocab=512, eps=1e-5), 30),
+    "mlp_block": ("mlp_block", dict(M=136, E=256, F=512), 0),
+    "dit_stack": ("dit_stack", dict(B=2, S=64, E=128, H=2, F=256, n=2), 0),
+}
+
+
+def pass_case_inputs(name):
+    """Seeded inputs of a PASS_CASES entry (shared with tests/test_oracle.py)."""
+    from megacute_b200 import workloads as W
+    kind, c, ctx = PASS_CASES[name]
+    if kind == "llama_decode":
+        w = W.llama_weights(c["E"], c["H"], c["KVH"], c["F"], c["n"], c["vocab"], 0, "cpu")
+        st, ids = W.llama_decode_state(c["B"], c["E"], c["H"], c["KVH"], c["n"], c["max_seq"], ctx, c["vocab"], 1, "cpu")
+        cos, sin = W.rope_tables(c["max_seq"], c["E"] // c["H"])
+        st["x"] = w["lm_head"][ids].clone()
+        return dict(cos=cos, sin=sin, **w, **st)
+    if kind == "mlp_block":
+        return W.mlp_block_inputs(c["M"], c["E"], c["F"], 0, "cpu")
+    return W.dit_inputs(c["B"], c["S"], c["E"], c["F"], c["n"], 0, "cpu")
+
+
+def ref_mlp_block(ref, M, E, F, eps=1e-5):
+    """The single-block graph of the reference's README (README.md:14-20), on its own Graph class."""
+    g = ref.Graph()
+    x = g.input("x", (M, E))
+    nw, w1, w2 = g.param("nw", (1, E)), g.param("w1", (2 * F, E)), g.param("w2", (E, F))
+    g.output(g.linear(g.linear(g.rms_norm(x, nw, eps), w1, act="swiglu"), w2, residual=x))
+    return g
+
+
+def gen_ref_passes(ref, llama, dit):
+    import importlib
+    from oracle.graph_oracle import evaluate
+    rt = importlib.import_module("megacute.runtime")
+    out = {}
+    for name, (kind, c, ctx) in PASS_CASES.items():
+        g = {"llama_decode": llama.llama_decode, "dit_stack": dit.dit_stack,
+             "mlp_block": lambda **kw: ref_mlp_block(ref, **kw)}[kind](**c)
+        g2 = rt.split_kv(rt.fuse_rope_attention(rt.split_k(rt.fold_norms(g), 148)), 148)      # runtime.py:235
+        t = pass_case_inputs(name)
+        a, sa = evaluate(g, t)
+        b, sb = evaluate(g2, t)
+        rec = {"rewritten": b[0], "plain_vs_rewritten": float((a[0] - b[0]).norm() / a[0].norm()), "ops": [type(o).__name__ for o in g2.ops],
+               "flags": sorted({k for o in g2.ops for k in ("rms_eps", "head_parallel", "k_new")
+                                if getattr(o, k, None) not in (None, False)} |
+                               ({"splits"} if any(getattr(o, "splits", 1) > 1 and type(o).__name__ == "DecodeAttention" for o in g2.ops) else set()) |
+                               ({"derived"} if any(b_.kind == "derived" for b_ in g2.buffers) else set()))}
+        if kind == "llama_decode":
+            L = c["max_seq"]
+            rows = [i * L + ctx for i in range(c["n"] * c["B"])]
+            assert int(sa["pos"]) == int(sb["pos"]) == ctx + 1
+            rec.update(pos_rewritten=sb["pos"], k_rows_rewritten=sb["k_cache"][rows].clone(),
+                       v_rows_rewritten=sb["v_cache"][rows].clone(),
+                       k_rows_equal=bool(torch.equal(sa["k_cache"][rows], sb["k_cache"][rows])))
+        out[name] = rec
+    torch.save(out, HERE / "ref_passes.pt")
+    return out
+
+
 def main():
     import megacute as ref                       # the reference package (PYTHONPATH)
     assert "reference" in str(pathlib.Path(ref.__file__).resolve()), ref.__file__
@@ -93,6 +163,8 @@ def main():
     o, _ = evaluate(graphs["dit_stack"], t)
     out["dit_stack"] = {"out": o[0]}
     torch.save(out, HERE / "oracle_small.pt")
+    for name, rec in gen_ref_passes(ref, llama, dit).items():
+        print(f"ref passes {name}: rel-L2 plain vs rewritten {rec['plain_vs_rewritten']:.2e}; flags {rec['flags']}; ops {sorted(set(rec['ops']))}")
     print("wrote", [p.name for p in HERE.iterdir()])
 
 
