@@ -66,13 +66,13 @@ typedef struct mk_caps {
 
 /* status words written by the device and returned by mk_program_status() */
 enum { MK_ST_CODE = 0, MK_ST_CTA, MK_ST_WARP, MK_ST_SEQ, MK_ST_WHERE, MK_ST_A, MK_ST_B, MK_ST_C, MK_ST_WORDS = 16 };
-/* MK_ST_CODE values */
+/* MK_ST_CODE values (MK_DEV_BAD_INST: an instruction names no op, or an op kind the kernel does not know) */
 enum { MK_DEV_OK = 0, MK_DEV_TIMEOUT_COUNTER = 1, MK_DEV_TIMEOUT_BARRIER = 2, MK_DEV_BAD_INST = 3 };
 
 enum {
     MK_OK = 0,
     MK_E_CUDA = -1,          /* a CUDA runtime call failed: see mk_last_cuda_error()        */
-    MK_E_ARG = -2,           /* null / out-of-range argument                                 */
+    MK_E_ARG = -2,           /* null / out-of-range argument: mk_last_cuda_error() may say which */
     MK_E_ARCH = -3,          /* the device is not compute capability 10.x                    */
     MK_E_DEVICE = -4,        /* the kernel reported an error in the status buffer            */
     MK_E_NOMEM = -5,
@@ -82,6 +82,7 @@ enum {
 typedef struct mk_program mk_program;
 
 const char* mk_strerror(int code);
+/* Detail of the calling thread's latest MK_E_CUDA or MK_E_ARG ("" when there is none). */
 const char* mk_last_cuda_error(void);
 
 /* Replaces: torch.cuda.get_device_properties(0).multi_processor_count (runtime.py:234). */
@@ -93,7 +94,8 @@ int mk_query(int device, mk_caps* caps);
  *                                  9 = first wait pair, 10 = #arrives, 11 = first arrive, 12 = seq
  *   waits    [n_waits][2]  int32   (counter, arrivals per launch)
  *   arrives  [n_arrives]   int32   counter ids
- *   grid                            CTAs to launch (normally the SM count); CTA c runs
+ *   grid                            CTAs to launch (normally the SM count, never more: every CTA must be
+ *                                  resident at once, a larger grid is MK_E_ARG); CTA c runs
  *                                  instructions c, c + grid, ...
  *   trace_cap                      per-(CTA, role) trace records, 0 = tracing off                 */
 int mk_program_create(int device, const int32_t* insts, int n_insts, const int32_t* waits, int n_waits,
@@ -101,7 +103,13 @@ int mk_program_create(int device, const int32_t* insts, int n_insts, const int32
                       int trace_cap, mk_program** out);
 
 /* (Re)bind operand addresses: copy n_ops descriptors to the device on `stream`.  Replaces the
- * per-call strided-view tuple of Program._view_tensors (runtime.py:356-369). */
+ * per-call strided-view tuple of Program._view_tensors (runtime.py:356-369).  Asynchronous (two
+ * pinned staging copies are used in turn; the stream is not synchronised).  Before anything is
+ * copied every instruction's arguments are checked against the extents its descriptor states
+ * (tile, head and split indices, output ranges): MK_E_ARG, with the instruction named by
+ * mk_last_cuda_error(), instead of an out-of-bounds access on the device.
+ * Every function of a program makes the program's device current for the duration of the call and
+ * puts the caller's current device back before it returns. */
 int mk_program_set_ops(mk_program* p, const mk_op_desc* ops, int n_ops, void* stream);
 
 /* One launch of the persistent kernel on `stream` (asynchronous).  Replaces
@@ -128,8 +136,9 @@ int mk_program_epoch(mk_program* p);
 int mk_program_tcgen05_ops(mk_program* p);
 /* Device memory the program holds for tile-image copies of the weights of those ops (made by
  * mk_program_set_ops unless MEGACUTE_B200_NO_WEIGHT_PACK is set, when a weight matrix is bound
- * for the first time; kept while that matrix stays bound, freed when it is no longer bound or the
- * program is destroyed).  The copies are snapshots of the weights. */
+ * for the first time; kept while that matrix stays bound; a copy that is no longer bound is not
+ * counted here and is freed once every launch enqueued before the rebind has finished).  The copies
+ * are snapshots of the weights. */
 long long mk_program_packed_bytes(mk_program* p);
 /* After changing weights in place: drop the packed copies (synchronises `stream`); the next
  * mk_program_set_ops packs again. */
@@ -163,11 +172,19 @@ void mk_program_destroy(mk_program* p);
  * outside any stream capture.  Every call on a device shares the one array and starts by clearing
  * the counters it uses on `stream`; two calls whose kernels may overlap on the GPU (different
  * streams) race on it -- serialise them.  Split-KV workspaces named by the descriptors must be zero
- * on entry, as for mk_launch. */
+ * on entry, as for mk_launch.  The wait and arrival tables are device memory the library cannot read:
+ * every counter id in them must be below n_counters (mk_program_create checks this for its host
+ * tables; here it is the caller's precondition).  grid must not exceed the device's SM count.  The
+ * caller's current device is unchanged on return. */
 #define MK_NOALLOC_MAX_COUNTERS 16384
 int mk_launch_noalloc(int device, const int32_t* d_insts, int n_insts, const int32_t* d_waits, int n_waits,
                       const int32_t* d_arrives, int n_arrives, const mk_op_desc* d_ops, int n_ops,
                       int n_counters, int grid, void* stream, int32_t status[MK_ST_WORDS]);
+
+/* Status words of the latest mk_launch_noalloc on `device`, for callers that passed status == NULL
+ * there: waits for `stream`, copies the 16 words out, MK_E_DEVICE if the kernel reported an error.
+ * Allocates nothing.  (No counterpart in the reference.) */
+int mk_noalloc_status(int device, void* stream, int32_t status[MK_ST_WORDS]);
 
 /* Greedy sampling: out[r] = index of the largest element of row r of `logits` (rows x cols, leading
  * dimension ld in elements; dtype 0 bf16 with ld % 8 == 0 and a 16-byte aligned base, 1 fp32), ties to

@@ -16,7 +16,7 @@ PKG = pathlib.Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB_PATH = pathlib.Path(os.environ.get("MEGACUTE_B200_LIB", PKG / "libmegacute_b200.so"))
 # Relocatable device code: each op body is its own translation unit so that ptxas allocates its
-# registers independently (csrc/ops.cuh says why).  -maxrregcount is the cap of a 9-warp CTA
+# registers independently (csrc/ops.cuh says why).  -maxrregcount is the cap of a 10-warp CTA
 # (three warps share one SM sub-partition's 16 K registers); callees in other translation units do
 # not see the kernel's __launch_bounds__.
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-rdc=true",
@@ -64,6 +64,7 @@ SYMBOLS = {
     "mk_program_destroy": (None, [_P]),
     "mk_launch_noalloc": (ctypes.c_int, [ctypes.c_int, _P, ctypes.c_int, _P, ctypes.c_int, _P, ctypes.c_int, _P, ctypes.c_int,
                                          ctypes.c_int, ctypes.c_int, _P, _I32P]),
+    "mk_noalloc_status": (ctypes.c_int, [ctypes.c_int, _P, _I32P]),
     "mk_argmax": (ctypes.c_int, [_P, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_longlong, _P, _P]),
 }
 
@@ -129,6 +130,8 @@ def check(rc: int, what: str = ""):
         return
     lib = load()
     msg = lib.mk_strerror(rc).decode()
-    if rc == -1:
-        msg += ": " + lib.mk_last_cuda_error().decode()
+    if rc in (-1, -2):                   # CUDA errors and argument errors carry a detail message
+        detail = lib.mk_last_cuda_error().decode()
+        if detail:
+            msg += ": " + detail
     raise MegakernelError(f"{what}: {msg}" if what else msg)

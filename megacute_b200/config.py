@@ -1,4 +1,4 @@
-"""Constants shared by the host scheduler and the CUDA kernel (mirrored in csrc/mk_abi.h).
+"""Constants shared by the host scheduler and the CUDA kernel (mirrored in csrc/mk_device.cuh and include/megacute_b200.h).
 
 The reference keeps its equivalents in ``megacute/config.py`` (CTA shape, tile sizes, instruction
 word layout) and ``megacute/runtime.py:28-29`` (split cost model); the values here are this
@@ -49,7 +49,7 @@ W_NWAIT, W_WAIT_OFF = 8, 9      # wait table slice: pairs (counter, target)
 W_NARRIVE, W_ARRIVE_OFF = 10, 11
 W_SEQ = 12                      # global instruction index
 
-# ---- device op kinds (mk_abi.h: MK_OP_*)
+# ---- device op kinds (include/megacute_b200.h: MK_OP_*)
 OP_GEMV, OP_GEMM, OP_FINALIZE, OP_ELTWISE, OP_NORM, OP_ATTENTION, OP_ROPE_APPEND, OP_DECODE_ATTN, OP_INCREMENT = \
     range(1, 10)
 

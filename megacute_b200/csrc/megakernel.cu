@@ -1,12 +1,15 @@
 // The persistent megakernel and its C ABI (include/megacute_b200.h).  sm_100a only.
 //
-// One launch executes a whole graph.  grid = number of SMs, one CTA per SM, 9 warps:
+// One launch executes a whole graph.  grid = number of SMs, one CTA per SM, 10 warps:
 //   warps 0-7  compute: fetch this CTA's next instruction (global indices c, c+grid, ...), wait
 //              for its dependency counters (acquire), run the op, publish its arrivals (release);
 //   warp 8     producer: walks the same instruction list ahead of the compute warps and streams
-//              the weight rows of every GEMV instruction into the shared-memory ring with bulk
-//              copies, across instruction boundaries -- weights depend on nothing in the launch,
-//              so HBM keeps streaming while the compute warps sit in a dependency hop.
+//              the weight rows of every streaming linear (and the weight tiles of every tcgen05
+//              tile GEMM) into shared memory with bulk copies, across instruction boundaries --
+//              weights depend on nothing in the launch, so HBM keeps streaming while the compute
+//              warps sit in a dependency hop;
+//   warp 9     finisher: adds the compute warps' partial tiles of a streaming linear, runs its
+//              epilogue and sends the instruction's arrivals.
 // This replaces the reference's JIT-traced kernel (megacute/kernel.py:251-571) and its per-op
 // role bodies (megacute/ops/*.py).
 #include <cuda.h>          // CUtensorMap and cuTensorMapEncodeTiled's signature (resolved at run time, libcuda is not linked)
@@ -220,14 +223,24 @@ struct mk_program {
     int32_t* d_arrives = nullptr;
     int32_t* d_counters = nullptr;
     mk_op_desc* d_ops = nullptr;
-    mk_op_desc* h_ops = nullptr;     // pinned staging copy
     uint8_t* d_tmaps = nullptr;      // per op: two 128-byte tensor maps (tile GEMM: activations, weights)
-    uint8_t* h_tmaps = nullptr;      // pinned staging copy
+    // Two pinned staging copies of the descriptor and tensor-map tables, used in turn: a rebind fills
+    // the one whose upload (two rebinds ago) has completed -- its event says so -- instead of
+    // synchronising the stream, so a caller that binds a fresh input tensor every call never
+    // waits for the previous launch.
+    mk_op_desc* h_ops[2] = {nullptr, nullptr};
+    uint8_t* h_tmaps[2] = {nullptr, nullptr};
+    cudaEvent_t staged[2] = {nullptr, nullptr};
+    int stage_turn = 0;
+    std::vector<int32_t> h_insts;    // host copy of the instruction words (argument checks at bind time)
     struct Packed {                  // tile-image copy of one weight matrix (see pack_weight_tiles)
         uint64_t src; int N, K, ld;
         uint8_t* buf; size_t bytes; bool used, fresh;
     };
     std::vector<Packed> packed;
+    struct Retired { uint8_t* buf; cudaEvent_t done; };   // packed copies no longer bound: freed once `done` has passed
+    std::vector<Retired> retired;
+    cudaStream_t last_stream = nullptr;                   // stream of the latest launch
     int64_t* d_trace = nullptr;
     int32_t* d_status = nullptr;
     int32_t* h_status = nullptr;     // pinned
@@ -249,6 +262,31 @@ static int cuda_fail(cudaError_t e, const char* what) {
         cudaError_t e_ = (call);                             \
         if (e_ != cudaSuccess) return cuda_fail(e_, #call);  \
     } while (0)
+
+// Makes `device` current for the lifetime of the object and puts the caller's device back after.
+// Every entry point that allocates, copies or launches runs under one: a program belongs to one GPU,
+// but the calling thread's current device is the caller's business (torch keeps its own notion of it).
+struct DeviceGuard {
+    int prev = -1;
+    bool ok = true;
+    explicit DeviceGuard(int device) {
+        if (cudaGetDevice(&prev) != cudaSuccess) { prev = -1; (void)cudaGetLastError(); }
+        if (prev != device) {
+            cudaError_t e = cudaSetDevice(device);
+            if (e != cudaSuccess) { cuda_fail(e, "cudaSetDevice"); ok = false; prev = -1; }
+        } else {
+            prev = -1;                                  // nothing to restore
+        }
+    }
+    ~DeviceGuard() {
+        if (prev >= 0) (void)cudaSetDevice(prev);
+    }
+    DeviceGuard(const DeviceGuard&) = delete;
+    DeviceGuard& operator=(const DeviceGuard&) = delete;
+};
+#define MK_ON_DEVICE(dev)            \
+    DeviceGuard guard_(dev);         \
+    if (!guard_.ok) return MK_E_CUDA
 
 // Tensor map over a row-major bf16 matrix {cols, rows} with row pitch `ld` elements: boxes of 64
 // columns x `box_rows` rows, stored with the 128-byte swizzle (the operand tile layout of the tcgen05 tile
@@ -298,6 +336,77 @@ static bool tile_gemm_on_tcgen05(const mk_op_desc& d) {
     return true;
 }
 
+// Bind-time check of the instruction table against the op descriptors: every argument an op body
+// turns into an address (tile, row-group, head, split indices; output-column ranges) must lie inside
+// the extents the descriptor states.  The kernel trusts its tables; this is where a table built for
+// another graph, or a descriptor with a shrunken extent, is caught -- as an error code here instead of
+// an out-of-bounds access on the device.  On failure the message names the instruction.
+static int verify_tables(const mk_program* p, const mk_op_desc* ops) {
+    const int W = MK_INST_WORDS;
+    auto ceil_div = [](long long a, long long b) { return (a + b - 1) / b; };
+    for (int k = 0; k < p->n_insts; ++k) {
+        const int32_t* w = p->h_insts.data() + (size_t)k * W;
+        const int opi = w[0] - 1;
+        const char* why = nullptr;
+        if (opi < 0 || opi >= p->n_ops) {
+            why = "op index out of range";
+        } else {
+            const mk_op_desc& d = ops[opi];
+            const long long a0 = w[1], a1 = w[2], a2 = w[3];
+            switch (d.kind) {
+                case MK_OP_GEMV:
+                    if (!(0 <= a0 && a0 < a1 && a1 <= d.i[1])) why = "streaming linear: output range outside [0, N)";
+                    break;
+                case MK_OP_GEMM:
+                    if (d.i[4] <= 0) why = "tile GEMM: split count";
+                    else if (a0 < 0 || a0 * 128 >= d.i[0]) why = "tile GEMM: m tile outside M";
+                    else if (a1 < 0 || a1 * 128 >= d.i[1]) why = "tile GEMM: n tile outside N";
+                    else if (a2 < 0 || a2 >= d.i[4]) why = "tile GEMM: K split index";
+                    break;
+                case MK_OP_FINALIZE:
+                    if (d.i[5] <= 0 || a0 < 0 || a0 >= ceil_div(d.i[0], d.i[5]) || a1 < 0 || a1 * 512 >= d.i[1]) why = "finalize: tile outside the output";
+                    break;
+                case MK_OP_ELTWISE:
+                    if (a0 < 0 || a0 * 32 >= d.i[0] || a1 < 0 || a1 * 512 >= d.i[1]) why = "pointwise: tile outside the output";
+                    break;
+                case MK_OP_NORM:
+                    if (d.i[3] <= 0 || a0 < 0 || a0 * d.i[3] >= d.i[0]) why = "norm: row group outside the rows";
+                    break;
+                case MK_OP_ATTENTION:
+                    if (a0 < 0 || a0 >= d.i[0] || a1 < 0 || a1 >= d.i[3] || a2 < 0 || a2 * 128 >= d.i[1]) why = "attention: (batch, head, query tile)";
+                    break;
+                case MK_OP_ROPE_APPEND:
+                    if (a0 < 0 || a0 * 8 >= d.i[0]) why = "rope_append: row group outside the batch";
+                    break;
+                case MK_OP_DECODE_ATTN: {
+                    const int hp = d.i[10] > 0 ? d.i[10] : 1;
+                    if (a0 < 0 || a0 >= d.i[0] || a1 < 0 || a1 + hp > d.i[2] || a2 < 0 || a2 >= (d.i[5] > 0 ? d.i[5] : 1))
+                        why = "decode attention: (sequence, kv head, split)";
+                    break;
+                }
+                case MK_OP_INCREMENT: break;
+                default: why = "unknown op kind";
+            }
+        }
+        if (why) {
+            snprintf(g_cuda_err, sizeof g_cuda_err, "instruction %d (op %d): %s", k, opi, why);
+            return MK_E_ARG;
+        }
+    }
+    return MK_OK;
+}
+
+static void free_retired(mk_program* p, bool wait) {
+    for (size_t e = 0; e < p->retired.size();) {
+        auto& r = p->retired[e];
+        if (wait) (void)cudaEventSynchronize(r.done);
+        else if (cudaEventQuery(r.done) != cudaSuccess) { (void)cudaGetLastError(); ++e; continue; }
+        cudaFree(r.buf);
+        cudaEventDestroy(r.done);
+        p->retired.erase(p->retired.begin() + e);
+    }
+}
+
 extern "C" {
 
 const char* mk_strerror(int code) {
@@ -333,16 +442,30 @@ int mk_query(int device, mk_caps* caps) {
     return MK_OK;
 }
 
-int mk_program_create(int device, const int32_t* insts, int n_insts, const int32_t* waits, int n_waits,
-                      const int32_t* arrives, int n_arrives, int n_counters, int n_ops, int grid, int trace_cap,
-                      mk_program** out) {
-    if (!out || !insts || n_insts <= 0 || n_ops <= 0 || grid <= 0 || n_waits < 0 || n_arrives < 0) return MK_E_ARG;
-    if ((n_waits && !waits) || (n_arrives && !arrives)) return MK_E_ARG;
+// The schedule is deadlock-free only if every CTA of the grid is resident at once (a CTA waits on
+// counters that CTAs with lower instruction numbers publish): one CTA per SM with this kernel's
+// shared memory, so a grid larger than the device's SM count is an argument error, not a timeout.
+static int check_grid(int device, int grid) {
     mk_caps caps;
     int rc = mk_query(device, &caps);
     if (rc != MK_OK) return rc;
     if (caps.max_smem_optin < mk::kSmemBytes) return MK_E_ARCH;
-    MK_CUDA(cudaSetDevice(device));
+    if (grid <= 0 || grid > caps.sm_count) {
+        snprintf(g_cuda_err, sizeof g_cuda_err, "grid %d: must be 1..%d (the device's SM count; all CTAs must be co-resident)", grid, caps.sm_count);
+        return MK_E_ARG;
+    }
+    return MK_OK;
+}
+
+int mk_program_create(int device, const int32_t* insts, int n_insts, const int32_t* waits, int n_waits,
+                      const int32_t* arrives, int n_arrives, int n_counters, int n_ops, int grid, int trace_cap,
+                      mk_program** out) {
+    g_cuda_err[0] = 0;
+    if (!out || !insts || n_insts <= 0 || n_ops <= 0 || grid <= 0 || n_waits < 0 || n_arrives < 0) return MK_E_ARG;
+    if ((n_waits && !waits) || (n_arrives && !arrives)) return MK_E_ARG;
+    int rc = check_grid(device, grid);
+    if (rc != MK_OK) return rc;
+    MK_ON_DEVICE(device);
     mk_program* p = new (std::nothrow) mk_program();
     if (!p) return MK_E_NOMEM;
     p->device = device; p->grid = grid; p->n_insts = n_insts; p->n_waits = n_waits; p->n_arrives = n_arrives;
@@ -353,6 +476,16 @@ int mk_program_create(int device, const int32_t* insts, int n_insts, const int32
     }
     for (int k = 0; k < n_arrives; ++k)
         if (arrives[k] < 0 || arrives[k] >= p->n_counters) { delete p; return MK_E_ARG; }
+    // every instruction's wait and arrival slices must lie inside their tables
+    for (int k = 0; k < n_insts; ++k) {
+        const int32_t* w = insts + (size_t)k * MK_INST_WORDS;
+        if (w[8] < 0 || w[9] < 0 || (long long)w[8] + w[9] > n_waits || w[10] < 0 || w[11] < 0 || (long long)w[10] + w[11] > n_arrives) {
+            delete p;
+            snprintf(g_cuda_err, sizeof g_cuda_err, "instruction %d: wait / arrival slice outside its table", k);
+            return MK_E_ARG;
+        }
+    }
+    p->h_insts.assign(insts, insts + (size_t)n_insts * MK_INST_WORDS);
 #define MK_TRY(call) do { cudaError_t e_ = (call); if (e_ != cudaSuccess) { cuda_fail(e_, #call); mk_program_destroy(p); return MK_E_CUDA; } } while (0)
     MK_TRY(cudaMalloc(&p->d_insts, (size_t)n_insts * MK_INST_WORDS * 4));
     MK_TRY(cudaMemcpy(p->d_insts, insts, (size_t)n_insts * MK_INST_WORDS * 4, cudaMemcpyHostToDevice));
@@ -363,9 +496,12 @@ int mk_program_create(int device, const int32_t* insts, int n_insts, const int32
     MK_TRY(cudaMalloc(&p->d_counters, (size_t)p->n_counters * 4));
     MK_TRY(cudaMemset(p->d_counters, 0, (size_t)p->n_counters * 4));
     MK_TRY(cudaMalloc(&p->d_ops, (size_t)n_ops * sizeof(mk_op_desc)));
-    MK_TRY(cudaMallocHost(&p->h_ops, (size_t)n_ops * sizeof(mk_op_desc)));
     MK_TRY(cudaMalloc(&p->d_tmaps, (size_t)n_ops * 256));
-    MK_TRY(cudaMallocHost(&p->h_tmaps, (size_t)n_ops * 256));
+    for (int b = 0; b < 2; ++b) {
+        MK_TRY(cudaMallocHost(&p->h_ops[b], (size_t)n_ops * sizeof(mk_op_desc)));
+        MK_TRY(cudaMallocHost(&p->h_tmaps[b], (size_t)n_ops * 256));
+        MK_TRY(cudaEventCreateWithFlags(&p->staged[b], cudaEventDisableTiming));
+    }
     MK_TRY(cudaMalloc(&p->d_status, MK_ST_WORDS * 4));
     MK_TRY(cudaMemset(p->d_status, 0, MK_ST_WORDS * 4));
     MK_TRY(cudaMallocHost(&p->h_status, MK_ST_WORDS * 4));
@@ -383,11 +519,19 @@ int mk_program_create(int device, const int32_t* insts, int n_insts, const int32
 }
 
 int mk_program_set_ops(mk_program* p, const mk_op_desc* ops, int n_ops, void* stream) {
+    g_cuda_err[0] = 0;
     if (!p || !ops || n_ops != p->n_ops) return MK_E_ARG;
+    int rc = verify_tables(p, ops);
+    if (rc != MK_OK) return rc;
+    MK_ON_DEVICE(p->device);
     cudaStream_t st = (cudaStream_t)stream;
-    // the staging copy may still be in flight from an earlier rebind on this stream
-    MK_CUDA(cudaStreamSynchronize(st));
-    memcpy(p->h_ops, ops, (size_t)n_ops * sizeof(mk_op_desc));
+    // this turn's staging copy was last uploaded two rebinds ago; wait for that upload only
+    const int turn = p->stage_turn;
+    p->stage_turn ^= 1;
+    MK_CUDA(cudaEventSynchronize(p->staged[turn]));
+    mk_op_desc* h_ops = p->h_ops[turn];
+    uint8_t* h_tmaps = p->h_tmaps[turn];
+    memcpy(h_ops, ops, (size_t)n_ops * sizeof(mk_op_desc));
     // Tile GEMMs get tensor maps over their activations and weights (ptr 11): with them the kernel
     // runs the tcgen05 body and streams the weight tiles through the producer warp's ring.
     bool any_map = false;
@@ -396,11 +540,11 @@ int mk_program_set_ops(mk_program* p, const mk_op_desc* ops, int n_ops, void* st
     const bool pack_off = getenv("MEGACUTE_B200_NO_WEIGHT_PACK") != nullptr;
     for (auto& e : p->packed) e.used = false;
     for (int k = 0; k < n_ops; ++k) {
-        mk_op_desc& d = p->h_ops[k];
+        mk_op_desc& d = h_ops[k];
         if (d.kind != MK_OP_GEMM) continue;
         d.ptr[11] = 0;
         if (tc_off || !tile_gemm_on_tcgen05(d)) continue;
-        uint8_t* maps = p->h_tmaps + (size_t)k * 256;
+        uint8_t* maps = h_tmaps + (size_t)k * 256;
         d.ptr[10] = 0;
         if (!encode_tile_map(maps, d.ptr[0], d.i[0], d.i[2], d.ld[0], d.i[0] <= 64 ? 64 : 128, false)) continue;
         // weights: the packed copy, made when a matrix (address, shape, pitch) is bound for the first
@@ -412,9 +556,16 @@ int mk_program_set_ops(mk_program* p, const mk_op_desc* ops, int n_ops, void* st
             for (auto& e : p->packed)
                 if (e.src == d.ptr[1] && e.N == d.i[1] && e.K == d.i[2] && e.ld == d.ld[1]) hit = &e;
             if (!hit) {
+                free_retired(p, false);
                 mk_program::Packed e{d.ptr[1], d.i[1], d.i[2], d.ld[1], nullptr, 0, false, true};
                 e.bytes = (size_t)((d.i[1] + 127) / 128) * 128 * (size_t)d.i[2] * 2;
-                if (cudaMalloc(&e.buf, e.bytes) == cudaSuccess) {
+                cudaError_t err = cudaMalloc(&e.buf, e.bytes);
+                if (err != cudaSuccess && !p->retired.empty()) {       // out of memory with copies waiting to be freed
+                    (void)cudaGetLastError();
+                    free_retired(p, true);
+                    err = cudaMalloc(&e.buf, e.bytes);
+                }
+                if (err == cudaSuccess) {
                     p->packed.push_back(e);
                     hit = &p->packed.back();
                 } else {
@@ -441,15 +592,30 @@ int mk_program_set_ops(mk_program* p, const mk_op_desc* ops, int n_ops, void* st
         }
     }
     p->tcgen05_ops = n_tc;
-    // packed copies of matrices that are no longer bound (the stream was synchronised above, so no
-    // launch is still reading them)
+    // Packed copies of matrices that are no longer bound are retired, not freed: launches enqueued
+    // before this rebind may still read them.  An event on `stream` (and on the stream of the latest
+    // launch, if another) marks the point after which they are free; they are released by a later
+    // rebind that finds the event passed, by mk_program_refresh_weights or by mk_program_destroy.
     for (size_t e = 0; e < p->packed.size();) {
         if (p->packed[e].used) { ++e; continue; }
-        cudaFree(p->packed[e].buf);
+        mk_program::Retired r{p->packed[e].buf, nullptr};
+        MK_CUDA(cudaEventCreateWithFlags(&r.done, cudaEventDisableTiming));
+        if (p->last_stream != st) {
+            // order this stream behind the latest launch, so that one event covers both
+            cudaEvent_t ev;
+            MK_CUDA(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+            MK_CUDA(cudaEventRecord(ev, p->last_stream));
+            MK_CUDA(cudaStreamWaitEvent(st, ev, 0));
+            MK_CUDA(cudaEventDestroy(ev));
+        }
+        MK_CUDA(cudaEventRecord(r.done, st));
+        p->retired.push_back(r);
         p->packed.erase(p->packed.begin() + e);
     }
-    if (any_map) MK_CUDA(cudaMemcpyAsync(p->d_tmaps, p->h_tmaps, (size_t)n_ops * 256, cudaMemcpyHostToDevice, st));
-    MK_CUDA(cudaMemcpyAsync(p->d_ops, p->h_ops, (size_t)n_ops * sizeof(mk_op_desc), cudaMemcpyHostToDevice, st));
+    free_retired(p, false);
+    if (any_map) MK_CUDA(cudaMemcpyAsync(p->d_tmaps, h_tmaps, (size_t)n_ops * 256, cudaMemcpyHostToDevice, st));
+    MK_CUDA(cudaMemcpyAsync(p->d_ops, h_ops, (size_t)n_ops * sizeof(mk_op_desc), cudaMemcpyHostToDevice, st));
+    MK_CUDA(cudaEventRecord(p->staged[turn], st));
     return MK_OK;
 }
 
@@ -461,6 +627,7 @@ int mk_program_set_timeout(mk_program* p, uint64_t ns) {
 
 int mk_launch(mk_program* p, void* stream) {
     if (!p) return MK_E_ARG;
+    MK_ON_DEVICE(p->device);
     cudaStream_t st = (cudaStream_t)stream;
     const int max_epoch = 0x7fffffff / (p->max_target > 0 ? p->max_target : 1) - 1;
     if (p->epoch >= max_epoch) {
@@ -468,6 +635,7 @@ int mk_launch(mk_program* p, void* stream) {
         p->epoch = 0;
     }
     p->epoch += 1;
+    p->last_stream = st;
     mk::Params prm;
     prm.insts = reinterpret_cast<const int4*>(p->d_insts);
     prm.n_insts = p->n_insts;
@@ -490,6 +658,7 @@ int mk_launch(mk_program* p, void* stream) {
 
 int mk_program_status(mk_program* p, void* stream, int32_t status[MK_ST_WORDS]) {
     if (!p) return MK_E_ARG;
+    MK_ON_DEVICE(p->device);
     cudaStream_t st = (cudaStream_t)stream;
     MK_CUDA(cudaMemcpyAsync(p->h_status, p->d_status, MK_ST_WORDS * 4, cudaMemcpyDeviceToHost, st));
     MK_CUDA(cudaStreamSynchronize(st));
@@ -503,6 +672,7 @@ int mk_program_status(mk_program* p, void* stream, int32_t status[MK_ST_WORDS]) 
 
 int mk_program_reset(mk_program* p, void* stream) {
     if (!p) return MK_E_ARG;
+    MK_ON_DEVICE(p->device);
     cudaStream_t st = (cudaStream_t)stream;
     MK_CUDA(cudaMemsetAsync(p->d_counters, 0, (size_t)p->n_counters * 4, st));
     MK_CUDA(cudaMemsetAsync(p->d_status, 0, MK_ST_WORDS * 4, st));
@@ -516,9 +686,12 @@ int mk_program_tcgen05_ops(mk_program* p) { return p ? p->tcgen05_ops : MK_E_ARG
 
 int mk_program_refresh_weights(mk_program* p, void* stream) {
     if (!p) return MK_E_ARG;
+    MK_ON_DEVICE(p->device);
     MK_CUDA(cudaStreamSynchronize((cudaStream_t)stream));       // no launch may still be reading the copies
+    if (p->last_stream != (cudaStream_t)stream) MK_CUDA(cudaStreamSynchronize(p->last_stream));
     for (auto& e : p->packed) cudaFree(e.buf);
     p->packed.clear();
+    free_retired(p, true);
     return MK_OK;
 }
 
@@ -531,6 +704,7 @@ long long mk_program_packed_bytes(mk_program* p) {
 
 int mk_program_read_counters(mk_program* p, int32_t* out, int n) {
     if (!p || !out || n < 0 || n > p->n_counters) return MK_E_ARG;
+    MK_ON_DEVICE(p->device);
     MK_CUDA(cudaMemcpy(out, p->d_counters, (size_t)n * 4, cudaMemcpyDeviceToHost));
     return MK_OK;
 }
@@ -538,6 +712,7 @@ int mk_program_read_counters(mk_program* p, int32_t* out, int n) {
 int mk_program_read_trace(mk_program* p, int64_t* out, size_t n_words) {
     if (!p || !out || !p->d_trace) return MK_E_ARG;
     if (n_words > (size_t)p->grid * mk::kTraceRoles * p->trace_cap * 4) return MK_E_ARG;
+    MK_ON_DEVICE(p->device);
     MK_CUDA(cudaMemcpy(out, p->d_trace, n_words * 8, cudaMemcpyDeviceToHost));
     return MK_OK;
 }
@@ -545,12 +720,14 @@ int mk_program_read_trace(mk_program* p, int64_t* out, size_t n_words) {
 int mk_program_clear_trace(mk_program* p, void* stream) {
     if (!p) return MK_E_ARG;
     if (!p->d_trace) return MK_OK;
+    MK_ON_DEVICE(p->device);
     MK_CUDA(cudaMemsetAsync(p->d_trace, 0, (size_t)p->grid * mk::kTraceRoles * p->trace_cap * 4 * 8, (cudaStream_t)stream));
     return MK_OK;
 }
 
 int mk_program_poke_wait(mk_program* p, int wait_index, int counter, int target) {
     if (!p || wait_index < 0 || wait_index >= p->n_waits || counter < 0 || counter >= p->n_counters) return MK_E_ARG;
+    MK_ON_DEVICE(p->device);
     int32_t pair[2] = {counter, target};
     MK_CUDA(cudaMemcpy(p->d_waits + 2 * wait_index, pair, 8, cudaMemcpyHostToDevice));
     return MK_OK;
@@ -558,11 +735,16 @@ int mk_program_poke_wait(mk_program* p, int wait_index, int counter, int target)
 
 void mk_program_destroy(mk_program* p) {
     if (!p) return;
+    DeviceGuard guard(p->device);
+    free_retired(p, true);
     cudaFree(p->d_insts); cudaFree(p->d_waits); cudaFree(p->d_arrives); cudaFree(p->d_counters);
     cudaFree(p->d_ops); cudaFree(p->d_trace); cudaFree(p->d_status); cudaFree(p->d_tmaps);
     for (auto& e : p->packed) cudaFree(e.buf);
-    if (p->h_ops) cudaFreeHost(p->h_ops);
-    if (p->h_tmaps) cudaFreeHost(p->h_tmaps);
+    for (int b = 0; b < 2; ++b) {
+        if (p->h_ops[b]) cudaFreeHost(p->h_ops[b]);
+        if (p->h_tmaps[b]) cudaFreeHost(p->h_tmaps[b]);
+        if (p->staged[b]) cudaEventDestroy(p->staged[b]);
+    }
     if (p->h_status) cudaFreeHost(p->h_status);
     delete p;
 }
@@ -591,24 +773,25 @@ static int32_t* g_noalloc_ptr[kMaxDevices];          // per device: looked-up ad
 extern "C" int mk_launch_noalloc(int device, const int32_t* d_insts, int n_insts, const int32_t* d_waits, int n_waits,
                                  const int32_t* d_arrives, int n_arrives, const mk_op_desc* d_ops, int n_ops,
                                  int n_counters, int grid, void* stream, int32_t status[MK_ST_WORDS]) {
+    g_cuda_err[0] = 0;
     if (device < 0 || device >= kMaxDevices || !d_insts || n_insts <= 0 || !d_ops || n_ops <= 0 || grid <= 0 ||
         n_waits < 0 || n_arrives < 0 || n_counters < 0 || (n_waits && !d_waits) || (n_arrives && !d_arrives))
         return MK_E_ARG;
     if (n_counters > MK_NOALLOC_MAX_COUNTERS) return MK_E_TOO_LARGE;
     cudaStream_t st = (cudaStream_t)stream;
-    int current = -1;
-    MK_CUDA(cudaGetDevice(&current));
-    if (current != device) MK_CUDA(cudaSetDevice(device));
+    MK_ON_DEVICE(device);                               // the caller's current device is put back on return
     if (!g_noalloc_ptr[device]) {
         // one-time set-up for this device (do this first call outside any stream capture)
-        mk_caps caps;
-        int rc = mk_query(device, &caps);
+        int rc = check_grid(device, grid);
         if (rc != MK_OK) return rc;
-        if (caps.max_smem_optin < mk::kSmemBytes) return MK_E_ARCH;
         int32_t* ptr = nullptr;
         MK_CUDA(cudaGetSymbolAddress((void**)&ptr, g_noalloc_scratch));
         MK_CUDA(cudaFuncSetAttribute(mk::megakernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, mk::kSmemBytes));
         g_noalloc_ptr[device] = ptr;
+    } else {
+        int sms = 0;
+        MK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+        if (grid > sms) return MK_E_ARG;               // all CTAs must be co-resident (see check_grid)
     }
     int32_t* scratch = g_noalloc_ptr[device];
     int32_t* d_status = scratch + MK_NOALLOC_MAX_COUNTERS;
@@ -637,4 +820,16 @@ extern "C" int mk_launch_noalloc(int device, const int32_t* d_insts, int n_insts
         if (status[MK_ST_CODE] != 0) return MK_E_DEVICE;
     }
     return MK_OK;
+}
+
+// Status of the latest mk_launch_noalloc on `device` for callers that passed status == NULL: waits for
+// `stream`, copies the static status words out.  Allocates nothing.
+extern "C" int mk_noalloc_status(int device, void* stream, int32_t status[MK_ST_WORDS]) {
+    if (device < 0 || device >= kMaxDevices || !status) return MK_E_ARG;
+    if (!g_noalloc_ptr[device]) return MK_E_ARG;        // no mk_launch_noalloc on this device yet
+    MK_ON_DEVICE(device);
+    cudaStream_t st = (cudaStream_t)stream;
+    MK_CUDA(cudaMemcpyAsync(status, g_noalloc_ptr[device] + MK_NOALLOC_MAX_COUNTERS, MK_ST_WORDS * 4, cudaMemcpyDeviceToHost, st));
+    MK_CUDA(cudaStreamSynchronize(st));
+    return status[MK_ST_CODE] != 0 ? MK_E_DEVICE : MK_OK;
 }

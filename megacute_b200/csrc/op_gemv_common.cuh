@@ -1,11 +1,12 @@
 // MK_OP_GEMV: linear with <= 8 activation rows, out = act(norm(x) @ w^T + bias) + residual.
 //
-// Pure weight streaming.  The producer warp copies weight rows into a ring of 32 KB stages with
-// 1-D bulk copies (one per row, completion counted on the stage's mbarrier) and runs ahead of the
-// compute warps across instruction boundaries, because weights never depend on anything in the
-// launch.  A stage holds 8 row slots x 2048 K-elements; compute thread t owns K-elements
-// [8t, 8t+8) of every slot, so its slice of the activation is loaded once per stage and reused
-// for the 8 rows.  Partial dot products are reduced across the CTA once per group of 8 rows.
+// Pure weight streaming.  The producer warp copies weight rows into a ring of two 64 KB stages with
+// 1-D bulk copies (one 4 KB copy per row segment, completion counted on the stage's mbarrier) and
+// runs ahead of the compute warps across instruction boundaries, because weights never depend on
+// anything in the launch.  On the tensor-core path (GEMV_F_UNITS, below) a stage holds 16 weight
+// rows x one 2048-element K segment; on the general CUDA-core path (op_gemv.cuh: K not a multiple of
+// 16) it holds 8 row slots x 2048 K-elements, compute thread t owns K-elements [8t, 8t+8) of every
+// slot, and partial dot products are reduced across the CTA once per group of 8 rows.
 //
 // descriptor: ptr 0 x, 1 w, 2 out, 3 bias, 4 residual, 5 norm gain
 //             i 0 M, 1 N_out, 2 K, 3 act, 4 x dtype, 5 out dtype, 6 residual dtype
@@ -19,7 +20,7 @@ namespace mk {
 
 constexpr int GEMV_F_SWIGLU = 1, GEMV_F_RMS = 2;
 // GEMV_F_UNITS (set by the host when K is a multiple of 16): the tensor-core streaming path.
-// A stage is 16 weight rows x one 1024-element K segment.  Each compute warp multiplies a 128-wide
+// A stage is 16 weight rows x one 2048-element K segment.  Each compute warp multiplies a 256-wide
 // K slice of the 16 rows with warp-level MMAs (weights are the A operand straight from the stage via
 // ldmatrix; the <= 8 activation rows are the B operand, split into bf16 high and low parts so the
 // product keeps ~16 mantissa bits of the activation), accumulates over the segments of the row

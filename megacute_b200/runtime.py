@@ -29,6 +29,15 @@ from .schedule import schedule
 
 
 class Program:
+    """A compiled graph bound to one GPU.
+
+    Tile-GEMM weights (linears with more than 8 activation rows) are read from packed tile copies the
+    library makes when a weight tensor is first bound.  The copies are snapshots: a parameter changed
+    in place through torch is noticed at the next call (its version counter moved) and packed again;
+    a change torch cannot see (a raw pointer write, another process) needs ``refresh_weights()``.
+    Linears with at most 8 rows stream the caller's tensors directly.
+    """
+
     def __init__(self, g: Graph, *, sm_count: int | None = None, verbose: bool = False, debug: bool = False,
                  trace: bool = False, device: int | None = None):
         t0 = time.time()
@@ -47,6 +56,13 @@ class Program:
         for op in self.g.ops:
             encode.validate(op)
         self.sched = schedule(self.g, self.sm_count)
+        if self.debug or os.environ.get("MEGACUTE_B200_VERIFY") == "1":
+            # exact host checks of the tables (see verify.py); the happens-before closure keeps
+            # n^2 / 8 bytes, so very long instruction streams (full prefill) get the table check only
+            from . import verify
+            verify.check_tables(self.g, self.sched)
+            if self.sched.n <= 40000:
+                verify.check_hazards(self.sched, self.g)
         groups = [[k] for k in range(len(self.g.ops))] if os.environ.get("MEGACUTE_NO_MERGE") == "1" \
             else merge_layers(self.g)
         self.node_of = [None] * len(self.g.ops)
@@ -59,6 +75,10 @@ class Program:
         self._bufs: dict[int, torch.Tensor] = {}
         self._desc = (_lib.OpDesc * max(1, len(self.g.ops)))()
         self._desc_key = None
+        self._ops_of_buf: dict[int, list[int]] = {}        # buffer id -> ops with an operand in it
+        for k, op in enumerate(self.g.ops):
+            for _, v in op.view_fields():
+                self._ops_of_buf.setdefault(v.buf.id, []).append(k)
         self.trace_cap = 0
         self.schedule_seconds = time.time() - t0
         self.compile_seconds = self.schedule_seconds
@@ -122,15 +142,37 @@ class Program:
         t = self._bufs[v.buf.id]
         return t.data_ptr() + (v.row0 * v.buf.cols + v.col0) * ELEM_BYTES[v.buf.dtype]
 
+    @staticmethod
+    def _version(t) -> int:
+        try:
+            return t._version
+        except RuntimeError:              # inference tensors keep no version counter
+            return 0
+
     def _descriptors(self, stream):
-        key = tuple(self._bufs[b.id].data_ptr() for b in self.g.inputs + self.g.params + self.g.states)
-        if key == self._desc_key:
+        """Bring the device's op descriptors up to date with the bound tensors.  Only the descriptors
+        of ops that touch a tensor whose address changed are re-encoded (a caller that passes a fresh
+        input tensor every call re-encodes the ops that read it, not the whole graph).  A parameter
+        changed in place since the last call (torch's version counter) makes the library drop its
+        packed tile copies of the weights, so tile GEMMs never run on a stale snapshot."""
+        named = self.g.inputs + self.g.params + self.g.states
+        ptrs = {b.id: self._bufs[b.id].data_ptr() for b in named}
+        vers = tuple(self._version(self._bufs[b.id]) for b in self.g.params)
+        old = self._desc_key
+        if old is not None and old[0] == ptrs and old[1] == vers:
             return
-        for k, op in enumerate(self.g.ops):
-            encode.fill(self._desc[k], op, self._addr)
+        if old is not None and old[1] != vers and self.packed_weight_bytes:
+            _lib.check(_lib.load().mk_program_refresh_weights(self._handle, stream), "mk_program_refresh_weights")
+        if old is None:
+            todo = range(len(self.g.ops))
+        else:
+            moved = {i for i, a in ptrs.items() if old[0].get(i) != a}
+            todo = sorted({k for i in moved for k in self._ops_of_buf.get(i, ())})
+        for k in todo:
+            encode.fill(self._desc[k], self.g.ops[k], self._addr)
         _lib.check(_lib.load().mk_program_set_ops(self._handle, ctypes.addressof(self._desc), len(self.g.ops), stream),
                    "mk_program_set_ops")
-        self._desc_key = key
+        self._desc_key = (ptrs, vers)
 
     # ---- run
     def __call__(self, **bindings):

@@ -126,7 +126,7 @@ def test_tile_linear_timeout_is_reported_not_hung(cuda):
 
 
 def test_streaming_and_tile_linears_alternate(cuda):
-    """Streaming linears (<= 8 rows: two-stage weight ring) and tcgen05 tile linears (seven single-tile
+    """Streaming linears (<= 8 rows: two-stage weight ring) and tcgen05 tile linears (eight single-tile
     weight slots in the same shared memory) alternate in one launch, several instructions of each
     per CTA: the producer warp must drain one kind of slot before it fills the other."""
     g = mc.Graph()
@@ -299,7 +299,7 @@ def test_llama_1b_decode_32_greedy_steps(cuda):
         ids = tok_r
     prog.check()
     print(f"greedy tokens identical on {exact}/32 steps; worst rel-L2 {worst:.2e}")
-    assert exact >= 24
+    assert exact >= 31
     assert worst < TOL, worst
     assert int(st["pos"]) == ctx + 32 == int(rs["pos"])
     changed = (st["k_cache"] != k0).any(-1).view(c["n"], max_seq)
@@ -308,3 +308,71 @@ def test_llama_1b_decode_32_greedy_steps(cuda):
     assert torch.equal(changed, want)                               # exactly the 32 appended rows per layer
     assert rel_l2(st["k_cache"].float(), rs["k_cache"].float()) < TOL
     assert np.array_equal(prog.counters(), prog.sched.counter_target * 32)
+
+
+def test_weight_changed_in_place_is_noticed(cuda):
+    """Tile-GEMM weights are read from packed snapshots.  A parameter updated in place through torch
+    (optimizer step, LoRA merge) moves its version counter; the next call packs again, without
+    refresh_weights() and without the tensor's address changing."""
+    g = mc.Graph()
+    g.output(g.linear(g.input("x", (64, 1024)), g.param("w", (512, 1024))))
+    t = {"x": rnd((64, 1024), 1.0, 1), "w": rnd((512, 1024), 0.03, 2)}
+    dev = {k: v.to(cuda).contiguous() for k, v in t.items()}
+    prog = mc.compile(g)
+    a = prog(**dev).float().cpu()
+    prog.check()
+    assert prog.tcgen05_ops == 1 and prog.packed_weight_bytes == 512 * 1024 * 2
+    ref, _ = evaluate(g, t)
+    assert rel_l2(a, ref[0]) < TOL
+    addr = dev["w"].data_ptr()
+    dev["w"].mul_(-0.5)                                  # in place: same address, new version
+    assert dev["w"].data_ptr() == addr
+    b = prog(**dev).float().cpu()
+    prog.check()
+    ref2, _ = evaluate(g, dict(t, w=dev["w"].cpu()))
+    assert rel_l2(b, ref2[0]) < TOL and rel_l2(b, a) > 1.0
+    assert prog.packed_weight_bytes == 512 * 1024 * 2
+
+
+def test_bind_checks_instruction_arguments(cuda):
+    """mk_program_set_ops checks every instruction against the extents its descriptor states: a
+    descriptor whose extent has shrunk under the instruction table is refused with MK_E_ARG (and the
+    instruction named) before anything reaches the device."""
+    import ctypes
+    from megacute_b200 import _lib
+    g = mc.Graph()
+    g.output(g.linear(g.input("x", (200, 256)), g.param("w", (384, 256)), act="relu"))
+    dev = {"x": rnd((200, 256), 1.0, 1).to(cuda), "w": rnd((384, 256), 0.05, 2).to(cuda)}
+    prog = mc.compile(g)
+    good = prog(**dev).clone()
+    prog.check()
+    lib = _lib.load()
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    bad = (_lib.OpDesc * len(prog.g.ops))()
+    ctypes.memmove(bad, prog._desc, ctypes.sizeof(bad))
+    k = next(i for i, o in enumerate(prog.g.ops) if o.kind == "Linear")
+    bad[k].i[0] = 100                                    # M = 100: the instruction of m tile 1 now starts past the rows
+    rc = lib.mk_program_set_ops(prog._handle, ctypes.addressof(bad), len(prog.g.ops), stream)
+    assert rc == -2 and b"m tile" in lib.mk_last_cuda_error()
+    again = prog(**dev)                                  # the refused table changed nothing
+    prog.check()
+    assert torch.equal(again, good)
+
+
+def test_program_on_another_device_than_the_current_one():
+    """A Program is bound to its device; the caller's current device is left alone by every call."""
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    other = torch.device("cuda", 1)
+    g = mc.Graph()
+    g.output(g.linear(g.input("x", (64, 512)), g.param("w", (256, 512)), act="gelu_tanh"))
+    t = {"x": rnd((64, 512), 1.0, 1), "w": rnd((256, 512), 0.05, 2)}
+    torch.cuda.set_device(0)
+    prog = mc.compile(g, device=1)
+    with torch.cuda.device(other):
+        stream_args = {k: v.to(other) for k, v in t.items()}
+    out = prog(**stream_args)
+    prog.check()
+    assert torch.cuda.current_device() == 0 and out.device == other
+    ref, _ = evaluate(g, t)
+    assert rel_l2(out.float().cpu(), ref[0]) < TOL

@@ -8,6 +8,7 @@ from megacute_b200 import config as C
 from megacute_b200.builders import dit_stack, llama_decode, llama_stack, mlp_block
 from megacute_b200.passes import fold_norms, fuse_rope_attention, run_all, split_k, split_kv
 from megacute_b200.schedule import schedule
+from megacute_b200.verify import VerifyError, check_hazards, check_tables
 from oracle.graph_oracle import evaluate, rel_l2
 from tests.helpers import small_decode
 
@@ -113,16 +114,11 @@ def _check_schedule(s, g):
 
 
 def _simulate(s, g, order_seed):
-    """Execute the stream in a random counter-legal order with `grid` in-order CTAs and check that
-    every conflicting pair of accesses (RAW / WAR / WAW) was ordered as in program order."""
-    from megacute_b200.schedule import tile_op, CONFLICTS
+    """Execute the stream in a random counter-legal order with `grid` in-order CTAs: some CTA can
+    always make progress and every instruction runs (no deadlock).  That every conflicting pair of
+    accesses is ORDERED is not decided by sampling executions but exactly, by `_ordered` below."""
     rng = np.random.default_rng(order_seed)
     grid = s.sm_count
-    tiled = [tile_op(op, grid) for op in g.ops]
-    acc = []                                         # per instruction: [(buf id, kind, box)]
-    for k, t in enumerate(tiled):
-        for j in range(len(t.args)):
-            acc.append([(a.buf.id, a.kind, tuple(a.boxes[j])) for a in t.accesses if a.buf.kind not in ("input", "param")])
     counters = np.zeros(s.num_counters, np.int64)
     nxt = list(range(min(grid, s.n)))                # next instruction of each CTA
     done_order = []
@@ -139,20 +135,14 @@ def _simulate(s, g, order_seed):
         nxt[c] += grid
         if nxt[c] >= s.n:
             live.discard(c)
-    rank = {i: r for r, i in enumerate(done_order)}
-    hit = lambda a, b: a[0] < b[1] and b[0] < a[1] and a[2] < b[3] and b[2] < a[3]
-    # Completion order is a legal serialisation; an instruction may START any time after its waits
-    # are met, so conflicting accesses must be ordered by a chain of waits, not by luck: check that
-    # for every conflicting pair (j < i, different ops) i's completion rank is larger for 20 random
-    # orders -- with random tie-breaking an unordered pair flips quickly.
-    for i in range(s.n):
-        for j in range(i):
-            if s.op_of[i] == s.op_of[j]:
-                continue
-            for (b1, k1, x1) in acc[i]:
-                for (b2, k2, x2) in acc[j]:
-                    if b1 == b2 and k2 in CONFLICTS[k1] and hit(x1, x2):
-                        assert rank[j] < rank[i], (j, i)
+    assert sorted(done_order) == list(range(s.n))       # every instruction ran: no deadlock in this order
+
+
+def _ordered(s, g):
+    """Tables of a schedule are complete: arguments and operand windows in range, and every hazard
+    ordered in the happens-before closure of the wait / arrival tables."""
+    check_tables(g, s)
+    assert check_hazards(s, g) > 0
 
 
 def test_finalize_fused_into_decode_attention():
@@ -168,8 +158,8 @@ def test_finalize_fused_into_decode_attention():
         assert any(o.kind == "LinearSplit" and o.ws.buf is a.q.buf for o in g2.ops)
     s = schedule(g2, 148)
     _check_schedule(s, g2)
-    for seed in range(3):
-        _simulate(s, g2, seed)
+    _simulate(s, g2, 0)
+    _ordered(s, g2)
     g1, *_ = small_decode(B=1)
     assert not any(o.zero_inputs for o in run_all(g1, 148).ops if o.kind == "DecodeAttention")
 
@@ -186,8 +176,8 @@ def test_kv_heads_per_instruction_choice_and_schedule():
     assert att and all(o.heads_per_inst > 1 and o.splits == 1 for o in att)
     s = schedule(g2, 148)
     _check_schedule(s, g2)
-    for seed in range(3):
-        _simulate(s, g2, seed)
+    _simulate(s, g2, 0)
+    _ordered(s, g2)
 
 
 def test_schedule_invariants_decode():
@@ -196,18 +186,96 @@ def test_schedule_invariants_decode():
         g2 = run_all(g, sm)
         s = schedule(g2, sm)
         _check_schedule(s, g2)
+        _ordered(s, g2)
 
 
 def test_schedule_orders_every_hazard():
     g, *_ = small_decode(B=1, n=2, E=128, H=2, KVH=1, F=256, vocab=256, max_seq=128, ctx=10)
     g2 = run_all(g, 6)
     s = schedule(g2, 6)
-    for seed in range(12):
-        _simulate(s, g2, seed)
+    _simulate(s, g2, 0)
+    _ordered(s, g2)
     m = run_all(mlp_block(256, 256, 512), 6)
     sm_ = schedule(m, 6)
-    for seed in range(6):
-        _simulate(sm_, m, seed)
+    _simulate(sm_, m, 0)
+    _ordered(sm_, m)
+    for build in (lambda: llama_stack(2, 256, 256, 4, 2, 512, 2, vocab=512), lambda: dit_stack(2, 64, 128, 2, 256, 2)):
+        gg = run_all(build(), 16)
+        _ordered(schedule(gg, 16), gg)
+
+
+def test_verifier_catches_a_dropped_wait_and_a_bad_argument():
+    """The checks fail when the tables are wrong: remove one wait (an unordered hazard appears), move
+    a tile index outside its op, shrink an operand below the window the kernel addresses."""
+    import copy
+    g, *_ = small_decode(B=1, n=1, E=128, H=2, KVH=1, F=256, vocab=256, max_seq=128, ctx=10)
+    g2 = run_all(g, 6)
+    s = schedule(g2, 6)
+    _ordered(s, g2)
+    # drop the only wait of the first instruction that has exactly one
+    one = [i for i in range(s.n) if s.wait_ptr[i + 1] - s.wait_ptr[i] == 1 and i >= 6]
+    assert one
+    hit = 0
+    for i in one[:8]:
+        bad = copy.copy(s)
+        keep = np.ones(len(s.wait_cnt), bool)
+        keep[s.wait_ptr[i]] = False
+        bad.wait_cnt, bad.wait_tgt = s.wait_cnt[keep], s.wait_tgt[keep]
+        bad.wait_ptr = s.wait_ptr.copy()
+        bad.wait_ptr[i + 1:] -= 1
+        try:
+            check_hazards(bad, g2)
+        except VerifyError:
+            hit += 1
+    assert hit > 0                                   # (a wait may be redundant through another chain; not all of them are)
+    bad = copy.copy(s)
+    bad.args = s.args.copy()
+    k = next(k for k, o in enumerate(g2.ops) if o.kind == "DecodeAttention")
+    bad.args[s.node_ranges[k][0], 1] = 7            # kv head 7 of 1
+    with pytest.raises(VerifyError):
+        check_tables(g2, bad)
+    op = g2.ops[k]
+    g3 = copy.copy(g2)
+    g3.ops = list(g2.ops)
+    g3.ops[k] = copy.copy(op)
+    g3.ops[k].k_cache = op.k_cache.rows_slice(0, op.k_cache.rows - 1)     # one row short of batch * max_seq
+    with pytest.raises(VerifyError):
+        check_tables(g3, s)
+
+
+def test_timeline_reports_on_synthetic_records():
+    """Timeline is pure host code over the trace buffer: feed it records and check every report."""
+    from megacute_b200.trace import Timeline
+
+    class FakeProg:
+        pass
+    g, *_ = small_decode(B=1, n=1, E=128, H=2, KVH=1, F=256, vocab=256, max_seq=128, ctx=10)
+    prog = FakeProg()
+    prog.g = run_all(g, 4)
+    prog.sched = schedule(prog.g, 4)
+    prog.node_of = [(k, 0) for k in range(len(prog.g.ops))]
+    prog.nodes = [[o] for o in prog.g.ops]
+    cap = -(-prog.sched.n // 4)
+    buf = np.zeros((4, 3, cap, 4), np.int64)
+    t = 1000
+    for i in range(prog.sched.n):
+        sm, slot = i % 4, i // 4
+        buf[sm, 1, slot] = (i, t, t + 100 * (i % 3), t + 500)
+        if i % 5 == 0:
+            buf[sm, 0, slot] = (i, t - 50, t - 50, t + 20)
+        t += 37
+    tl = Timeline(prog, buf)
+    comp = [r for r in tl.records if r[1] == 1]
+    assert len(comp) == prog.sched.n and all(isinstance(x, int) for x in comp[0])
+    assert tl.t_base == 950 and abs(tl.span_us() - (t - 37 + 500 - 950) / 1e3) < 1e-9
+    tab = tl.node_table()
+    assert int(tab["insts"].sum()) == prog.sched.n and (tab["end"] >= tab["start"]).all()
+    text = tl.summary()
+    assert "Linear" in text and f"{prog.sched.n} instructions traced" in text
+    ev = tl.chrome_events()
+    waits = sum(1 for i in range(prog.sched.n) if i % 3)
+    assert len(ev) == prog.sched.n + waits + sum(1 for i in range(prog.sched.n) if i % 5 == 0)
+    assert {e["tid"] for e in ev} == {"producer", "compute"} and all(e["dur"] >= 0 for e in ev)
 
 
 def test_schedule_sizes_baseline_configs():
@@ -215,6 +283,10 @@ def test_schedule_sizes_baseline_configs():
     s = schedule(run_all(g, 148), 148)
     assert s.n < 13000 and int(np.diff(s.wait_ptr).max()) <= 16
     _check_schedule(s, run_all(g, 148))
+    _ordered(s, run_all(g, 148))
+    # batch 64 at full size (split-K tile GEMMs, workspace-fed attention, several kv heads per instruction)
+    g64 = run_all(llama_decode(64, 2048, 32, 8, 8192, 16, 1152, 128256, 1e-5), 148)
+    _ordered(schedule(g64, 148), g64)
 
 
 def test_builders_prefill_and_dit_schedule():

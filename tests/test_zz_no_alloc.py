@@ -76,3 +76,73 @@ def test_noalloc_rejects_oversized_graph(cuda):
     rc = lib.mk_launch_noalloc(cuda.index or 0, dummy.data_ptr(), 1, None, 0, None, 0, dummy.data_ptr(), 1,
                                16384 + 1, 1, None, None)
     assert rc == -6 and b"MK_NOALLOC_MAX_COUNTERS" in lib.mk_strerror(rc)
+
+
+def test_noalloc_runs_tile_gemm_and_decode_attention(cuda, monkeypatch):
+    """A batch-16 decode step through mk_launch_noalloc: tile GEMMs (their mma.sync body, since the
+    caller's descriptors carry no library-made tensor maps), split-K reductions, the fused decode
+    attention with a two-way KV split (partial and arrival-count workspaces, zeroed by the caller as
+    the header requires), norms and the increment.  Checked, on two calls in a row, against the
+    ordinary launch of the same graph with its mma.sync body, the oracle, and the integer state."""
+    from tests.helpers import small_decode
+    monkeypatch.setenv("MEGACUTE_B200_KV_SPLITS", "2")
+    monkeypatch.setenv("MEGACUTE_B200_NO_TCGEN05", "1")
+    g, params, st0, ids = small_decode(B=16, E=256, H=4, KVH=2, F=512, n=2, max_seq=256, ctx=120, vocab=1000)
+    prog = mc.compile(g)
+    kinds = {o.kind for o in prog.g.ops}
+    assert {"LinearSplit", "DecodeAttention", "Norm"} <= kinds
+    assert all(o.splits == 2 for o in prog.g.ops if o.kind == "DecodeAttention")
+    dp = {k: v.to(cuda) for k, v in params.items()}
+    ds = {k: v.to(cuda) for k, v in st0.items()}
+    want = prog(**dp, **ds).float().cpu()
+    prog.check()
+    assert prog.tcgen05_ops == 0
+    want_k = ds["k_cache"].clone()
+    ref, ref_st = evaluate(g, {**params, **st0})
+    assert rel_l2(want, ref[0]) < TOL
+
+    insts, waits, arrives = (a.to(cuda) for a in prog._tables)
+    desc = torch.frombuffer(bytearray(bytes(prog._desc)), dtype=torch.uint8).to(cuda)
+    out = prog._bufs[prog.g.outputs[0].buf.id]
+    lib = _lib.load()
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    status = (ctypes.c_int32 * _lib.ST_WORDS)()
+    s = prog.sched
+    before = torch.cuda.current_device()
+    for call in range(2):
+        for k, v in st0.items():                   # same tensors (the descriptors hold their addresses), fresh contents
+            ds[k].copy_(v)
+        for b in prog.g.buffers:                   # workspaces are zero on entry: the caller's duty here
+            if b.kind == "workspace":
+                prog._bufs[b.id].zero_()
+        out.zero_()
+        rc = lib.mk_launch_noalloc(cuda.index or 0, insts.data_ptr(), s.n, waits.data_ptr(), len(s.wait_cnt),
+                                   arrives.data_ptr(), len(s.arr_cnt), desc.data_ptr(), len(prog.g.ops),
+                                   s.num_counters, prog.sm_count, stream, None)
+        _lib.check(rc, f"mk_launch_noalloc call {call}")
+        _lib.check(lib.mk_noalloc_status(cuda.index or 0, stream, status), "mk_noalloc_status")
+        assert list(status)[0] == 0
+        got = out.float().cpu()
+        assert rel_l2(got, want) < 1e-3            # split-K partial sums arrive in any order: equal up to fp32 rounding
+        assert rel_l2(got, ref[0]) < TOL
+        assert int(ds["pos"]) == int(ref_st["pos"]) == 121
+        assert rel_l2(ds["k_cache"].float(), want_k.float()) < 1e-3
+        for b in prog.g.buffers:                   # ... and zero again on exit
+            if b.kind == "workspace":
+                assert not prog._bufs[b.id].any()
+    assert torch.cuda.current_device() == before   # the entry point leaves the caller's device alone
+
+
+def test_grid_larger_than_the_device_is_an_argument_error(cuda):
+    """All CTAs must be resident at once; a grid above the SM count is refused up front (it would
+    otherwise end in a dependency timeout)."""
+    g = _graph()
+    caps = _lib.Caps()
+    _lib.check(_lib.load().mk_query(cuda.index or 0, ctypes.byref(caps)))
+    with pytest.raises(_lib.MegakernelError, match="grid"):
+        mc.compile(g, sm_count=caps.sm_count + 1)
+    lib = _lib.load()
+    dummy = torch.zeros(64, dtype=torch.int32, device=cuda)
+    rc = lib.mk_launch_noalloc(cuda.index or 0, dummy.data_ptr(), 1, None, 0, None, 0, dummy.data_ptr(), 1, 1,
+                               caps.sm_count + 1, None, None)
+    assert rc == -2
