@@ -292,7 +292,8 @@ struct DeviceGuard {
 // columns x `box_rows` rows, stored with the 128-byte swizzle (the operand tile layout of the tcgen05 tile
 // GEMM), rows outside the matrix read as zero.  The driver entry point is looked up once; false
 // when it is missing or refuses the arguments (the kernel then runs its mma.sync body).
-static bool encode_tile_map(void* out, uint64_t base, long long rows, long long cols, long long ld, int box_rows, bool streamed) {
+static bool encode_tile_map(void* out, uint64_t base, long long rows, long long cols, long long ld, int box_rows, bool streamed,
+                            bool fp16 = false) {
     typedef CUresult (*encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -313,7 +314,7 @@ static bool encode_tile_map(void* out, uint64_t base, long long rows, long long 
     const cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
     const cuuint32_t estr[2] = {1, 1};
     alignas(64) CUtensorMap m;
-    if (fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, reinterpret_cast<void*>(base), dims, strides, box, estr,
+    if (fn(&m, fp16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, reinterpret_cast<void*>(base), dims, strides, box, estr,
            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
            streamed ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
@@ -546,7 +547,8 @@ int mk_program_set_ops(mk_program* p, const mk_op_desc* ops, int n_ops, void* st
         if (tc_off || !tile_gemm_on_tcgen05(d)) continue;
         uint8_t* maps = h_tmaps + (size_t)k * 256;
         d.ptr[10] = 0;
-        if (!encode_tile_map(maps, d.ptr[0], d.i[0], d.i[2], d.ld[0], d.i[0] <= 64 ? 64 : 128, false)) continue;
+        if (d.i[9] != mk::DT_BF16 && d.i[9] != mk::DT_F16) continue;
+        if (!encode_tile_map(maps, d.ptr[0], d.i[0], d.i[2], d.ld[0], d.i[0] <= 64 ? 64 : 128, false, d.i[9] == mk::DT_F16)) continue;
         // weights: the packed copy, made when a matrix (address, shape, pitch) is bound for the first
         // time and kept while it stays bound -- rebinding other operands (a new input tensor every
         // call) must not copy gigabytes of weights again; weights changed in place need

@@ -3,6 +3,7 @@
 #pragma once
 
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -265,13 +266,31 @@ __device__ __forceinline__ float warp_max(float v) {
     return v;
 }
 
-// load 8 consecutive elements as fp32 from a bf16 (dtype 0) or fp32 (dtype 1) row; 16-byte aligned.
+// Element types of activations (descriptor dtype codes; graph.py DTYPE_CODE): 0 bf16, 1 fp32, 2 fp16.
+// fp16 is what runtime-private activations that feed a tile GEMM are kept in: the tensor core takes it
+// as it takes bf16, with 11 instead of 8 significant bits; conversions saturate at +-65504.
+enum { DT_BF16 = 0, DT_F32 = 1, DT_F16 = 2 };
+__device__ __forceinline__ uint32_t pack2h(float a, float b) {
+    uint32_t r;
+    asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
+    return r;
+}
+__device__ __forceinline__ float2 unpack2h(uint32_t w) {
+    return __half22float2(*reinterpret_cast<const __half2*>(&w));
+}
+// two consecutive values in the 16-bit type `dtype` (DT_BF16 or DT_F16)
+__device__ __forceinline__ uint32_t pack2t(int dtype, float a, float b) { return dtype == DT_F16 ? pack2h(a, b) : pack2(a, b); }
+// load 8 consecutive elements as fp32 from a bf16, fp32 or fp16 row; 16-byte aligned.
 // Loads go to L2 (ld.global.cg): activations are rewritten by other SMs inside one launch and L1
 // is not coherent, so a line cached by an earlier instruction of this SM could be stale.
 __device__ __forceinline__ void load8(const void* base, long long elem, int dtype, float* f) {
-    if (dtype == 0) {
+    if (dtype == DT_BF16) {
         uint4 v = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(base) + elem));
         unpack8(v, f);
+    } else if (dtype == DT_F16) {
+        const uint4 v = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(base) + elem));
+        const float2 a = unpack2h(v.x), b = unpack2h(v.y), c = unpack2h(v.z), d = unpack2h(v.w);
+        f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
     } else {
         const float4* p = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + elem);
         float4 a = __ldcg(p), b = __ldcg(p + 1);
@@ -279,8 +298,11 @@ __device__ __forceinline__ void load8(const void* base, long long elem, int dtyp
     }
 }
 __device__ __forceinline__ void store8(void* base, long long elem, int dtype, const float* f) {
-    if (dtype == 0) {
+    if (dtype == DT_BF16) {
         *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(base) + elem) = pack8(f);
+    } else if (dtype == DT_F16) {
+        *reinterpret_cast<uint4*>(reinterpret_cast<__half*>(base) + elem) =
+            make_uint4(pack2h(f[0], f[1]), pack2h(f[2], f[3]), pack2h(f[4], f[5]), pack2h(f[6], f[7]));
     } else {
         float4* p = reinterpret_cast<float4*>(reinterpret_cast<float*>(base) + elem);
         p[0] = make_float4(f[0], f[1], f[2], f[3]);
@@ -288,14 +310,14 @@ __device__ __forceinline__ void store8(void* base, long long elem, int dtype, co
     }
 }
 __device__ __forceinline__ float load1(const void* base, long long elem, int dtype) {
-    if (dtype == 0) {
-        const unsigned short u = __ldcg(reinterpret_cast<const unsigned short*>(base) + elem);
-        return __uint_as_float((uint32_t)u << 16);
-    }
-    return __ldcg(reinterpret_cast<const float*>(base) + elem);
+    if (dtype == DT_F32) return __ldcg(reinterpret_cast<const float*>(base) + elem);
+    const unsigned short u = __ldcg(reinterpret_cast<const unsigned short*>(base) + elem);
+    if (dtype == DT_F16) return __half2float(__ushort_as_half(u));
+    return __uint_as_float((uint32_t)u << 16);
 }
 __device__ __forceinline__ void store1(void* base, long long elem, int dtype, float v) {
-    if (dtype == 0) reinterpret_cast<__nv_bfloat16*>(base)[elem] = __float2bfloat16_rn(v);
+    if (dtype == DT_BF16) reinterpret_cast<__nv_bfloat16*>(base)[elem] = __float2bfloat16_rn(v);
+    else if (dtype == DT_F16) reinterpret_cast<unsigned short*>(base)[elem] = (unsigned short)(pack2h(v, 0.f) & 0xffffu);
     else reinterpret_cast<float*>(base)[elem] = v;
 }
 

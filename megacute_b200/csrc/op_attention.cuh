@@ -7,7 +7,7 @@
 // portable first implementation; the tcgen05 / TMEM version is the planned replacement.
 //
 // ptr 0 q, 1 k, 2 v, 3 out; i 0 batch, 1 seq_q, 2 seq_k, 3 heads, 4 kv_heads, 5 head_dim,
-// 6 causal; f 0 scale.  args: 0 b, 1 h, 2 query tile.
+// 6 causal, 7 out dtype (DT_BF16 or DT_F16); f 0 scale.  args: 0 b, 1 h, 2 query tile.
 #pragma once
 #include "mk_device.cuh"
 #include "mma.cuh"
@@ -174,7 +174,7 @@ static __device__ __noinline__ void op_attention(const mk_op_desc* op, int a0, i
 #pragma unroll
         for (int j = 0; j < D / 8; ++j)
             *reinterpret_cast<uint32_t*>(O + (long long)qr * op->ld[3] + j * 8 + (lane & 3) * 2) =
-                pack2(oacc[j][r * 2] * inv, oacc[j][r * 2 + 1] * inv);
+                pack2t(op->i[7], oacc[j][r * 2] * inv, oacc[j][r * 2 + 1] * inv);
     }
     compute_sync();
 }

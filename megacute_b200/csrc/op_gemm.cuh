@@ -5,14 +5,16 @@
 // rest: a K range per instruction that is not a multiple of 64, operands not aligned for 16-byte
 // accesses, launches whose descriptors the library never saw (mk_launch_noalloc).
 // Operands stream through a cp.async pipeline of 32- or 64-wide k-tiles; the math is mma.sync
-// m16n8k16 bf16 -> fp32 (8 warps as 2 x 4).  Two shapes: 128 activation rows per tile with 4 stages
+// m16n8k16 bf16 -> fp32 (8 warps as 2 x 4); with fp16 activations (descriptor i 9) the weight fragments are
+// converted to fp16 in registers and the fp16 form of the instruction is used.  Two shapes: 128 activation rows per tile with 4 stages
 // (warp tile 64 x 32), and, when the op has at most 64 rows (batched decode, where the op is bound
 // by streaming the weights), 64 rows per tile (warp tile 32 x 32): no MMAs on padding rows and more
 // weight bytes in flight.
 //
 // ptr 0 x, 1 w, 2 out (or ws), 3 bias, 4 residual
 // i 0 M, 1 N (weight rows), 2 K, 3 act, 4 splits, 5 out dtype, 6 accumulate, 7 residual dtype,
-//   8 swiglu (weight tile = 64 gate rows then 64 up rows; the tile writes 64 output columns)
+//   8 swiglu (weight tile = 64 gate rows then 64 up rows; the tile writes 64 output columns),
+//   9 x dtype (DT_BF16 or DT_F16)
 // args: 0 m tile, 1 n tile, 2 k split
 #pragma once
 #include "mk_device.cuh"
@@ -32,6 +34,7 @@ static __device__ __noinline__ void op_gemm(const mk_op_desc* op, int a0, int a1
     static_assert(kGemmStages * (kATileBytes + kBTileBytes) <= kWorkBytes, "GEMM stages exceed the work area");
     const int M = op->i[0], N = op->i[1], K = op->i[2], act = op->i[3], splits = op->i[4];
     const int odt = op->i[5], accum = op->i[6], rdt = op->i[7], swi = op->i[8];
+    const bool xh = op->i[9] == DT_F16;
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     const int wm = warp >> 2, wn = warp & 3;
     const int m0 = a0 * kGemmBM, n0 = a1 * kGemmBN;
@@ -95,10 +98,19 @@ static __device__ __noinline__ void op_gemm(const mk_op_desc* op, int a0, int a1
                 ldmatrix_x4(b_base + row * kGemmRowBytes + (kk * 16 + ((lane >> 3) & 1) * 8) * 2, bf[pr * 2][0],
                             bf[pr * 2][1], bf[pr * 2 + 1][0], bf[pr * 2 + 1][1]);
             }
+            if (xh) {
 #pragma unroll
-            for (int i = 0; i < MI; ++i)
+                for (int j = 0; j < 4; ++j) { bf[j][0] = bf16x2_to_f16x2(bf[j][0]); bf[j][1] = bf16x2_to_f16x2(bf[j][1]); }
 #pragma unroll
-                for (int j = 0; j < 4; ++j) mma_bf16(acc[i][j], af[i], bf[j][0], bf[j][1]);
+                for (int i = 0; i < MI; ++i)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) mma_f16(acc[i][j], af[i], bf[j][0], bf[j][1]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < MI; ++i)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) mma_bf16(acc[i][j], af[i], bf[j][0], bf[j][1]);
+            }
         }
     }
     cp_async_wait<0>();
@@ -145,7 +157,7 @@ static __device__ __noinline__ void op_gemm(const mk_op_desc* op, int a0, int a1
                 } else if (odt == 1) {
                     *reinterpret_cast<float2*>(reinterpret_cast<float*>(O) + e) = make_float2(v0, v1);
                 } else {
-                    *reinterpret_cast<uint32_t*>(reinterpret_cast<__nv_bfloat16*>(O) + e) = pack2(v0, v1);
+                    *reinterpret_cast<uint32_t*>(reinterpret_cast<__nv_bfloat16*>(O) + e) = pack2t(odt, v0, v1);
                 }
             }
         }

@@ -30,8 +30,12 @@
 
 namespace mk {
 
-// instruction descriptor, kind::f16: D = f32, A = B = bf16, both K-major, N = 128, M = 128
-constexpr uint32_t kTcIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+// instruction descriptor, kind::f16: D = f32 (bits 4-5 = 1), A format (bits 7-9: 0 = fp16, 1 = bf16), B = bf16
+// (bits 10-12 = 1), both K-major, N = 128 (bits 17-22 = N / 8), M = 128 (bits 24-28 = M / 16).  The weights are
+// always bf16; the activations are bf16 or -- runtime-private ones, see passes.promote_temps -- fp16.
+__device__ __forceinline__ uint32_t tc_idesc(bool a_fp16) {
+    return (1u << 4) | ((a_fp16 ? 0u : 1u) << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+}
 
 // shared-memory matrix descriptor of a K-major tile with the 128-byte swizzle: start address,
 // leading byte offset 16 (unused by swizzled K-major layouts), 1024 bytes between 8-row groups,
@@ -40,10 +44,10 @@ constexpr uint32_t kTcIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) 
 __device__ __forceinline__ uint64_t tc_smem_desc(uint32_t saddr) {
     return (uint64_t)((saddr & 0x3ffffu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
 }
-__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
         "{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p; }" ::"r"(tmem_d),
-        "l"(adesc), "l"(bdesc), "r"(kTcIdesc), "r"(accumulate)
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 // arrives on the mbarrier once every tcgen05.mma this thread has issued so far has completed
@@ -109,17 +113,22 @@ __device__ __forceinline__ void tc_write_rows(const mk_op_desc* op, const float*
             for (int j = 0; j < 4; ++j) f[j] = apply_act(act, f[j] + b4[j]);
             if (R) {
                 const long long er = (long long)(m0 + row) * op->ld[4] + col;
-                if (rdt == 1) {
+                if (rdt == DT_F32) {
                     const float4 x = __ldcg(reinterpret_cast<const float4*>(R + er * 4));
                     f[0] += x.x; f[1] += x.y; f[2] += x.z; f[3] += x.w;
                 } else {
                     const uint2 w = __ldcg(reinterpret_cast<const uint2*>(R + er * 2));
-                    f[0] += bf16_lo(w.x); f[1] += bf16_hi(w.x); f[2] += bf16_lo(w.y); f[3] += bf16_hi(w.y);
+                    if (rdt == DT_F16) {
+                        const float2 lo = unpack2h(w.x), hi = unpack2h(w.y);
+                        f[0] += lo.x; f[1] += lo.y; f[2] += hi.x; f[3] += hi.y;
+                    } else {
+                        f[0] += bf16_lo(w.x); f[1] += bf16_hi(w.x); f[2] += bf16_lo(w.y); f[3] += bf16_hi(w.y);
+                    }
                 }
             }
         }
-        if (odt == 1) *reinterpret_cast<float4*>(O + eo * 4) = make_float4(f[0], f[1], f[2], f[3]);
-        else *reinterpret_cast<uint2*>(O + eo * 2) = make_uint2(pack2(f[0], f[1]), pack2(f[2], f[3]));
+        if (odt == DT_F32) *reinterpret_cast<float4*>(O + eo * 4) = make_float4(f[0], f[1], f[2], f[3]);
+        else *reinterpret_cast<uint2*>(O + eo * 2) = make_uint2(pack2t(odt, f[0], f[1]), pack2t(odt, f[2], f[3]));
     }
 }
 
@@ -174,6 +183,7 @@ __device__ __forceinline__ int op_gemm_tc(const Params& p, Ctrl* c, uint8_t* rin
     } else if (warp == 3 && lane == 0) {
         // ---- MMAs: accumulator[128 activation rows][128 weight rows] += x tile . w tile^T ----
         uint32_t n = 0, acc = 0;
+        const uint32_t idesc = tc_idesc(op->i[9] == DT_F16);
         bool ok = true;
         int ws = c->w_slot;
         uint32_t wph = c->w_phase;
@@ -186,7 +196,7 @@ __device__ __forceinline__ int op_gemm_tc(const Params& p, Ctrl* c, uint8_t* rin
             const uint64_t ad = tc_smem_desc(smem_u32(xs + s * xbytes)), bd = tc_smem_desc(smem_u32(ring + tc_wslot_off(ws)));
 #pragma unroll
             for (int k16 = 0; k16 < 4; ++k16) {
-                tc_mma(tmem, ad + 2 * k16, bd + 2 * k16, acc);
+                tc_mma(tmem, ad + 2 * k16, bd + 2 * k16, idesc, acc);
                 acc = 1;
             }
             tc_commit(&c->x_empty[s]);

@@ -54,9 +54,10 @@ static __device__ __noinline__ void op_finalize(const mk_op_desc* op, int a0, in
 
 // MK_OP_ELTWISE.  ptr 0 a (x / gate), 1 b (b / up / scale / cos), 2 c (shift / sin), 3 out
 // i 0 R, 1 C, 2 mode, 3 fn (activation or binary code), 4 group (rows of a per row of b; rope: seq),
-//   5 head_dim (rope).  All operands bf16.  args: 0 row tile, 1 col tile.
+//   5 head_dim (rope), 6..9 dtypes of a, b, c, out (DT_*).  args: 0 row tile, 1 col tile.
 static __device__ __noinline__ void op_eltwise(const mk_op_desc* op, int a0, int a1) {
     const int R = op->i[0], Cc = op->i[1], mode = op->i[2], fn = op->i[3], group = op->i[4];
+    const int adt = op->i[6], bdt = op->i[7], cdt = op->i[8], odt = op->i[9];
     const int r0 = a0 * kEwRows, c0 = a1 * kEwCols;
     const int rows = min(kEwRows, R - r0), cols = min(kEwCols, Cc - c0);
     const void* A = reinterpret_cast<const void*>(op->ptr[0]);
@@ -73,19 +74,19 @@ static __device__ __noinline__ void op_eltwise(const mk_op_desc* op, int a0, int
             const int col = c0 + (rem / hv) * D + (rem % hv) * 8;
             const int tok = r % group, dc = (rem % hv) * 8;
             float x1[8], x2[8], c1[8], c2[8], s1[8], s2[8], o1[8], o2[8];
-            load8(A, (long long)r * op->ld[0] + col, 0, x1);
-            load8(A, (long long)r * op->ld[0] + col + half, 0, x2);
-            load8(B, (long long)tok * op->ld[1] + dc, 0, c1);
-            load8(B, (long long)tok * op->ld[1] + dc + half, 0, c2);
-            load8(Cp, (long long)tok * op->ld[2] + dc, 0, s1);
-            load8(Cp, (long long)tok * op->ld[2] + dc + half, 0, s2);
+            load8(A, (long long)r * op->ld[0] + col, adt, x1);
+            load8(A, (long long)r * op->ld[0] + col + half, adt, x2);
+            load8(B, (long long)tok * op->ld[1] + dc, bdt, c1);
+            load8(B, (long long)tok * op->ld[1] + dc + half, bdt, c2);
+            load8(Cp, (long long)tok * op->ld[2] + dc, cdt, s1);
+            load8(Cp, (long long)tok * op->ld[2] + dc + half, cdt, s2);
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
                 o1[e] = x1[e] * c1[e] - x2[e] * s1[e];
                 o2[e] = x2[e] * c2[e] + x1[e] * s2[e];
             }
-            store8(O, (long long)r * op->ld[3] + col, 0, o1);
-            store8(O, (long long)r * op->ld[3] + col + half, 0, o2);
+            store8(O, (long long)r * op->ld[3] + col, odt, o1);
+            store8(O, (long long)r * op->ld[3] + col + half, odt, o2);
         }
         return;
     }
@@ -93,33 +94,33 @@ static __device__ __noinline__ void op_eltwise(const mk_op_desc* op, int a0, int
     for (int v = threadIdx.x; v < rows * vpr; v += kComputeThreads) {
         const int r = r0 + v / vpr, col = c0 + (v % vpr) * 8;
         float a[8], b[8], cc[8];
-        load8(A, (long long)r * op->ld[0] + col, 0, a);
+        load8(A, (long long)r * op->ld[0] + col, adt, a);
         if (mode == EW_UNARY) {
 #pragma unroll
             for (int e = 0; e < 8; ++e) a[e] = apply_act(fn, a[e]);
         } else if (mode == EW_BINARY) {
-            load8(B, (long long)(r / group) * op->ld[1] + col, 0, b);
+            load8(B, (long long)(r / group) * op->ld[1] + col, bdt, b);
 #pragma unroll
             for (int e = 0; e < 8; ++e) a[e] = apply_bin(fn, a[e], b[e]);
         } else if (mode == EW_SWIGLU) {
-            load8(B, (long long)r * op->ld[1] + col, 0, b);
+            load8(B, (long long)r * op->ld[1] + col, bdt, b);
 #pragma unroll
             for (int e = 0; e < 8; ++e) a[e] = apply_act(fn, a[e]) * b[e];
         } else {  // EW_MODULATE: x * (1 + scale[g]) + shift[g]
-            load8(B, (long long)(r / group) * op->ld[1] + col, 0, b);
-            load8(Cp, (long long)(r / group) * op->ld[2] + col, 0, cc);
+            load8(B, (long long)(r / group) * op->ld[1] + col, bdt, b);
+            load8(Cp, (long long)(r / group) * op->ld[2] + col, cdt, cc);
 #pragma unroll
             for (int e = 0; e < 8; ++e) a[e] = a[e] * (1.0f + b[e]) + cc[e];
         }
-        store8(O, (long long)r * op->ld[3] + col, 0, a);
+        store8(O, (long long)r * op->ld[3] + col, odt, a);
     }
 }
 
 // MK_OP_NORM.  ptr 0 x, 1 out, 2 weight, 3 bias; i 0 R, 1 C, 2 rms, 3 rows per instruction (8: one
-// row per warp, 1: one row over the whole CTA), 4 x dtype; f 0 eps.  args: 0 row tile.
+// row per warp, 1: one row over the whole CTA), 4 x dtype, 5 out dtype; f 0 eps.  args: 0 row tile.
 // var = E[x^2] - mean^2 in fp32 (as the reference's norm kernel, megacute/ops/norm.py:94-114).
 static __device__ __noinline__ void op_norm(const mk_op_desc* op, int a0, uint8_t* work) {
-    const int R = op->i[0], Cc = op->i[1], rms = op->i[2], rpi = op->i[3], xdt = op->i[4];
+    const int R = op->i[0], Cc = op->i[1], rms = op->i[2], rpi = op->i[3], xdt = op->i[4], odt = op->i[5];
     const float eps = op->f[0];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const void* X = reinterpret_cast<const void*>(op->ptr[0]);
@@ -173,7 +174,7 @@ static __device__ __noinline__ void op_norm(const mk_op_desc* op, int a0, uint8_
                 if (W) keep[e] *= gk[e];
                 if (Bv) keep[e] += bk[e];
             }
-            store8(O, (long long)r * op->ld[1] + first * 8, 0, keep);
+            store8(O, (long long)r * op->ld[1] + first * 8, odt, keep);
         }
         return;
     }
@@ -192,7 +193,7 @@ static __device__ __noinline__ void op_norm(const mk_op_desc* op, int a0, uint8_
 #pragma unroll
             for (int e = 0; e < 8; ++e) f[e] += g[e];
         }
-        store8(O, (long long)r * op->ld[1] + v * 8, 0, f);
+        store8(O, (long long)r * op->ld[1] + v * 8, odt, f);
     }
 }
 

@@ -11,12 +11,12 @@ view's first element.  Field meaning per kind (the kernel side repeats it next t
   GEMV         ptr x, w, out, bias, residual, norm gain; i M, N_out, K, act, x dtype, out dtype,
                residual dtype; f eps; flags 1 = swiglu, 2 = rms-normalise x, 4 = tensor-core streaming path
   GEMM         ptr x, w, out, bias, residual; i M, N (weight rows), K, act, splits, out dtype,
-               accumulate, residual dtype, swiglu  (ptr 10, 11: set by the C library when it binds
-               the op to its tcgen05 body: packed weight tiles, tensor maps)
+               accumulate, residual dtype, swiglu, x dtype (bf16 or fp16)  (ptr 10, 11: set by the C
+               library when it binds the op to its tcgen05 body: packed weight tiles, tensor maps)
   FINALIZE     ptr ws, out, bias, residual; i R, C, act, out dtype, residual dtype, rows per instruction
-  ELTWISE      ptr a, b, c, out; i R, C, mode, fn, group, head_dim
-  NORM         ptr x, out, weight, bias; i R, C, rms, rows per instruction, x dtype; f eps
-  ATTENTION    ptr q, k, v, out; i batch, seq_q, seq_k, heads, kv_heads, head_dim, causal; f scale
+  ELTWISE      ptr a, b, c, out; i R, C, mode, fn, group, head_dim, dtypes of a, b, c, out
+  NORM         ptr x, out, weight, bias; i R, C, rms, rows per instruction, x dtype, out dtype; f eps
+  ATTENTION    ptr q, k, v, out; i batch, seq_q, seq_k, heads, kv_heads, head_dim, causal, out dtype; f scale
   ROPE_APPEND  ptr qkv, cos, sin, pos, q_out, k_cache, v_cache; i B, H, KVH, D, max_seq, qkv dtype
   DECODE_ATTN  ptr q, k_cache, v_cache, pos, out, k_new, v_new, cos, sin, part, count;
                i B, H, KVH, D, max_seq, splits, fused, q dtype, out dtype; f scale
@@ -32,6 +32,8 @@ from .graph import DTYPE_CODE, ELEM_BYTES, Op, View
 from .schedule import finalize_rows, is_gemv, norm_rows
 
 BF16 = torch.bfloat16
+F16 = torch.float16
+F32 = torch.float32
 
 
 def _aligned(v: View, what: str):
@@ -55,16 +57,19 @@ def validate(op: Op):
         if op.x.cols % 8:
             raise ValueError(f"{k}: K={op.x.cols} must be a multiple of 8")
         if not is_gemv(op):
-            _want(op.x, (BF16,), k)
+            _want(op.x, (BF16, F16), k)
+        _want(getattr(op, "bias", None), (BF16,), k)
     if k in ("Unary", "Binary", "SwiGLU", "Modulate", "Rope", "Norm"):
         for name, v in op.view_fields():
-            if not (k == "Norm" and name == "x"):          # the norm reads bf16 or fp32 rows
+            if k == "Norm" and name in ("weight", "bias"):
                 _want(v, (BF16,), f"{k}.{name}")
+            else:
+                _want(v, (BF16, F16, F32), f"{k}.{name}")
         if op.out.cols % 8:
             raise ValueError(f"{k}: column count {op.out.cols} must be a multiple of 8")
     if k == "Attention":
         for name, v in op.view_fields():
-            _want(v, (BF16,), f"{k}.{name}")
+            _want(v, (BF16, F16) if name == "out" else (BF16,), f"{k}.{name}")
 
 
 def gemv_units(op: Op) -> bool:
@@ -93,7 +98,7 @@ def fill(d, op: Op, addr) -> None:
         ptrs = [op.x, op.w, out, None if split else op.bias, None if split else op.residual]
         act = None if split else op.act
         ints = [op.x.rows, op.w.rows, op.x.cols, C.ACT_CODE[act], op.splits if split else 1, dt(out), int(split),
-                0 if split else dt(op.residual), int(act == "swiglu")]
+                0 if split else dt(op.residual), int(act == "swiglu"), dt(op.x)]
     elif k == "SplitFinalize":
         d.kind = C.OP_FINALIZE
         ptrs = [op.ws, op.out, op.bias, op.residual]
@@ -111,15 +116,16 @@ def fill(d, op: Op, addr) -> None:
             ptrs, ints = [op.x, op.scale, op.shift, op.out], [R, Cc, C.EW_MODULATE, 0, op.group, 0]
         else:
             ptrs, ints = [op.x, op.cos, op.sin, op.out], [R, Cc, C.EW_ROPE, 0, op.seq, op.head_dim]
+        ints += [dt(v) for v in ptrs]
     elif k == "Norm":
         d.kind = C.OP_NORM
         ptrs = [op.x, op.out, op.weight, op.bias]
-        ints = [op.x.rows, op.x.cols, int(bool(op.rms)), norm_rows(op.x.rows), dt(op.x)]
+        ints = [op.x.rows, op.x.cols, int(bool(op.rms)), norm_rows(op.x.rows), dt(op.x), dt(op.out)]
         d.f[0] = float(op.eps)
     elif k == "Attention":
         d.kind = C.OP_ATTENTION
         ptrs = [op.q, op.k, op.v, op.out]
-        ints = [op.batch, op.seq_q, op.seq_k, op.heads, op.kv_heads, op.head_dim, int(op.causal)]
+        ints = [op.batch, op.seq_q, op.seq_k, op.heads, op.kv_heads, op.head_dim, int(op.causal), dt(op.out)]
         d.f[0] = float(op.scale)
     elif k == "RopeAppend":
         d.kind = C.OP_ROPE_APPEND

@@ -22,8 +22,12 @@ from typing import Optional
 
 import torch
 
-ELEM_BYTES = {torch.bfloat16: 2, torch.float32: 4, torch.int32: 4}
-DTYPE_CODE = {torch.bfloat16: 0, torch.float32: 1, torch.int32: 2}
+ELEM_BYTES = {torch.bfloat16: 2, torch.float32: 4, torch.int32: 4, torch.float16: 2}
+# device dtype codes of activations (csrc/mk_device.cuh DT_*).  fp16 is never a caller-visible dtype (the
+# builder methods accept bf16 / fp32 / int32, as the reference does): only passes.promote_temps makes
+# fp16 buffers, for runtime-private activations.
+DTYPE_CODE = {torch.bfloat16: 0, torch.float32: 1, torch.float16: 2, torch.int32: 3}
+USER_DTYPES = (torch.bfloat16, torch.float32, torch.int32)
 BUFFER_KINDS = ("input", "param", "state", "temp", "output", "workspace")
 
 UNARY_FNS = ("relu", "silu", "gelu_tanh", "gelu", "exp", "neg", "sigmoid", "square", "identity")
@@ -335,6 +339,8 @@ class Graph:
     # ---- buffers
     def _new(self, name, shape, kind, dtype=None) -> View:
         rows, cols = shape
+        if (dtype or self.dtype) not in USER_DTYPES:
+            raise TypeError(f"{name}: unsupported dtype {dtype or self.dtype}")
         b = Buffer(name, rows, cols, dtype or self.dtype, kind)
         self.buffers.append(b)
         return b.full

@@ -217,18 +217,27 @@ def split_k(g: Graph, sm_count: int) -> Graph:
     return out
 
 
-def _accepts_fp32(op: Op, field: str) -> bool:
-    """Can the kernel read / write operand `field` of `op` as fp32 instead of bf16?"""
+def _accepts(op: Op, field: str, dtype) -> bool:
+    """Can the kernel read / write operand `field` of `op` in `dtype` (fp32 or fp16) instead of bf16?"""
     k = op.kind
+    f32 = dtype == torch.float32
     if k == "Linear":
         streaming = gemv_eligible(op.x.rows, op.x.cols)
-        return field in ("out", "residual") or (field == "x" and streaming)
+        if field == "x":                                # the tensor core takes 16-bit operands; the streaming linear converts
+            return streaming or not f32
+        return field in ("out", "residual")
     if k == "LinearSplit":
-        return field == "ws"
+        return (field == "ws" and f32) or (field == "x" and not f32)
     if k == "SplitFinalize":
-        return field in ("out", "residual", "ws")
+        return field in ("out", "residual") or (field == "ws" and f32)
     if k == "Norm":
-        return field == "x"
+        return field in ("x", "out")
+    if k in ("Unary", "Binary", "SwiGLU", "Modulate"):
+        return True
+    if k == "Rope":
+        return field in ("x", "out")
+    if k == "Attention":
+        return field == "out" and not f32
     if k == "RopeAppend":
         return field == "qkv"
     if k == "DecodeAttention":
@@ -238,13 +247,24 @@ def _accepts_fp32(op: Op, field: str) -> bool:
     return False
 
 
+# runtime-private activations up to this size are kept in fp32 when every op touching them can; larger
+# ones (prefill, DiT: megabytes per tensor, streamed through L2 by bandwidth-bound pointwise ops) in fp16
+F32_TEMP_BYTES = 4 << 20
+
+
 def promote_temps(g: Graph) -> Graph:
-    """Keep runtime-private activations in fp32 wherever every op that touches them can: the
-    residual stream, the QKV row, the attention output and the MLP hidden of a decode step are
-    never seen by the caller, and rounding each of them to bf16 at every layer is the main source
-    of drift against an fp32 evaluation (16 layers: ~2.5e-2 rel-L2 on the logits with bf16
-    intermediates, ~3e-3 with fp32).  Buffers the caller sees (outputs, states) keep their dtype."""
+    """Keep runtime-private activations in more than bf16's 8 significant bits wherever every op that
+    touches them can: the residual stream, the QKV row, the attention output and the MLP hidden of a
+    step are never seen by the caller, and rounding each of them to bf16 at every layer is the main
+    source of drift against an fp32 evaluation (16 layers of the 1B shape: 1.5e-2 to 2.5e-2 rel-L2 on
+    the logits with bf16 intermediates, ~2e-3 without).  fp32 for small tensors when every user
+    accepts it (decode); otherwise fp16 -- the same bytes as bf16, 11 significant bits, accepted by the
+    tensor cores as the A operand of a tile GEMM beside bf16 weights; conversions saturate at +-65504.
+    Buffers the caller sees (inputs, params, states, outputs) keep their dtype.
+    MEGACUTE_B200_BF16_TEMPS=1 leaves every temp in bf16."""
     out = g.derive()
+    if os.environ.get("MEGACUTE_B200_BF16_TEMPS") == "1":
+        return out
     users: dict[int, list] = {}
     for op in g.ops:
         for name, v in op.view_fields():
@@ -255,8 +275,12 @@ def promote_temps(g: Graph) -> Graph:
             continue
         if any(v.buf is b for v in g.outputs):
             continue
-        if all(_accepts_fp32(op, name) for op, name in users[b.id]):
-            swap[b.id] = Buffer(b.name, b.rows, b.cols, torch.float32, "temp")
+        for dt in (torch.float32, torch.float16):
+            if dt == torch.float32 and b.rows * b.cols * 4 > F32_TEMP_BYTES:
+                continue
+            if all(_accepts(op, name, dt) for op, name in users[b.id]):
+                swap[b.id] = Buffer(b.name, b.rows, b.cols, dt, "temp")
+                break
     if not swap:
         return out
     move = lambda v: View(swap[v.buf.id], v.row0, v.col0, v.rows, v.cols) if v is not None and v.buf.id in swap else v
