@@ -21,6 +21,7 @@
 #include <vector>
 
 #include "mk_device.cuh"
+#include "mma.cuh"
 #include "op_gemv_common.cuh"
 #include "ops.cuh"
 
@@ -196,14 +197,18 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
 // k-tile-major on purpose: the CTAs of an op walk K in step, each on its own n tile, so at any
 // moment they read neighbouring blocks (one sequential stream over the chip) instead of addresses a
 // large power of two apart.
+// to_fp16: the copy holds the weights as fp16 -- for ops whose activations are fp16, because the tensor
+// core wants both operands of one type.  Exact for every bf16 value of normal fp16 magnitude
+// (6.1e-5 .. 65504); smaller ones land on fp16's subnormal grid (absolute error below 3e-8).
 __global__ void pack_weight_tiles(const __nv_bfloat16* __restrict__ w, long long ld, int N, int K, uint4* __restrict__ out,
-                                  long long chunks) {
+                                  long long chunks, int to_fp16) {
     const int kchunks = K / 8, ntiles = (N + 127) / 128;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < chunks; i += (long long)gridDim.x * blockDim.x) {
         const int row = (int)(i / kchunks), kc = (int)(i % kchunks);
         const int j = row >> 7, r = row & 127, t = kc >> 3, c = kc & 7;
         uint4 v = make_uint4(0u, 0u, 0u, 0u);
         if (row < N) v = __ldg(reinterpret_cast<const uint4*>(w + (long long)row * ld + (long long)kc * 8));
+        if (to_fp16) v = make_uint4(bf16x2_to_f16x2(v.x), bf16x2_to_f16x2(v.y), bf16x2_to_f16x2(v.z), bf16x2_to_f16x2(v.w));
         out[((long long)t * ntiles + j) * (kTcTileBytes / 16) + r * 8 + (c ^ (r & 7))] = v;
     }
 }
@@ -236,6 +241,7 @@ struct mk_program {
     struct Packed {                  // tile-image copy of one weight matrix (see pack_weight_tiles)
         uint64_t src; int N, K, ld;
         uint8_t* buf; size_t bytes; bool used, fresh;
+        bool fp16;                   // weights converted to fp16 (the ops reading it have fp16 activations)
     };
     std::vector<Packed> packed;
     struct Retired { uint8_t* buf; cudaEvent_t done; };   // packed copies no longer bound: freed once `done` has passed
@@ -548,6 +554,11 @@ int mk_program_set_ops(mk_program* p, const mk_op_desc* ops, int n_ops, void* st
         uint8_t* maps = h_tmaps + (size_t)k * 256;
         d.ptr[10] = 0;
         if (d.i[9] != mk::DT_BF16 && d.i[9] != mk::DT_F16) continue;
+        const bool xh = d.i[9] == mk::DT_F16;
+        // fp16 activations need fp16 weights (the tensor core takes one 16-bit type per instruction;
+        // mixing fp16 activations with bf16 weights raised an illegal-instruction fault): only the packed
+        // copy can provide them.  Without one, the op runs the mma.sync body, which converts in registers.
+        if (xh && (pack_off || (d.ptr[1] & 15) || d.ld[1] % 8 != 0)) continue;
         if (!encode_tile_map(maps, d.ptr[0], d.i[0], d.i[2], d.ld[0], d.i[0] <= 64 ? 64 : 128, false, d.i[9] == mk::DT_F16)) continue;
         // weights: the packed copy, made when a matrix (address, shape, pitch) is bound for the first
         // time and kept while it stays bound -- rebinding other operands (a new input tensor every
@@ -556,10 +567,10 @@ int mk_program_set_ops(mk_program* p, const mk_op_desc* ops, int n_ops, void* st
         if (!pack_off && !(d.ptr[1] & 15) && d.ld[1] % 8 == 0) {
             mk_program::Packed* hit = nullptr;
             for (auto& e : p->packed)
-                if (e.src == d.ptr[1] && e.N == d.i[1] && e.K == d.i[2] && e.ld == d.ld[1]) hit = &e;
+                if (e.src == d.ptr[1] && e.N == d.i[1] && e.K == d.i[2] && e.ld == d.ld[1] && e.fp16 == xh) hit = &e;
             if (!hit) {
                 free_retired(p, false);
-                mk_program::Packed e{d.ptr[1], d.i[1], d.i[2], d.ld[1], nullptr, 0, false, true};
+                mk_program::Packed e{d.ptr[1], d.i[1], d.i[2], d.ld[1], nullptr, 0, false, true, xh};
                 e.bytes = (size_t)((d.i[1] + 127) / 128) * 128 * (size_t)d.i[2] * 2;
                 cudaError_t err = cudaMalloc(&e.buf, e.bytes);
                 if (err != cudaSuccess && !p->retired.empty()) {       // out of memory with copies waiting to be freed
@@ -579,7 +590,7 @@ int mk_program_set_ops(mk_program* p, const mk_op_desc* ops, int n_ops, void* st
                     const long long chunks = (long long)(hit->bytes / 16);
                     const int blocks = (int)((chunks + 255) / 256 < 4096 ? (chunks + 255) / 256 : 4096);
                     mk::pack_weight_tiles<<<blocks, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(hit->src), hit->ld, hit->N,
-                                                                  hit->K, reinterpret_cast<uint4*>(hit->buf), chunks);
+                                                                  hit->K, reinterpret_cast<uint4*>(hit->buf), chunks, hit->fp16 ? 1 : 0);
                     MK_CUDA(cudaGetLastError());
                     hit->fresh = false;
                 }
@@ -587,6 +598,7 @@ int mk_program_set_ops(mk_program* p, const mk_op_desc* ops, int n_ops, void* st
                 d.ptr[10] = reinterpret_cast<uint64_t>(hit->buf);
             }
         }
+        if (xh && !d.ptr[10]) continue;                 // (the copy could not be allocated)
         if (d.ptr[10] || encode_tile_map(maps + 128, d.ptr[1], d.i[1], d.i[2], d.ld[1], 128, true)) {
             d.ptr[11] = reinterpret_cast<uint64_t>(p->d_tmaps + (size_t)k * 256);
             any_map = true;

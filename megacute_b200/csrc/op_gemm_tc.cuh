@@ -30,11 +30,13 @@
 
 namespace mk {
 
-// instruction descriptor, kind::f16: D = f32 (bits 4-5 = 1), A format (bits 7-9: 0 = fp16, 1 = bf16), B = bf16
-// (bits 10-12 = 1), both K-major, N = 128 (bits 17-22 = N / 8), M = 128 (bits 24-28 = M / 16).  The weights are
-// always bf16; the activations are bf16 or -- runtime-private ones, see passes.promote_temps -- fp16.
-__device__ __forceinline__ uint32_t tc_idesc(bool a_fp16) {
-    return (1u << 4) | ((a_fp16 ? 0u : 1u) << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+// instruction descriptor, kind::f16: D = f32 (bits 4-5 = 1), A format (bits 7-9) and B format (bits 10-12):
+// 0 = fp16, 1 = bf16, both K-major, N = 128 (bits 17-22 = N / 8), M = 128 (bits 24-28 = M / 16).  Both
+// operands have one type: bf16, or -- when the activations are runtime-private ones kept in fp16, see
+// passes.promote_temps -- fp16, with the packed weight copy converted to fp16 by the host library.
+__device__ __forceinline__ uint32_t tc_idesc(bool fp16) {
+    const uint32_t fmt = fp16 ? 0u : 1u;
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
 }
 
 // shared-memory matrix descriptor of a K-major tile with the 128-byte swizzle: start address,

@@ -127,8 +127,9 @@ def test_noalloc_runs_tile_gemm_and_decode_attention(cuda, monkeypatch):
         assert rel_l2(got, ref[0]) < TOL
         assert int(ds["pos"]) == int(ref_st["pos"]) == 121
         assert rel_l2(ds["k_cache"].float(), want_k.float()) < 1e-3
-        for b in prog.g.buffers:                   # ... and zero again on exit
-            if b.kind == "workspace":
+        parts = {o.part.buf.id for o in prog.g.ops if o.kind == "DecodeAttention"}
+        for b in prog.g.buffers:                   # ... and zero again on exit (split-K sums, arrival counts; the
+            if b.kind == "workspace" and b.id not in parts:      # split-KV partial rows are overwritten, not zeroed)
                 assert not prog._bufs[b.id].any()
     assert torch.cuda.current_device() == before   # the entry point leaves the caller's device alone
 
