@@ -39,6 +39,11 @@ DECODE_MERGE_BYTES = 88 * 1024   # shared memory the merging split may fill with
 DEC_FIXED_US, DEC_MERGE_US, DEC_MERGE_US_PER_SPLIT, DEC_TILE_US = 4.0, 1.0, 0.05, 1.1
 # of the fixed cost, the part an instruction pays once however many kv heads it handles (fetch, dependency wait, arrival)
 DEC_SHARED_US = 2.5
+# many-sequence form (one instruction = a sequence's KV split over all kv heads, whole rows through bulk copies):
+# used from this many sequences on; us per instruction, us per 16-row tile per KB of cache row, merge (base, per split)
+BULK_MIN_BATCH = 8
+BULK_FIXED_US, BULK_TILE_US_PER_KB, BULK_MERGE_US, BULK_MERGE_US_PER_SPLIT = 4.0, 0.7, 1.0, 0.1
+BULK_TILE_ROWS = 16
 
 # ---- instruction word layout (16 x int32)
 IW = 16

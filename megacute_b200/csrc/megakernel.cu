@@ -56,6 +56,12 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
         }
         c->w_slot = c->w_phase = 0;
         mbar_init(&c->acc_full, 1);
+        for (int s = 0; s < kKvSlots; ++s) {
+            mbar_init(&c->kv_full[s], 1);
+            mbar_init(&c->kv_empty[s], kComputeWarps);
+        }
+        mbar_init(&c->kv_go, 1);
+        c->kv_cons = 0;
         c->acc_uses = 0;
         c->tmem_base = kTcNoTmem;
         c->abort = 0;
@@ -175,6 +181,12 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
         for (int s = 0; s < kTcWSlots; ++s) {
             unsigned long long t0 = globaltimer();
             while (!(mbar_try_wait(&c->w_full[s], 0) || mbar_try_wait(&c->w_full[s], 1))) {
+                if (globaltimer() - t0 > 20000000ull) break;
+            }
+        }
+        for (int s = 0; s < kKvSlots; ++s) {                       // KV tiles of the many-sequence decode attention
+            unsigned long long t0 = globaltimer();
+            while (!(mbar_try_wait(&c->kv_full[s], 0) || mbar_try_wait(&c->kv_full[s], 1))) {
                 if (globaltimer() - t0 > 20000000ull) break;
             }
         }

@@ -47,6 +47,11 @@ constexpr int kTcXOff = 512;                              // first 1024-aligned 
 constexpr int kTcCols = 128;                              // fp32 accumulator columns in tensor memory
 constexpr uint32_t kTcNoTmem = 0xffffffffu;               // Ctrl::tmem_base before the CTA's first allocation
 static_assert((kRingBytes + kTcXOff) % 1024 == 0 && kTcXOff + kTcXStages * kTcTileBytes + kTcTileBytes / 2 <= kWorkBytes, "activation tiles");
+// many-sequence decode attention (op_decode_bulk.cuh): five slots in the work area, each one tile of 16
+// whole cache rows (at most 1 KB each) stored as four 4-row groups 32 bytes apart beyond their size
+constexpr int kKvSlots = 5;
+constexpr int kKvSlotBytes = 4 * (4 * 1024 + 32);
+static_assert(kKvSlots * kKvSlotBytes <= kWorkBytes, "KV slots exceed the work area");
 constexpr int kTcWSlots = 8;
 __host__ __device__ constexpr int tc_wslot_off(int slot) { return slot * kTcTileBytes; }
 static_assert(kTcWSlots * kTcTileBytes <= kRingBytes, "weight slots");
@@ -93,6 +98,10 @@ struct Ctrl {                     // lives in the last kCtrlBytes of shared memo
     unsigned long long w_full[kTcWSlots];    // ... a weight k-tile has landed in its slot of the ring
     unsigned long long w_empty[kTcWSlots];   // ... the MMAs that read it have completed
     unsigned long long acc_full;      // ... every MMA of the instruction has completed: the accumulator can be read
+    unsigned long long kv_full[kKvSlots];    // many-sequence decode attention: a K or V tile has landed in its slot
+    unsigned long long kv_empty[kKvSlots];   // ... every compute warp has read it
+    unsigned long long kv_go;                // ... the compute warps have handed the work area to the finisher warp's copies
+    uint32_t kv_cons;                        // ... the compute warps' position in the slots (slot | phase << 8)
     uint32_t tmem_base;               // ... tensor-memory address of the accumulator (written by tcgen05.alloc)
     uint8_t x_use_load[2 * kTcXStages];   // ... how often each stage has been filled / consumed since the launch
     uint8_t x_use_mma[2 * kTcXStages];    //     began (the parities of x_empty / x_full)

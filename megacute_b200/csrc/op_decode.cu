@@ -7,6 +7,7 @@ __device__ bool mk_op_decode_attn(const Params& p, const mk_op_desc* op, int a0,
                                   int seq, int narrive, int arrive_off) {
     const SmemMap m = smem_map();
     const int D = op->i[3], G = op->i[1] / op->i[2];
+    if (op->i[11]) return mk_op_decode_bulk(p, op, a0, a2, nwait, wait_off, seq, narrive, arrive_off);
     if (op->i[10] > 1) {        // several kv heads per instruction (batched decode)
         if (D == 64) {
             if (G <= 4) return op_decode_attn_heads<64, 4>(p, m.ctrl, op, a0, a1, a2, m.work, nwait, wait_off, seq, narrive, arrive_off);

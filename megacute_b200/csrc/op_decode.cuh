@@ -22,7 +22,8 @@
 // i 0 B, 1 H, 2 KVH, 3 D, 4 max_seq, 5 splits, 6 fused, 7 dtype of q / k_new / v_new, 8 out dtype,
 //   9 zero q / k_new / v_new after use (they are fp32 columns of a split-K workspace: the instruction that
 //     writes the pair's output hands them back zeroed, as the SplitFinalize it replaces would),
-//   10 kv heads per instruction;  f 0 scale
+//   10 kv heads per instruction, 11 many-sequence form (op_decode_bulk.cuh: all kv heads, whole rows by bulk copies);
+//   f 0 scale
 // args: 0 b, 1 kv head, 2 split
 #pragma once
 #include "mk_device.cuh"

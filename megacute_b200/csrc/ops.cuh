@@ -25,6 +25,9 @@ __device__ void mk_op_attention(const mk_op_desc* op, int a0, int a1, int a2);
 // (waits for its own dependencies and publishes its own arrivals; returns whether the CTA is aborting)
 __device__ bool mk_op_decode_attn(const Params& p, const mk_op_desc* op, int a0, int a1, int a2, int nwait, int wait_off,
                                   int seq, int narrive, int arrive_off);
+// (many-sequence form: all kv heads of a sequence per instruction, whole cache rows through bulk copies)
+__device__ bool mk_op_decode_bulk(const Params& p, const mk_op_desc* op, int b, int s, int nwait, int wait_off, int seq,
+                                  int narrive, int arrive_off);
 // finalize / eltwise / norm / rope_append / increment; returns false for an unknown kind
 __device__ bool mk_op_pointwise(const mk_op_desc* op, int a0, int a1);
 

@@ -19,7 +19,8 @@ view's first element.  Field meaning per kind (the kernel side repeats it next t
   ATTENTION    ptr q, k, v, out; i batch, seq_q, seq_k, heads, kv_heads, head_dim, causal, out dtype; f scale
   ROPE_APPEND  ptr qkv, cos, sin, pos, q_out, k_cache, v_cache; i B, H, KVH, D, max_seq, qkv dtype
   DECODE_ATTN  ptr q, k_cache, v_cache, pos, out, k_new, v_new, cos, sin, part, count;
-               i B, H, KVH, D, max_seq, splits, fused, q dtype, out dtype; f scale
+               i B, H, KVH, D, max_seq, splits, fused, q dtype, out dtype, zero inputs, kv heads per
+               instruction, many-sequence form; f scale
   INCREMENT    ptr pos
 """
 
@@ -135,7 +136,8 @@ def fill(d, op: Op, addr) -> None:
         d.kind = C.OP_DECODE_ATTN
         ptrs = [op.q, op.k_cache, op.v_cache, op.pos, op.out, op.k_new, op.v_new, op.cos, op.sin, op.part, op.count]
         ints = [op.batch, op.heads, op.kv_heads, op.head_dim, op.max_seq, op.splits, int(op.k_new is not None),
-                dt(op.q), dt(op.out), int(bool(op.zero_inputs)), int(op.heads_per_inst or 1)]
+                dt(op.q), dt(op.out), int(bool(op.zero_inputs)), int(op.heads_per_inst or 1), int(bool(op.bulk))]
+        assert not op.bulk or (op.heads_per_inst == op.kv_heads and op.head_dim == 64 and op.kv_heads <= C.COMPUTE_WARPS)
         assert not op.zero_inputs or dt(op.q) == 1
         assert op.k_new is None or dt(op.k_new) == dt(op.v_new) == dt(op.q)
         assert op.splits <= C.MAX_KV_SPLITS

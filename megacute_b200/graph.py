@@ -123,7 +123,8 @@ OP_TABLE = {
                         ("heads", "kv_heads", "head_dim", "max_seq")),
     "DecodeAttention": (("q", "k_cache", "v_cache", "pos", "k_new", "v_new", "cos", "sin", "part", "count"),
                         ("out", "part", "count"),
-                        ("batch", "heads", "kv_heads", "head_dim", "max_seq", "scale", "splits", "zero_inputs", "heads_per_inst")),
+                        ("batch", "heads", "kv_heads", "head_dim", "max_seq", "scale", "splits", "zero_inputs", "heads_per_inst",
+                         "bulk")),
     "Increment":       ((), ("pos",), ()),
 }
 
@@ -276,7 +277,10 @@ def _chk_decode_attention(o):
     D = o.head_dim
     o.splits = o.splits or 1
     o.heads_per_inst = o.heads_per_inst or 1
-    assert o.kv_heads % o.heads_per_inst == 0 and (o.heads_per_inst == 1 or o.splits == 1)
+    o.bulk = bool(o.bulk)
+    # several kv heads per instruction: unsplit (one head after the other), or the many-sequence form (all of them at once)
+    assert o.kv_heads % o.heads_per_inst == 0 and (o.heads_per_inst == 1 or o.splits == 1 or o.bulk)
+    assert not o.bulk or (o.heads_per_inst == o.kv_heads and D == 64)
     assert o.heads % o.kv_heads == 0 and o.heads // o.kv_heads <= 8, "decode attention: GQA group <= 8"
     assert D in (64, 128) and o.max_seq % 128 == 0
     assert o.q.shape == o.out.shape == (o.batch, o.heads * D)

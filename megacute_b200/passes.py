@@ -128,10 +128,54 @@ def kv_heads_per_instruction(pairs: int, kv_heads: int, max_seq: int, sm_count: 
     return best
 
 
+def bulk_eligible(op: Op) -> bool:
+    """Can this decode attention run in the many-sequence form (csrc/op_decode_bulk.cuh)?  One warp per
+    kv head, head_dim 64, and cache views that are whole rows of their buffers, 128 bytes per kv head,
+    so that consecutive rows are one contiguous run of memory."""
+    if os.environ.get("MEGACUTE_B200_ATT_BULK") == "0":
+        return False
+    whole = all(v.col0 == 0 and v.cols == v.buf.cols for v in (op.k_cache, op.v_cache))
+    ok = op.head_dim == 64 and op.kv_heads <= C.COMPUTE_WARPS and whole and op.k_cache.cols == op.kv_heads * 64
+    if os.environ.get("MEGACUTE_B200_ATT_BULK") == "1":
+        return ok
+    return ok and op.batch >= C.BULK_MIN_BATCH
+
+
+def bulk_kv_splits(batch: int, kv_heads: int, max_seq: int, sm_count: int) -> int:
+    """KV splits per sequence in the many-sequence form: the count with the lowest modelled time
+    waves x (fixed cost + 16-row tiles per split x time per tile [+ partials and merge when split]).
+    Unlike the per-head form every instruction streams whole rows, so long contexts want enough
+    instructions to fill the last wave evenly.  MEGACUTE_B200_KV_SPLITS overrides the choice."""
+    cap = max(1, min(max_seq // C.MIN_SPLIT_KEYS, C.MAX_KV_SPLITS))
+    if os.environ.get("MEGACUTE_B200_KV_SPLITS"):
+        return max(1, min(cap, int(os.environ["MEGACUTE_B200_KV_SPLITS"])))
+    tile_us = C.BULK_TILE_US_PER_KB * kv_heads * 128 / 1024
+    best, best_cost = 1, float("inf")
+    for s in range(1, cap + 1):
+        waves = -(-(batch * s) // sm_count)
+        tiles = -(-(-(-max_seq // s)) // C.BULK_TILE_ROWS)
+        merge = C.BULK_MERGE_US + C.BULK_MERGE_US_PER_SPLIT * s if s > 1 else 0.0
+        cost = waves * (C.BULK_FIXED_US + merge + tiles * tile_us)
+        if cost < best_cost - 1e-9:
+            best, best_cost = s, cost
+    return best
+
+
 def split_kv(g: Graph, sm_count: int) -> Graph:
     out = g.derive()
     ops = []
     for op in g.ops:
+        if op.kind == "DecodeAttention" and op.splits == 1 and bulk_eligible(op):
+            s = bulk_kv_splits(op.batch, op.kv_heads, op.max_seq, sm_count)
+            op = op.clone(heads_per_inst=op.kv_heads, bulk=True)
+            if s > 1:
+                G, D = op.heads // op.kv_heads, op.head_dim
+                cols = -(-(G * D + 2 * G) // 4) * 4          # per (kv head, split): O (G x D), running max (G), sum (G)
+                part = out.workspace((op.batch * op.kv_heads * s, cols), torch.float32)
+                count = out.workspace((op.batch * op.kv_heads, 1), torch.int32)
+                op = op.clone(splits=s, part=part, count=count)
+            ops.append(op)
+            continue
         if op.kind == "DecodeAttention" and op.splits == 1:
             pairs = op.batch * op.kv_heads
             s = kv_splits(pairs, op.max_seq, sm_count, op.head_dim)

@@ -228,8 +228,8 @@ def tile_op(op: Op, sm_count: int) -> Tiled:
                     _acc(op.v_new, WRITE, b, b + 1, h * D, (h + hp) * D, n=n, covers=S == 1)]
         if S > 1:
             r = b * op.kv_heads + h
-            acc += [_acc(op.part, WRITE, r * S, (r + 1) * S, n=n, covers=False),
-                    _acc(op.count, WRITE, r, r + 1, n=n, covers=False)]
+            acc += [_acc(op.part, WRITE, r * S, (r + hp) * S, n=n, covers=False),
+                    _acc(op.count, WRITE, r, r + hp, n=n, covers=False)]
         return Tiled(_args(n, b, h, s), acc)
     if k == "Increment":
         return Tiled(_args(1), [_acc(op.pos, WRITE, n=1)])

@@ -210,16 +210,21 @@ def test_small_dit_stack(cuda):
     assert_close(outs, ref)
 
 
-@pytest.mark.parametrize("B,att_heads", [(16, None), (64, None), (64, "2")])
-def test_batched_decode_small(cuda, monkeypatch, B, att_heads):
-    """More than 8 sequences: unfolded norms, tile GEMMs with split-K, many-pair decode attention --
-    one kv head per instruction, or (forced here; chosen when there are more pairs than SMs) several."""
+@pytest.mark.parametrize("B,att_heads,bulk", [(16, None, "0"), (64, None, "0"), (64, "2", "0"), (16, None, None), (64, None, None)])
+def test_batched_decode_small(cuda, monkeypatch, B, att_heads, bulk):
+    """More than 8 sequences: unfolded norms, tile GEMMs with split-K, and the decode attention in its
+    many-sequence form (the default from 8 sequences on: all kv heads of a sequence per instruction) or,
+    with that switched off, in the per-head form -- one kv head per instruction, or (forced here;
+    chosen when there are more pairs than SMs) several."""
     if att_heads:
         monkeypatch.setenv("MEGACUTE_B200_ATT_HEADS", att_heads)
+    if bulk:
+        monkeypatch.setenv("MEGACUTE_B200_ATT_BULK", bulk)
     g, params, st, ids = small_decode(B=B, E=256, H=4, KVH=2, F=512, n=2, max_seq=256, ctx=120, vocab=1000)
     prog = mc.compile(g)
     hp = {o.heads_per_inst for o in prog.g.ops if o.kind == "DecodeAttention"}
-    assert hp == ({2} if att_heads else {1})
+    assert hp == ({2} if att_heads or not bulk else {1})
+    assert {bool(o.bulk) for o in prog.g.ops if o.kind == "DecodeAttention"} == {not bulk}
     dp = {k: v.to(cuda) for k, v in params.items()}
     ds = {k: v.to(cuda) for k, v in st.items()}
     rs = {k: v.clone() for k, v in st.items()}
@@ -237,12 +242,14 @@ def test_batched_decode_small(cuda, monkeypatch, B, att_heads):
     assert np.array_equal(prog.counters(), prog.sched.counter_target * 3)
 
 
-def test_batched_decode_workspace_inputs_with_kv_splits(cuda, monkeypatch):
+@pytest.mark.parametrize("bulk", ["0", "1"])
+def test_batched_decode_workspace_inputs_with_kv_splits(cuda, monkeypatch, bulk):
     """Split-K QKV projection feeding the fused decode attention straight from its fp32 workspace, with
-    the KV range split over several instructions: the pair's last instruction to arrive zeroes the
-    workspace columns, so three consecutive steps (which accumulate into the same workspace) stay
-    right."""
+    the KV range split over several instructions: the pair's (many-sequence form: the sequence's) last
+    instruction to arrive zeroes the workspace columns, so three consecutive steps (which accumulate
+    into the same workspace) stay right."""
     monkeypatch.setenv("MEGACUTE_B200_KV_SPLITS", "3")
+    monkeypatch.setenv("MEGACUTE_B200_ATT_BULK", bulk)
     g, params, st, ids = small_decode(B=16, E=2048, H=32, KVH=8, F=512, n=1, max_seq=512, ctx=300, vocab=512)
     prog = mc.compile(g)
     att = [o for o in prog.g.ops if o.kind == "DecodeAttention"]

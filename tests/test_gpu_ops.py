@@ -167,6 +167,26 @@ def test_streaming_linear_chain_and_counters(cuda):
 @pytest.mark.parametrize("fused", [False, True])
 def test_decode_attention(cuda, B, H, KVH, D, max_seq, ctx, fused):
     """rope_append + decode_attention, kept separate (q_out is also an output) or fused by the pass."""
+    _decode_attention_case(cuda, B, H, KVH, D, max_seq, ctx, fused)
+
+
+@pytest.mark.parametrize("B,H,KVH,max_seq,ctx,splits", [
+    (9, 8, 2, 128, 37, 1), (9, 8, 2, 128, 37, 2), (12, 16, 2, 256, 45, 3), (16, 32, 8, 384, 300, 1), (16, 32, 8, 384, 300, 5),
+    (3, 32, 8, 256, 17, 4), (70, 32, 8, 128, 0, 2), (24, 8, 8, 256, 200, 3), (150, 32, 8, 256, 129, 2)])
+@pytest.mark.parametrize("fused", [False, True])
+def test_decode_attention_many_sequences(cuda, monkeypatch, B, H, KVH, max_seq, ctx, splits, fused):
+    """The many-sequence form: one instruction = a sequence's KV split over all kv heads, whole cache rows
+    through bulk copies, one warp per kv head.  GQA groups of 1, 4 and 8, fewer kv heads than warps,
+    contexts that are not a multiple of the 16-row tile, shorter than one tile, or empty; splits that get
+    no keys; the last split of a sequence to arrive merges."""
+    monkeypatch.setenv("MEGACUTE_B200_ATT_BULK", "1")
+    monkeypatch.setenv("MEGACUTE_B200_KV_SPLITS", str(splits))
+    prog = _decode_attention_case(cuda, B, H, KVH, 64, max_seq, ctx, fused)
+    att = [o for o in prog.g.ops if o.kind == "DecodeAttention"]
+    assert att and all(o.bulk and o.heads_per_inst == KVH and o.splits == min(splits, max_seq // 64) for o in att)
+
+
+def _decode_attention_case(cuda, B, H, KVH, D, max_seq, ctx, fused):
     g = mc.Graph()
     qkv = g.input("qkv", (B, (H + 2 * KVH) * D))
     cos = g.input("cos", (max_seq, D))
@@ -204,6 +224,8 @@ def test_decode_attention(cuda, B, H, KVH, D, max_seq, ctx, fused):
     for b in prog.g.buffers:
         if b.kind == "workspace" and b.dtype == torch.int32:
             assert int(prog.buffer(b).abs().sum()) == 0
+    assert np.array_equal(prog.counters(), prog.sched.counter_target * 2)
+    return prog
 
 
 # ---------------------------------------------------------------------------------------------

@@ -164,10 +164,35 @@ def test_finalize_fused_into_decode_attention():
     assert not any(o.zero_inputs for o in run_all(g1, 148).ops if o.kind == "DecodeAttention")
 
 
-def test_kv_heads_per_instruction_choice_and_schedule():
-    """More (sequence, kv head) pairs than SMs: several kv heads per attention instruction; the
-    schedule of such a graph still orders every hazard."""
+def test_many_sequence_attention_choice_and_schedule(monkeypatch):
+    """From 8 sequences on the decode attention runs in its many-sequence form: one instruction per
+    (sequence, KV split) over all kv heads, split count from the context length; the schedule of such
+    a graph orders every hazard, partial-row and arrival-count workspaces included."""
+    from megacute_b200.passes import bulk_kv_splits
+    assert bulk_kv_splits(64, 8, 1152, 148) == 2 and bulk_kv_splits(64, 8, 32896, 148) > 4
+    for B, splits in ((40, None), (16, "3")):
+        if splits:
+            monkeypatch.setenv("MEGACUTE_B200_KV_SPLITS", splits)
+        g, *_ = small_decode(B=B, n=2, E=512, H=8, KVH=8, F=512, vocab=512, max_seq=256, ctx=10)
+        g2 = run_all(g, 148)
+        att = [o for o in g2.ops if o.kind == "DecodeAttention"]
+        assert att and all(o.bulk and o.heads_per_inst == 8 for o in att)
+        if splits:
+            assert all(o.splits == 3 and o.part.rows == B * 8 * 3 for o in att)
+        s = schedule(g2, 148)
+        assert s.node_ranges[g2.ops.index(att[0])][1] - s.node_ranges[g2.ops.index(att[0])][0] == B * att[0].splits
+        _check_schedule(s, g2)
+        _simulate(s, g2, 0)
+        _ordered(s, g2)
+    g1, *_ = small_decode(B=2)
+    assert not any(o.bulk for o in run_all(g1, 148).ops if o.kind == "DecodeAttention")
+
+
+def test_kv_heads_per_instruction_choice_and_schedule(monkeypatch):
+    """The per-head form with more (sequence, kv head) pairs than SMs: several kv heads per attention
+    instruction; the schedule of such a graph still orders every hazard."""
     from megacute_b200.passes import kv_heads_per_instruction
+    monkeypatch.setenv("MEGACUTE_B200_ATT_BULK", "0")
     assert kv_heads_per_instruction(512, 8, 1280, 148) == 4            # batch 64 of the 1B shape: one wave of 128
     assert kv_heads_per_instruction(128, 8, 1280, 148) == 1            # fewer pairs than SMs: nothing to amortise over
     g, *_ = small_decode(B=40, n=1, E=512, H=8, KVH=8, F=512, vocab=512, max_seq=128, ctx=10)
