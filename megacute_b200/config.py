@@ -39,10 +39,13 @@ DECODE_MERGE_BYTES = 88 * 1024   # shared memory the merging split may fill with
 DEC_FIXED_US, DEC_MERGE_US, DEC_MERGE_US_PER_SPLIT, DEC_TILE_US = 4.0, 1.0, 0.05, 1.1
 # of the fixed cost, the part an instruction pays once however many kv heads it handles (fetch, dependency wait, arrival)
 DEC_SHARED_US = 2.5
-# many-sequence form (one instruction = a sequence's KV split over all kv heads, whole rows through bulk copies):
-# used from this many sequences on; us per instruction, us per 16-row tile per KB of cache row, merge (base, per split)
-BULK_MIN_BATCH = 8
-BULK_FIXED_US, BULK_TILE_US_PER_KB, BULK_MERGE_US, BULK_MERGE_US_PER_SPLIT = 4.0, 0.7, 1.0, 0.1
+# many-sequence form (one instruction = a sequence's KV split over all kv heads, whole rows through bulk copies),
+# constants measured on B200 at batch 64 (contexts 256 .. 32K, 1 .. 30 splits): used from BULK_MIN_BATCH sequences
+# on, or from BULK_MIN_BATCH_LONG when the cache is at least BULK_LONG_SEQ rows long (batch 8 and 16 at context
+# 1K were 5 - 10 % faster in the per-head form: more instructions to spread, and the stream is short);
+# us per 16-row tile per KB of cache row (all SMs streaming: the HBM rate); us per instruction = max(fixed, per split x S - 3)
+BULK_MIN_BATCH, BULK_MIN_BATCH_LONG, BULK_LONG_SEQ = 32, 8, 8192
+BULK_TILE_US_PER_KB, BULK_FIXED_US, BULK_US_PER_SPLIT = 0.745, 3.0, 0.8
 BULK_TILE_ROWS = 16
 
 # ---- instruction word layout (16 x int32)

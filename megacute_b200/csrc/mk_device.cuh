@@ -47,11 +47,23 @@ constexpr int kTcXOff = 512;                              // first 1024-aligned 
 constexpr int kTcCols = 128;                              // fp32 accumulator columns in tensor memory
 constexpr uint32_t kTcNoTmem = 0xffffffffu;               // Ctrl::tmem_base before the CTA's first allocation
 static_assert((kRingBytes + kTcXOff) % 1024 == 0 && kTcXOff + kTcXStages * kTcTileBytes + kTcTileBytes / 2 <= kWorkBytes, "activation tiles");
-// many-sequence decode attention (op_decode_bulk.cuh): five slots in the work area, each one tile of 16
-// whole cache rows (at most 1 KB each) stored as four 4-row groups 32 bytes apart beyond their size
-constexpr int kKvSlots = 5;
+// many-sequence decode attention (op_decode_bulk.cuh): the ring's memory as seven slots, each one tile of
+// 16 whole cache rows (at most 1 KB each) stored as four 4-row groups 32 bytes apart beyond their size.
+// A third kind of slot beside the streaming linear's stages and the tile GEMM's weight slots: the
+// producer warp drains one kind before it fills another.
+constexpr int kKvSlots = 7;
 constexpr int kKvSlotBytes = 4 * (4 * 1024 + 32);
-static_assert(kKvSlots * kKvSlotBytes <= kWorkBytes, "KV slots exceed the work area");
+static_assert(kKvSlots * kKvSlotBytes <= kRingBytes, "KV slots exceed the ring");
+constexpr int kKvTileRows = 16;
+constexpr int kKvGroupRows = 4;
+constexpr int kKvGroupSkew = 32;                          // bytes between groups beyond their size
+// rows [k_begin, k_end) of a sequence's n cached keys that split s of S attends; multiples of 16 so that
+// tiles never straddle the end of a sequence's cache rows (max_seq is a multiple of 128)
+__host__ __device__ inline void kv_split_range(int n, int S, int s, int& k_begin, int& k_end) {
+    const int per = (((n + S - 1) / S) + kKvTileRows - 1) / kKvTileRows * kKvTileRows;
+    k_begin = s * per < n ? s * per : n;
+    k_end = k_begin + per < n ? k_begin + per : n;
+}
 constexpr int kTcWSlots = 8;
 __host__ __device__ constexpr int tc_wslot_off(int slot) { return slot * kTcTileBytes; }
 static_assert(kTcWSlots * kTcTileBytes <= kRingBytes, "weight slots");
@@ -100,7 +112,7 @@ struct Ctrl {                     // lives in the last kCtrlBytes of shared memo
     unsigned long long acc_full;      // ... every MMA of the instruction has completed: the accumulator can be read
     unsigned long long kv_full[kKvSlots];    // many-sequence decode attention: a K or V tile has landed in its slot
     unsigned long long kv_empty[kKvSlots];   // ... every compute warp has read it
-    unsigned long long kv_go;                // ... the compute warps have handed the work area to the finisher warp's copies
+    unsigned long long kv_go;                // ... (unfused form) the instruction's dependencies are met: the row appended in this launch may be read
     uint32_t kv_cons;                        // ... the compute warps' position in the slots (slot | phase << 8)
     uint32_t tmem_base;               // ... tensor-memory address of the accumulator (written by tcgen05.alloc)
     uint8_t x_use_load[2 * kTcXStages];   // ... how often each stage has been filled / consumed since the launch

@@ -7,12 +7,17 @@
 // 128-byte row pieces with cp.async.  An SM draws ~33 GB/s through cp.async pieces and ~45 GB/s through
 // bulk copies of 4 KB and more, so with every SM streaming the KV cache moves at the HBM rate.
 //
-// Roles.  The finisher warp (idle in this op otherwise) issues the copies: it walks the instruction
-// list like the producer warp does, and for every instruction of this form streams the split's K and
-// V tiles through five 16 KB slots in the work area (kv_full / kv_empty barriers), starting when the
-// compute warps hand the work area over (kv_go).  Compute warp w owns kv head w for the whole split:
-// its own running max, sum and output accumulators, so nothing is merged across warps; the S splits
-// of a sequence are merged by the last one to arrive, as in the per-head form.
+// Roles.  The producer warp issues the copies (op_gemv_common.cuh, producer_loop): for every instruction
+// of this form on its walk down the CTA's instruction list it streams the split's K and V tiles through
+// seven 16 KB slots in the ring's memory (kv_full / kv_empty barriers) -- ahead of the compute warps and
+// across instruction boundaries, like weights: in the fused form the rows read (below pos) are written
+// by nothing in the launch, so the KV stream keeps running through dependency hops.  (The unfused form
+// also reads the row a RopeAppend of this launch appended: there the producer waits on kv_go, which the
+// compute warps signal once the instruction's dependencies are met.)  Compute warp w owns kv head w for
+// the whole split: its own running max, sum and output accumulators, so nothing is merged across warps;
+// the S splits of a sequence are merged by the last one to arrive, as in the per-head form.
+// Bytes in flight are what sets the rate: with five slots (80 KB, ~3 in flight) the stream ran at
+// ~29 GB/s per SM, no faster than the cp.async form.
 //
 // Shared-memory reads without bank conflicts.  Rows of a tile are 128 x KVH bytes apart, a multiple
 // of 128: the same 16-byte slot of every row falls into the same banks, and an MMA fragment needs
@@ -37,10 +42,6 @@
 
 namespace mk {
 
-constexpr int kKvTileRows = 16;
-constexpr int kKvGroupRows = 4;
-constexpr int kKvGroupSkew = 32;                                      // bytes between groups beyond their size
-
 __device__ __forceinline__ uint4 kv_lds128(uint32_t addr) {
     uint4 v;
     asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
@@ -52,14 +53,6 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
     return r;
 }
 
-// rows [k_begin, k_end) of the sequence's cached keys that split s of S attends; multiples of 16 so
-// that tiles never straddle the end of a sequence's cache rows (max_seq is a multiple of 128)
-__device__ __forceinline__ void kv_split_range(int n, int S, int s, int& k_begin, int& k_end) {
-    const int per = (((n + S - 1) / S) + kKvTileRows - 1) / kKvTileRows * kKvTileRows;
-    k_begin = min(n, s * per);
-    k_end = min(n, k_begin + per);
-}
-
 struct KvPos {
     int slot = 0;
     uint32_t phase = 0;
@@ -68,55 +61,10 @@ struct KvPos {
     }
 };
 
-// ---- finisher warp: stream the K and V tiles of one instruction.  Returns false when the launch is failing. ----
-__device__ __forceinline__ bool kv_issue(const Params& p, Ctrl* c, uint8_t* work, const mk_op_desc* op, int b, int s, int seq,
-                                         KvPos& pos, uint32_t& go_par) {
-    const int lane = threadIdx.x & 31;
-    int ok = 1;
-    if (lane == 0) {
-        const int KVH = op->i[2], L = op->i[4], S = op->i[5];
-        const bool fused = op->i[6] != 0;
-        const int rb = KVH * 64 * 2;                                  // bytes of a cache row
-        // the work area is ours once the compute warps have entered the instruction (unfused mode: once
-        // its dependencies are met -- the row a RopeAppend of this launch wrote is among the rows read)
-        ok = wait_barrier(p, c, &c->kv_go, go_par, seq, WHERE_DEP) ? 1 : 0;
-        if (ok) {
-            asm volatile("fence.proxy.async;" ::: "memory");          // earlier instructions wrote the work area with plain stores
-            const int posv = *reinterpret_cast<const volatile int*>(op->ptr[3]);
-            int k_begin, k_end;
-            kv_split_range(fused ? posv : posv + 1, S, s, k_begin, k_end);
-            const int ntiles = (k_end - k_begin + kKvTileRows - 1) / kKvTileRows;
-            const unsigned long long policy = l2_policy_evict_first();
-            for (int t = 0; t < ntiles && ok; ++t) {
-                const long long row = (long long)b * L + k_begin + t * kKvTileRows;
-#pragma unroll 1
-                for (int kv = 0; kv < 2 && ok; ++kv) {
-                    ok = wait_barrier(p, c, &c->kv_empty[pos.slot], pos.phase ^ 1u, seq, WHERE_RING_EMPTY) ? 1 : 0;
-                    if (!ok) break;
-                    const uint8_t* src = reinterpret_cast<const uint8_t*>(op->ptr[1 + kv]) + row * op->ld[1 + kv] * 2;
-                    uint8_t* dst = work + pos.slot * kKvSlotBytes;
-                    mbar_arrive_expect_tx(&c->kv_full[pos.slot], (uint32_t)(kKvTileRows * rb));
-#pragma unroll
-                    for (int g = 0; g < kKvTileRows / kKvGroupRows; ++g)
-                        bulk_g2s_hint(dst + g * (kKvGroupRows * rb + kKvGroupSkew), src + (long long)g * kKvGroupRows * op->ld[1 + kv] * 2,
-                                      (uint32_t)(kKvGroupRows * rb), &c->kv_full[pos.slot], policy);
-                    pos.advance();
-                }
-            }
-        }
-    }
-    go_par ^= 1u;
-    ok = __shfl_sync(0xffffffffu, ok, 0);
-    // (every lane keeps lane 0's position)
-    pos.slot = __shfl_sync(0xffffffffu, pos.slot, 0);
-    pos.phase = __shfl_sync(0xffffffffu, pos.phase, 0);
-    return ok != 0;
-}
-
 // ---- compute warps ----
 // All compute threads call this.  Returns after the instruction's global writes (the caller publishes).
 template <int GMAX>
-__device__ __forceinline__ void decode_bulk_body(const Params& p, Ctrl* c, const mk_op_desc* op, int b, int s, uint8_t* work,
+__device__ __forceinline__ void decode_bulk_body(const Params& p, Ctrl* c, const mk_op_desc* op, int b, int s, uint8_t* ring,
                                                  int nwait, int wait_off, int seq) {
     constexpr int D = 64;
     constexpr float NEG_INF = -__builtin_huge_valf();
@@ -140,9 +88,12 @@ __device__ __forceinline__ void decode_bulk_body(const Params& p, Ctrl* c, const
     kp.phase = (c->kv_cons >> 8) & 1u;
 
     // Fused mode reads only cache rows below pos, which nothing in this launch writes: the tiles
-    // stream while this instruction waits for its dependencies.  Unfused mode waits first.
-    if (!fused && wait_deps(p, c, nwait, wait_off, seq)) return;
-    if (t == 0) mbar_arrive(&c->kv_go);
+    // stream while this instruction waits for its dependencies.  Unfused mode waits first and tells
+    // the producer warp.
+    if (!fused) {
+        if (wait_deps(p, c, nwait, wait_off, seq)) return;
+        if (t == 0) mbar_arrive(&c->kv_go);
+    }
     // rope table row of pos: the chunks q4 and q4 + 4 of cos and sin
     float cs[16], sn[16];
     if (fused) {
@@ -240,7 +191,7 @@ __device__ __forceinline__ void decode_bulk_body(const Params& p, Ctrl* c, const
     const uint32_t k_first = (uint32_t)((q4 + 4 * (g & 1)) * 16), k_second = (uint32_t)((q4 + 4 * ((g & 1) ^ 1)) * 16);
     // V: rows 4 q4 .. 4 q4 + 3 (group q4), chunk g
     const uint32_t v_off = (uint32_t)(q4 * (kKvGroupRows * rb + kKvGroupSkew) + warp * (D * 2) + g * 16);
-    const uint32_t work_s = smem_u32(work);
+    const uint32_t work_s = smem_u32(ring);
     bool ok = true;
 #pragma unroll 1
     for (int tile = 0; tile < ntiles; ++tile) {
@@ -392,26 +343,30 @@ __device__ __forceinline__ void decode_bulk_body(const Params& p, Ctrl* c, const
     phase_mark(p, c, 2);
     if (!c->flag) return;
     __threadfence();
-    // ---- last split to arrive: merge the S partials of every head (warp w: head w), straight from L2 ----
+    // ---- last split to arrive: merge the S partials of every head (warp w: head w), straight from L2.
+    // The loads of different splits are independent of each other: the loops are unrolled and free of
+    // branches so that many are in flight at once (one split per L2 round trip costs ~1 us each). ----
     if (hrow) {
         const float* base = part + (long long)(b * KVH + warp) * S * ldp;
         float mx = NEG_INF;
+#pragma unroll 8
         for (int k = 0; k < S; ++k) mx = fmaxf(mx, __ldcg(base + k * ldp + GD + g));
         float acc[16], l = 0.f;
 #pragma unroll
         for (int e = 0; e < 16; ++e) acc[e] = 0.f;
-        if (mx != NEG_INF) {
-            for (int k = 0; k < S; ++k) {
-                const float mk_ = __ldcg(base + k * ldp + GD + g);
-                if (mk_ == NEG_INF) continue;
-                const float w = ex2(mk_ - mx);
-                l = fmaf(w, __ldcg(base + k * ldp + GD + G + g), l);
+#pragma unroll 4
+        for (int k = 0; k < S; ++k) {
+            const float mk_ = __ldcg(base + k * ldp + GD + g);
+            const float lk = __ldcg(base + k * ldp + GD + G + g);
+            float4 v[4];
 #pragma unroll
-                for (int e = 0; e < 16; e += 4) {
-                    const float4 v = __ldcg(reinterpret_cast<const float4*>(base + k * ldp + g * D + q4 * 16 + e));
-                    acc[e] = fmaf(w, v.x, acc[e]); acc[e + 1] = fmaf(w, v.y, acc[e + 1]);
-                    acc[e + 2] = fmaf(w, v.z, acc[e + 2]); acc[e + 3] = fmaf(w, v.w, acc[e + 3]);
-                }
+            for (int e = 0; e < 4; ++e) v[e] = __ldcg(reinterpret_cast<const float4*>(base + k * ldp + g * D + q4 * 16 + 4 * e));
+            const float w = mk_ == NEG_INF ? 0.f : ex2(mk_ - mx);        // (a split without keys wrote zeros)
+            l = fmaf(w, lk, l);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                acc[4 * e] = fmaf(w, v[e].x, acc[4 * e]); acc[4 * e + 1] = fmaf(w, v[e].y, acc[4 * e + 1]);
+                acc[4 * e + 2] = fmaf(w, v[e].z, acc[4 * e + 2]); acc[4 * e + 3] = fmaf(w, v[e].w, acc[4 * e + 3]);
             }
         }
         const float inv = l == 0.f ? 0.f : rcp(l);
@@ -425,9 +380,9 @@ __device__ __forceinline__ void decode_bulk_body(const Params& p, Ctrl* c, const
 
 // Waits for its own dependencies and publishes its own arrivals.  Returns whether the CTA is aborting.
 template <int GMAX>
-static __device__ __noinline__ bool op_decode_bulk(const Params& p, Ctrl* c, const mk_op_desc* op, int b, int s, uint8_t* work,
+static __device__ __noinline__ bool op_decode_bulk(const Params& p, Ctrl* c, const mk_op_desc* op, int b, int s, uint8_t* ring,
                                                    int nwait, int wait_off, int seq, int narrive, int arrive_off) {
-    decode_bulk_body<GMAX>(p, c, op, b, s, work, nwait, wait_off, seq);
+    decode_bulk_body<GMAX>(p, c, op, b, s, ring, nwait, wait_off, seq);
     return publish(p, c, narrive, arrive_off);
 }
 

@@ -72,6 +72,13 @@ struct StageCursor {
     const uint8_t* wpack;
     long long wtile0;
     int wstride;
+    // many-sequence decode attention (op_decode_bulk.cuh): the K and V tiles [kv_t, kv_nt) of the
+    // instruction's KV split are still to be copied; kv_which alternates K (0) and V (1)
+    bool kv;
+    int kv_t, kv_nt, kv_which, kv_rb;
+    bool kv_gated;           // unfused form: the first copy waits for kv_go
+    const uint8_t* kv_src[2];
+    long long kv_pitch[2];   // bytes between cache rows
 
     // position on the next streaming-linear instruction at or after `idx`
     __device__ __forceinline__ void seek(const Params& p) {
@@ -80,9 +87,27 @@ struct StageCursor {
             const int opi = in.opi - 1;
             if (opi < 0 || opi >= p.n_ops) { idx = p.n_insts; return; }
             const mk_op_desc* op = p.ops + opi;
+            if (op->kind == MK_OP_DECODE_ATTN && op->i[11]) {
+                const int KVH = op->i[2], L = op->i[4], S = op->i[5];
+                const bool fused = op->i[6] != 0;
+                // pos is rewritten only by the launch's last instruction, behind every reader's arrival
+                const int posv = *reinterpret_cast<const volatile int*>(op->ptr[3]);
+                int k_begin, k_end;
+                kv_split_range(fused ? posv : posv + 1, S, in.a2, k_begin, k_end);
+                gemm = false; kv = true; seq = in.seq;
+                kv_t = 0; kv_nt = (k_end - k_begin + kKvTileRows - 1) / kKvTileRows; kv_which = 0;
+                kv_rb = KVH * 64 * 2;
+                kv_gated = !fused;
+                for (int w = 0; w < 2; ++w) {
+                    kv_pitch[w] = (long long)op->ld[1 + w] * 2;
+                    kv_src[w] = reinterpret_cast<const uint8_t*>(op->ptr[1 + w]) + ((long long)in.a0 * L + k_begin) * kv_pitch[w];
+                }
+                if (kv_nt > 0 || kv_gated) return;     // (a gated instruction without tiles still consumes its kv_go)
+                continue;
+            }
             if (op->kind == MK_OP_GEMM && op->ptr[11]) {
                 const int kc = op->i[2] / op->i[4];
-                gemm = true; seq = in.seq; kt = 0; nk = kc / 64; kbeg = in.a2 * kc; n0 = in.a1 * 128;
+                gemm = true; kv = false; seq = in.seq; kt = 0; nk = kc / 64; kbeg = in.a2 * kc; n0 = in.a1 * 128;
                 wmap = reinterpret_cast<const uint8_t*>(op->ptr[11]) + 128;
                 wpack = reinterpret_cast<const uint8_t*>(op->ptr[10]);
                 wstride = (op->i[1] + 127) / 128;
@@ -91,7 +116,7 @@ struct StageCursor {
                 continue;
             }
             if (op->kind != MK_OP_GEMV) continue;
-            gemm = false;
+            gemm = false; kv = false;
             seq = in.seq; o0 = in.a0; o1 = in.a1; K = op->i[2]; flags = op->flags;
             w = reinterpret_cast<const __nv_bfloat16*>(op->ptr[1]);
             ldw = op->ld[1];
@@ -111,7 +136,7 @@ struct StageCursor {
     }
     __device__ __forceinline__ bool valid(const Params& p) const { return idx < p.n_insts; }
     __device__ __forceinline__ void advance(const Params& p) {
-        if (gemm) {                                   // (the L2 prefetch cursor: whole instruction at once)
+        if (gemm || kv) {                             // (the L2 prefetch cursor: whole instruction at once)
             idx += gridDim.x;
             seek(p);
             return;
@@ -126,7 +151,7 @@ struct StageCursor {
     __device__ __forceinline__ void piece(int lane, const __nv_bfloat16*& src, int& bytes, int& dst_off) const {
         const bool swi = flags & GEMV_F_SWIGLU;
         src = w; bytes = 0; dst_off = 0;
-        if (gemm) return;
+        if (gemm || kv) return;
         if (flags & GEMV_F_UNITS) {
             const int r = lane & 15;
             const int o = o0 + (swi ? g >> 1 : g) * 16 + r;
@@ -155,18 +180,25 @@ __device__ __forceinline__ void producer_loop(const Params& p, Ctrl* c, uint8_t*
     long long t_first = 0;
     int slot_first = 0;
     const unsigned long long stream_policy = l2_policy_evict_first();
-    // tile GEMM weight slots: position, and which kind of slot the ring's memory currently serves
+    // tile GEMM weight slots and decode attention KV slots: positions, and which kind of slot the
+    // ring's memory currently serves
     int wslot = 0;
     uint32_t wphase = 0;
-    bool gemm_mode = false;
+    int kvslot = 0;
+    uint32_t kvphase = 0, kvgo = 0;
+    enum { MODE_STAGES = 0, MODE_WTILES = 1, MODE_KVTILES = 2 };
+    int mode = MODE_STAGES;
     // Wait until the compute side has released every slot of the kind used so far (slot s was last
     // filled in the current round if s < position, else in the previous one).
-    auto drain = [&](bool tiles) -> bool {
+    auto drain = [&](int kind) -> bool {
         int ok = 1;
         if (lane == 0) {
-            if (tiles) {
+            if (kind == MODE_WTILES) {
                 for (int s = 0; s < kTcWSlots && ok; ++s)
                     ok = wait_barrier(p, c, &c->w_empty[s], (wphase ^ (s < wslot ? 1u : 0u)) ^ 1u, rc.seq, WHERE_RING_EMPTY) ? 1 : 0;
+            } else if (kind == MODE_KVTILES) {
+                for (int s = 0; s < kKvSlots && ok; ++s)
+                    ok = wait_barrier(p, c, &c->kv_empty[s], (kvphase ^ (s < kvslot ? 1u : 0u)) ^ 1u, rc.seq, WHERE_RING_EMPTY) ? 1 : 0;
             } else {
                 for (int s = 0; s < kStages && ok; ++s)
                     ok = wait_barrier(p, c, &c->empty[s], (pos.phase ^ (s < pos.stage ? 1u : 0u)) ^ 1u, rc.seq, WHERE_RING_EMPTY) ? 1 : 0;
@@ -174,17 +206,58 @@ __device__ __forceinline__ void producer_loop(const Params& p, Ctrl* c, uint8_t*
         }
         return __shfl_sync(0xffffffffu, ok, 0) != 0;
     };
+    auto enter = [&](int kind) -> bool {              // make the ring's memory serve `kind`
+        if (mode == kind) return true;
+        if (!drain(mode)) return false;
+        mode = kind;
+        return true;
+    };
     while (rc.valid(p)) {
+        if (rc.kv) {
+            // decode attention, many-sequence form: one tile of 16 whole cache rows per slot, as four
+            // copies of four rows issued by four lanes at once; K and V tiles alternate.  The whole
+            // instruction is streamed from this tight loop: measured, a single lane that issued every
+            // copy and walked the outer loop per slot spent ~950 cycles per 16 KB slot (32 GB/s).
+            if (!enter(MODE_KVTILES)) return;
+            if (rc.kv_gated) {                        // unfused form: the appended row is readable once the dependencies are met
+                int go = 1;
+                if (lane == 0) go = wait_barrier(p, c, &c->kv_go, kvgo, rc.seq, WHERE_DEP) ? 1 : 0;
+                if (!__shfl_sync(0xffffffffu, go, 0)) return;
+                kvgo ^= 1u;
+            }
+            const int g = lane & 3;
+            const uint32_t group_bytes = (uint32_t)(kKvGroupRows * rc.kv_rb), tile_bytes = (uint32_t)(kKvTileRows * rc.kv_rb);
+            const uint8_t* src[2] = {rc.kv_src[0] + (long long)g * kKvGroupRows * rc.kv_pitch[0],
+                                     rc.kv_src[1] + (long long)g * kKvGroupRows * rc.kv_pitch[1]};
+            const long long step[2] = {(long long)kKvTileRows * rc.kv_pitch[0], (long long)kKvTileRows * rc.kv_pitch[1]};
+            uint8_t* dst = ring + g * (group_bytes + kKvGroupSkew);
+#pragma unroll 1
+            for (int t = 0; t < rc.kv_nt; ++t) {
+#pragma unroll
+                for (int w = 0; w < 2; ++w) {
+                    int ok = 1;
+                    if (lane == 0) {
+                        ok = wait_barrier(p, c, &c->kv_empty[kvslot], kvphase ^ 1u, rc.seq, WHERE_RING_EMPTY) ? 1 : 0;
+                        if (ok) mbar_arrive_expect_tx(&c->kv_full[kvslot], tile_bytes);
+                    }
+                    if (!__shfl_sync(0xffffffffu, ok, 0)) return;      // (also: the expected bytes are registered before any copy is issued)
+                    if (lane < kKvTileRows / kKvGroupRows)
+                        bulk_g2s_hint(dst + kvslot * kKvSlotBytes, src[w], group_bytes, &c->kv_full[kvslot], stream_policy);
+                    src[w] += step[w];
+                    if (++kvslot == kKvSlots) { kvslot = 0; kvphase ^= 1u; }
+                }
+            }
+            rc.idx += gridDim.x;
+            rc.seek(p);
+            continue;
+        }
         if (rc.gemm) {
             // tile GEMM: one weight k-tile (128 rows x 64 K-elements, 16 KB) per slot -- one plain bulk
             // copy when the weights are packed, one bulk tensor copy otherwise.  Eight single-tile
             // slots rather than two large ones: a slot is refilled the moment its tile has been
             // consumed, so ~100 KB stay in flight (with 64 KB + 48 KB slots the refill of a slot
             // waited for its last tile and the stream reached 33 GB/s per SM instead of 45).
-            if (!gemm_mode) {
-                if (!drain(false)) return;
-                gemm_mode = true;
-            }
+            if (!enter(MODE_WTILES)) return;
             int ok = 1;
             if (lane == 0) {
                 ok = wait_barrier(p, c, &c->w_empty[wslot], wphase ^ 1u, rc.seq, WHERE_RING_EMPTY) ? 1 : 0;
@@ -202,10 +275,7 @@ __device__ __forceinline__ void producer_loop(const Params& p, Ctrl* c, uint8_t*
             if (++rc.kt >= rc.nk) { rc.idx += gridDim.x; rc.seek(p); }
             continue;
         }
-        if (gemm_mode) {
-            if (!drain(true)) return;
-            gemm_mode = false;
-        }
+        if (!enter(MODE_STAGES)) return;
         // one lane looks whether the ring has a free stage (non-blocking)
         int free_now = 0;
         if (lane == 0) free_now = mbar_try_wait(&c->empty[pos.stage], pos.phase ^ 1u) ? 1 : 0;

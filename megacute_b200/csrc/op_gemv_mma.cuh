@@ -26,7 +26,6 @@
 #pragma once
 #include "mma.cuh"
 #include "op_gemv_common.cuh"
-#include "op_decode_bulk.cuh"
 
 namespace mk {
 
@@ -230,17 +229,11 @@ __device__ __forceinline__ void gemv_finisher(const Params& p, Ctrl* c, uint8_t*
     const float4* red = reinterpret_cast<const float4*>(work + kMmaRedOff);
     const float* rowstat = reinterpret_cast<const float*>(work + kMmaStatOff);
     uint32_t fullpar = 0;                                                     // parities of slot_full[0..3], bit 4: deps_met
-    KvPos kvpos;                                                              // many-sequence decode attention: position in the KV slots
-    uint32_t kvgo = 0;                                                        // ... parity of kv_go
     for (int idx = blockIdx.x; idx < p.n_insts; idx += gridDim.x) {
         const Inst in = fetch_inst(p, idx);
         const int opi = in.opi - 1;
         if (opi < 0 || opi >= p.n_ops) return;
         const mk_op_desc* op = p.ops + opi;
-        if (op->kind == MK_OP_DECODE_ATTN && op->i[11]) {                     // this warp streams the instruction's KV tiles
-            if (!kv_issue(p, c, work, op, in.a0, in.a2, in.seq, kvpos, kvgo)) return;
-            continue;
-        }
         if (op->kind != MK_OP_GEMV || !(op->flags & GEMV_F_UNITS)) continue;
         const int M = op->i[0], K = op->i[2], act = op->i[3], odt = op->i[5], rdt = op->i[6];
         const bool swi = op->flags & GEMV_F_SWIGLU, rms = op->flags & GEMV_F_RMS;

@@ -138,14 +138,15 @@ def bulk_eligible(op: Op) -> bool:
     ok = op.head_dim == 64 and op.kv_heads <= C.COMPUTE_WARPS and whole and op.k_cache.cols == op.kv_heads * 64
     if os.environ.get("MEGACUTE_B200_ATT_BULK") == "1":
         return ok
-    return ok and op.batch >= C.BULK_MIN_BATCH
+    return ok and (op.batch >= C.BULK_MIN_BATCH or (op.batch >= C.BULK_MIN_BATCH_LONG and op.max_seq >= C.BULK_LONG_SEQ))
 
 
 def bulk_kv_splits(batch: int, kv_heads: int, max_seq: int, sm_count: int) -> int:
     """KV splits per sequence in the many-sequence form: the count with the lowest modelled time
-    waves x (fixed cost + 16-row tiles per split x time per tile [+ partials and merge when split]).
-    Unlike the per-head form every instruction streams whole rows, so long contexts want enough
-    instructions to fill the last wave evenly.  MEGACUTE_B200_KV_SPLITS overrides the choice."""
+    rounds x (cost per instruction + 16-row tiles per split x time per tile), rounds = instructions per
+    SM.  Long contexts want enough instructions to fill the last round evenly (batch 64: 2 splits
+    leave 20 SMs idle, 9 splits fill 3.9 rounds of 4); the measured cost per instruction grows with
+    the split count, which caps it.  MEGACUTE_B200_KV_SPLITS overrides the choice."""
     cap = max(1, min(max_seq // C.MIN_SPLIT_KEYS, C.MAX_KV_SPLITS))
     if os.environ.get("MEGACUTE_B200_KV_SPLITS"):
         return max(1, min(cap, int(os.environ["MEGACUTE_B200_KV_SPLITS"])))
@@ -154,8 +155,7 @@ def bulk_kv_splits(batch: int, kv_heads: int, max_seq: int, sm_count: int) -> in
     for s in range(1, cap + 1):
         waves = -(-(batch * s) // sm_count)
         tiles = -(-(-(-max_seq // s)) // C.BULK_TILE_ROWS)
-        merge = C.BULK_MERGE_US + C.BULK_MERGE_US_PER_SPLIT * s if s > 1 else 0.0
-        cost = waves * (C.BULK_FIXED_US + merge + tiles * tile_us)
+        cost = waves * (max(C.BULK_FIXED_US, C.BULK_US_PER_SPLIT * s - 3.0) + tiles * tile_us)
         if cost < best_cost - 1e-9:
             best, best_cost = s, cost
     return best

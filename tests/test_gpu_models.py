@@ -210,10 +210,10 @@ def test_small_dit_stack(cuda):
     assert_close(outs, ref)
 
 
-@pytest.mark.parametrize("B,att_heads,bulk", [(16, None, "0"), (64, None, "0"), (64, "2", "0"), (16, None, None), (64, None, None)])
+@pytest.mark.parametrize("B,att_heads,bulk", [(16, None, "0"), (64, None, "0"), (64, "2", "0"), (16, None, "1"), (64, None, None)])
 def test_batched_decode_small(cuda, monkeypatch, B, att_heads, bulk):
     """More than 8 sequences: unfolded norms, tile GEMMs with split-K, and the decode attention in its
-    many-sequence form (the default from 8 sequences on: all kv heads of a sequence per instruction) or,
+    many-sequence form (the default from 32 sequences on: all kv heads of a sequence per instruction) or,
     with that switched off, in the per-head form -- one kv head per instruction, or (forced here;
     chosen when there are more pairs than SMs) several."""
     if att_heads:
@@ -223,8 +223,8 @@ def test_batched_decode_small(cuda, monkeypatch, B, att_heads, bulk):
     g, params, st, ids = small_decode(B=B, E=256, H=4, KVH=2, F=512, n=2, max_seq=256, ctx=120, vocab=1000)
     prog = mc.compile(g)
     hp = {o.heads_per_inst for o in prog.g.ops if o.kind == "DecodeAttention"}
-    assert hp == ({2} if att_heads or not bulk else {1})
-    assert {bool(o.bulk) for o in prog.g.ops if o.kind == "DecodeAttention"} == {not bulk}
+    assert hp == ({2} if att_heads or bulk != "0" else {1})
+    assert {bool(o.bulk) for o in prog.g.ops if o.kind == "DecodeAttention"} == {bulk != "0"}
     dp = {k: v.to(cuda) for k, v in params.items()}
     ds = {k: v.to(cuda) for k, v in st.items()}
     rs = {k: v.clone() for k, v in st.items()}

@@ -165,14 +165,15 @@ def test_finalize_fused_into_decode_attention():
 
 
 def test_many_sequence_attention_choice_and_schedule(monkeypatch):
-    """From 8 sequences on the decode attention runs in its many-sequence form: one instruction per
-    (sequence, KV split) over all kv heads, split count from the context length; the schedule of such
-    a graph orders every hazard, partial-row and arrival-count workspaces included."""
+    """From 32 sequences on (8 with long caches) the decode attention runs in its many-sequence form:
+    one instruction per (sequence, KV split) over all kv heads, split count from the context length;
+    the schedule of such a graph orders every hazard, partial-row and arrival-count workspaces included."""
     from megacute_b200.passes import bulk_kv_splits
     assert bulk_kv_splits(64, 8, 1152, 148) == 2 and bulk_kv_splits(64, 8, 32896, 148) > 4
     for B, splits in ((40, None), (16, "3")):
         if splits:
             monkeypatch.setenv("MEGACUTE_B200_KV_SPLITS", splits)
+            monkeypatch.setenv("MEGACUTE_B200_ATT_BULK", "1")
         g, *_ = small_decode(B=B, n=2, E=512, H=8, KVH=8, F=512, vocab=512, max_seq=256, ctx=10)
         g2 = run_all(g, 148)
         att = [o for o in g2.ops if o.kind == "DecodeAttention"]
@@ -184,8 +185,11 @@ def test_many_sequence_attention_choice_and_schedule(monkeypatch):
         _check_schedule(s, g2)
         _simulate(s, g2, 0)
         _ordered(s, g2)
-    g1, *_ = small_decode(B=2)
-    assert not any(o.bulk for o in run_all(g1, 148).ops if o.kind == "DecodeAttention")
+    monkeypatch.delenv("MEGACUTE_B200_ATT_BULK")
+    monkeypatch.delenv("MEGACUTE_B200_KV_SPLITS")
+    for B, L, want in ((2, 256, False), (16, 256, False), (16, 8192, True), (32, 256, True)):
+        gb, *_ = small_decode(B=B, n=1, max_seq=L)
+        assert all(bool(o.bulk) == want for o in run_all(gb, 148).ops if o.kind == "DecodeAttention"), (B, L)
 
 
 def test_kv_heads_per_instruction_choice_and_schedule(monkeypatch):
