@@ -5,14 +5,14 @@
 
 Headline workload (the reference's batch-1 decode benchmark): 16 layers, hidden 2048, 32 q / 8 kv heads,
 head_dim 64, SwiGLU 8192, vocab 128256 tied, bf16 random-init weights, batch 1, KV caches prefilled to
-context 1024, greedy decode.  A step is what the reference times in examples/llama/llama1b.py:103-121:
-embedding gather into x, one megakernel launch, argmax.  With N > 1 every rank runs its own replica on
+context 1024, greedy decode.  A step is what the reference times in examples/llama/llama1b.py:103-121
+(embedding gather, one megakernel launch, argmax), here with the gather and the argmax inside the launch.  With N > 1 every rank runs its own replica on
 its own sequences (batch-sharded, weights replicated, no collective on the hot path).
 
 Prints ONE JSON line (rank 0):
   value / ms_per_step   median over `repeats` blocks of exactly K steps (device time, CUDA events, slowest
                         rank), everything resident in HBM; `ms_per_step_min` is the best block
-  kernel_ms             the megakernel launch alone, same scheme
+  kernel_ms             the megakernel launches alone: the same number, a step being one launch
   e2e                   the same loop driven from pinned host memory (token ids copied in and out every step)
   roofline              algorithmic bytes of a step / kernel_ms against the measured HBM copy bandwidth
   sweep                 the metric's other points: batch 1 and batch 64 at context 256 ... 32768 (one GPU), or,
@@ -126,14 +126,19 @@ class ClockSampler:
 
 
 def build_workload(B, ctx, device, seed=0, weights=None):
+    """The decode step as one self-feeding launch: state `ids` (B, 1) int32 holds the current tokens; the
+    launch gathers their embedding rows, runs the 16 layers and the lm_head, and overwrites ids with the
+    greedy tokens (builders.llama_decode(fused_step=True))."""
     import megacute_b200 as mc
     from megacute_b200 import workloads as W
     from megacute_b200.builders import llama_decode
     c = W.LLAMA_1B
     max_seq = -(-(ctx + 128) // 128) * 128
-    g = llama_decode(B, c["E"], c["H"], c["KVH"], c["F"], c["n"], max_seq, c["vocab"], c["eps"])
+    g = llama_decode(B, c["E"], c["H"], c["KVH"], c["F"], c["n"], max_seq, c["vocab"], c["eps"], fused_step=True)
     w = weights if weights is not None else W.llama_weights(c["E"], c["H"], c["KVH"], c["F"], c["n"], c["vocab"], seed, device)
     st, ids = W.llama_decode_state(B, c["E"], c["H"], c["KVH"], c["n"], max_seq, ctx, c["vocab"], seed + 1, device)
+    del st["x"]
+    st["ids"] = ids.to(torch.int32).reshape(B, 1).contiguous()
     cos, sin = W.rope_tables(max_seq, c["E"] // c["H"], c["theta"], device)
     return mc, g, dict(cos=cos, sin=sin, **w), st, ids, max_seq
 
@@ -142,16 +147,12 @@ def cpu_oracle_ms(B, ctx, steps, seed=0):
     """Time the fp32 torch oracle of the same graph on the host cores: ms per decode step."""
     from oracle.graph_oracle import evaluate
     _, g, params, st, ids, _ = build_workload(B, ctx, "cpu", seed)
-    emb = params["lm_head"]
     times = []
     for _ in range(steps + 1):
-        st["x"] = emb[ids].clone()
         t0 = time.perf_counter()
-        out, new = evaluate(g, {**params, **st})
+        out, new = evaluate(g, {**params, **st})          # gather + layers + lm_head + argmax, states updated
         times.append((time.perf_counter() - t0) * 1e3)
-        for n in ("pos", "k_cache", "v_cache"):
-            st[n] = new[n]
-        ids = out[0].argmax(-1)
+        st = dict(new)
     return statistics.median(times[1:]) if steps > 1 else times[-1]
 
 
@@ -196,51 +197,37 @@ def measure_decode(mc, timing, B, ctx, dev, weights, steps, warmup, seed, with_e
     medians over the repeated blocks (ms per step)."""
     _, g, params, st, ids, max_seq = build_workload(B, ctx, dev, seed, weights)
     prog = mc.compile(g)
-    emb = params["lm_head"]
     args = dict(params, **st)
-    cur = [ids]
     room = max_seq - ctx - 1                 # steps before pos must go back to ctx
-
-    def step(tok):
-        torch.index_select(emb, 0, tok, out=st["x"])       # embedding rows of this step's tokens, straight into x
-        return mc.argmax(prog(**args))
 
     def reset_state():
         st["pos"].fill_(ctx)
 
-    def run_steps(n):
-        for i in range(n):
-            if i % room == room - 1:
-                reset_state()
-            cur[0] = step(cur[0])
-
-    def run_kernel_only(n):
+    def run_steps(n):                        # a step IS one launch: gather, layers, lm_head and argmax run inside it
         for i in range(n):
             if i % room == room - 1:
                 reset_state()
             prog(**args)
 
-    h_in = torch.empty(B, dtype=torch.int64).pin_memory()
-    h_out = torch.empty(B, dtype=torch.int64).pin_memory()
-    d_ids = torch.empty(B, dtype=torch.int64, device=dev)
+    h_in = torch.empty(B, 1, dtype=torch.int32).pin_memory()
+    h_out = torch.empty(B, 1, dtype=torch.int32).pin_memory()
 
     def run_e2e(n):
-        h_in.copy_(cur[0].cpu())
+        h_in.copy_(st["ids"].cpu())
         for i in range(n):
             if i % room == room - 1:
                 reset_state()
-            d_ids.copy_(h_in, non_blocking=True)                 # host -> device: this step's token ids
-            nxt = step(d_ids)
-            h_out.copy_(nxt, non_blocking=True)                  # device -> host: the sampled tokens
+            st["ids"].copy_(h_in, non_blocking=True)             # host -> device: this step's token ids
+            prog(**args)
+            h_out.copy_(st["ids"], non_blocking=True)            # device -> host: the sampled tokens
             torch.cuda.current_stream().synchronize()
             h_in.copy_(h_out)
 
     run_steps(max(3, warmup))
     prog.check()
     t_step = timing.repeated(run_steps, steps, reset_state)
-    t_kern = timing.repeated(run_kernel_only, steps, reset_state)
     out = {"ms_per_step": statistics.median(t_step), "ms_per_step_min": min(t_step), "repeats": len(t_step),
-           "kernel_ms": statistics.median(t_kern), "kernel_ms_min": min(t_kern)}
+           "kernel_ms": statistics.median(t_step), "kernel_ms_min": min(t_step)}
     if with_e2e:
         t_e2e = timing.repeated(run_e2e, steps, reset_state)
         out["e2e_ms"] = statistics.median(t_e2e)
@@ -295,7 +282,7 @@ def main():
               "batch_per_gpu": a.batch, "ctx": a.ctx,
               "layers": 16, "hidden": 2048, "vocab": 128256, "parallelism": f"replica x{world} (batch-sharded)",
               "l2": "weights (2.47 GB) exceed L2 (126 MB): every step re-reads them from HBM",
-              "step": "torch index_select (embedding rows) + megakernel + mk_argmax"}
+              "step": "one megakernel launch: embedding gather, 16 layers, lm_head, greedy argmax (token ids stay on the device)"}
     base = {"metric": "decode ms/step, 1B Llama-shape", "unit": "ms/step", "n_gpus": world, "steps": a.steps,
             "warmup": a.warmup, "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic", "config": config}
@@ -364,11 +351,11 @@ def main():
     pub = PUBLISHED_MS.get((a.batch, a.ctx))
     line = dict(base, value=m["ms_per_step"], ms_per_step=m["ms_per_step"], ms_per_step_min=m["ms_per_step_min"],
                 repeats=m["repeats"], tokens_per_s=world * a.batch * 1e3 / m["ms_per_step"],
-                e2e={"value": m["e2e_ms"], "unit": "ms/step", "h2d_bytes_per_step": a.batch * 8,
-                     "d2h_bytes_per_step": a.batch * 8},
-                # our kernels inside one timed block of `steps` steps: the megakernel and mk_argmax's kernel per
-                # step (torch's index_select is a third launch per step, not ours)
-                gpu_launches=2 * a.steps,
+                e2e={"value": m["e2e_ms"], "unit": "ms/step", "h2d_bytes_per_step": a.batch * 4,
+                     "d2h_bytes_per_step": a.batch * 4},
+                # our kernels inside one timed block of `steps` steps: one megakernel launch per step (embedding
+                # gather and greedy argmax are its first and last instructions), nothing else on the stream
+                gpu_launches=a.steps,
                 kernel_ms=m["kernel_ms"], kernel_ms_min=m["kernel_ms_min"], clocks=clocks,
                 reference_published_ms=pub,
                 roofline={"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": frac,

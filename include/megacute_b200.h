@@ -32,7 +32,9 @@ enum {
     MK_OP_ATTENTION = 6,   /* prefill flash attention tile                                          */
     MK_OP_ROPE_APPEND = 7, /* decode: rotate q,k of the new token, append k,v                       */
     MK_OP_DECODE_ATTN = 8, /* decode attention over the cache (optionally fused rope+append, split) */
-    MK_OP_INCREMENT = 9    /* pos += 1                                                              */
+    MK_OP_INCREMENT = 9,   /* pos += 1                                                              */
+    MK_OP_GATHER = 10,     /* out[r] = table[ids[r]]: the embedding lookup of a decode step         */
+    MK_OP_ARGMAX = 11      /* ids[r] = argmax(x[r]): greedy sampling, column chunks merged in-op    */
 };
 
 #define MK_MAX_PTRS 12

@@ -69,13 +69,25 @@ def llama_stack(B: int, S: int, E: int, H: int, KVH: int, F: int, n: int, eps: f
 
 
 def llama_decode(B: int, E: int, H: int, KVH: int, F: int, n: int, max_seq: int, vocab: int | None = None,
-                 eps: float = 1e-6) -> Graph:
+                 eps: float = 1e-6, fused_step: bool = False) -> Graph:
     """One decode step for B sequences.  States: x (B, E) embedded tokens, pos (1, 1) int32,
     k_cache / v_cache (n*B*max_seq, KVH*D) with layer i at rows [i*B*max_seq, ...) and sequence b of
-    it at [b*max_seq, ...).  Output: (B, vocab) logits, or the hidden state without ``vocab``."""
+    it at [b*max_seq, ...).  Output: (B, vocab) logits, or the hidden state without ``vocab``.
+
+    ``fused_step`` (needs ``vocab``; tied embeddings) puts the two ends of the step inside the launch:
+    the state is ``ids`` (B, 1) int32 instead of x -- the launch gathers the embedding rows itself and
+    overwrites ids with the greedy tokens, so a decode loop is one launch per step with nothing
+    around it (the reference's step is index_select + copy_ + launch + argmax,
+    examples/llama/llama1b.py:103-105)."""
     D = E // H
     g = Graph()
-    x = g.state("x", (B, E))
+    if fused_step:
+        assert vocab, "fused_step samples from the logits: it needs the lm_head"
+        ids = g.state("ids", (B, 1), torch.int32)
+        head = g.param("lm_head", (vocab, E))
+        x = g.gather(head, ids)
+    else:
+        x = g.state("x", (B, E))
     cos, sin = g.input("cos", (max_seq, D)), g.input("sin", (max_seq, D))
     pos = g.state("pos", (1, 1), torch.int32)
     kc = g.state("k_cache", (n * B * max_seq, KVH * D))
@@ -93,7 +105,9 @@ def llama_decode(B: int, E: int, H: int, KVH: int, F: int, n: int, max_seq: int,
         x = g.linear(g.linear(g.rms_norm(x, p["mlp_norm"], eps), p["wgu"], act="swiglu"), p["wd"], residual=x)
     g.layer = None
     if vocab:
-        x = g.linear(g.rms_norm(x, g.param("final_norm", (1, E)), eps), g.param("lm_head", (vocab, E)))
+        x = g.linear(g.rms_norm(x, g.param("final_norm", (1, E)), eps), head if fused_step else g.param("lm_head", (vocab, E)))
+    if fused_step:
+        g.argmax(x, ids)
     g.increment(pos)
     g.output(x)
     return g

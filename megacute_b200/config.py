@@ -58,8 +58,10 @@ W_NARRIVE, W_ARRIVE_OFF = 10, 11
 W_SEQ = 12                      # global instruction index
 
 # ---- device op kinds (include/megacute_b200.h: MK_OP_*)
-OP_GEMV, OP_GEMM, OP_FINALIZE, OP_ELTWISE, OP_NORM, OP_ATTENTION, OP_ROPE_APPEND, OP_DECODE_ATTN, OP_INCREMENT = \
-    range(1, 10)
+OP_GEMV, OP_GEMM, OP_FINALIZE, OP_ELTWISE, OP_NORM, OP_ATTENTION, OP_ROPE_APPEND, OP_DECODE_ATTN, OP_INCREMENT, \
+    OP_GATHER, OP_ARGMAX = range(1, 12)
+GATHER_ROWS = 8                 # rows per gather instruction (one per compute warp)
+ARGMAX_MAX_CHUNKS = 256         # column chunks per row of an argmax (the merging instruction takes one partial per thread)
 
 ACT_CODE = {None: 0, "identity": 0, "relu": 1, "silu": 2, "gelu_tanh": 3, "gelu": 3, "exp": 4, "neg": 5,
             "sigmoid": 6, "square": 7, "swiglu": 8}

@@ -404,6 +404,13 @@ static int verify_tables(const mk_program* p, const mk_op_desc* ops) {
                     break;
                 }
                 case MK_OP_INCREMENT: break;
+                case MK_OP_GATHER:
+                    if (a0 < 0 || a0 * 8 >= d.i[0] || a1 < 0 || a1 * 512 >= d.i[1]) why = "gather: tile outside the output";
+                    break;
+                case MK_OP_ARGMAX:
+                    if (a0 < 0 || a0 >= d.i[0] || a1 < 0 || a1 >= d.i[2] || d.i[2] > 256 || d.i[3] % 8 || (long long)d.i[2] * d.i[3] < d.i[1])
+                        why = "argmax: (row, chunk)";
+                    break;
                 default: why = "unknown op kind";
             }
         }

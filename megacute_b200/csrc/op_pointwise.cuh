@@ -248,6 +248,104 @@ static __device__ __noinline__ void op_rope_append(const mk_op_desc* op, int a0)
     }
 }
 
+// MK_OP_GATHER: out[r] = table[ids[r]] -- the embedding lookup of a decode step as the launch's first
+// instructions (the reference's step calls torch.index_select before its launch,
+// examples/llama/llama1b.py:103-104).  An index outside the table reads row 0.
+// ptr 0 table (bf16), 1 ids (int32 column), 2 out; i 0 rows, 1 cols, 2 table rows, 3 out dtype
+// args: 0 row tile (8 rows, one per warp), 1 col tile (kEwCols)
+static __device__ __noinline__ void op_gather(const mk_op_desc* op, int a0, int a1) {
+    const int R = op->i[0], Cc = op->i[1], T = op->i[2], odt = op->i[3];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int r = a0 * kComputeWarps + warp;
+    if (r >= R) return;
+    int id = __ldcg(reinterpret_cast<const int*>(op->ptr[1]) + (long long)r * op->ld[1]);
+    if (id < 0 || id >= T) id = 0;
+    const int c0 = a1 * kEwCols, cols = min(kEwCols, Cc - c0);
+    const void* row = reinterpret_cast<const __nv_bfloat16*>(op->ptr[0]) + (long long)id * op->ld[0];
+    for (int v = lane; v < (cols >> 3); v += 32) {
+        float f[8];
+        load8(row, c0 + v * 8, DT_BF16, f);
+        store8(reinterpret_cast<void*>(op->ptr[2]), (long long)r * op->ld[2] + c0 + v * 8, odt, f);
+    }
+}
+
+// MK_OP_ARGMAX: ids[r] = argmax(x[r]), ties to the lowest index, NaN never selected -- greedy sampling as
+// the launch's last instructions (the reference's step calls torch's argmax after its launch,
+// examples/llama/llama1b.py:105).  A row is cut into `chunks` column ranges, one instruction each;
+// every instruction leaves its best (value, index) in `part` and bumps the row's arrival count; the
+// last to arrive picks the winner (one partial per thread) and resets the count.
+// ptr 0 x, 1 ids (int32 column), 2 part (fp32, per row: `chunks` values, then from column ceil4(chunks) on the bits
+// of their indices), 3 count
+// i 0 rows, 1 cols, 2 chunks, 3 columns per chunk (multiple of 8), 4 x dtype.  args: 0 row, 1 chunk.
+struct Best {
+    float v;
+    int i;
+};
+__device__ __forceinline__ Best better(Best a, Best b) {        // NaN never wins; equal values: lower index
+    return (b.v > a.v || (b.v == a.v && b.i < a.i)) ? b : a;
+}
+__device__ __forceinline__ Best warp_best(Best b) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const Best other{__shfl_xor_sync(0xffffffffu, b.v, o), __shfl_xor_sync(0xffffffffu, b.i, o)};
+        b = better(b, other);
+    }
+    return b;
+}
+static __device__ __noinline__ void op_argmax(const mk_op_desc* op, int a0, int a1, Ctrl* c, uint8_t* work) {
+    const int Cc = op->i[1], chunks = op->i[2], width = op->i[3], xdt = op->i[4];
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const int r = a0, c0 = a1 * width, c1 = min(Cc, c0 + width);
+    const void* X = reinterpret_cast<const void*>(op->ptr[0]);
+    Best best{-__builtin_huge_valf(), 0x7fffffff};
+    for (int col = c0 + t * 8; col < c1; col += kComputeThreads * 8) {
+        float f[8];
+        load8(X, (long long)r * op->ld[0] + col, xdt, f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) best = better(best, Best{f[e], col + e});
+    }
+    best = warp_best(best);
+    float* sv = reinterpret_cast<float*>(work);
+    int* si = reinterpret_cast<int*>(work) + kComputeWarps;
+    if (lane == 0) { sv[warp] = best.v; si[warp] = best.i; }
+    compute_sync();
+    int* ids = reinterpret_cast<int*>(op->ptr[1]) + (long long)r * op->ld[1];
+    if (warp == 0) {
+        best = lane < kComputeWarps ? Best{sv[lane], si[lane]} : Best{-__builtin_huge_valf(), 0x7fffffff};
+        best = warp_best(best);
+        if (lane == 0) {
+            if (chunks == 1) {
+                *ids = best.i == 0x7fffffff ? 0 : best.i;
+            } else {
+                float* part = reinterpret_cast<float*>(op->ptr[2]) + (long long)r * op->ld[2];
+                part[a1] = best.v;
+                part[((chunks + 3) & ~3) + a1] = __int_as_float(best.i);
+                __threadfence();
+                int* count = reinterpret_cast<int*>(op->ptr[3]) + (long long)r * op->ld[3];
+                const int old = atomicAdd(count, 1);
+                c->flag = (old == chunks - 1);
+                if (old == chunks - 1) *count = 0;            // back to zero for the next launch
+            }
+        }
+    }
+    if (chunks == 1) return;
+    compute_sync();
+    if (!c->flag) return;
+    __threadfence();
+    const float* part = reinterpret_cast<const float*>(op->ptr[2]) + (long long)r * op->ld[2];
+    best = Best{-__builtin_huge_valf(), 0x7fffffff};
+    if (t < chunks) best = Best{__ldcg(part + t), __float_as_int(__ldcg(part + ((chunks + 3) & ~3) + t))};
+    best = warp_best(best);
+    compute_sync();                                           // sv / si of the first pass have been read
+    if (lane == 0) { sv[warp] = best.v; si[warp] = best.i; }
+    compute_sync();
+    if (warp == 0) {
+        best = lane < kComputeWarps ? Best{sv[lane], si[lane]} : Best{-__builtin_huge_valf(), 0x7fffffff};
+        best = warp_best(best);
+        if (lane == 0) *ids = best.i == 0x7fffffff ? 0 : best.i;
+    }
+}
+
 // MK_OP_INCREMENT.  ptr 0 pos.
 __device__ __forceinline__ void op_increment(const mk_op_desc* op) {
     if (threadIdx.x == 0) {

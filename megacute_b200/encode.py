@@ -22,6 +22,8 @@ view's first element.  Field meaning per kind (the kernel side repeats it next t
                i B, H, KVH, D, max_seq, splits, fused, q dtype, out dtype, zero inputs, kv heads per
                instruction, many-sequence form; f scale
   INCREMENT    ptr pos
+  GATHER       ptr table, ids, out; i rows, cols, table rows, out dtype
+  ARGMAX       ptr x, ids, part, count; i rows, cols, chunks, columns per chunk, x dtype
 """
 
 from __future__ import annotations
@@ -30,7 +32,7 @@ import torch
 
 from . import config as C
 from .graph import DTYPE_CODE, ELEM_BYTES, Op, View
-from .schedule import finalize_rows, is_gemv, norm_rows
+from .schedule import argmax_chunk_cols, finalize_rows, is_gemv, norm_rows
 
 BF16 = torch.bfloat16
 F16 = torch.float16
@@ -145,6 +147,14 @@ def fill(d, op: Op, addr) -> None:
     elif k == "Increment":
         d.kind = C.OP_INCREMENT
         ptrs = [op.pos]
+    elif k == "Gather":
+        d.kind = C.OP_GATHER
+        ptrs = [op.table, op.ids, op.out]
+        ints = [op.out.rows, op.out.cols, op.table.rows, dt(op.out)]
+    elif k == "Argmax":
+        d.kind = C.OP_ARGMAX
+        ptrs = [op.x, op.ids, op.part, op.count]
+        ints = [op.x.rows, op.x.cols, op.chunks, argmax_chunk_cols(op.x.cols, op.chunks), dt(op.x)]
     else:
         raise NotImplementedError(k)
     for n, v in enumerate(ints):

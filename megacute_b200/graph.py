@@ -126,6 +126,10 @@ OP_TABLE = {
                         ("batch", "heads", "kv_heads", "head_dim", "max_seq", "scale", "splits", "zero_inputs", "heads_per_inst",
                          "bulk")),
     "Increment":       ((), ("pos",), ()),
+    # the two ends of a decode step, inside the launch (no counterpart among the reference's ops: its
+    # step does them in torch around the launch, examples/llama/llama1b.py:103-105)
+    "Gather":          (("table", "ids"), ("out",), ()),
+    "Argmax":          (("x", "part", "count"), ("ids", "part", "count"), ("chunks",)),
 }
 
 
@@ -292,10 +296,23 @@ def _chk_increment(o):
     assert o.pos.shape == (1, 1) and o.pos.buf.dtype == torch.int32
 
 
+def _chk_gather(o):
+    assert o.ids.cols == 1 and o.ids.buf.dtype == torch.int32, "gather: ids is a (rows, 1) int32 column"
+    assert o.out.shape == (o.ids.rows, o.table.cols) and o.table.cols % 8 == 0
+    assert o.table.buf.dtype == torch.bfloat16, "gather: bf16 table"
+
+
+def _chk_argmax(o):
+    assert o.ids.shape == (o.x.rows, 1) and o.ids.buf.dtype == torch.int32, "argmax: ids is a (rows, 1) int32 column"
+    assert o.x.cols % 8 == 0
+    o.chunks = o.chunks or 1
+
+
 _CHECKS = {"Linear": _chk_linear, "LinearSplit": _chk_linear_split, "SplitFinalize": _chk_finalize,
            "Unary": _chk_unary, "Binary": _chk_binary, "SwiGLU": _chk_swiglu, "Modulate": _chk_modulate,
            "Norm": _chk_norm, "Rope": _chk_rope, "Attention": _chk_attention, "RopeAppend": _chk_rope_append,
-           "DecodeAttention": _chk_decode_attention, "Increment": _chk_increment}
+           "DecodeAttention": _chk_decode_attention, "Increment": _chk_increment, "Gather": _chk_gather,
+           "Argmax": _chk_argmax}
 
 
 def swiglu_weight(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
@@ -467,6 +484,22 @@ class Graph:
     def increment(self, pos):
         """``pos += 1`` on device after every reader of pos in the launch."""
         self._emit("Increment", pos=pos)
+
+    def gather(self, table, ids, out=None) -> View:
+        """``out[r] = table[ids[r, 0]]``: the embedding lookup of a decode step as the launch's first
+        instructions.  ``ids`` is a (rows, 1) int32 view.  (The reference's step gathers in torch before
+        the launch, examples/llama/llama1b.py:103-104; this op has no counterpart in its Graph.)"""
+        out = out or self.temp((ids.rows, table.cols))
+        self._emit("Gather", table=table, ids=ids, out=out)
+        return out
+
+    def argmax(self, x, ids) -> View:
+        """``ids[r, 0] = argmax(x[r])`` (ties: lowest index; NaN never wins): greedy sampling as the
+        launch's last instructions, into a (rows, 1) int32 view -- with ``gather`` reading the same view,
+        a decode step feeds itself.  (The reference's step calls torch's argmax after the launch,
+        examples/llama/llama1b.py:105.)"""
+        self._emit("Argmax", x=x, ids=ids)
+        return ids
 
     def __repr__(self):
         head = f"Graph({len(self.buffers)} buffers, {len(self.ops)} ops)"

@@ -284,6 +284,10 @@ def _accepts(op: Op, field: str, dtype) -> bool:
         return field == "out" and not f32
     if k == "RopeAppend":
         return field == "qkv"
+    if k == "Gather":
+        return field == "out"
+    if k == "Argmax":
+        return field == "x"
     if k == "DecodeAttention":
         if field in ("q", "k_new", "v_new"):          # one dtype code covers all three
             return op.k_new is None or (op.q.buf is op.k_new.buf is op.v_new.buf)
@@ -360,7 +364,27 @@ def fuse_finalize_attention(g: Graph) -> Graph:
     return out
 
 
+def split_argmax(g: Graph, sm_count: int) -> Graph:
+    """An argmax over few long rows is cut into column chunks, about two instructions per SM in all;
+    every chunk leaves its best (value, index) in a workspace and the last chunk of a row to arrive
+    picks the winner (the scheme of the split decode attention)."""
+    out = g.derive()
+    ops = []
+    for op in g.ops:
+        if op.kind == "Argmax" and op.part is None:
+            rows, cols = op.x.shape
+            chunks = max(1, min(C.ARGMAX_MAX_CHUNKS, -(-2 * sm_count // rows), cols // 1024))
+            if chunks > 1:
+                # per row: the chunks' best values, then (from a 16-byte boundary on) the bits of their indices
+                op = op.clone(chunks=chunks, part=out.workspace((rows, 2 * (-(-chunks // 4) * 4)), torch.float32),
+                              count=out.workspace((rows, 1), torch.int32))
+        ops.append(op)
+    out.ops = ops
+    return out
+
+
 def run_all(g: Graph, sm_count: int) -> Graph:
     """The pass pipeline of ``compile`` (reference order: runtime.py:235, plus promote_temps and
     fuse_finalize_attention)."""
-    return fuse_finalize_attention(promote_temps(split_kv(fuse_rope_attention(split_k(fold_norms(g), sm_count)), sm_count)))
+    g = split_argmax(split_kv(fuse_rope_attention(split_k(fold_norms(g), sm_count)), sm_count), sm_count)
+    return fuse_finalize_attention(promote_temps(g))

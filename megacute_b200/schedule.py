@@ -233,7 +233,29 @@ def tile_op(op: Op, sm_count: int) -> Tiled:
         return Tiled(_args(n, b, h, s), acc)
     if k == "Increment":
         return Tiled(_args(1), [_acc(op.pos, WRITE, n=1)])
+    if k == "Gather":
+        R, Cc = op.out.shape
+        rt, ct = np.divmod(np.arange(_ceil(R, C.GATHER_ROWS) * _ceil(Cc, C.EW_COLS)), _ceil(Cc, C.EW_COLS))
+        n = len(rt)
+        r0, r1, c0, c1 = rt * C.GATHER_ROWS, (rt + 1) * C.GATHER_ROWS, ct * C.EW_COLS, (ct + 1) * C.EW_COLS
+        return Tiled(_args(n, rt, ct), [_acc(op.ids, READ, r0, r1, n=n), _acc(op.table, READ, n=n, covers=False),
+                                        _acc(op.out, WRITE, r0, r1, c0, c1, n=n)])
+    if k == "Argmax":
+        R, Cc = op.x.shape
+        ch = op.chunks
+        width = argmax_chunk_cols(Cc, ch)
+        r, cidx = np.divmod(np.arange(R * ch), ch)
+        n = len(r)
+        acc = [_acc(op.x, READ, r, r + 1, cidx * width, (cidx + 1) * width, n=n), _acc(op.ids, WRITE, r, r + 1, n=n, covers=ch == 1)]
+        if ch > 1:
+            acc += [_acc(op.part, WRITE, r, r + 1, n=n, covers=False), _acc(op.count, WRITE, r, r + 1, n=n, covers=False)]
+        return Tiled(_args(n, r, cidx), acc)
     raise NotImplementedError(k)
+
+
+def argmax_chunk_cols(cols: int, chunks: int) -> int:
+    """Columns per chunk of a split argmax: a multiple of 8 (16-byte loads of bf16)."""
+    return _ceil(_ceil(cols, chunks), 8) * 8
 
 
 def finalize_rows(rows: int, cols: int) -> int:

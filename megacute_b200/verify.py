@@ -100,6 +100,13 @@ def operand_windows(op) -> dict:
         return win
     if k == "Increment":
         return {"pos": (1, 1)}
+    if k == "Gather":
+        return {"table": op.table.shape, "ids": op.ids.shape, "out": op.out.shape}
+    if k == "Argmax":
+        win = {"x": op.x.shape, "ids": op.ids.shape}
+        if op.chunks > 1:
+            win.update(part=(op.x.rows, _ceil(op.chunks, 4) * 4 + op.chunks), count=(op.x.rows, 1))
+        return win
     raise NotImplementedError(k)
 
 
@@ -127,6 +134,10 @@ def op_grid(op, sm_count: int):
         return (op.batch, op.kv_heads - (op.heads_per_inst or 1) + 1, op.splits or 1)
     if k == "Increment":
         return ()
+    if k == "Gather":
+        return (_ceil(op.out.rows, C.GATHER_ROWS), _ceil(op.out.cols, C.EW_COLS))
+    if k == "Argmax":
+        return (op.x.rows, op.chunks)
     raise NotImplementedError(k)
 
 

@@ -383,3 +383,39 @@ def test_program_on_another_device_than_the_current_one():
     assert torch.cuda.current_device() == 0 and out.device == other
     ref, _ = evaluate(g, t)
     assert rel_l2(out.float().cpu(), ref[0]) < TOL
+
+
+@pytest.mark.parametrize("B,vocab", [(1, 5000), (5, 1000), (40, 20000)])
+def test_fused_step_feeds_itself(cuda, B, vocab):
+    """The decode step as one launch: embedding gather as its first instructions, greedy argmax (column
+    chunks merged by the last to arrive) as its last, token ids staying on the device.  Over 32 steps the
+    ids the launch leaves equal mk_argmax of the logits it returns, bit for bit, and the logits stay
+    within tolerance of the oracle fed the same ids."""
+    E, H, KVH, F, n, L, ctx = 256, 4, 2, 512, 2, 256, 60
+    g = llama_decode(B, E, H, KVH, F, n, L, vocab, 1e-5, fused_step=True)
+    w = W.llama_weights(E, H, KVH, F, n, vocab, 0, "cpu")
+    st, ids = W.llama_decode_state(B, E, H, KVH, n, L, ctx, vocab, 1, "cpu")
+    del st["x"]
+    st["ids"] = ids.to(torch.int32).reshape(B, 1)
+    cos, sin = W.rope_tables(L, E // H)
+    params = dict(cos=cos, sin=sin, **w)
+    prog = mc.compile(g)
+    am = [o for o in prog.g.ops if o.kind == "Argmax"]
+    assert [o.kind for o in prog.g.ops][0] == "Gather" and len(am) == 1 and (am[0].chunks > 1) == (vocab >= 2048)
+    dp = {k: v.to(cuda) for k, v in params.items()}
+    ds = {k: v.to(cuda) for k, v in st.items()}
+    rs = {k: v.clone() for k, v in st.items()}
+    for step in range(32):
+        rs["ids"] = ds["ids"].cpu().clone()                  # the oracle follows the tokens the device chose
+        logits = prog(**dp, **ds)
+        assert torch.equal(ds["ids"].flatten().long(), mc.argmax(logits))
+        ref, new = evaluate(g, {**params, **rs})
+        assert rel_l2(logits.float().cpu(), ref[0]) < TOL, step
+        for name in ("pos", "k_cache", "v_cache"):
+            rs[name] = new[name]
+    prog.check()
+    assert int(ds["pos"]) == ctx + 32
+    assert np.array_equal(prog.counters(), prog.sched.counter_target * 32)
+    for b in prog.g.buffers:
+        if b.kind == "workspace" and b.dtype == torch.int32:
+            assert int(prog.buffer(b).abs().sum()) == 0

@@ -325,3 +325,34 @@ def test_builders_prefill_and_dit_schedule():
     d = dit_stack(2, 64, 128, 2, 256, 2)
     s = schedule(run_all(d, 16), 16)
     _check_schedule(s, run_all(d, 16))
+
+
+def test_fused_step_graph_and_oracle():
+    """gather / argmax (the two ends of a decode step inside the launch): oracle semantics, the pass that
+    cuts the argmax into column chunks, and a schedule that orders the ids hazard (gather reads the ids
+    the argmax overwrites)."""
+    from megacute_b200 import workloads as W
+    B, vocab = 3, 4096
+    g = llama_decode(B, 256, 4, 2, 512, 2, 256, vocab, 1e-5, fused_step=True)
+    assert [b.name for b in g.states] == ["ids", "pos", "k_cache", "v_cache"]
+    w = W.llama_weights(256, 4, 2, 512, 2, vocab, 0, "cpu")
+    st, ids = W.llama_decode_state(B, 256, 4, 2, 2, 256, 40, vocab, 1, "cpu")
+    cos, sin = W.rope_tables(256, 64)
+    x = st.pop("x")
+    st["ids"] = ids.to(torch.int32).reshape(B, 1)
+    out, new = evaluate(g, dict(cos=cos, sin=sin, **w, **st))
+    plain = llama_decode(B, 256, 4, 2, 512, 2, 256, vocab, 1e-5)
+    out0, _ = evaluate(plain, dict(cos=cos, sin=sin, **w, **st, x=w["lm_head"][ids].clone()))
+    assert torch.equal(out[0], out0[0])                               # gather == the embedding lookup done outside
+    assert torch.equal(new["ids"].flatten().long(), out[0].argmax(-1)) and new["ids"].dtype == torch.int32
+    g2 = run_all(g, 148)
+    am = [o for o in g2.ops if o.kind == "Argmax"]
+    assert len(am) == 1 and am[0].chunks == 4 and am[0].part.shape == (B, 8)
+    out2, new2 = evaluate(g2, dict(cos=cos, sin=sin, **w, **st))
+    assert torch.equal(new2["ids"], new["ids"])
+    s = schedule(g2, 148)
+    _check_schedule(s, g2)
+    _simulate(s, g2, 0)
+    _ordered(s, g2)
+    with pytest.raises(AssertionError):
+        mc.Graph().gather(g.params[0].full, g.states[2].full)        # ids must be an int32 column
