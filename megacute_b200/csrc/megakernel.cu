@@ -144,7 +144,8 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
                     }
                     break;
                 case MK_OP_GEMM:
-                    npos = mk_op_gemm(p, op, in.a0, in.a1, in.a2, in.seq, ppos);
+                    npos = (op->i[10] == 256 && op->ptr[11]) ? mk_op_gemm_wide(p, op, in.a0, in.a1, in.a2, in.seq, ppos)
+                                                             : mk_op_gemm(p, op, in.a0, in.a1, in.a2, in.seq, ppos);
                     aborting = npos < 0;
                     break;
                 case MK_OP_ATTENTION: mk_op_attention(op, in.a0, in.a1, in.a2); break;
@@ -379,7 +380,8 @@ static int verify_tables(const mk_program* p, const mk_op_desc* ops) {
                 case MK_OP_GEMM:
                     if (d.i[4] <= 0) why = "tile GEMM: split count";
                     else if (a0 < 0 || a0 * 128 >= d.i[0]) why = "tile GEMM: m tile outside M";
-                    else if (a1 < 0 || a1 * 128 >= d.i[1]) why = "tile GEMM: n tile outside N";
+                    else if (d.i[10] != 0 && d.i[10] != 128 && !(d.i[10] == 256 && d.i[1] % 256 == 0)) why = "tile GEMM: weight rows per tile";
+                    else if (a1 < 0 || a1 * (long long)(d.i[10] == 256 ? 256 : 128) >= d.i[1]) why = "tile GEMM: n tile outside N";
                     else if (a2 < 0 || a2 >= d.i[4]) why = "tile GEMM: K split index";
                     break;
                 case MK_OP_FINALIZE:

@@ -44,7 +44,7 @@ constexpr int kSmemBytes = kRingBytes + kWorkBytes + kCtrlBytes;
 constexpr int kTcTileBytes = 128 * 128;
 constexpr int kTcXStages = 5;
 constexpr int kTcXOff = 512;                              // first 1024-aligned byte of the work area
-constexpr int kTcCols = 128;                              // fp32 accumulator columns in tensor memory
+constexpr int kTcCols = 256;                              // fp32 accumulator columns in tensor memory (a 128 x 256 tile)
 constexpr uint32_t kTcNoTmem = 0xffffffffu;               // Ctrl::tmem_base before the CTA's first allocation
 static_assert((kRingBytes + kTcXOff) % 1024 == 0 && kTcXOff + kTcXStages * kTcTileBytes + kTcTileBytes / 2 <= kWorkBytes, "activation tiles");
 // many-sequence decode attention (op_decode_bulk.cuh): the ring's memory as seven slots, each one tile of

@@ -14,7 +14,8 @@
 // ptr 0 x, 1 w, 2 out (or ws), 3 bias, 4 residual
 // i 0 M, 1 N (weight rows), 2 K, 3 act, 4 splits, 5 out dtype, 6 accumulate, 7 residual dtype,
 //   8 swiglu (weight tile = 64 gate rows then 64 up rows; the tile writes 64 output columns),
-//   9 x dtype (DT_BF16 or DT_F16)
+//   9 x dtype (DT_BF16 or DT_F16), 10 weight rows per output tile (128, or 256: the n tile argument then
+//   names a pair of 128-row tiles)
 // args: 0 m tile, 1 n tile, 2 k split
 #pragma once
 #include "mk_device.cuh"

@@ -172,7 +172,7 @@ __device__ __forceinline__ int op_gemm_tc(const Params& p, Ctrl* c, uint8_t* rin
         // asynchronous one, and read activations other SMs stored with plain stores
         asm volatile("fence.proxy.async;" ::: "memory");
         unsigned long long keep;
-        asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(keep));
+        asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(keep));
         // stage of k-tile kt: kt mod the number of stages; a barrier's parity follows from how often
         // the stage has been used since the launch began (ops with 5 and with 10 stages may alternate)
         for (int kt = 0; kt < nk; ++kt) {

@@ -1,0 +1,203 @@
+// MK_OP_GEMM on tcgen05 with 128 x 256 output tiles (descriptor i 10 = 256): the body of op_gemm_tc.cuh with two
+// accumulator halves of 128 columns in tensor memory.  One activation k-tile feeds two weight tiles, which halves
+// the activation bytes per flop: the main loop of a tile GEMM is bound by the operand bytes an SM draws from L2
+// (~64 GB/s measured: 0.5 us per 32 KB k-tile of a 128 x 128 tile, 0.75 us per 48 KB of a 128 x 256 one with
+// twice the flops).  The two weight tiles of a k-tile travel through the same single-tile ring slots, one after
+// the other (the producer warp knows the shape: op_gemv_common.cuh); the epilogue handles the halves in turn,
+// each exactly as the narrow tile's.  A body of its own (and a translation unit of its own, op_gemm_wide.cu)
+// rather than a parameter of the narrow one: sharing the code cost the narrow tile's main loop spilled registers.
+#pragma once
+#include "op_gemm_tc.cuh"
+
+namespace mk {
+
+// tc_write_rows of the narrow tile with one difference: the residual rows of a batch of eight output rows are all
+// requested before the first is used.  With a 16384-row activation the residual comes from HBM; two loads in
+// flight per warp made the residual epilogue of a 128 x 128 half take 14 us against 6.5 us without residual.
+__device__ __forceinline__ void tc_write_rows_batched(const mk_op_desc* op, const float* stage, int m0, int rows, int col0, int n_out) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int act = op->i[3], odt = op->i[5], rdt = op->i[7];
+    uint8_t* O = reinterpret_cast<uint8_t*>(op->ptr[2]);
+    const uint8_t* bias = reinterpret_cast<const uint8_t*>(op->ptr[3]);
+    const uint8_t* R = reinterpret_cast<const uint8_t*>(op->ptr[4]);
+    const int c4 = lane * 4, col = col0 + c4;
+    if (col >= n_out) return;
+    float b4[4] = {0.f, 0.f, 0.f, 0.f};
+    if (bias) {
+        const uint2 w = __ldg(reinterpret_cast<const uint2*>(bias + (long long)col * 2));
+        b4[0] = bf16_lo(w.x); b4[1] = bf16_hi(w.x); b4[2] = bf16_lo(w.y); b4[3] = bf16_hi(w.y);
+    }
+#pragma unroll 1
+    for (int base = warp; base < rows; base += 8 * kComputeWarps) {
+        float4 res[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int row = base + j * kComputeWarps;
+            res[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (R && row < rows) {
+                const long long er = (long long)(m0 + row) * op->ld[4] + col;
+                if (rdt == DT_F32) {
+                    res[j] = __ldcg(reinterpret_cast<const float4*>(R + er * 4));
+                } else {
+                    const uint2 w = __ldcg(reinterpret_cast<const uint2*>(R + er * 2));
+                    if (rdt == DT_F16) {
+                        const float2 lo = unpack2h(w.x), hi = unpack2h(w.y);
+                        res[j] = make_float4(lo.x, lo.y, hi.x, hi.y);
+                    } else {
+                        res[j] = make_float4(bf16_lo(w.x), bf16_hi(w.x), bf16_lo(w.y), bf16_hi(w.y));
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int row = base + j * kComputeWarps;
+            if (row >= rows) break;
+            const float4 q = *reinterpret_cast<const float4*>(stage + row * kTcStagePitch + c4);
+            const float f0 = apply_act(act, q.x + b4[0]) + res[j].x, f1 = apply_act(act, q.y + b4[1]) + res[j].y;
+            const float f2 = apply_act(act, q.z + b4[2]) + res[j].z, f3 = apply_act(act, q.w + b4[3]) + res[j].w;
+            const long long eo = (long long)(m0 + row) * op->ld[2] + col;
+            if (odt == DT_F32) *reinterpret_cast<float4*>(O + eo * 4) = make_float4(f0, f1, f2, f3);
+            else *reinterpret_cast<uint2*>(O + eo * 2) = make_uint2(pack2t(odt, f0, f1), pack2t(odt, f2, f3));
+        }
+    }
+}
+
+__device__ __forceinline__ int op_gemm_tc_wide(const Params& p, Ctrl* c, uint8_t* ring, uint8_t* work, const mk_op_desc* op, int a0,
+                                          int a1, int a2, int seq) {
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const int M = op->i[0], N = op->i[1], K = op->i[2], splits = op->i[4];
+    const int swi = op->i[8];
+    constexpr int halves = 2;                                             // 128-column accumulator halves of the output tile
+    const int m0 = a0 * 128, n0 = a1 * 128 * halves;
+    const int kc = K / splits, kbeg = a2 * kc, nk = kc / 64;
+    const uint8_t* tmaps = reinterpret_cast<const uint8_t*>(op->ptr[11]);
+    uint8_t* xs = work + kTcXOff;
+    // activation stages: whole 128-row tiles, or twice as many 64-row half tiles
+    const int xbytes = M <= 64 ? kTcTileBytes / 2 : kTcTileBytes;
+    const uint32_t xstages = M <= 64 ? 2 * kTcXStages : kTcXStages;
+
+    // Tensor memory is allocated by the CTA's first tile GEMM instruction and kept until the kernel
+    // ends (the kernel frees it on every path); the permit to allocate is never relinquished.
+    // (the test is on a word that only changes behind a barrier, so every thread takes the same branch)
+    const uint32_t uses = *(volatile uint32_t*)&c->acc_uses;
+    if (uses == 0) {
+        if (warp == 0)
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&c->tmem_base)), "r"(kTcCols)
+                         : "memory");
+        tc_fence_before();
+        compute_sync();
+        tc_fence_after();
+    }
+    const uint32_t tmem = *(volatile uint32_t*)&c->tmem_base;
+    const uint32_t apar = uses & 1u;
+
+    phase_mark(p, c, 0);
+    if (warp == 2 && lane == 0) {
+        // ---- activation tiles: {64 K-elements, 128 rows} at (kbeg + 64 kt, m0) ----
+        // earlier instructions wrote the work area through the generic proxy (all of that is behind
+        // the barrier that ended the dependency wait); the bulk copies below write it through the
+        // asynchronous one, and read activations other SMs stored with plain stores
+        asm volatile("fence.proxy.async;" ::: "memory");
+        unsigned long long keep;
+        asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(keep));
+        // stage of k-tile kt: kt mod the number of stages; a barrier's parity follows from how often
+        // the stage has been used since the launch began (ops with 5 and with 10 stages may alternate)
+        for (int kt = 0; kt < nk; ++kt) {
+            const int s = kt % xstages;
+            const uint32_t par = c->x_use_load[s]++ & 1u;
+            if (!wait_barrier(p, c, &c->x_empty[s], par ^ 1u, seq, WHERE_RING_EMPTY)) break;
+            mbar_arrive_expect_tx(&c->x_full[s], (uint32_t)xbytes);
+            tma_load_2d(xs + s * xbytes, tmaps, kbeg + kt * 64, m0, &c->x_full[s], keep);
+        }
+    } else if (warp == 3 && lane == 0) {
+        // ---- MMAs: accumulator[128 activation rows][128 weight rows] += x tile . w tile^T ----
+        uint32_t n = 0, acc = 0;
+        const uint32_t idesc = tc_idesc(op->i[9] == DT_F16);
+        bool ok = true;
+        int ws = c->w_slot;
+        uint32_t wph = c->w_phase;
+        for (int kt = 0; kt < nk && ok; ++kt, ++n) {
+            const int s = n % xstages;
+            ok = wait_barrier(p, c, &c->x_full[s], c->x_use_mma[s]++ & 1u, seq, WHERE_RING_FULL);
+            const uint64_t ad = tc_smem_desc(smem_u32(xs + s * xbytes));
+#pragma unroll
+            for (int h = 0; h < halves; ++h) {                                 // one weight tile (slot) per accumulator half
+                if (!ok) break;
+                ok = wait_barrier(p, c, &c->w_full[ws], wph, seq, WHERE_RING_FULL);
+                if (!ok) break;
+                tc_fence_after();
+                const uint64_t bd = tc_smem_desc(smem_u32(ring + tc_wslot_off(ws)));
+#pragma unroll
+                for (int k16 = 0; k16 < 4; ++k16) tc_mma(tmem + 128 * h, ad + 2 * k16, bd + 2 * k16, idesc, (acc | (uint32_t)k16) ? 1u : 0u);
+                tc_commit(&c->w_empty[ws]);
+                if (++ws == kTcWSlots) { ws = 0; wph ^= 1u; }
+            }
+            if (!ok) break;
+            acc = 1;
+            tc_commit(&c->x_empty[s]);
+        }
+        c->w_slot = (uint8_t)ws;
+        c->w_phase = (uint8_t)wph;
+        tc_commit(&c->acc_full);
+        if (p.trace_cap > 0) c->t_phase[1] = (long long)globaltimer();     // last MMA issued
+    }
+    __syncwarp();
+
+    // ---- epilogue: warp w owns lanes 32 (w & 3) .. +31 (activation rows) and column half w >> 2 ----
+    int ok = 1;
+    if (lane == 0) ok = wait_barrier(p, c, &c->acc_full, apar, seq, WHERE_COMBINE) ? 1 : 0;
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    tc_fence_after();
+    phase_mark(p, c, 2);                                                    // accumulator complete
+    // Per 128-column accumulator half -- first: tensor memory -> shared memory.  Warp w reads lanes
+    // 32 (w & 3) .. +31 (activation rows) and column half w >> 2; the activation stages are free now
+    // (every MMA has completed).  Then row-contiguous global accesses from shared memory.
+    const int qd = warp & 3, h = warp >> 2;
+    float* stage = reinterpret_cast<float*>(work + kTcXOff);
+    const int rows = min(128, M - m0);
+#pragma unroll 1
+    for (int hf = 0; hf < halves; ++hf) {
+        const int nh = n0 + 128 * hf;                                        // first weight row of this half
+        if (hf) compute_sync();                                              // the previous half's rows have been read
+        if (ok && qd * 32 < rows) {
+            const uint32_t tl = tmem + ((uint32_t)(qd * 32) << 16) + 128 * hf;
+            float* srow = stage + (qd * 32 + lane) * kTcStagePitch;
+            float v[32];
+            if (swi) {
+                // gate columns 32 h .. +31 and the up columns 64 further of the same outputs
+                float u[32];
+                tc_ld32(tl + h * 32, v);
+                tc_ld32(tl + 64 + h * 32, u);
+#pragma unroll
+                for (int j = 0; j < 32; j += 4)
+                    *reinterpret_cast<float4*>(srow + h * 32 + j) =
+                        make_float4(v[j] * sigmoidf_(v[j]) * u[j], v[j + 1] * sigmoidf_(v[j + 1]) * u[j + 1],
+                                    v[j + 2] * sigmoidf_(v[j + 2]) * u[j + 2], v[j + 3] * sigmoidf_(v[j + 3]) * u[j + 3]);
+            } else {
+#pragma unroll 1
+                for (int ch = 0; ch < 2; ++ch) {
+                    const int tcol = h * 64 + ch * 32;
+                    if (nh + tcol >= N) break;
+                    tc_ld32(tl + tcol, v);
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(srow + tcol + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                }
+            }
+        }
+        tc_fence_before();
+        compute_sync();
+        if (ok) {
+            if (swi) tc_write_rows(op, stage, m0, rows, 64, nh / 2, N / 2);
+            else if (op->i[6]) tc_write_rows(op, stage, m0, rows, 128, nh, N);          // split-K partial: reduce-add
+            else tc_write_rows_batched(op, stage, m0, rows, nh, N);
+        }
+    }
+    tc_fence_before();
+    const bool aborting = compute_sync_or(!ok || *(volatile int*)&c->abort);
+    if (t == 0) c->acc_uses = uses + 1;
+    if (aborting) return -1;
+    return 0;
+}
+
+}  // namespace mk

@@ -65,7 +65,7 @@ struct StageCursor {
     // tile GEMM on the tcgen05 path (op_gemm_tc.cuh): the weight k-tiles [kt, nk) of the instruction
     // are still to be copied, through the tensor map `wmap`, from coordinates (kbeg + 64 kt, n0)
     bool gemm;
-    int kt, nk, kbeg, n0;
+    int kt, nk, kbeg, n0, wide;
     const void* wmap;
     // ... or, when the host library has packed the weights into tile images (ptr 10), the 16 KB
     // block `wtile0 + kt * wstride` of that array (k-tile-major: wstride = number of n tiles)
@@ -106,12 +106,15 @@ struct StageCursor {
                 continue;
             }
             if (op->kind == MK_OP_GEMM && op->ptr[11]) {
+                // a 256-wide output tile (i 10) takes two 128-row weight tiles per k-tile, one after the
+                // other through the same single-tile slots: `kt` counts weight tiles, `wide` of them per k-tile
                 const int kc = op->i[2] / op->i[4];
-                gemm = true; kv = false; seq = in.seq; kt = 0; nk = kc / 64; kbeg = in.a2 * kc; n0 = in.a1 * 128;
+                wide = op->i[10] == 256 ? 2 : 1;
+                gemm = true; kv = false; seq = in.seq; kt = 0; nk = kc / 64 * wide; kbeg = in.a2 * kc; n0 = in.a1 * 128 * wide;
                 wmap = reinterpret_cast<const uint8_t*>(op->ptr[11]) + 128;
                 wpack = reinterpret_cast<const uint8_t*>(op->ptr[10]);
                 wstride = (op->i[1] + 127) / 128;
-                wtile0 = (long long)(kbeg / 64) * wstride + in.a1;
+                wtile0 = (long long)(kbeg / 64) * wstride + in.a1 * wide;
                 if (nk > 0) return;
                 continue;
             }
@@ -255,24 +258,31 @@ __device__ __forceinline__ void producer_loop(const Params& p, Ctrl* c, uint8_t*
             // tile GEMM: one weight k-tile (128 rows x 64 K-elements, 16 KB) per slot -- one plain bulk
             // copy when the weights are packed, one bulk tensor copy otherwise.  Eight single-tile
             // slots rather than two large ones: a slot is refilled the moment its tile has been
-            // consumed, so ~100 KB stay in flight (with 64 KB + 48 KB slots the refill of a slot
-            // waited for its last tile and the stream reached 33 GB/s per SM instead of 45).
+            // consumed, so ~100 KB stay in flight.  The instruction's tiles are issued from this tight
+            // single-lane loop: walking the outer loop (cursor, warp votes) once per tile cost ~950
+            // cycles per 16 KB -- the 0.5 us per k-tile that looked like a copy-path limit of the SM.
             if (!enter(MODE_WTILES)) return;
             int ok = 1;
             if (lane == 0) {
-                ok = wait_barrier(p, c, &c->w_empty[wslot], wphase ^ 1u, rc.seq, WHERE_RING_EMPTY) ? 1 : 0;
-                if (ok) {
+                const uint8_t* src = rc.wpack ? rc.wpack + rc.wtile0 * (long long)kTcTileBytes : nullptr;
+                const long long kstep = (long long)rc.wstride * kTcTileBytes;
+#pragma unroll 1
+                for (int kt = 0; kt < rc.nk; ++kt) {
+                    if (!wait_barrier(p, c, &c->w_empty[wslot], wphase ^ 1u, rc.seq, WHERE_RING_EMPTY)) { ok = 0; break; }
                     uint8_t* dst = ring + tc_wslot_off(wslot);
                     mbar_arrive_expect_tx(&c->w_full[wslot], (uint32_t)kTcTileBytes);
-                    if (rc.wpack)
-                        bulk_g2s_hint(dst, rc.wpack + (rc.wtile0 + (long long)rc.kt * rc.wstride) * kTcTileBytes, (uint32_t)kTcTileBytes, &c->w_full[wslot], stream_policy);
-                    else
-                        tma_load_2d(dst, rc.wmap, rc.kbeg + rc.kt * 64, rc.n0, &c->w_full[wslot], stream_policy);
+                    const int ktile = rc.wide == 2 ? kt >> 1 : kt, half = rc.wide == 2 ? kt & 1 : 0;
+                    if (src) bulk_g2s_hint(dst, src + ktile * kstep + half * kTcTileBytes, (uint32_t)kTcTileBytes, &c->w_full[wslot], stream_policy);
+                    else tma_load_2d(dst, rc.wmap, rc.kbeg + ktile * 64, rc.n0 + half * 128, &c->w_full[wslot], stream_policy);
+                    if (++wslot == kTcWSlots) { wslot = 0; wphase ^= 1u; }
                 }
             }
-            if (!__shfl_sync(0xffffffffu, ok, 0)) return;
-            if (++wslot == kTcWSlots) { wslot = 0; wphase ^= 1u; }
-            if (++rc.kt >= rc.nk) { rc.idx += gridDim.x; rc.seek(p); }
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            wslot = __shfl_sync(0xffffffffu, wslot, 0);
+            wphase = __shfl_sync(0xffffffffu, wphase, 0);
+            if (!ok) return;
+            rc.idx += gridDim.x;
+            rc.seek(p);
             continue;
         }
         if (!enter(MODE_STAGES)) return;

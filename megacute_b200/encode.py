@@ -11,7 +11,7 @@ view's first element.  Field meaning per kind (the kernel side repeats it next t
   GEMV         ptr x, w, out, bias, residual, norm gain; i M, N_out, K, act, x dtype, out dtype,
                residual dtype; f eps; flags 1 = swiglu, 2 = rms-normalise x, 4 = tensor-core streaming path
   GEMM         ptr x, w, out, bias, residual; i M, N (weight rows), K, act, splits, out dtype,
-               accumulate, residual dtype, swiglu, x dtype (bf16 or fp16)  (ptr 10, 11: set by the C
+               accumulate, residual dtype, swiglu, x dtype (bf16 or fp16), weight rows per tile (128 / 256)  (ptr 10, 11: set by the C
                library when it binds the op to its tcgen05 body: packed weight tiles, tensor maps)
   FINALIZE     ptr ws, out, bias, residual; i R, C, act, out dtype, residual dtype, rows per instruction
   ELTWISE      ptr a, b, c, out; i R, C, mode, fn, group, head_dim, dtypes of a, b, c, out
@@ -101,7 +101,7 @@ def fill(d, op: Op, addr) -> None:
         ptrs = [op.x, op.w, out, None if split else op.bias, None if split else op.residual]
         act = None if split else op.act
         ints = [op.x.rows, op.w.rows, op.x.cols, C.ACT_CODE[act], op.splits if split else 1, dt(out), int(split),
-                0 if split else dt(op.residual), int(act == "swiglu"), dt(op.x)]
+                0 if split else dt(op.residual), int(act == "swiglu"), dt(op.x), int(op.bn or C.GEMM_BN)]
     elif k == "SplitFinalize":
         d.kind = C.OP_FINALIZE
         ptrs = [op.ws, op.out, op.bias, op.residual]

@@ -108,8 +108,8 @@ class View:
 # An operand listed in both columns is updated in place by the op.  Optional operands may be
 # None.  The semantic definition of each kind is in the builder method's docstring below.
 OP_TABLE = {
-    "Linear":          (("x", "w", "bias", "residual", "norm_w"), ("out",), ("act", "rms_eps")),
-    "LinearSplit":     (("x", "w", "norm_w"), ("ws",), ("splits", "rms_eps")),
+    "Linear":          (("x", "w", "bias", "residual", "norm_w"), ("out",), ("act", "rms_eps", "bn")),
+    "LinearSplit":     (("x", "w", "norm_w"), ("ws",), ("splits", "rms_eps", "bn")),
     "SplitFinalize":   (("ws", "bias", "residual"), ("out", "ws"), ("act",)),
     "Unary":           (("x",), ("out",), ("fn",)),
     "Binary":          (("a", "b"), ("out",), ("fn", "b_group")),

@@ -364,6 +364,31 @@ def fuse_finalize_attention(g: Graph) -> Graph:
     return out
 
 
+def wide_tiles(g: Graph, sm_count: int) -> Graph:
+    """Tile linears with many rows get 128 x 256 output tiles when that is modelled faster: the main
+    loop of a tile GEMM is bound by the operand bytes an SM draws from L2, and a 256-wide tile reuses
+    each activation k-tile for two weight tiles (48 KB instead of 64 KB per 128 x 256 x 64 block).
+    rounds x (k-tiles x time per k-tile + epilogue), rounds = instructions per SM.
+    MEGACUTE_B200_WIDE_TILES=0 / 1 forces the choice where the shape allows it."""
+    force = os.environ.get("MEGACUTE_B200_WIDE_TILES")
+    out = g.derive()
+    ops = []
+    for op in g.ops:
+        if op.kind in ("Linear", "LinearSplit") and not gemv_eligible(op.x.rows, op.x.cols) and not op.bn:
+            M, K = op.x.shape
+            N = op.w.rows
+            splits = op.splits if op.kind == "LinearSplit" else 1
+            if N % C.GEMM_BN_WIDE == 0 and K % (64 * splits) == 0 and M > C.WIDE_MIN_ROWS and force != "0":
+                mt, kt = -(-M // C.GEMM_BM), K // 64 // splits
+                narrow = -(-(mt * (N // C.GEMM_BN) * splits) // sm_count) * (kt * C.KTILE_US + C.EPILOGUE_US)
+                wide = -(-(mt * (N // C.GEMM_BN_WIDE) * splits) // sm_count) * (kt * C.KTILE_US_WIDE + C.EPILOGUE_US_WIDE)
+                if wide < narrow or force == "1":
+                    op = op.clone(bn=C.GEMM_BN_WIDE)
+        ops.append(op)
+    out.ops = ops
+    return out
+
+
 def split_argmax(g: Graph, sm_count: int) -> Graph:
     """An argmax over few long rows is cut into column chunks, about two instructions per SM in all;
     every chunk leaves its best (value, index) in a workspace and the last chunk of a row to arrive
@@ -386,5 +411,5 @@ def split_argmax(g: Graph, sm_count: int) -> Graph:
 def run_all(g: Graph, sm_count: int) -> Graph:
     """The pass pipeline of ``compile`` (reference order: runtime.py:235, plus promote_temps and
     fuse_finalize_attention)."""
-    g = split_argmax(split_kv(fuse_rope_attention(split_k(fold_norms(g), sm_count)), sm_count), sm_count)
+    g = split_argmax(split_kv(fuse_rope_attention(wide_tiles(split_k(fold_norms(g), sm_count), sm_count)), sm_count), sm_count)
     return fuse_finalize_attention(promote_temps(g))

@@ -128,7 +128,8 @@ def tile_op(op: Op, sm_count: int) -> Tiled:
         out = op.out if k == "Linear" else op.ws
         M = out.rows
         swi = k == "Linear" and op.act == "swiglu"
-        on = C.GEMM_BN // 2 if swi else C.GEMM_BN
+        BN = op.bn or C.GEMM_BN                       # weight rows per tile: 128, or 256 (passes.wide_tiles)
+        on = BN // 2 if swi else BN
         m, nn = gemm_raster(_ceil(M, C.GEMM_BM), _ceil(out.cols, on))
         splits = op.splits if k == "LinearSplit" else 1
         kc = op.x.cols // splits
@@ -136,7 +137,7 @@ def tile_op(op: Op, sm_count: int) -> Tiled:
         n = len(m)
         r0, r1 = m * C.GEMM_BM, (m + 1) * C.GEMM_BM
         acc = [_acc(op.x, READ, r0, r1, ks * kc, (ks + 1) * kc, n=n),
-               _acc(op.w, READ, nn * C.GEMM_BN, (nn + 1) * C.GEMM_BN, ks * kc, (ks + 1) * kc, n=n),
+               _acc(op.w, READ, nn * BN, (nn + 1) * BN, ks * kc, (ks + 1) * kc, n=n),
                _acc(out, ACCUM if k == "LinearSplit" else WRITE, r0, r1, nn * on, (nn + 1) * on, n=n)]
         if k == "Linear":
             acc += [_acc(op.bias, READ, 0, 1, nn * on, (nn + 1) * on, n=n),

@@ -118,7 +118,8 @@ def op_grid(op, sm_count: int):
     if k in ("Linear", "LinearSplit"):
         out = op.out if k == "Linear" else op.ws
         swi = k == "Linear" and op.act == "swiglu"
-        return (_ceil(out.rows, C.GEMM_BM), _ceil(out.cols, C.GEMM_BN // 2 if swi else C.GEMM_BN),
+        bn = op.bn or C.GEMM_BN
+        return (_ceil(out.rows, C.GEMM_BM), _ceil(out.cols, bn // 2 if swi else bn),
                 op.splits if k == "LinearSplit" else 1)
     if k == "SplitFinalize":
         return (_ceil(op.out.rows, finalize_rows(*op.out.shape)), _ceil(op.out.cols, C.EW_COLS))

@@ -419,3 +419,35 @@ def test_fused_step_feeds_itself(cuda, B, vocab):
     for b in prog.g.buffers:
         if b.kind == "workspace" and b.dtype == torch.int32:
             assert int(prog.buffer(b).abs().sum()) == 0
+
+
+@pytest.mark.parametrize("M,K,N,act,bias,res", [
+    (256, 2048, 512, None, True, True),
+    (200, 512, 768, "gelu_tanh", True, False),
+    (300, 1024, 1024, "swiglu", False, False),
+    (130, 256, 256, "relu", True, True),
+    (520, 4096, 256, None, False, True),
+    (1100, 512, 1280, None, False, False),
+])
+def test_tile_linear_wide_tiles(cuda, monkeypatch, M, K, N, act, bias, res):
+    """128 x 256 output tiles (one activation k-tile feeds two weight tiles, two accumulator halves in tensor
+    memory): plain, swiglu and split-K epilogues, ragged last row tile, several tiles per CTA."""
+    monkeypatch.setenv("MEGACUTE_B200_WIDE_TILES", "1")
+    g = mc.Graph()
+    x = g.input("x", (M, K))
+    w = g.param("w", (N, K))
+    n_out = N // 2 if act == "swiglu" else N
+    h = g.unary(x, "identity")                      # a runtime-owned (fp16) activation, as inside a model
+    y = g.linear(h, w, bias=g.param("b", (1, n_out)) if bias else None, act=act,
+                 residual=g.input("r", (M, n_out)) if res else None)
+    g.output(y)
+    t = {"x": rnd((M, K), 1.0, 1), "w": rnd((N, K), 0.03, 2)}
+    if bias:
+        t["b"] = rnd((1, n_out), 0.5, 4)
+    if res:
+        t["r"] = rnd((M, n_out), 1.0, 5)
+    outs, ref, _, _, prog = run_both(g, t, cuda, steps=2)
+    lin = [o for o in prog.g.ops if o.kind in ("Linear", "LinearSplit")]
+    assert lin and all(o.bn == 256 for o in lin) and prog.tcgen05_ops == len(lin)
+    assert_close(outs, ref)
+    assert np.array_equal(prog.counters(), prog.sched.counter_target * 2)
