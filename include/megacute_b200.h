@@ -136,6 +136,8 @@ int mk_program_epoch(mk_program* p);
  * bulk-tensor-copied operands (the others, if any, run the mma.sync body: K range per instruction
  * not a multiple of 64, unaligned operands, or MEGACUTE_B200_NO_TCGEN05 set). */
 int mk_program_tcgen05_ops(mk_program* p);
+/* ... and how many prefill attention ops (head_dim 64; the others run the mma.sync body). */
+int mk_program_tcgen05_attention_ops(mk_program* p);
 /* Device memory the program holds for tile-image copies of the weights of those ops (made by
  * mk_program_set_ops unless MEGACUTE_B200_NO_WEIGHT_PACK is set, when a weight matrix is bound
  * for the first time; kept while that matrix stays bound; a copy that is no longer bound is not

@@ -55,6 +55,7 @@ SYMBOLS = {
     "mk_program_reset": (ctypes.c_int, [_P, _P]),
     "mk_program_epoch": (ctypes.c_int, [_P]),
     "mk_program_tcgen05_ops": (ctypes.c_int, [_P]),
+    "mk_program_tcgen05_attention_ops": (ctypes.c_int, [_P]),
     "mk_program_packed_bytes": (ctypes.c_longlong, [_P]),
     "mk_program_refresh_weights": (ctypes.c_int, [_P, ctypes.c_void_p]),
     "mk_program_read_counters": (ctypes.c_int, [_P, _I32P, ctypes.c_int]),

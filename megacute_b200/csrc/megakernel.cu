@@ -148,7 +148,10 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
                                                              : mk_op_gemm(p, op, in.a0, in.a1, in.a2, in.seq, ppos);
                     aborting = npos < 0;
                     break;
-                case MK_OP_ATTENTION: mk_op_attention(op, in.a0, in.a1, in.a2); break;
+                case MK_OP_ATTENTION:
+                    if (op->ptr[11]) aborting = mk_op_attention_tc(p, op, in.a0, in.a1, in.a2, in.seq) < 0;
+                    else mk_op_attention(op, in.a0, in.a1, in.a2);
+                    break;
                 case MK_OP_DECODE_ATTN:
                     aborting = mk_op_decode_attn(p, op, in.a0, in.a1, in.a2, in.nwait, wait_off, in.seq, in.narrive, arrive_off);
                     if (TRACE) t1 = c->t_dep;
@@ -161,7 +164,7 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
             if (!self_wait) aborting = publish(p, c, in.narrive, arrive_off) || aborting;
             if (threadIdx.x == 0) {
                 trace_rec<TRACE>(p, 1, slot, in.seq, t0, t1, (long long)globaltimer());
-                if (TRACE && (self_wait || op->kind == MK_OP_GEMM)) trace_rec<TRACE>(p, 2, slot, in.seq, c->t_phase[0], c->t_phase[1], c->t_phase[2]);
+                if (TRACE && (self_wait || op->kind == MK_OP_GEMM || op->kind == MK_OP_ATTENTION)) trace_rec<TRACE>(p, 2, slot, in.seq, c->t_phase[0], c->t_phase[1], c->t_phase[2]);
             }
             if (aborting) break;
         }
@@ -241,7 +244,7 @@ struct mk_program {
     int32_t* d_arrives = nullptr;
     int32_t* d_counters = nullptr;
     mk_op_desc* d_ops = nullptr;
-    uint8_t* d_tmaps = nullptr;      // per op: two 128-byte tensor maps (tile GEMM: activations, weights)
+    uint8_t* d_tmaps = nullptr;      // per op: kMapBytes of 128-byte tensor maps (tile GEMM: activations, weights; attention: q, k, v)
     // Two pinned staging copies of the descriptor and tensor-map tables, used in turn: a rebind fills
     // the one whose upload (two rebinds ago) has completed -- its event says so -- instead of
     // synchronising the stream, so a caller that binds a fresh input tensor every call never
@@ -267,9 +270,11 @@ struct mk_program {
     int max_target = 1;
     unsigned long long timeout_ns = 2000000000ull;
     int tcgen05_ops = 0;             // tile GEMMs bound to the tcgen05 body by the last set_ops
+    int tcgen05_attn_ops = 0;        // ... prefill attention ops
     int pf_stages = 0;               // L2 prefetch distance of the producer warp, in ring stages (0 = off)
 };
 
+static const size_t kMapBytes = 512;       // tensor-map space per op
 static thread_local char g_cuda_err[256] = "";
 
 static int cuda_fail(cudaError_t e, const char* what) {
@@ -524,10 +529,10 @@ int mk_program_create(int device, const int32_t* insts, int n_insts, const int32
     MK_TRY(cudaMalloc(&p->d_counters, (size_t)p->n_counters * 4));
     MK_TRY(cudaMemset(p->d_counters, 0, (size_t)p->n_counters * 4));
     MK_TRY(cudaMalloc(&p->d_ops, (size_t)n_ops * sizeof(mk_op_desc)));
-    MK_TRY(cudaMalloc(&p->d_tmaps, (size_t)n_ops * 256));
+    MK_TRY(cudaMalloc(&p->d_tmaps, (size_t)n_ops * kMapBytes));
     for (int b = 0; b < 2; ++b) {
         MK_TRY(cudaMallocHost(&p->h_ops[b], (size_t)n_ops * sizeof(mk_op_desc)));
-        MK_TRY(cudaMallocHost(&p->h_tmaps[b], (size_t)n_ops * 256));
+        MK_TRY(cudaMallocHost(&p->h_tmaps[b], (size_t)n_ops * kMapBytes));
         MK_TRY(cudaEventCreateWithFlags(&p->staged[b], cudaEventDisableTiming));
     }
     MK_TRY(cudaMalloc(&p->d_status, MK_ST_WORDS * 4));
@@ -567,12 +572,34 @@ int mk_program_set_ops(mk_program* p, const mk_op_desc* ops, int n_ops, void* st
     const bool tc_off = getenv("MEGACUTE_B200_NO_TCGEN05") != nullptr;
     const bool pack_off = getenv("MEGACUTE_B200_NO_WEIGHT_PACK") != nullptr;
     for (auto& e : p->packed) e.used = false;
+    int n_attn = 0;
     for (int k = 0; k < n_ops; ++k) {
         mk_op_desc& d = h_ops[k];
+        if (d.kind == MK_OP_ATTENTION) {
+            // head_dim 64: tensor maps over q, k, v select the tcgen05 body (op_attention_tc.cuh)
+            d.ptr[11] = 0;
+            uint8_t* maps = h_tmaps + (size_t)k * kMapBytes;
+            const long long B = d.i[0], Sq = d.i[1], Sk = d.i[2], H = d.i[3], KVH = d.i[4];
+            // Off unless MEGACUTE_B200_ATTN_TCGEN05=1: measured on 4 x 4096 causal tokens (32 heads, 8 kv heads) the
+            // tcgen05 body takes 4.4 ms against the mma.sync body's 2.1 ms -- its softmax runs on four warps, one
+            // per scheduler, as chains of dependent instructions (0.18 instructions per cycle), while the mma.sync
+            // body spreads the same arithmetic over eight warps.
+            const char* attn_tc = getenv("MEGACUTE_B200_ATTN_TCGEN05");
+            if (!attn_tc || attn_tc[0] != '1') continue;
+            if (tc_off || d.i[5] != 64 || (d.ptr[3] & 15) || d.ld[3] % 8) continue;
+            if (encode_tile_map(maps, d.ptr[0], B * Sq, H * 64, d.ld[0], 128, false) &&
+                encode_tile_map(maps + 128, d.ptr[1], B * Sk, KVH * 64, d.ld[1], 128, false) &&
+                encode_tile_map(maps + 256, d.ptr[2], B * Sk, KVH * 64, d.ld[2], 128, false)) {
+                d.ptr[11] = reinterpret_cast<uint64_t>(p->d_tmaps + (size_t)k * kMapBytes);
+                any_map = true;
+                ++n_attn;
+            }
+            continue;
+        }
         if (d.kind != MK_OP_GEMM) continue;
         d.ptr[11] = 0;
         if (tc_off || !tile_gemm_on_tcgen05(d)) continue;
-        uint8_t* maps = h_tmaps + (size_t)k * 256;
+        uint8_t* maps = h_tmaps + (size_t)k * kMapBytes;
         d.ptr[10] = 0;
         if (d.i[9] != mk::DT_BF16 && d.i[9] != mk::DT_F16) continue;
         const bool xh = d.i[9] == mk::DT_F16;
@@ -621,12 +648,13 @@ int mk_program_set_ops(mk_program* p, const mk_op_desc* ops, int n_ops, void* st
         }
         if (xh && !d.ptr[10]) continue;                 // (the copy could not be allocated)
         if (d.ptr[10] || encode_tile_map(maps + 128, d.ptr[1], d.i[1], d.i[2], d.ld[1], 128, true)) {
-            d.ptr[11] = reinterpret_cast<uint64_t>(p->d_tmaps + (size_t)k * 256);
+            d.ptr[11] = reinterpret_cast<uint64_t>(p->d_tmaps + (size_t)k * kMapBytes);
             any_map = true;
             ++n_tc;
         }
     }
     p->tcgen05_ops = n_tc;
+    p->tcgen05_attn_ops = n_attn;
     // Packed copies of matrices that are no longer bound are retired, not freed: launches enqueued
     // before this rebind may still read them.  An event on `stream` (and on the stream of the latest
     // launch, if another) marks the point after which they are free; they are released by a later
@@ -648,7 +676,7 @@ int mk_program_set_ops(mk_program* p, const mk_op_desc* ops, int n_ops, void* st
         p->packed.erase(p->packed.begin() + e);
     }
     free_retired(p, false);
-    if (any_map) MK_CUDA(cudaMemcpyAsync(p->d_tmaps, h_tmaps, (size_t)n_ops * 256, cudaMemcpyHostToDevice, st));
+    if (any_map) MK_CUDA(cudaMemcpyAsync(p->d_tmaps, h_tmaps, (size_t)n_ops * kMapBytes, cudaMemcpyHostToDevice, st));
     MK_CUDA(cudaMemcpyAsync(p->d_ops, h_ops, (size_t)n_ops * sizeof(mk_op_desc), cudaMemcpyHostToDevice, st));
     MK_CUDA(cudaEventRecord(p->staged[turn], st));
     return MK_OK;
@@ -718,6 +746,8 @@ int mk_program_reset(mk_program* p, void* stream) {
 int mk_program_epoch(mk_program* p) { return p ? p->epoch : MK_E_ARG; }
 
 int mk_program_tcgen05_ops(mk_program* p) { return p ? p->tcgen05_ops : MK_E_ARG; }
+
+int mk_program_tcgen05_attention_ops(mk_program* p) { return p ? p->tcgen05_attn_ops : MK_E_ARG; }
 
 int mk_program_refresh_weights(mk_program* p, void* stream) {
     if (!p) return MK_E_ARG;

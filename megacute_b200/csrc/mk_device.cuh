@@ -32,7 +32,8 @@ constexpr int kSegStride = kSegElems * 2 + 16;            // bytes between row s
 constexpr int kStageBytes = 16 * kSegStride;              // 65 792 B
 constexpr int kStages = 2;
 constexpr int kRingBytes = kStages * kStageBytes;         // 128.5 KB, written only by bulk copies
-constexpr int kWorkBytes = 96 * 1024;                     // scratch of the instruction being executed
+constexpr int kWorkBytes = 96 * 1024 + 512;               // scratch of the instruction being executed (with the 512 bytes in front of
+                                                          // its first 1024-byte boundary: six whole 16 KB operand tiles)
 constexpr int kXbufBytes = 64 * 1024;                     // GEMV: fp32 activation rows (front of work)
 constexpr int kCtrlBytes = 2048;                          // mbarriers, flags, staged instruction metadata
 constexpr int kSmemBytes = kRingBytes + kWorkBytes + kCtrlBytes;
@@ -44,7 +45,8 @@ constexpr int kSmemBytes = kRingBytes + kWorkBytes + kCtrlBytes;
 constexpr int kTcTileBytes = 128 * 128;
 constexpr int kTcXStages = 5;
 constexpr int kTcXOff = 512;                              // first 1024-aligned byte of the work area
-constexpr int kTcCols = 256;                              // fp32 accumulator columns in tensor memory (a 128 x 256 tile)
+constexpr int kTcCols = 512;                              // tensor-memory columns held by the CTA: a 128 x 256 accumulator (tile GEMM),
+                                                          // or two S tiles and O (prefill attention)
 constexpr uint32_t kTcNoTmem = 0xffffffffu;               // Ctrl::tmem_base before the CTA's first allocation
 static_assert((kRingBytes + kTcXOff) % 1024 == 0 && kTcXOff + kTcXStages * kTcTileBytes + kTcTileBytes / 2 <= kWorkBytes, "activation tiles");
 // many-sequence decode attention (op_decode_bulk.cuh): the ring's memory as seven slots, each one tile of
@@ -97,6 +99,10 @@ struct Meta {
     int arrives[2][kMetaArrives];
 };
 
+struct AttnBars {                 // tcgen05 prefill attention (op_attention_tc.cuh): re-initialised by every instruction
+    unsigned long long q_full, k_full[2], k_empty[2], v_full, v_empty, s_full[2], s_empty[2], p_full, pv_done;
+};
+
 struct Ctrl {                     // lives in the last kCtrlBytes of shared memory
     Meta meta;
     unsigned long long full[kStages];
@@ -114,6 +120,7 @@ struct Ctrl {                     // lives in the last kCtrlBytes of shared memo
     unsigned long long kv_empty[kKvSlots];   // ... every compute warp has read it
     unsigned long long kv_go;                // ... (unfused form) the instruction's dependencies are met: the row appended in this launch may be read
     uint32_t kv_cons;                        // ... the compute warps' position in the slots (slot | phase << 8)
+    AttnBars attn;
     uint32_t tmem_base;               // ... tensor-memory address of the accumulator (written by tcgen05.alloc)
     uint8_t x_use_load[2 * kTcXStages];   // ... how often each stage has been filled / consumed since the launch
     uint8_t x_use_mma[2 * kTcXStages];    //     began (the parities of x_empty / x_full)

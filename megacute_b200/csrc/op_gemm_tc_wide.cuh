@@ -81,7 +81,7 @@ __device__ __forceinline__ int op_gemm_tc_wide(const Params& p, Ctrl* c, uint8_t
     // ends (the kernel frees it on every path); the permit to allocate is never relinquished.
     // (the test is on a word that only changes behind a barrier, so every thread takes the same branch)
     const uint32_t uses = *(volatile uint32_t*)&c->acc_uses;
-    if (uses == 0) {
+    if (*(volatile uint32_t*)&c->tmem_base == kTcNoTmem) {     // (the attention op may have allocated it already)
         if (warp == 0)
             asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&c->tmem_base)), "r"(kTcCols)
                          : "memory");

@@ -200,6 +200,11 @@ class Program:
         return int(_lib.load().mk_program_tcgen05_ops(self._handle)) if self._handle is not None else 0
 
     @property
+    def tcgen05_attention_ops(self) -> int:
+        """Prefill attention ops bound to the tcgen05 body at the last launch (head_dim 64)."""
+        return int(_lib.load().mk_program_tcgen05_attention_ops(self._handle)) if self._handle is not None else 0
+
+    @property
     def packed_weight_bytes(self) -> int:
         """Device memory held for tile-image copies of tile-GEMM weights (snapshots taken when a weight
         tensor is first bound; `refresh_weights()` after changing weights in place)."""

@@ -79,9 +79,12 @@ def test_llama_1b_decode_batch64(cuda, ctx):
     assert np.array_equal(prog.counters(), prog.sched.counter_target * steps)
 
 
-def test_llama_1b_prefill_4x4096(cuda):
+@pytest.mark.parametrize("attention", ["mma.sync", "tcgen05"])
+def test_llama_1b_prefill_4x4096(cuda, monkeypatch, attention):
     """Prefill at full size: 16 layers of causal GQA attention over 4 x 4096 tokens, then the final
-    norm and the lm_head on each prompt's last token."""
+    norm and the lm_head on each prompt's last token; with the default (mma.sync) and the tcgen05 body of
+    the attention."""
+    monkeypatch.setenv("MEGACUTE_B200_ATTN_TCGEN05", "1" if attention == "tcgen05" else "0")
     c = C1B
     B, S = 4, 4096
     g = llama_stack(B, S, c["E"], c["H"], c["KVH"], c["F"], c["n"], eps=c["eps"], vocab=c["vocab"])
@@ -94,6 +97,7 @@ def test_llama_1b_prefill_4x4096(cuda):
     prog.check()
     assert np.array_equal(prog.counters(), prog.sched.counter_target)
     assert prog.tcgen05_ops == sum(o.kind in ("Linear", "LinearSplit") and o.x.rows > 8 for o in prog.g.ops)
+    assert prog.tcgen05_attention_ops == (c["n"] if attention == "tcgen05" else 0)
     ref, _ = evaluate(g, t, device=cuda)
     err = rel_l2(logits, ref[0])
     print(f"prefill 4 x 4096: logits rel-L2 {err:.2e}")

@@ -177,29 +177,60 @@ def test_mlp_block_config(cuda):
 @pytest.mark.parametrize("B,Sq,Sk,H,KVH,D,causal", [
     (2, 128, 128, 4, 4, 64, False), (2, 256, 256, 4, 2, 64, True), (1, 200, 200, 2, 1, 64, True),
     (3, 96, 160, 2, 2, 64, False), (1, 256, 256, 2, 1, 128, True), (2, 130, 130, 2, 2, 128, False),
-    (1, 1024, 1024, 8, 2, 64, True),
+    (1, 1024, 1024, 8, 2, 64, True), (2, 300, 300, 4, 1, 64, True), (1, 64, 700, 2, 2, 64, False), (5, 128, 128, 3, 3, 64, True),
 ])
-def test_prefill_attention(cuda, B, Sq, Sk, H, KVH, D, causal):
+@pytest.mark.parametrize("body", ["mma.sync", "tcgen05"])
+def test_prefill_attention(cuda, monkeypatch, B, Sq, Sk, H, KVH, D, causal, body):
+    if body == "tcgen05":
+        if D != 64:
+            pytest.skip("the tcgen05 body takes head_dim 64")
+        monkeypatch.setenv("MEGACUTE_B200_ATTN_TCGEN05", "1")
     g = mc.Graph()
     q = g.input("q", (B * Sq, H * D))
     kv = g.input("kv", (B * Sk, 2 * KVH * D))          # k and v are column slices of one buffer
     g.output(g.attention(q, kv.cols_slice(0, KVH * D), kv.cols_slice(KVH * D, KVH * D), batch=B, heads=H,
                          head_dim=D, causal=causal, kv_heads=KVH))
     t = {"q": rnd((B * Sq, H * D), 1, 1), "kv": rnd((B * Sk, 2 * KVH * D), 1, 2)}
-    outs, ref, *_ = run_both(g, t, cuda)
+    outs, ref, _, _, prog = run_both(g, t, cuda, steps=2)
     assert_close(outs, ref)
+    # the counter says which body ran: tcgen05 (S and O in tensor memory) when asked for, else mma.sync
+    assert prog.tcgen05_attention_ops == (1 if body == "tcgen05" else 0)
 
 
-def test_small_prefill_stack(cuda):
+def test_prefill_attention_both_bodies_agree(cuda, monkeypatch):
+    """The tcgen05 body and the mma.sync body (MEGACUTE_B200_NO_TCGEN05) of the prefill attention on the same
+    inputs: scores with a wide range (so that the lazy rescale of the running maximum triggers), causal,
+    GQA, a ragged last query tile."""
+    B, S, H, KVH, D = 2, 333, 4, 2, 64
+    g = mc.Graph()
+    q = g.input("q", (B * S, H * D))
+    kv = g.input("kv", (B * S, 2 * KVH * D))
+    g.output(g.attention(q, kv.cols_slice(0, KVH * D), kv.cols_slice(KVH * D, KVH * D), batch=B, heads=H, head_dim=D,
+                         causal=True, kv_heads=KVH))
+    t = {"q": rnd((B * S, H * D), 3.0, 1), "kv": rnd((B * S, 2 * KVH * D), 3.0, 2)}       # logits of +-70: maxima jump
+    monkeypatch.setenv("MEGACUTE_B200_ATTN_TCGEN05", "1")
+    outs_tc, ref, _, _, prog_tc = run_both(g, t, cuda)
+    monkeypatch.setenv("MEGACUTE_B200_ATTN_TCGEN05", "0")
+    outs_mma, _, _, _, prog_mma = run_both(g, t, cuda)
+    assert prog_tc.tcgen05_attention_ops == 1 and prog_mma.tcgen05_attention_ops == 0
+    assert_close(outs_tc, ref)
+    assert_close(outs_mma, ref)
+    assert rel_l2(outs_tc[0], outs_mma[0]) < 5e-3
+
+
+@pytest.mark.parametrize("attn_tc", ["0", "1"])
+def test_small_prefill_stack(cuda, monkeypatch, attn_tc):
+    monkeypatch.setenv("MEGACUTE_B200_ATTN_TCGEN05", attn_tc)
     B, S, E, H, KVH, F, n, V = 2, 192, 256, 4, 2, 512, 2, 1000
     g = llama_stack(B, S, E, H, KVH, F, n, eps=1e-5, vocab=V)
     w = W.llama_weights(E, H, KVH, F, n, V, 0, "cpu")
     cos, sin = W.rope_tables(S, E // H)
     ids = torch.randint(0, V, (B * S,), generator=torch.Generator().manual_seed(1))
     t = dict(x=w["lm_head"][ids].contiguous(), cos=cos, sin=sin, **w)
-    outs, ref, *_ = run_both(g, t, cuda)
+    outs, ref, _, _, prog = run_both(g, t, cuda)
     assert_close(outs, ref)
     assert torch.equal(outs[0].argmax(-1), ref[0].argmax(-1))
+    assert prog.tcgen05_attention_ops == (n if attn_tc == "1" else 0)
 
 
 def test_small_dit_stack(cuda):
