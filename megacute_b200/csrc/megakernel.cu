@@ -587,9 +587,10 @@ int mk_program_set_ops(mk_program* p, const mk_op_desc* ops, int n_ops, void* st
             const char* attn_tc = getenv("MEGACUTE_B200_ATTN_TCGEN05");
             if (!attn_tc || attn_tc[0] != '1') continue;
             if (tc_off || d.i[5] != 64 || (d.ptr[3] & 15) || d.ld[3] % 8) continue;
-            if (encode_tile_map(maps, d.ptr[0], B * Sq, H * 64, d.ld[0], 128, false) &&
-                encode_tile_map(maps + 128, d.ptr[1], B * Sk, KVH * 64, d.ld[1], 128, false) &&
-                encode_tile_map(maps + 256, d.ptr[2], B * Sk, KVH * 64, d.ld[2], 128, false)) {
+            const bool h16 = d.i[8] == mk::DT_F16;
+            if (encode_tile_map(maps, d.ptr[0], B * Sq, H * 64, d.ld[0], 128, false, h16) &&
+                encode_tile_map(maps + 128, d.ptr[1], B * Sk, KVH * 64, d.ld[1], 128, false, h16) &&
+                encode_tile_map(maps + 256, d.ptr[2], B * Sk, KVH * 64, d.ld[2], 128, false, h16)) {
                 d.ptr[11] = reinterpret_cast<uint64_t>(p->d_tmaps + (size_t)k * kMapBytes);
                 any_map = true;
                 ++n_attn;

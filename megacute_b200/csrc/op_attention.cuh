@@ -7,7 +7,7 @@
 // portable first implementation; the tcgen05 / TMEM version is the planned replacement.
 //
 // ptr 0 q, 1 k, 2 v, 3 out; i 0 batch, 1 seq_q, 2 seq_k, 3 heads, 4 kv_heads, 5 head_dim,
-// 6 causal, 7 out dtype (DT_BF16 or DT_F16); f 0 scale.  args: 0 b, 1 h, 2 query tile.
+// 6 causal, 7 out dtype (DT_BF16 or DT_F16), 8 dtype of q, k and v (DT_BF16 or DT_F16); f 0 scale.  args: 0 b, 1 h, 2 query tile.
 #pragma once
 #include "mk_device.cuh"
 #include "mma.cuh"
@@ -16,7 +16,9 @@ namespace mk {
 
 constexpr int kAttnBQ = 128, kAttnBK = 64;
 
-template <int D>
+// F16: q, k and v (runtime-private activations, see passes.promote_temps) are fp16 instead of bf16; P is then
+// rounded to fp16 too, since one MMA takes one operand type.
+template <int D, bool F16>
 static __device__ __noinline__ void op_attention(const mk_op_desc* op, int a0, int a1, int a2, uint8_t* work) {
     constexpr int ROWB = D * 2 + 16;                       // padded row: conflict-free ldmatrix
     constexpr int KT_BYTES = kAttnBK * ROWB;               // one K or V tile
@@ -95,8 +97,8 @@ static __device__ __noinline__ void op_attention(const mk_op_desc* op, int a0, i
                 uint32_t b0, b1, b2, b3;
                 ldmatrix_x4(kb + (jp * 16 + (lane & 7) + (lane >> 4) * 8) * ROWB + (kk * 16 + ((lane >> 3) & 1) * 8) * 2,
                             b0, b1, b2, b3);
-                mma_bf16(s[jp * 2], qf[kk], b0, b1);
-                mma_bf16(s[jp * 2 + 1], qf[kk], b2, b3);
+                if (F16) { mma_f16(s[jp * 2], qf[kk], b0, b1); mma_f16(s[jp * 2 + 1], qf[kk], b2, b3); }
+                else { mma_bf16(s[jp * 2], qf[kk], b0, b1); mma_bf16(s[jp * 2 + 1], qf[kk], b2, b3); }
             }
         }
         // ---- mask + online softmax (log2 domain) ----
@@ -132,11 +134,11 @@ static __device__ __noinline__ void op_attention(const mk_op_desc* op, int a0, i
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const float m = mnew[e >> 1];
-                p[e] = (s[j][e] == NEG_INF || m == NEG_INF) ? 0.f : round_bf16(ex2(s[j][e] - m));
+                p[e] = (s[j][e] == NEG_INF || m == NEG_INF) ? 0.f : (F16 ? round_f16(ex2(s[j][e] - m)) : round_bf16(ex2(s[j][e] - m)));
                 sum[e >> 1] += p[e];
             }
-            pf[j >> 1][(j & 1) * 2] = pack2(p[0], p[1]);          // rows r
-            pf[j >> 1][(j & 1) * 2 + 1] = pack2(p[2], p[3]);      // rows r + 8
+            pf[j >> 1][(j & 1) * 2] = F16 ? pack2h(p[0], p[1]) : pack2(p[0], p[1]);          // rows r
+            pf[j >> 1][(j & 1) * 2 + 1] = F16 ? pack2h(p[2], p[3]) : pack2(p[2], p[3]);      // rows r + 8
         }
 #pragma unroll
         for (int r = 0; r < 2; ++r) lrow[r] = lrow[r] * alpha[r] + sum[r];
@@ -153,8 +155,8 @@ static __device__ __noinline__ void op_attention(const mk_op_desc* op, int a0, i
                 uint32_t b0, b1, b2, b3;
                 ldmatrix_x4_trans(vb + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ROWB + (jp * 16 + (lane >> 4) * 8) * 2,
                                   b0, b1, b2, b3);
-                mma_bf16(oacc[jp * 2], pf[kk], b0, b1);
-                mma_bf16(oacc[jp * 2 + 1], pf[kk], b2, b3);
+                if (F16) { mma_f16(oacc[jp * 2], pf[kk], b0, b1); mma_f16(oacc[jp * 2 + 1], pf[kk], b2, b3); }
+                else { mma_bf16(oacc[jp * 2], pf[kk], b0, b1); mma_bf16(oacc[jp * 2 + 1], pf[kk], b2, b3); }
             }
         }
         compute_sync();                                      // the stage is overwritten by the next issue

@@ -26,7 +26,7 @@
 // head_dim 128 and operands the tensor maps cannot describe run the mma.sync body.
 //
 // ptr 0 q, 1 k, 2 v, 3 out, 11 tensor maps; i 0 batch, 1 seq_q, 2 seq_k, 3 heads, 4 kv_heads, 5 head_dim,
-// 6 causal, 7 out dtype; f 0 scale.  args: 0 b, 1 h, 2 query tile.
+// 6 causal, 7 out dtype, 8 dtype of q, k, v; f 0 scale.  args: 0 b, 1 h, 2 query tile.
 #pragma once
 #include "mk_device.cuh"
 #include "op_gemm_tc.cuh"
@@ -42,9 +42,16 @@ constexpr uint32_t kAtSCol = 0, kAtOCol = 256;                // tensor-memory c
 static_assert(kAtOCol + 64 <= kTcCols, "attention accumulators exceed the tensor memory held");
 constexpr float kAtRescale = 8.0f;                            // raise the running maximum only past 2^8
 
-// instruction descriptors, kind::f16, bf16 operands, fp32 accumulator, M = 128
-constexpr uint32_t kAtIdescS = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);               // N = 128, A and B K-major
-constexpr uint32_t kAtIdescO = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((64u >> 3) << 17) | ((128u >> 4) << 24);   // N = 64, B MN-major
+// instruction descriptors, kind::f16, fp32 accumulator, M = 128; operand format bits 7-9 / 10-12: 1 = bf16, 0 = fp16
+// (q, k, v -- and with them P -- are bf16, or fp16 when they are runtime-private activations)
+__device__ __forceinline__ uint32_t at_idesc_s(bool f16) {      // N = 128, A and B K-major
+    const uint32_t f = f16 ? 0u : 1u;
+    return (1u << 4) | (f << 7) | (f << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+}
+__device__ __forceinline__ uint32_t at_idesc_o(bool f16) {      // N = 64, B MN-major
+    const uint32_t f = f16 ? 0u : 1u;
+    return (1u << 4) | (f << 7) | (f << 10) | (1u << 16) | ((64u >> 3) << 17) | ((128u >> 4) << 24);
+}
 
 // 2-D tiled bulk tensor copy global -> shared without a cache hint
 __device__ __forceinline__ void tma_load_2d_plain(void* dst, const void* tmap, int x, int y, unsigned long long* bar) {
@@ -83,7 +90,7 @@ __device__ __forceinline__ int op_attention_tc(const Params& p, Ctrl* c, uint8_t
     constexpr float NEG_INF = -__builtin_huge_valf();
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     const int Sq = op->i[1], Sk = op->i[2], H = op->i[3], KVH = op->i[4], odt = op->i[7];
-    const bool causal = op->i[6] != 0;
+    const bool causal = op->i[6] != 0, f16 = op->i[8] == DT_F16;
     const int hk = h / (H / KVH);
     const int q0 = qi * 128;
     const int kend = causal ? min(Sk, q0 + 128) : Sk;
@@ -150,6 +157,7 @@ __device__ __forceinline__ int op_attention_tc(const Params& p, Ctrl* c, uint8_t
         // V as MN-major operand: 8-key groups 1024 bytes apart; 16 keys further = 2048 bytes
         const uint64_t vd = tc_smem_desc(smem_u32(vs));
         const uint64_t pd0 = tc_smem_desc(smem_u32(ps)), pd1 = tc_smem_desc(smem_u32(ps + kTcTileBytes));
+        const uint32_t idesc_s = at_idesc_s(f16), idesc_o = at_idesc_o(f16);
         auto issue_s = [&](int j) -> bool {        // S of block j into tensor-memory buffer j & 1
             const int u = j & 1;
             if (!wait_barrier(p, c, &a->k_full[u], (uint32_t)(j >> 1) & 1u, seq, WHERE_RING_FULL)) return false;
@@ -157,7 +165,7 @@ __device__ __forceinline__ int op_attention_tc(const Params& p, Ctrl* c, uint8_t
             tc_fence_after();
             const uint64_t kd = tc_smem_desc(smem_u32(ks + u * kTcTileBytes));
 #pragma unroll
-            for (int k16 = 0; k16 < D / 16; ++k16) tc_mma_i(tmem + kAtSCol + 128 * u, qd + 2 * k16, kd + 2 * k16, kAtIdescS, k16 ? 1u : 0u);
+            for (int k16 = 0; k16 < D / 16; ++k16) tc_mma_i(tmem + kAtSCol + 128 * u, qd + 2 * k16, kd + 2 * k16, idesc_s, k16 ? 1u : 0u);
             tc_commit(&a->k_empty[u]);
             tc_commit(&a->s_full[u]);
             return true;
@@ -172,7 +180,7 @@ __device__ __forceinline__ int op_attention_tc(const Params& p, Ctrl* c, uint8_t
 #pragma unroll
             for (int k16 = 0; k16 < 8; ++k16) {
                 const uint64_t pd = (k16 < 4 ? pd0 : pd1) + 2 * (k16 & 3);       // 16 keys further inside a 64-key tile: 32 bytes
-                tc_mma_i(tmem + kAtOCol, pd, vd + 128 * k16, kAtIdescO, (j > 0 || k16 > 0) ? 1u : 0u);   // 16 keys of V: 2048 bytes
+                tc_mma_i(tmem + kAtOCol, pd, vd + 128 * k16, idesc_o, (j > 0 || k16 > 0) ? 1u : 0u);   // 16 keys of V: 2048 bytes
             }
             tc_commit(&a->v_empty);
             tc_commit(&a->pv_done);
@@ -241,10 +249,11 @@ __device__ __forceinline__ int op_attention_tc(const Params& p, Ctrl* c, uint8_t
                     for (int u = 0; u < 2; ++u) {
                         const int key = key0 + ch * 32 + e + u;
                         const bool dead = (edge && (key >= kend || (causal && key > qrow))) || m_used == NEG_INF;
-                        pv[u] = dead ? 0.f : round_bf16(ex2(s[e + u] * sl2 - m_used));
+                        const float pe = dead ? 0.f : ex2(s[e + u] * sl2 - m_used);
+                        pv[u] = f16 ? round_f16(pe) : round_bf16(pe);
                         l += pv[u];
                     }
-                    pk[e >> 1] = pack2(pv[0], pv[1]);
+                    pk[e >> 1] = f16 ? pack2h(pv[0], pv[1]) : pack2(pv[0], pv[1]);
                 }
                 // 32 keys = 64 bytes = four 16-byte chunks of tile (ch >> 1), chunk index 4 (ch & 1) + q, swizzled with the row
                 uint8_t* tile = prow + (ch >> 1) * kTcTileBytes;

@@ -16,7 +16,8 @@ view's first element.  Field meaning per kind (the kernel side repeats it next t
   FINALIZE     ptr ws, out, bias, residual; i R, C, act, out dtype, residual dtype, rows per instruction
   ELTWISE      ptr a, b, c, out; i R, C, mode, fn, group, head_dim, dtypes of a, b, c, out
   NORM         ptr x, out, weight, bias; i R, C, rms, rows per instruction, x dtype, out dtype; f eps
-  ATTENTION    ptr q, k, v, out; i batch, seq_q, seq_k, heads, kv_heads, head_dim, causal, out dtype; f scale
+  ATTENTION    ptr q, k, v, out; i batch, seq_q, seq_k, heads, kv_heads, head_dim, causal, out dtype,
+               dtype of q / k / v (one for all three: bf16 or fp16); f scale
   ROPE_APPEND  ptr qkv, cos, sin, pos, q_out, k_cache, v_cache; i B, H, KVH, D, max_seq, qkv dtype
   DECODE_ATTN  ptr q, k_cache, v_cache, pos, out, k_new, v_new, cos, sin, part, count;
                i B, H, KVH, D, max_seq, splits, fused, q dtype, out dtype, zero inputs, kv heads per
@@ -72,7 +73,7 @@ def validate(op: Op):
             raise ValueError(f"{k}: column count {op.out.cols} must be a multiple of 8")
     if k == "Attention":
         for name, v in op.view_fields():
-            _want(v, (BF16, F16) if name == "out" else (BF16,), f"{k}.{name}")
+            _want(v, (BF16, F16), f"{k}.{name}")
 
 
 def gemv_units(op: Op) -> bool:
@@ -128,7 +129,9 @@ def fill(d, op: Op, addr) -> None:
     elif k == "Attention":
         d.kind = C.OP_ATTENTION
         ptrs = [op.q, op.k, op.v, op.out]
-        ints = [op.batch, op.seq_q, op.seq_k, op.heads, op.kv_heads, op.head_dim, int(op.causal), dt(op.out)]
+        ints = [op.batch, op.seq_q, op.seq_k, op.heads, op.kv_heads, op.head_dim, int(op.causal), dt(op.out), dt(op.q)]
+        if not dt(op.q) == dt(op.k) == dt(op.v):
+            raise TypeError(f"Attention: q, k and v must share one dtype, got {op.q.buf.dtype}, {op.k.buf.dtype}, {op.v.buf.dtype}")
         d.f[0] = float(op.scale)
     elif k == "RopeAppend":
         d.kind = C.OP_ROPE_APPEND

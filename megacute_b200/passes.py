@@ -280,8 +280,8 @@ def _accepts(op: Op, field: str, dtype) -> bool:
         return True
     if k == "Rope":
         return field in ("x", "out")
-    if k == "Attention":
-        return field == "out" and not f32
+    if k == "Attention":                              # (q, k and v must end up with one dtype: promote_temps checks the trio)
+        return not f32
     if k == "RopeAppend":
         return field == "qkv"
     if k == "Gather":
@@ -329,6 +329,19 @@ def promote_temps(g: Graph) -> Graph:
             if all(_accepts(op, name, dt) for op, name in users[b.id]):
                 swap[b.id] = Buffer(b.name, b.rows, b.cols, dt, "temp")
                 break
+    # an attention's q, k and v share one dtype (one tensor-core instruction takes one operand type): a trio of
+    # which not every member changes to fp16 stays as it was
+    changed = True
+    while changed:
+        changed = False
+        for op in g.ops:
+            if op.kind != "Attention":
+                continue
+            new = [swap[v.buf.id].dtype if v.buf.id in swap else v.buf.dtype for v in (op.q, op.k, op.v)]
+            if len(set(new)) > 1:
+                for v in (op.q, op.k, op.v):
+                    if swap.pop(v.buf.id, None) is not None:
+                        changed = True
     if not swap:
         return out
     move = lambda v: View(swap[v.buf.id], v.row0, v.col0, v.rows, v.cols) if v is not None and v.buf.id in swap else v
