@@ -48,8 +48,8 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
         for (int s = 0; s < 2 * kTcXStages; ++s) {
             mbar_init(&c->x_full[s], 1);
             mbar_init(&c->x_empty[s], 1);
-            c->x_use_load[s] = c->x_use_mma[s] = 0;
         }
+        c->x_par_load = c->x_par_mma = 0;
         for (int s = 0; s < kTcWSlots; ++s) {
             mbar_init(&c->w_full[s], 1);
             mbar_init(&c->w_empty[s], 1);

@@ -122,8 +122,8 @@ struct Ctrl {                     // lives in the last kCtrlBytes of shared memo
     uint32_t kv_cons;                        // ... the compute warps' position in the slots (slot | phase << 8)
     AttnBars attn;
     uint32_t tmem_base;               // ... tensor-memory address of the accumulator (written by tcgen05.alloc)
-    uint8_t x_use_load[2 * kTcXStages];   // ... how often each stage has been filled / consumed since the launch
-    uint8_t x_use_mma[2 * kTcXStages];    //     began (the parities of x_empty / x_full)
+    uint32_t x_par_load;                  // ... bit s: parity of the next completion of x_empty[s] / of x_full[s]
+    uint32_t x_par_mma;                   //     (an even number of completions so far: 0)
     uint8_t w_slot, w_phase;              // ... the MMA thread's position in the weight slots
     uint32_t acc_uses;                // ... instructions that have used acc_full (its parity)
     int abort;                    // set once a wait of this CTA gave up or saw the global abort
@@ -159,6 +159,19 @@ __device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, uint32_t 
     uint32_t ok;
     asm volatile(
         "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Non-blocking form.  Measured on B200 in a stand-alone loop: a try_wait costs its thread ~95 ns even when
+// the phase is already complete (it may suspend the thread), a test_wait ~1 ns; whatever the thread that
+// issues tcgen05.mma or bulk copies executes between two of them leaves the pipe it feeds idle, so every
+// wait below first asks with test_wait.
+__device__ __forceinline__ bool mbar_test_wait(unsigned long long* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{ .reg .pred p; mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
         : "=r"(ok)
         : "r"(smem_u32(bar)), "r"(parity)
         : "memory");
@@ -374,7 +387,7 @@ enum { WHERE_RING_FULL = 1, WHERE_RING_EMPTY = 2, WHERE_DEP = 3, WHERE_DRAIN = 4
 
 __device__ __forceinline__ bool wait_barrier(const Params& p, Ctrl* c, unsigned long long* bar, uint32_t parity,
                                              int seq, int where) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_test_wait(bar, parity)) return true;
     unsigned long long t0 = 0;
     for (uint32_t it = 1;; ++it) {
         if (mbar_try_wait(bar, parity)) return true;

@@ -101,42 +101,48 @@ __device__ __forceinline__ int op_gemm_tc_wide(const Params& p, Ctrl* c, uint8_t
         asm volatile("fence.proxy.async;" ::: "memory");
         unsigned long long keep;
         asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(keep));
-        // stage of k-tile kt: kt mod the number of stages; a barrier's parity follows from how often
-        // the stage has been used since the launch began (ops with 5 and with 10 stages may alternate)
+        // stage of k-tile kt: kt mod the number of stages; bit s of x_par_load is the parity of the next
+        // completion of x_empty[s] (ops with 5 and with 10 stages may alternate: the bit follows the barrier)
+        uint32_t xpar = c->x_par_load, s = 0;
         for (int kt = 0; kt < nk; ++kt) {
-            const int s = kt % xstages;
-            const uint32_t par = c->x_use_load[s]++ & 1u;
-            if (!wait_barrier(p, c, &c->x_empty[s], par ^ 1u, seq, WHERE_RING_EMPTY)) break;
+            if (!wait_barrier(p, c, &c->x_empty[s], ((xpar >> s) & 1u) ^ 1u, seq, WHERE_RING_EMPTY)) break;
             mbar_arrive_expect_tx(&c->x_full[s], (uint32_t)xbytes);
             tma_load_2d(xs + s * xbytes, tmaps, kbeg + kt * 64, m0, &c->x_full[s], keep);
+            xpar ^= 1u << s;
+            if (++s == xstages) s = 0;
         }
+        c->x_par_load = xpar;
     } else if (warp == 3 && lane == 0) {
-        // ---- MMAs: accumulator[128 activation rows][128 weight rows] += x tile . w tile^T ----
-        uint32_t n = 0, acc = 0;
+        // ---- MMAs: accumulator half h [128 activation rows][128 weight rows] += x tile . w tile h ^T ----
+        // (the loop's shape follows the narrow tile's; the halves' MMAs alternate: two independent accumulators
+        // run at 36 ns per instruction where a chain into one runs at 46)
         const uint32_t idesc = tc_idesc(op->i[9] == DT_F16);
-        bool ok = true;
-        int ws = c->w_slot;
-        uint32_t wph = c->w_phase;
-        for (int kt = 0; kt < nk && ok; ++kt, ++n) {
-            const int s = n % xstages;
-            ok = wait_barrier(p, c, &c->x_full[s], c->x_use_mma[s]++ & 1u, seq, WHERE_RING_FULL);
-            const uint64_t ad = tc_smem_desc(smem_u32(xs + s * xbytes));
+        const uint64_t ad0 = tc_smem_desc(smem_u32(xs)), bd0 = tc_smem_desc(smem_u32(ring));
+        const uint32_t xunits = (uint32_t)xbytes >> 4;
+        uint32_t acc = 0, s = 0, xpar = c->x_par_mma;
+        uint32_t ws = c->w_slot, wph = c->w_phase;
+        for (int kt = 0; kt < nk; ++kt) {
+            const uint32_t ws1 = ws + 1 == kTcWSlots ? 0u : ws + 1, wph1 = ws + 1 == kTcWSlots ? wph ^ 1u : wph;
+            if (!wait_barrier(p, c, &c->w_full[ws1], wph1, seq, WHERE_RING_FULL) || !wait_barrier(p, c, &c->w_full[ws], wph, seq, WHERE_RING_FULL) ||
+                !wait_barrier(p, c, &c->x_full[s], (xpar >> s) & 1u, seq, WHERE_RING_FULL))
+                break;
+            tc_fence_after();
+            const uint64_t ad = ad0 + s * xunits, b0 = bd0 + ws * (kTcTileBytes >> 4), b1 = bd0 + ws1 * (kTcTileBytes >> 4);
 #pragma unroll
-            for (int h = 0; h < halves; ++h) {                                 // one weight tile (slot) per accumulator half
-                if (!ok) break;
-                ok = wait_barrier(p, c, &c->w_full[ws], wph, seq, WHERE_RING_FULL);
-                if (!ok) break;
-                tc_fence_after();
-                const uint64_t bd = tc_smem_desc(smem_u32(ring + tc_wslot_off(ws)));
-#pragma unroll
-                for (int k16 = 0; k16 < 4; ++k16) tc_mma(tmem + 128 * h, ad + 2 * k16, bd + 2 * k16, idesc, (acc | (uint32_t)k16) ? 1u : 0u);
-                tc_commit(&c->w_empty[ws]);
-                if (++ws == kTcWSlots) { ws = 0; wph ^= 1u; }
+            for (int k16 = 0; k16 < 4; ++k16) {
+                tc_mma(tmem, ad + 2 * k16, b0 + 2 * k16, idesc, acc);
+                tc_mma(tmem + 128, ad + 2 * k16, b1 + 2 * k16, idesc, acc);
+                acc = 1;
             }
-            if (!ok) break;
-            acc = 1;
+            tc_commit(&c->w_empty[ws]);
+            tc_commit(&c->w_empty[ws1]);
             tc_commit(&c->x_empty[s]);
+            xpar ^= 1u << s;
+            if (++s == xstages) s = 0;
+            ws = ws1 + 1 == kTcWSlots ? 0u : ws1 + 1;
+            wph = ws1 + 1 == kTcWSlots ? wph1 ^ 1u : wph1;
         }
+        c->x_par_mma = xpar;
         c->w_slot = (uint8_t)ws;
         c->w_phase = (uint8_t)wph;
         tc_commit(&c->acc_full);

@@ -1,11 +1,14 @@
 """Kernel-time measurements of the tensor-bound benchmark configurations (the decode step has its own
 driver, ``bench.py``):
 
-    python -m megacute_b200.measure [mlp_block] [dit] [prefill]
+    python -m megacute_b200.measure [mlp_block] [dit] [prefill] [decode_b64_small] [prefill_small]
 
 * ``mlp_block``: RMS norm -> gate/up + swiglu -> down + residual, 256 rows, 2048 -> 2 x 5632 -> 2048
 * ``dit``: 28 DiT blocks, 32 images x 256 tokens, width 1024, 16 heads, MLP 4096
 * ``prefill``: Llama-3.2-1B shape, 4 sequences x 4096 tokens, 16 layers + lm_head
+* ``decode_b64_small``, ``prefill_small``: cut-down cases of the same kernels for profiler captures
+  (batch-64 decode at context 4096 with 4 layers and a 32768-row lm_head, 2.2 GB of cache; prefill
+  with 2 layers): a few GB on the device, a handful of launches
 
 Synthetic bf16 inputs and weights of those shapes; each configuration is compiled once, warmed up
 twice, then timed over a few launches with CUDA events on the launching stream.  Prints one line
@@ -66,11 +69,46 @@ def measure_prefill(dev):
     return ms, 3.63e13, prog
 
 
-CONFIGS = {"mlp_block": measure_mlp_block, "dit": measure_dit, "prefill": measure_prefill}
+def measure_prefill_small(dev):
+    c = W.LLAMA_1B
+    n = 2
+    g = llama_stack(4, 4096, c["E"], c["H"], c["KVH"], c["F"], n, vocab=c["vocab"])
+    prog = mc.compile(g)
+    w = W.llama_weights(c["E"], c["H"], c["KVH"], c["F"], n, c["vocab"], 0, dev)
+    x = torch.randn(4 * 4096, c["E"], device=dev, dtype=torch.bfloat16)
+    cos, sin = W.rope_tables(4096, c["E"] // c["H"], c["theta"], dev)
+    names = {b.name for b in prog.g.inputs + prog.g.params + prog.g.states}
+    args = {k: v for k, v in dict(x=x, cos=cos, sin=sin, **w).items() if k in names}
+    ms = _time(prog, args, 2)
+    T, E, F, D, KVH = 4 * 4096, c["E"], c["F"], c["E"] // c["H"], c["KVH"]
+    layer = 2 * T * E * (E + 2 * KVH * D) + 2 * T * E * E + 6 * T * E * F + 4 * 4 * c["H"] * D * 4096 * 4096 // 2
+    return ms, n * layer + 2 * 4 * E * c["vocab"], prog
+
+
+def measure_decode_b64_small(dev):
+    from megacute_b200.builders import llama_decode
+    c = W.LLAMA_1B
+    B, ctx, n, vocab = 64, 4096, 4, 32768
+    max_seq = ctx + 128
+    g = llama_decode(B, c["E"], c["H"], c["KVH"], c["F"], n, max_seq, vocab, c["eps"])
+    prog = mc.compile(g)
+    w = W.llama_weights(c["E"], c["H"], c["KVH"], c["F"], n, vocab, 0, dev)
+    st, _ = W.llama_decode_state(B, c["E"], c["H"], c["KVH"], n, max_seq, ctx, vocab, 1, dev)
+    cos, sin = W.rope_tables(max_seq, c["E"] // c["H"], c["theta"], dev)
+    ms = _time(prog, dict(cos=cos, sin=sin, **w, **st), 2)
+    kv_bytes = n * B * (ctx + 3) * 2 * c["KVH"] * (c["E"] // c["H"]) * 2          # the cache rows the third launch reads
+    print(f"decode_b64_small: cache bytes read per launch {kv_bytes}")
+    E, F, D, KVH = c["E"], c["F"], c["E"] // c["H"], c["KVH"]
+    return ms, 2 * B * (n * (E * (E + 2 * KVH * D) + E * E + 3 * E * F) + E * vocab), prog
+
+
+CONFIGS = {"mlp_block": measure_mlp_block, "dit": measure_dit, "prefill": measure_prefill,
+           "decode_b64_small": measure_decode_b64_small, "prefill_small": measure_prefill_small}
+DEFAULT = ["mlp_block", "dit", "prefill"]
 
 
 def main(argv):
-    names = argv or list(CONFIGS)
+    names = argv or DEFAULT
     unknown = [n for n in names if n not in CONFIGS]
     if unknown:
         raise SystemExit(f"unknown configuration(s) {unknown}; choose from {list(CONFIGS)}")
