@@ -49,13 +49,13 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
             mbar_init(&c->x_full[s], 1);
             mbar_init(&c->x_empty[s], 1);
         }
-        c->x_par_load = c->x_par_mma = 0;
+        c->x_par = 0;
         for (int s = 0; s < kTcWSlots; ++s) {
             mbar_init(&c->w_full[s], 1);
             mbar_init(&c->w_empty[s], 1);
         }
         c->w_slot = c->w_phase = 0;
-        mbar_init(&c->acc_full, 1);
+        mbar_init(&c->acc_full, kTcIssuers);
         for (int s = 0; s < kKvSlots; ++s) {
             mbar_init(&c->kv_full[s], 1);
             mbar_init(&c->kv_empty[s], kComputeWarps);

@@ -67,6 +67,7 @@ __host__ __device__ inline void kv_split_range(int n, int S, int s, int& k_begin
     k_end = k_begin + per < n ? k_begin + per : n;
 }
 constexpr int kTcWSlots = 8;
+constexpr int kTcIssuers = 2;                             // threads that issue tcgen05.mma, each into an accumulator of its own
 __host__ __device__ constexpr int tc_wslot_off(int slot) { return slot * kTcTileBytes; }
 static_assert(kTcWSlots * kTcTileBytes <= kRingBytes, "weight slots");
 
@@ -115,15 +116,15 @@ struct Ctrl {                     // lives in the last kCtrlBytes of shared memo
     unsigned long long x_empty[2 * kTcXStages];  // ... the MMAs that read it have completed
     unsigned long long w_full[kTcWSlots];    // ... a weight k-tile has landed in its slot of the ring
     unsigned long long w_empty[kTcWSlots];   // ... the MMAs that read it have completed
-    unsigned long long acc_full;      // ... every MMA of the instruction has completed: the accumulator can be read
+    unsigned long long acc_full;      // ... every MMA of the instruction has completed (one arrival per issuing thread)
     unsigned long long kv_full[kKvSlots];    // many-sequence decode attention: a K or V tile has landed in its slot
     unsigned long long kv_empty[kKvSlots];   // ... every compute warp has read it
     unsigned long long kv_go;                // ... (unfused form) the instruction's dependencies are met: the row appended in this launch may be read
     uint32_t kv_cons;                        // ... the compute warps' position in the slots (slot | phase << 8)
     AttnBars attn;
     uint32_t tmem_base;               // ... tensor-memory address of the accumulator (written by tcgen05.alloc)
-    uint32_t x_par_load;                  // ... bit s: parity of the next completion of x_empty[s] / of x_full[s]
-    uint32_t x_par_mma;                   //     (an even number of completions so far: 0)
+    uint32_t x_par;                       // ... bit s: parity of the next completion of x_full[s] and of x_empty[s] (between
+                                          //     instructions both have completed equally often); set at an instruction's end
     uint8_t w_slot, w_phase;              // ... the MMA thread's position in the weight slots
     uint32_t acc_uses;                // ... instructions that have used acc_full (its parity)
     int abort;                    // set once a wait of this CTA gave up or saw the global abort

@@ -75,6 +75,31 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, float* v) {
     for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
 }
 
+// the same columns of two accumulators, `second` columns apart, added (second == 0: one accumulator)
+__device__ __forceinline__ void tc_ld32_sum(uint32_t taddr, uint32_t second, float* v) {
+    tc_ld32(taddr, v);
+    if (second) {
+        float w[32];
+        tc_ld32(taddr + second, w);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] += w[j];
+    }
+}
+
+// State the next tile GEMM instruction of this CTA starts from, written by one thread behind the barrier that
+// ends the epilogue: the accumulator barrier's use count, the parities of the activation stages (stage s was
+// used once more per full round through the stages, and once more if s < nk mod stages) and the position in
+// the weight slots (wper slots per k-tile).
+__device__ __forceinline__ void tc_finish_state(Ctrl* c, uint32_t uses, uint32_t xpar0, uint32_t ws0, uint32_t wph0, int nk,
+                                                uint32_t xstages, int wper) {
+    c->acc_uses = uses + 1;
+    const uint32_t full = (uint32_t)nk / xstages, rem = (uint32_t)nk - full * xstages;
+    c->x_par = xpar0 ^ ((full & 1u) ? (1u << xstages) - 1u : 0u) ^ ((1u << rem) - 1u);
+    const uint32_t pos = ws0 + (uint32_t)(nk * wper);
+    c->w_slot = (uint8_t)(pos % kTcWSlots);
+    c->w_phase = (uint8_t)((wph0 ^ (pos / kTcWSlots)) & 1u);
+}
+
 // Epilogue, second half.  The accumulator tile has been copied to shared memory (fp32, row pitch
 // kTcStagePitch words); here a warp instruction covers one output row (or two half rows), four
 // consecutive columns per lane, so every global access of the epilogue -- bias, residual, store or
@@ -165,7 +190,9 @@ __device__ __forceinline__ int op_gemm_tc(const Params& p, Ctrl* c, uint8_t* rin
     const uint32_t apar = uses & 1u;
 
     phase_mark(p, c, 0);
-    if (warp == 2 && lane == 0) {
+    const uint32_t xpar0 = c->x_par;            // parities at the instruction's start (written behind the previous one's last barrier)
+    const uint32_t ws0 = c->w_slot, wph0 = c->w_phase;
+    if (warp == 2 && lane < 2) {
         // ---- activation tiles: {64 K-elements, 128 rows} at (kbeg + 64 kt, m0) ----
         // earlier instructions wrote the work area through the generic proxy (all of that is behind
         // the barrier that ended the dependency wait); the bulk copies below write it through the
@@ -173,50 +200,56 @@ __device__ __forceinline__ int op_gemm_tc(const Params& p, Ctrl* c, uint8_t* rin
         asm volatile("fence.proxy.async;" ::: "memory");
         unsigned long long keep;
         asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(keep));
-        // stage of k-tile kt: kt mod the number of stages; bit s of x_par_load is the parity of the next
-        // completion of x_empty[s] (ops with 5 and with 10 stages may alternate: the bit follows the barrier)
-        uint32_t xpar = c->x_par_load, s = 0;
-        for (int kt = 0; kt < nk; ++kt) {
-            if (!wait_barrier(p, c, &c->x_empty[s], ((xpar >> s) & 1u) ^ 1u, seq, WHERE_RING_EMPTY)) break;
+        // k-tile kt goes to stage kt mod the number of stages, each instruction starting at stage 0; the
+        // parity of a stage's barriers is the one it had at the instruction's start, flipped once per
+        // round through the stages (ops with 5 and with 10 stages may alternate: bit s follows barrier s)
+        // (two lanes, every other k-tile each: one lane's wait / expect / copy sequence takes as long as a k-tile's MMAs)
+        uint32_t s = lane, round = 1;
+        for (int kt = lane; kt < nk; kt += 2) {
+            if (!wait_barrier(p, c, &c->x_empty[s], ((xpar0 >> s) & 1u) ^ round, seq, WHERE_RING_EMPTY)) break;
             mbar_arrive_expect_tx(&c->x_full[s], (uint32_t)xbytes);
             tma_load_2d(xs + s * xbytes, tmaps, kbeg + kt * 64, m0, &c->x_full[s], keep);
-            xpar ^= 1u << s;
-            if (++s == xstages) s = 0;
+            s += 2;
+            if (s >= xstages) { s -= xstages; round ^= 1u; }
         }
-        c->x_par_load = xpar;
-    } else if (warp == 3 && lane == 0) {
+    } else if ((warp == 3 || warp == 1) && lane == 0) {
         // ---- MMAs: accumulator[128 activation rows][128 weight rows] += x tile . w tile^T ----
-        // Whatever this thread executes between two tcgen05.mma leaves the tensor pipe idle (measured with a
-        // stand-alone loop: a k-tile's four MMAs take 0.19 us; each mbarrier.try_wait added ~95 ns even on a
-        // completed phase, each tcgen05.commit ~34 ns, the integer divisions of `kt % stages` as much again).
-        // So: counters that step and wrap, descriptors by addition, waits that first ask with test_wait.
+        // Two issuing threads, each with an accumulator of its own (columns 128 i ..): this one takes the
+        // k-tiles kt = i, i + 2, ...; the epilogue adds the two.  What a thread executes between two
+        // tcgen05.mma leaves the tensor pipe idle -- the instruction does not return before the previous
+        // MMA is nearly done, so nothing is queued behind it.  Measured with a stand-alone loop: the four
+        // MMAs of a k-tile take 0.19 us, the loop around them (two waits, two commits, counters) as much
+        // again; a second thread's MMAs fill those gaps (0.43 -> 0.26 us per k-tile).  For the same reason
+        // the loop has counters that step and wrap instead of divisions, descriptors by addition, and
+        // waits that first ask with test_wait (a try_wait costs ~95 ns even on a completed phase).
+        const uint32_t i = warp == 3 ? 0u : 1u;
         const uint32_t idesc = tc_idesc(op->i[9] == DT_F16);
         const uint64_t ad0 = tc_smem_desc(smem_u32(xs)), bd0 = tc_smem_desc(smem_u32(ring));
         const uint32_t xunits = (uint32_t)xbytes >> 4;                        // descriptor addresses count 16 bytes
-        uint32_t acc = 0, s = 0, xpar = c->x_par_mma;
-        uint32_t ws = c->w_slot, wph = c->w_phase;
-        for (int kt = 0; kt < nk; ++kt) {
+        const uint32_t acc_at = tmem + 128 * i;
+        uint32_t acc = 0, s = i, round = 0;
+        uint32_t ws = ws0 + i, wph = wph0;
+        if (ws >= kTcWSlots) { ws -= kTcWSlots; wph ^= 1u; }
+        for (int kt = (int)i; kt < nk; kt += kTcIssuers) {
             if (!wait_barrier(p, c, &c->w_full[ws], wph, seq, WHERE_RING_FULL) ||
-                !wait_barrier(p, c, &c->x_full[s], (xpar >> s) & 1u, seq, WHERE_RING_FULL))
+                !wait_barrier(p, c, &c->x_full[s], ((xpar0 >> s) & 1u) ^ round, seq, WHERE_RING_FULL))
                 break;
             tc_fence_after();
             const uint64_t ad = ad0 + s * xunits, bd = bd0 + ws * (kTcTileBytes >> 4);
 #pragma unroll
             for (int k16 = 0; k16 < 4; ++k16) {
-                tc_mma(tmem, ad + 2 * k16, bd + 2 * k16, idesc, acc);
+                tc_mma(acc_at, ad + 2 * k16, bd + 2 * k16, idesc, acc);
                 acc = 1;
             }
             tc_commit(&c->x_empty[s]);
             tc_commit(&c->w_empty[ws]);
-            xpar ^= 1u << s;
-            if (++s == xstages) s = 0;
-            if (++ws == kTcWSlots) { ws = 0; wph ^= 1u; }
+            s += kTcIssuers;
+            if (s >= xstages) { s -= xstages; round ^= 1u; }
+            ws += kTcIssuers;
+            if (ws >= kTcWSlots) { ws -= kTcWSlots; wph ^= 1u; }
         }
-        c->x_par_mma = xpar;
-        c->w_slot = (uint8_t)ws;
-        c->w_phase = (uint8_t)wph;
-        tc_commit(&c->acc_full);
-        if (p.trace_cap > 0) c->t_phase[1] = (long long)globaltimer();     // last MMA issued
+        tc_commit(&c->acc_full);                                            // (arrives at once when this thread had no k-tile)
+        if (p.trace_cap > 0 && i == 0) c->t_phase[1] = (long long)globaltimer();     // last MMA issued
     }
     __syncwarp();
 
@@ -231,6 +264,7 @@ __device__ __forceinline__ int op_gemm_tc(const Params& p, Ctrl* c, uint8_t* rin
     const int qd = warp & 3, h = warp >> 2;
     float* stage = reinterpret_cast<float*>(work + kTcXOff);
     const int rows = min(128, M - m0);
+    const uint32_t two = nk > 1 ? 128u : 0u;                               // columns to the second issuing thread's accumulator, if it has a part
     if (ok && qd * 32 < rows) {
         const uint32_t tl = tmem + ((uint32_t)(qd * 32) << 16);
         float* srow = stage + (qd * 32 + lane) * kTcStagePitch;
@@ -238,8 +272,8 @@ __device__ __forceinline__ int op_gemm_tc(const Params& p, Ctrl* c, uint8_t* rin
         if (swi) {
             // gate columns 32 h .. +31 and the up columns 64 further of the same outputs
             float u[32];
-            tc_ld32(tl + h * 32, v);
-            tc_ld32(tl + 64 + h * 32, u);
+            tc_ld32_sum(tl + h * 32, two, v);
+            tc_ld32_sum(tl + 64 + h * 32, two, u);
 #pragma unroll
             for (int j = 0; j < 32; j += 4)
                 *reinterpret_cast<float4*>(srow + h * 32 + j) =
@@ -250,7 +284,7 @@ __device__ __forceinline__ int op_gemm_tc(const Params& p, Ctrl* c, uint8_t* rin
             for (int ch = 0; ch < 2; ++ch) {
                 const int tcol = h * 64 + ch * 32;
                 if (n0 + tcol >= N) break;
-                tc_ld32(tl + tcol, v);
+                tc_ld32_sum(tl + tcol, two, v);
 #pragma unroll
                 for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(srow + tcol + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
             }
@@ -264,7 +298,7 @@ __device__ __forceinline__ int op_gemm_tc(const Params& p, Ctrl* c, uint8_t* rin
     }
     tc_fence_before();
     const bool aborting = compute_sync_or(!ok || *(volatile int*)&c->abort);
-    if (t == 0) c->acc_uses = uses + 1;
+    if (t == 0) tc_finish_state(c, uses, xpar0, ws0, wph0, nk, xstages, 1);
     if (aborting) return -1;
     return 0;
 }

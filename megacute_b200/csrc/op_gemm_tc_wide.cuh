@@ -93,60 +93,58 @@ __device__ __forceinline__ int op_gemm_tc_wide(const Params& p, Ctrl* c, uint8_t
     const uint32_t apar = uses & 1u;
 
     phase_mark(p, c, 0);
-    if (warp == 2 && lane == 0) {
-        // ---- activation tiles: {64 K-elements, 128 rows} at (kbeg + 64 kt, m0) ----
-        // earlier instructions wrote the work area through the generic proxy (all of that is behind
-        // the barrier that ended the dependency wait); the bulk copies below write it through the
-        // asynchronous one, and read activations other SMs stored with plain stores
+    const uint32_t xpar0 = c->x_par;
+    const uint32_t ws0 = c->w_slot, wph0 = c->w_phase;
+    if (warp == 2 && lane < 2) {
+        // ---- activation tiles: {64 K-elements, 128 rows} at (kbeg + 64 kt, m0) ---- (as in the narrow tile)
         asm volatile("fence.proxy.async;" ::: "memory");
         unsigned long long keep;
         asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(keep));
-        // stage of k-tile kt: kt mod the number of stages; bit s of x_par_load is the parity of the next
-        // completion of x_empty[s] (ops with 5 and with 10 stages may alternate: the bit follows the barrier)
-        uint32_t xpar = c->x_par_load, s = 0;
-        for (int kt = 0; kt < nk; ++kt) {
-            if (!wait_barrier(p, c, &c->x_empty[s], ((xpar >> s) & 1u) ^ 1u, seq, WHERE_RING_EMPTY)) break;
+        // (two lanes, every other k-tile each: one lane's wait / expect / copy sequence takes as long as a k-tile's MMAs)
+        uint32_t s = lane, round = 1;
+        for (int kt = lane; kt < nk; kt += 2) {
+            if (!wait_barrier(p, c, &c->x_empty[s], ((xpar0 >> s) & 1u) ^ round, seq, WHERE_RING_EMPTY)) break;
             mbar_arrive_expect_tx(&c->x_full[s], (uint32_t)xbytes);
             tma_load_2d(xs + s * xbytes, tmaps, kbeg + kt * 64, m0, &c->x_full[s], keep);
-            xpar ^= 1u << s;
-            if (++s == xstages) s = 0;
+            s += 2;
+            if (s >= xstages) { s -= xstages; round ^= 1u; }
         }
-        c->x_par_load = xpar;
-    } else if (warp == 3 && lane == 0) {
+    } else if ((warp == 3 || warp == 1) && lane == 0) {
         // ---- MMAs: accumulator half h [128 activation rows][128 weight rows] += x tile . w tile h ^T ----
-        // (the loop's shape follows the narrow tile's; the halves' MMAs alternate: two independent accumulators
-        // run at 36 ns per instruction where a chain into one runs at 46)
+        // Two issuing threads as in the narrow tile, each with a 256-column accumulator (columns 256 i ..) and
+        // every other k-tile; the halves' MMAs alternate (two independent accumulators run at 36 ns per
+        // instruction where a chain into one runs at 46).
+        const uint32_t i = warp == 3 ? 0u : 1u;
         const uint32_t idesc = tc_idesc(op->i[9] == DT_F16);
         const uint64_t ad0 = tc_smem_desc(smem_u32(xs)), bd0 = tc_smem_desc(smem_u32(ring));
         const uint32_t xunits = (uint32_t)xbytes >> 4;
-        uint32_t acc = 0, s = 0, xpar = c->x_par_mma;
-        uint32_t ws = c->w_slot, wph = c->w_phase;
-        for (int kt = 0; kt < nk; ++kt) {
+        const uint32_t acc_at = tmem + 256 * i;
+        uint32_t acc = 0, s = i, round = 0;
+        uint32_t ws = ws0 + 2 * i, wph = wph0;
+        if (ws >= kTcWSlots) { ws -= kTcWSlots; wph ^= 1u; }
+        for (int kt = (int)i; kt < nk; kt += kTcIssuers) {
             const uint32_t ws1 = ws + 1 == kTcWSlots ? 0u : ws + 1, wph1 = ws + 1 == kTcWSlots ? wph ^ 1u : wph;
             if (!wait_barrier(p, c, &c->w_full[ws1], wph1, seq, WHERE_RING_FULL) || !wait_barrier(p, c, &c->w_full[ws], wph, seq, WHERE_RING_FULL) ||
-                !wait_barrier(p, c, &c->x_full[s], (xpar >> s) & 1u, seq, WHERE_RING_FULL))
+                !wait_barrier(p, c, &c->x_full[s], ((xpar0 >> s) & 1u) ^ round, seq, WHERE_RING_FULL))
                 break;
             tc_fence_after();
             const uint64_t ad = ad0 + s * xunits, b0 = bd0 + ws * (kTcTileBytes >> 4), b1 = bd0 + ws1 * (kTcTileBytes >> 4);
 #pragma unroll
             for (int k16 = 0; k16 < 4; ++k16) {
-                tc_mma(tmem, ad + 2 * k16, b0 + 2 * k16, idesc, acc);
-                tc_mma(tmem + 128, ad + 2 * k16, b1 + 2 * k16, idesc, acc);
+                tc_mma(acc_at, ad + 2 * k16, b0 + 2 * k16, idesc, acc);
+                tc_mma(acc_at + 128, ad + 2 * k16, b1 + 2 * k16, idesc, acc);
                 acc = 1;
             }
             tc_commit(&c->w_empty[ws]);
             tc_commit(&c->w_empty[ws1]);
             tc_commit(&c->x_empty[s]);
-            xpar ^= 1u << s;
-            if (++s == xstages) s = 0;
-            ws = ws1 + 1 == kTcWSlots ? 0u : ws1 + 1;
-            wph = ws1 + 1 == kTcWSlots ? wph1 ^ 1u : wph1;
+            s += kTcIssuers;
+            if (s >= xstages) { s -= xstages; round ^= 1u; }
+            ws += 2 * kTcIssuers;
+            if (ws >= kTcWSlots) { ws -= kTcWSlots; wph ^= 1u; }
         }
-        c->x_par_mma = xpar;
-        c->w_slot = (uint8_t)ws;
-        c->w_phase = (uint8_t)wph;
         tc_commit(&c->acc_full);
-        if (p.trace_cap > 0) c->t_phase[1] = (long long)globaltimer();     // last MMA issued
+        if (p.trace_cap > 0 && i == 0) c->t_phase[1] = (long long)globaltimer();     // last MMA issued
     }
     __syncwarp();
 
@@ -162,6 +160,7 @@ __device__ __forceinline__ int op_gemm_tc_wide(const Params& p, Ctrl* c, uint8_t
     const int qd = warp & 3, h = warp >> 2;
     float* stage = reinterpret_cast<float*>(work + kTcXOff);
     const int rows = min(128, M - m0);
+    const uint32_t two = nk > 1 ? 256u : 0u;                               // columns to the second issuing thread's accumulator, if it has a part
 #pragma unroll 1
     for (int hf = 0; hf < halves; ++hf) {
         const int nh = n0 + 128 * hf;                                        // first weight row of this half
@@ -173,8 +172,8 @@ __device__ __forceinline__ int op_gemm_tc_wide(const Params& p, Ctrl* c, uint8_t
             if (swi) {
                 // gate columns 32 h .. +31 and the up columns 64 further of the same outputs
                 float u[32];
-                tc_ld32(tl + h * 32, v);
-                tc_ld32(tl + 64 + h * 32, u);
+                tc_ld32_sum(tl + h * 32, two, v);
+                tc_ld32_sum(tl + 64 + h * 32, two, u);
 #pragma unroll
                 for (int j = 0; j < 32; j += 4)
                     *reinterpret_cast<float4*>(srow + h * 32 + j) =
@@ -185,7 +184,7 @@ __device__ __forceinline__ int op_gemm_tc_wide(const Params& p, Ctrl* c, uint8_t
                 for (int ch = 0; ch < 2; ++ch) {
                     const int tcol = h * 64 + ch * 32;
                     if (nh + tcol >= N) break;
-                    tc_ld32(tl + tcol, v);
+                    tc_ld32_sum(tl + tcol, two, v);
 #pragma unroll
                     for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(srow + tcol + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
                 }
@@ -201,7 +200,7 @@ __device__ __forceinline__ int op_gemm_tc_wide(const Params& p, Ctrl* c, uint8_t
     }
     tc_fence_before();
     const bool aborting = compute_sync_or(!ok || *(volatile int*)&c->abort);
-    if (t == 0) c->acc_uses = uses + 1;
+    if (t == 0) tc_finish_state(c, uses, xpar0, ws0, wph0, nk, xstages, halves);
     if (aborting) return -1;
     return 0;
 }

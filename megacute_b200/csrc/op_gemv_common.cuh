@@ -259,27 +259,34 @@ __device__ __forceinline__ void producer_loop(const Params& p, Ctrl* c, uint8_t*
             // copy when the weights are packed, one bulk tensor copy otherwise.  Eight single-tile
             // slots rather than two large ones: a slot is refilled the moment its tile has been
             // consumed, so ~100 KB stay in flight.  The instruction's tiles are issued from this tight
-            // single-lane loop: walking the outer loop (cursor, warp votes) once per tile cost ~950
-            // cycles per 16 KB -- the 0.5 us per k-tile that looked like a copy-path limit of the SM.
+            // loop by four lanes at once, lane l taking tiles l, l + 4, ...: one lane's wait / expect /
+            // copy sequence takes ~0.2 us (measured: 16 KB copies from one thread top out at 68 GB/s
+            // however many are in flight), more than the MMAs of a tile; walking the outer loop (cursor,
+            // warp votes) once per tile cost ~950 cycles.
             if (!enter(MODE_WTILES)) return;
-            int ok = 1;
-            if (lane == 0) {
+            constexpr int kLanes = 4;
+            bool mine = true;
+            if (lane < kLanes) {
                 const uint8_t* src = rc.wpack ? rc.wpack + rc.wtile0 * (long long)kTcTileBytes : nullptr;
                 const long long kstep = (long long)rc.wstride * kTcTileBytes;
+                uint32_t sl = (uint32_t)wslot + lane, ph = wphase;
+                if (sl >= kTcWSlots) { sl -= kTcWSlots; ph ^= 1u; }
 #pragma unroll 1
-                for (int kt = 0; kt < rc.nk; ++kt) {
-                    if (!wait_barrier(p, c, &c->w_empty[wslot], wphase ^ 1u, rc.seq, WHERE_RING_EMPTY)) { ok = 0; break; }
-                    uint8_t* dst = ring + tc_wslot_off(wslot);
-                    mbar_arrive_expect_tx(&c->w_full[wslot], (uint32_t)kTcTileBytes);
+                for (int kt = lane; kt < rc.nk; kt += kLanes) {
+                    if (!wait_barrier(p, c, &c->w_empty[sl], ph ^ 1u, rc.seq, WHERE_RING_EMPTY)) { mine = false; break; }
+                    uint8_t* dst = ring + tc_wslot_off(sl);
+                    mbar_arrive_expect_tx(&c->w_full[sl], (uint32_t)kTcTileBytes);
                     const int ktile = rc.wide == 2 ? kt >> 1 : kt, half = rc.wide == 2 ? kt & 1 : 0;
-                    if (src) bulk_g2s_hint(dst, src + ktile * kstep + half * kTcTileBytes, (uint32_t)kTcTileBytes, &c->w_full[wslot], stream_policy);
-                    else tma_load_2d(dst, rc.wmap, rc.kbeg + ktile * 64, rc.n0 + half * 128, &c->w_full[wslot], stream_policy);
-                    if (++wslot == kTcWSlots) { wslot = 0; wphase ^= 1u; }
+                    if (src) bulk_g2s_hint(dst, src + ktile * kstep + half * kTcTileBytes, (uint32_t)kTcTileBytes, &c->w_full[sl], stream_policy);
+                    else tma_load_2d(dst, rc.wmap, rc.kbeg + ktile * 64, rc.n0 + half * 128, &c->w_full[sl], stream_policy);
+                    sl += kLanes;
+                    if (sl >= kTcWSlots) { sl -= kTcWSlots; ph ^= 1u; }
                 }
             }
-            ok = __shfl_sync(0xffffffffu, ok, 0);
-            wslot = __shfl_sync(0xffffffffu, wslot, 0);
-            wphase = __shfl_sync(0xffffffffu, wphase, 0);
+            const bool ok = __all_sync(0xffffffffu, mine);
+            const uint32_t wpos = (uint32_t)wslot + (uint32_t)rc.nk;
+            wslot = (int)(wpos % kTcWSlots);
+            wphase ^= (wpos / kTcWSlots) & 1u;
             if (!ok) return;
             rc.idx += gridDim.x;
             rc.seek(p);
