@@ -68,8 +68,11 @@ typedef struct mk_caps {
 
 /* status words written by the device and returned by mk_program_status() */
 enum { MK_ST_CODE = 0, MK_ST_CTA, MK_ST_WARP, MK_ST_SEQ, MK_ST_WHERE, MK_ST_A, MK_ST_B, MK_ST_C, MK_ST_WORDS = 16 };
-/* MK_ST_CODE values (MK_DEV_BAD_INST: an instruction names no op, or an op kind the kernel does not know) */
-enum { MK_DEV_OK = 0, MK_DEV_TIMEOUT_COUNTER = 1, MK_DEV_TIMEOUT_BARRIER = 2, MK_DEV_BAD_INST = 3 };
+/* MK_ST_CODE values (MK_DEV_BAD_INST: an instruction names no op, or an op kind the kernel does not know;
+ * MK_DEV_CHECK: a library built with -DMK_CHECK found a shared-memory barrier in a state its protocol rules out --
+ * armed or released twice in one phase -- recorded which (MK_ST_A: barrier, MK_ST_B: parity) and ended the launch
+ * instead of going on) */
+enum { MK_DEV_OK = 0, MK_DEV_TIMEOUT_COUNTER = 1, MK_DEV_TIMEOUT_BARRIER = 2, MK_DEV_BAD_INST = 3, MK_DEV_CHECK = 4 };
 
 enum {
     MK_OK = 0,

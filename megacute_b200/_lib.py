@@ -14,7 +14,11 @@ import subprocess
 
 PKG = pathlib.Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
-LIB_PATH = pathlib.Path(os.environ.get("MEGACUTE_B200_LIB", PKG / "libmegacute_b200.so"))
+# MEGACUTE_B200_CHECK=1 selects the self-checking build (-DMK_CHECK: the kernel verifies the state of its shared-memory
+# barriers before it arms or releases them and reports instead of going on; csrc/mk_device.cuh check_phase), a library
+# file of its own beside the normal one.
+CHECK_BUILD = os.environ.get("MEGACUTE_B200_CHECK") == "1"
+LIB_PATH = pathlib.Path(os.environ.get("MEGACUTE_B200_LIB", PKG / ("libmegacute_b200_check.so" if CHECK_BUILD else "libmegacute_b200.so")))
 # Relocatable device code: each op body is its own translation unit so that ptxas allocates its
 # registers independently (csrc/ops.cuh says why).  -maxrregcount is the cap of a 10-warp CTA
 # (three warps share one SM sub-partition's 16 K registers); callees in other translation units do
@@ -75,18 +79,22 @@ def sources():
 
 
 def needs_build() -> bool:
-    if not LIB_PATH.exists():
-        return True
-    t = LIB_PATH.stat().st_mtime
-    return any(s.stat().st_mtime > t for s in sources())
+    return needs_build_of(LIB_PATH)
 
 
-def build(force: bool = False, verbose: bool = False) -> pathlib.Path:
-    """Compile the library with nvcc (cross-compiles without a GPU)."""
-    if not force and not needs_build():
-        return LIB_PATH
+def needs_build_of(path: pathlib.Path) -> bool:
+    return not path.exists() or any(s.stat().st_mtime > path.stat().st_mtime for s in sources())
+
+
+def build(force: bool = False, verbose: bool = False, check: bool | None = None) -> pathlib.Path:
+    """Compile the library with nvcc (cross-compiles without a GPU).  `check`: the -DMK_CHECK build (default: the
+    one this process loads)."""
+    check = CHECK_BUILD if check is None else check
+    out = LIB_PATH if check == CHECK_BUILD else PKG / ("libmegacute_b200_check.so" if check else "libmegacute_b200.so")
+    if not force and not needs_build_of(out):
+        return out
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
-    cmd = [nvcc, *NVCC_FLAGS, "-o", str(LIB_PATH), *[str(f) for f in sorted(CSRC.glob("*.cu"))]]
+    cmd = [nvcc, *NVCC_FLAGS, *(["-DMK_CHECK"] if check else []), "-o", str(out), *[str(f) for f in sorted(CSRC.glob("*.cu"))]]
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")
@@ -95,7 +103,7 @@ def build(force: bool = False, verbose: bool = False) -> pathlib.Path:
         raise RuntimeError(f"nvcc failed:\n{' '.join(cmd)}\n{r.stdout}\n{r.stderr}")
     if verbose:
         print(r.stderr)
-    return LIB_PATH
+    return out
 
 
 _lib = None

@@ -24,9 +24,10 @@ MIN_SPLIT_KTILES = 8            # k-tiles (of GEMM_BK) per K split
 MAX_K_SPLITS = 8
 INST_US, SM_GBPS = 2.0, 40.0    # split-K cost model: fixed us per instruction, GB/s one SM draws from HBM
 # 256-wide output tiles (one activation k-tile feeds two weight tiles) for ops with more than WIDE_MIN_ROWS rows:
-# us per 64-element k-tile of a 128 x 128 / 128 x 256 tile (an SM draws ~64 GB/s from L2), us per epilogue
+# us per 64-element k-tile of a 128 x 128 / 128 x 256 tile and us per epilogue, from the kernel's timeline (two issuing
+# threads; a 128 x 256 k-tile is one 32 KB weight slot and one N = 256 instruction per 16 K-elements)
 GEMM_BN_WIDE, WIDE_MIN_ROWS = 256, 128
-KTILE_US, KTILE_US_WIDE, EPILOGUE_US, EPILOGUE_US_WIDE = 0.5, 0.75, 3.0, 6.0
+KTILE_US, KTILE_US_WIDE, EPILOGUE_US, EPILOGUE_US_WIDE = 0.27, 0.42, 3.5, 7.0
 
 # ---- pointwise / norm / attention tiling
 EW_ROWS, EW_COLS = 32, 512

@@ -55,6 +55,11 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
             mbar_init(&c->w_empty[s], 1);
         }
         c->w_slot = c->w_phase = 0;
+        for (int s = 0; s < kTcWideSlots; ++s) {
+            mbar_init(&c->ww_full[s], 1);
+            mbar_init(&c->ww_empty[s], 1);
+        }
+        c->ww_slot = c->ww_phase = 0;
         mbar_init(&c->acc_full, kTcIssuers);
         for (int s = 0; s < kKvSlots; ++s) {
             mbar_init(&c->kv_full[s], 1);
@@ -185,6 +190,12 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
         for (int s = 0; s < kTcWSlots; ++s) {
             unsigned long long t0 = globaltimer();
             while (!(mbar_try_wait(&c->w_full[s], 0) || mbar_try_wait(&c->w_full[s], 1))) {
+                if (globaltimer() - t0 > 20000000ull) break;
+            }
+        }
+        for (int s = 0; s < kTcWideSlots; ++s) {
+            unsigned long long t0 = globaltimer();
+            while (!(mbar_try_wait(&c->ww_full[s], 0) || mbar_try_wait(&c->ww_full[s], 1))) {
                 if (globaltimer() - t0 > 20000000ull) break;
             }
         }

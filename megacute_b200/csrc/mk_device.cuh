@@ -43,12 +43,16 @@ constexpr int kSmemBytes = kRingBytes + kWorkBytes + kCtrlBytes;
 // the streaming linear's two stages -- before it fills the other kind); activation tiles use the
 // work area.
 constexpr int kTcTileBytes = 128 * 128;
-constexpr int kTcXStages = 5;
+constexpr int kTcXStages = 6;                             // activation stages of 128 rows ...
+constexpr int kTcXHalfStages = 10;                        // ... or of 64 rows (ops with at most 64): the MMA still reads 128 rows from a
+                                                          // stage's start, so half a tile of the work area must follow the last one
 constexpr int kTcXOff = 512;                              // first 1024-aligned byte of the work area
 constexpr int kTcCols = 512;                              // tensor-memory columns held by the CTA: a 128 x 256 accumulator (tile GEMM),
                                                           // or two S tiles and O (prefill attention)
 constexpr uint32_t kTcNoTmem = 0xffffffffu;               // Ctrl::tmem_base before the CTA's first allocation
-static_assert((kRingBytes + kTcXOff) % 1024 == 0 && kTcXOff + kTcXStages * kTcTileBytes + kTcTileBytes / 2 <= kWorkBytes, "activation tiles");
+static_assert((kRingBytes + kTcXOff) % 1024 == 0 && kTcXOff + kTcXStages * kTcTileBytes <= kWorkBytes &&
+                  kTcXOff + (kTcXHalfStages + 1) * (kTcTileBytes / 2) <= kWorkBytes && kTcXHalfStages <= 2 * kTcXStages,
+              "activation tiles");
 // many-sequence decode attention (op_decode_bulk.cuh): the ring's memory as seven slots, each one tile of
 // 16 whole cache rows (at most 1 KB each) stored as four 4-row groups 32 bytes apart beyond their size.
 // A third kind of slot beside the streaming linear's stages and the tile GEMM's weight slots: the
@@ -67,7 +71,13 @@ __host__ __device__ inline void kv_split_range(int n, int S, int s, int& k_begin
     k_end = k_begin + per < n ? k_begin + per : n;
 }
 constexpr int kTcWSlots = 8;
+constexpr int kTcWideSlots = 4;                           // ... of a 128 x 256 tile: the same memory as pairs of slots (256 rows x 64 K-elements, 32 KB)
 constexpr int kTcIssuers = 2;                             // threads that issue tcgen05.mma, each into an accumulator of its own
+// k-tiles alternate between the issuing threads, and a thread waits for a stage or slot by the parity of its barrier's
+// phase: that is only sound if the same thread consumed the stage's previous round (a thread waiting one round early
+// would find the parity of the round before that complete and read a tile still in flight -- with five activation
+// stages this happened, rarely, as a hang or a launch failure).  So every stage count is a multiple of the issuers.
+static_assert(kTcXStages % kTcIssuers == 0 && kTcXHalfStages % kTcIssuers == 0 && kTcWSlots % kTcIssuers == 0 && kTcWideSlots % kTcIssuers == 0, "stage counts vs issuing threads");
 __host__ __device__ constexpr int tc_wslot_off(int slot) { return slot * kTcTileBytes; }
 static_assert(kTcWSlots * kTcTileBytes <= kRingBytes, "weight slots");
 
@@ -116,6 +126,8 @@ struct Ctrl {                     // lives in the last kCtrlBytes of shared memo
     unsigned long long x_empty[2 * kTcXStages];  // ... the MMAs that read it have completed
     unsigned long long w_full[kTcWSlots];    // ... a weight k-tile has landed in its slot of the ring
     unsigned long long w_empty[kTcWSlots];   // ... the MMAs that read it have completed
+    unsigned long long ww_full[kTcWideSlots];    // ... the same for the 32 KB slots of 128 x 256 tiles (barriers and positions of their
+    unsigned long long ww_empty[kTcWideSlots];   //     own: the producer drains one kind before it fills the other)
     unsigned long long acc_full;      // ... every MMA of the instruction has completed (one arrival per issuing thread)
     unsigned long long kv_full[kKvSlots];    // many-sequence decode attention: a K or V tile has landed in its slot
     unsigned long long kv_empty[kKvSlots];   // ... every compute warp has read it
@@ -126,6 +138,7 @@ struct Ctrl {                     // lives in the last kCtrlBytes of shared memo
     uint32_t x_par;                       // ... bit s: parity of the next completion of x_full[s] and of x_empty[s] (between
                                           //     instructions both have completed equally often); set at an instruction's end
     uint8_t w_slot, w_phase;              // ... the MMA thread's position in the weight slots
+    uint8_t ww_slot, ww_phase;            // ... and in the 32 KB slots
     uint32_t acc_uses;                // ... instructions that have used acc_full (its parity)
     int abort;                    // set once a wait of this CTA gave up or saw the global abort
     int flag;                     // scratch broadcast word (split-KV last arriver)
@@ -384,10 +397,13 @@ __device__ __forceinline__ void report(const Params& p, Ctrl* c, int code, int s
     }
 }
 
-enum { WHERE_RING_FULL = 1, WHERE_RING_EMPTY = 2, WHERE_DEP = 3, WHERE_DRAIN = 4, WHERE_COMBINE = 5 };
+enum { WHERE_RING_FULL = 1, WHERE_RING_EMPTY = 2, WHERE_DEP = 3, WHERE_DRAIN = 4, WHERE_COMBINE = 5, WHERE_CHECK_ARM = 6, WHERE_CHECK_RELEASE = 7 };
 
+// `patience`: multiple of the time limit this wait allows.  A role that by design waits through everything the CTA does
+// before (the finisher warp, for the dependencies of a streaming linear far down the program) gives twice the limit, so
+// that when something earlier is stuck, the wait that is stuck reports first.
 __device__ __forceinline__ bool wait_barrier(const Params& p, Ctrl* c, unsigned long long* bar, uint32_t parity,
-                                             int seq, int where) {
+                                             int seq, int where, unsigned patience = 1) {
     if (mbar_test_wait(bar, parity)) return true;
     unsigned long long t0 = 0;
     for (uint32_t it = 1;; ++it) {
@@ -397,12 +413,27 @@ __device__ __forceinline__ bool wait_barrier(const Params& p, Ctrl* c, unsigned 
             if (ld_volatile(&p.status[MK_ST_CODE]) != 0) { c->abort = 1; return false; }
             unsigned long long now = globaltimer();
             if (t0 == 0) t0 = now;
-            else if (now - t0 > p.timeout_ns) {
+            else if (now - t0 > p.timeout_ns * patience) {
                 report(p, c, MK_DEV_TIMEOUT_BARRIER, seq, where, (int)(bar - c->full), (int)parity, 0);
                 return false;
             }
         }
     }
+}
+
+// -DMK_CHECK builds (libmegacute_b200_check.so; the package loads it when MEGACUTE_B200_CHECK=1): before a barrier of a
+// producer / consumer pair is armed (arrive.expect_tx) or released (tcgen05.commit, arrive) for the phase of parity
+// `parity`, the phase before it must be complete -- else the hand-off protocol has lost count (a slot filled twice, a
+// release for a fill that never came), which otherwise shows as a hang or as corrupted operands much later.  The
+// check records the barrier and ends the launch; without MK_CHECK it compiles to nothing.
+__device__ __forceinline__ bool check_phase(const Params& p, Ctrl* c, unsigned long long* bar, uint32_t parity, int seq, int where) {
+#ifdef MK_CHECK
+    if (!mbar_test_wait(bar, parity ^ 1u)) {
+        report(p, c, MK_DEV_CHECK, seq, where, (int)(bar - c->full), (int)parity, 0);
+        return false;
+    }
+#endif
+    return true;
 }
 
 __device__ __forceinline__ bool wait_counter(const Params& p, Ctrl* c, int counter, int target, int seq) {

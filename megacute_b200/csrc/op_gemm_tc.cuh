@@ -15,7 +15,7 @@
 //                boundaries: they depend on nothing in the launch, so the next instruction's first
 //                128 KB are already on their way while this one waits for its dependencies
 //   activations  one compute thread -> single-tile stages in the work area, after the instruction's
-//                dependencies are met: 5 stages of 128 rows, or 10 of 64 rows when the op has at most
+//                dependencies are met: 6 stages of 128 rows, or 10 of 64 rows when the op has at most
 //                64 (the MMA still reads 128 rows: the upper 64 accumulator rows are never looked at)
 //   MMA          one compute thread: 4 x tcgen05.mma (128 x 128 x 16) per k-tile; tcgen05.commit
 //                returns the activation stage and the ring slot when the MMAs that read them are done
@@ -34,10 +34,11 @@ namespace mk {
 // 0 = fp16, 1 = bf16, both K-major, N = 128 (bits 17-22 = N / 8), M = 128 (bits 24-28 = M / 16).  Both
 // operands have one type: bf16, or -- when the activations are runtime-private ones kept in fp16, see
 // passes.promote_temps -- fp16, with the packed weight copy converted to fp16 by the host library.
-__device__ __forceinline__ uint32_t tc_idesc(bool fp16) {
+__device__ __forceinline__ uint32_t tc_idesc_n(bool fp16, uint32_t n) {
     const uint32_t fmt = fp16 ? 0u : 1u;
-    return (1u << 4) | (fmt << 7) | (fmt << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | ((n >> 3) << 17) | ((128u >> 4) << 24);
 }
+__device__ __forceinline__ uint32_t tc_idesc(bool fp16) { return tc_idesc_n(fp16, 128); }
 
 // shared-memory matrix descriptor of a K-major tile with the 128-byte swizzle: start address,
 // leading byte offset 16 (unused by swizzled K-major layouts), 1024 bytes between 8-row groups,
@@ -89,15 +90,20 @@ __device__ __forceinline__ void tc_ld32_sum(uint32_t taddr, uint32_t second, flo
 // State the next tile GEMM instruction of this CTA starts from, written by one thread behind the barrier that
 // ends the epilogue: the accumulator barrier's use count, the parities of the activation stages (stage s was
 // used once more per full round through the stages, and once more if s < nk mod stages) and the position in
-// the weight slots (wper slots per k-tile).
+// the weight slots (of the kind the instruction used).
 __device__ __forceinline__ void tc_finish_state(Ctrl* c, uint32_t uses, uint32_t xpar0, uint32_t ws0, uint32_t wph0, int nk,
-                                                uint32_t xstages, int wper) {
+                                                uint32_t xstages, bool wide) {
     c->acc_uses = uses + 1;
     const uint32_t full = (uint32_t)nk / xstages, rem = (uint32_t)nk - full * xstages;
     c->x_par = xpar0 ^ ((full & 1u) ? (1u << xstages) - 1u : 0u) ^ ((1u << rem) - 1u);
-    const uint32_t pos = ws0 + (uint32_t)(nk * wper);
-    c->w_slot = (uint8_t)(pos % kTcWSlots);
-    c->w_phase = (uint8_t)((wph0 ^ (pos / kTcWSlots)) & 1u);
+    const uint32_t pos = ws0 + (uint32_t)nk;               // one weight slot per k-tile
+    if (wide) {
+        c->ww_slot = (uint8_t)(pos % kTcWideSlots);
+        c->ww_phase = (uint8_t)((wph0 ^ (pos / kTcWideSlots)) & 1u);
+    } else {
+        c->w_slot = (uint8_t)(pos % kTcWSlots);
+        c->w_phase = (uint8_t)((wph0 ^ (pos / kTcWSlots)) & 1u);
+    }
 }
 
 // Epilogue, second half.  The accumulator tile has been copied to shared memory (fp32, row pitch
@@ -108,7 +114,7 @@ __device__ __forceinline__ void tc_finish_state(Ctrl* c, uint32_t uses, uint32_t
 // apart, lines not in L2) the stores of one tile took 9.5 us to issue.
 constexpr int kTcStagePitch = 132;                          // words: conflict-free 16-byte writes by row, reads by column
 static_assert(kTcXOff + 128 * kTcStagePitch * 4 <= kWorkBytes, "epilogue staging tile");
-__device__ __forceinline__ void tc_write_rows(const mk_op_desc* op, const float* stage, int m0, int rows, int ncols, int col0,
+static __device__ __noinline__ void tc_write_rows(const mk_op_desc* op, const float* stage, int m0, int rows, int ncols, int col0,
                                               int n_out) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int act = op->i[3], odt = op->i[5], accum = op->i[6], rdt = op->i[7];
@@ -159,6 +165,84 @@ __device__ __forceinline__ void tc_write_rows(const mk_op_desc* op, const float*
     }
 }
 
+// Epilogue, second half, plain tiles (not a split-K partial, not swiglu): out = act(acc + bias) + residual, 128 columns.
+// Specialised at compile time on output type, residual kind and whether there is an activation: with those as
+// run-time switches inside the row loop the writer was instruction-bound (4.2 us per 128 x 128 tile against 1.3 us
+// for the same stores from a specialised loop, measured stand-alone).  All residual rows of a warp (16) are
+// requested before the first is used: two loads in flight per warp made a residual tile take 8.7 us, sixteen 2.3 us.
+template <int ODT, int RKIND, bool ACT>              // RKIND 0: no residual, 1: 16-bit (bf16 / fp16 by rdt), 2: fp32
+static __device__ __noinline__ void tc_store_rows_t(const mk_op_desc* op, const float* stage, int m0, int rows, int col0, int n_out) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int act = op->i[3], rdt = op->i[7];
+    const int c4 = lane * 4, col = col0 + c4;
+    if (col >= n_out) return;
+    float b4[4] = {0.f, 0.f, 0.f, 0.f};
+    if (const uint8_t* bias = reinterpret_cast<const uint8_t*>(op->ptr[3])) {
+        const uint2 w = __ldg(reinterpret_cast<const uint2*>(bias + (long long)col * 2));
+        b4[0] = bf16_lo(w.x); b4[1] = bf16_hi(w.x); b4[2] = bf16_lo(w.y); b4[3] = bf16_hi(w.y);
+    }
+    constexpr int kRows = 128 / kComputeWarps;          // rows of the tile per warp
+    const long long ldo = op->ld[2], ldr = op->ld[4];
+    uint8_t* O = reinterpret_cast<uint8_t*>(op->ptr[2]) + ((long long)m0 * ldo + col) * (ODT == DT_F32 ? 4 : 2);
+    const uint8_t* R = reinterpret_cast<const uint8_t*>(op->ptr[4]) + ((long long)m0 * ldr + col) * (RKIND == 2 ? 4 : 2);
+    uint2 r16[RKIND == 1 ? kRows : 1];
+    float4 r32[RKIND == 2 ? kRows : 1];
+    if (RKIND == 1) {
+#pragma unroll
+        for (int j = 0; j < kRows; ++j) {
+            const int row = warp + j * kComputeWarps;
+            r16[j] = row < rows ? __ldcg(reinterpret_cast<const uint2*>(R + row * ldr * 2)) : make_uint2(0u, 0u);
+        }
+    }
+    if (RKIND == 2) {
+#pragma unroll
+        for (int j = 0; j < kRows; ++j) {
+            const int row = warp + j * kComputeWarps;
+            r32[j] = row < rows ? __ldcg(reinterpret_cast<const float4*>(R + row * ldr * 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < kRows; ++j) {
+        const int row = warp + j * kComputeWarps;
+        if (row >= rows) break;
+        const float4 q = *reinterpret_cast<const float4*>(stage + row * kTcStagePitch + c4);
+        float f[4] = {q.x + b4[0], q.y + b4[1], q.z + b4[2], q.w + b4[3]};
+        if (ACT) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) f[e] = apply_act(act, f[e]);
+        }
+        if (RKIND == 1) {
+            if (rdt == DT_F16) {
+                const float2 lo = unpack2h(r16[j].x), hi = unpack2h(r16[j].y);
+                f[0] += lo.x; f[1] += lo.y; f[2] += hi.x; f[3] += hi.y;
+            } else {
+                f[0] += bf16_lo(r16[j].x); f[1] += bf16_hi(r16[j].x); f[2] += bf16_lo(r16[j].y); f[3] += bf16_hi(r16[j].y);
+            }
+        }
+        if (RKIND == 2) { f[0] += r32[j].x; f[1] += r32[j].y; f[2] += r32[j].z; f[3] += r32[j].w; }
+        if (ODT == DT_F32) *reinterpret_cast<float4*>(O + row * ldo * 4) = make_float4(f[0], f[1], f[2], f[3]);
+        else if (ODT == DT_F16) *reinterpret_cast<uint2*>(O + row * ldo * 2) = make_uint2(pack2h(f[0], f[1]), pack2h(f[2], f[3]));
+        else *reinterpret_cast<uint2*>(O + row * ldo * 2) = make_uint2(pack2(f[0], f[1]), pack2(f[2], f[3]));
+    }
+}
+template <int ODT>
+__device__ __forceinline__ void tc_store_rows_o(const mk_op_desc* op, const float* stage, int m0, int rows, int col0, int n_out) {
+    const int rk = !op->ptr[4] ? 0 : op->i[7] == DT_F32 ? 2 : 1;
+    if (op->i[3] != ACT_NONE) {                       // activations are rare in front of a residual: one instance takes every residual kind
+        if (rk == 0) tc_store_rows_t<ODT, 0, true>(op, stage, m0, rows, col0, n_out);
+        else if (rk == 1) tc_store_rows_t<ODT, 1, true>(op, stage, m0, rows, col0, n_out);
+        else tc_store_rows_t<ODT, 2, true>(op, stage, m0, rows, col0, n_out);
+    } else if (rk == 0) tc_store_rows_t<ODT, 0, false>(op, stage, m0, rows, col0, n_out);
+    else if (rk == 1) tc_store_rows_t<ODT, 1, false>(op, stage, m0, rows, col0, n_out);
+    else tc_store_rows_t<ODT, 2, false>(op, stage, m0, rows, col0, n_out);
+}
+__device__ __forceinline__ void tc_store_rows(const mk_op_desc* op, const float* stage, int m0, int rows, int col0, int n_out) {
+    const int odt = op->i[5];
+    if (odt == DT_F32) tc_store_rows_o<DT_F32>(op, stage, m0, rows, col0, n_out);
+    else if (odt == DT_F16) tc_store_rows_o<DT_F16>(op, stage, m0, rows, col0, n_out);
+    else tc_store_rows_o<DT_BF16>(op, stage, m0, rows, col0, n_out);
+}
+
 // All compute threads call this after the instruction's dependencies are met.  Returns 0, or -1
 // when the CTA is aborting.
 __device__ __forceinline__ int op_gemm_tc(const Params& p, Ctrl* c, uint8_t* ring, uint8_t* work, const mk_op_desc* op, int a0,
@@ -172,7 +256,7 @@ __device__ __forceinline__ int op_gemm_tc(const Params& p, Ctrl* c, uint8_t* rin
     uint8_t* xs = work + kTcXOff;
     // activation stages: whole 128-row tiles, or twice as many 64-row half tiles
     const int xbytes = M <= 64 ? kTcTileBytes / 2 : kTcTileBytes;
-    const uint32_t xstages = M <= 64 ? 2 * kTcXStages : kTcXStages;
+    const uint32_t xstages = M <= 64 ? kTcXHalfStages : kTcXStages;
 
     // Tensor memory is allocated by the CTA's first tile GEMM instruction and kept until the kernel
     // ends (the kernel frees it on every path); the permit to allocate is never relinquished.
@@ -202,11 +286,12 @@ __device__ __forceinline__ int op_gemm_tc(const Params& p, Ctrl* c, uint8_t* rin
         asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(keep));
         // k-tile kt goes to stage kt mod the number of stages, each instruction starting at stage 0; the
         // parity of a stage's barriers is the one it had at the instruction's start, flipped once per
-        // round through the stages (ops with 5 and with 10 stages may alternate: bit s follows barrier s)
+        // round through the stages (ops with 6 and with 10 stages may alternate: bit s follows barrier s)
         // (two lanes, every other k-tile each: one lane's wait / expect / copy sequence takes as long as a k-tile's MMAs)
         uint32_t s = lane, round = 1;
         for (int kt = lane; kt < nk; kt += 2) {
             if (!wait_barrier(p, c, &c->x_empty[s], ((xpar0 >> s) & 1u) ^ round, seq, WHERE_RING_EMPTY)) break;
+            if (!check_phase(p, c, &c->x_full[s], ((xpar0 >> s) & 1u) ^ round ^ 1u, seq, WHERE_CHECK_ARM)) break;
             mbar_arrive_expect_tx(&c->x_full[s], (uint32_t)xbytes);
             tma_load_2d(xs + s * xbytes, tmaps, kbeg + kt * 64, m0, &c->x_full[s], keep);
             s += 2;
@@ -241,6 +326,9 @@ __device__ __forceinline__ int op_gemm_tc(const Params& p, Ctrl* c, uint8_t* rin
                 tc_mma(acc_at, ad + 2 * k16, bd + 2 * k16, idesc, acc);
                 acc = 1;
             }
+            if (!check_phase(p, c, &c->x_empty[s], ((xpar0 >> s) & 1u) ^ round, seq, WHERE_CHECK_RELEASE) ||
+                !check_phase(p, c, &c->w_empty[ws], wph, seq, WHERE_CHECK_RELEASE))
+                break;
             tc_commit(&c->x_empty[s]);
             tc_commit(&c->w_empty[ws]);
             s += kTcIssuers;
@@ -294,11 +382,12 @@ __device__ __forceinline__ int op_gemm_tc(const Params& p, Ctrl* c, uint8_t* rin
     compute_sync();
     if (ok) {
         if (swi) tc_write_rows(op, stage, m0, rows, 64, a1 * 64, N / 2);
-        else tc_write_rows(op, stage, m0, rows, 128, n0, N);
+        else if (op->i[6]) tc_write_rows(op, stage, m0, rows, 128, n0, N);              // split-K partial: reduce-add
+        else tc_store_rows(op, stage, m0, rows, n0, N);
     }
     tc_fence_before();
     const bool aborting = compute_sync_or(!ok || *(volatile int*)&c->abort);
-    if (t == 0) tc_finish_state(c, uses, xpar0, ws0, wph0, nk, xstages, 1);
+    if (t == 0) tc_finish_state(c, uses, xpar0, ws0, wph0, nk, xstages, false);
     if (aborting) return -1;
     return 0;
 }

@@ -11,58 +11,6 @@
 
 namespace mk {
 
-// tc_write_rows of the narrow tile with one difference: the residual rows of a batch of eight output rows are all
-// requested before the first is used.  With a 16384-row activation the residual comes from HBM; two loads in
-// flight per warp made the residual epilogue of a 128 x 128 half take 14 us against 6.5 us without residual.
-__device__ __forceinline__ void tc_write_rows_batched(const mk_op_desc* op, const float* stage, int m0, int rows, int col0, int n_out) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int act = op->i[3], odt = op->i[5], rdt = op->i[7];
-    uint8_t* O = reinterpret_cast<uint8_t*>(op->ptr[2]);
-    const uint8_t* bias = reinterpret_cast<const uint8_t*>(op->ptr[3]);
-    const uint8_t* R = reinterpret_cast<const uint8_t*>(op->ptr[4]);
-    const int c4 = lane * 4, col = col0 + c4;
-    if (col >= n_out) return;
-    float b4[4] = {0.f, 0.f, 0.f, 0.f};
-    if (bias) {
-        const uint2 w = __ldg(reinterpret_cast<const uint2*>(bias + (long long)col * 2));
-        b4[0] = bf16_lo(w.x); b4[1] = bf16_hi(w.x); b4[2] = bf16_lo(w.y); b4[3] = bf16_hi(w.y);
-    }
-#pragma unroll 1
-    for (int base = warp; base < rows; base += 8 * kComputeWarps) {
-        float4 res[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const int row = base + j * kComputeWarps;
-            res[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (R && row < rows) {
-                const long long er = (long long)(m0 + row) * op->ld[4] + col;
-                if (rdt == DT_F32) {
-                    res[j] = __ldcg(reinterpret_cast<const float4*>(R + er * 4));
-                } else {
-                    const uint2 w = __ldcg(reinterpret_cast<const uint2*>(R + er * 2));
-                    if (rdt == DT_F16) {
-                        const float2 lo = unpack2h(w.x), hi = unpack2h(w.y);
-                        res[j] = make_float4(lo.x, lo.y, hi.x, hi.y);
-                    } else {
-                        res[j] = make_float4(bf16_lo(w.x), bf16_hi(w.x), bf16_lo(w.y), bf16_hi(w.y));
-                    }
-                }
-            }
-        }
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const int row = base + j * kComputeWarps;
-            if (row >= rows) break;
-            const float4 q = *reinterpret_cast<const float4*>(stage + row * kTcStagePitch + c4);
-            const float f0 = apply_act(act, q.x + b4[0]) + res[j].x, f1 = apply_act(act, q.y + b4[1]) + res[j].y;
-            const float f2 = apply_act(act, q.z + b4[2]) + res[j].z, f3 = apply_act(act, q.w + b4[3]) + res[j].w;
-            const long long eo = (long long)(m0 + row) * op->ld[2] + col;
-            if (odt == DT_F32) *reinterpret_cast<float4*>(O + eo * 4) = make_float4(f0, f1, f2, f3);
-            else *reinterpret_cast<uint2*>(O + eo * 2) = make_uint2(pack2t(odt, f0, f1), pack2t(odt, f2, f3));
-        }
-    }
-}
-
 __device__ __forceinline__ int op_gemm_tc_wide(const Params& p, Ctrl* c, uint8_t* ring, uint8_t* work, const mk_op_desc* op, int a0,
                                           int a1, int a2, int seq) {
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
@@ -75,7 +23,7 @@ __device__ __forceinline__ int op_gemm_tc_wide(const Params& p, Ctrl* c, uint8_t
     uint8_t* xs = work + kTcXOff;
     // activation stages: whole 128-row tiles, or twice as many 64-row half tiles
     const int xbytes = M <= 64 ? kTcTileBytes / 2 : kTcTileBytes;
-    const uint32_t xstages = M <= 64 ? 2 * kTcXStages : kTcXStages;
+    const uint32_t xstages = M <= 64 ? kTcXHalfStages : kTcXStages;
 
     // Tensor memory is allocated by the CTA's first tile GEMM instruction and kept until the kernel
     // ends (the kernel frees it on every path); the permit to allocate is never relinquished.
@@ -94,7 +42,7 @@ __device__ __forceinline__ int op_gemm_tc_wide(const Params& p, Ctrl* c, uint8_t
 
     phase_mark(p, c, 0);
     const uint32_t xpar0 = c->x_par;
-    const uint32_t ws0 = c->w_slot, wph0 = c->w_phase;
+    const uint32_t ws0 = c->ww_slot, wph0 = c->ww_phase;
     if (warp == 2 && lane < 2) {
         // ---- activation tiles: {64 K-elements, 128 rows} at (kbeg + 64 kt, m0) ---- (as in the narrow tile)
         asm volatile("fence.proxy.async;" ::: "memory");
@@ -104,44 +52,45 @@ __device__ __forceinline__ int op_gemm_tc_wide(const Params& p, Ctrl* c, uint8_t
         uint32_t s = lane, round = 1;
         for (int kt = lane; kt < nk; kt += 2) {
             if (!wait_barrier(p, c, &c->x_empty[s], ((xpar0 >> s) & 1u) ^ round, seq, WHERE_RING_EMPTY)) break;
+            if (!check_phase(p, c, &c->x_full[s], ((xpar0 >> s) & 1u) ^ round ^ 1u, seq, WHERE_CHECK_ARM)) break;
             mbar_arrive_expect_tx(&c->x_full[s], (uint32_t)xbytes);
             tma_load_2d(xs + s * xbytes, tmaps, kbeg + kt * 64, m0, &c->x_full[s], keep);
             s += 2;
             if (s >= xstages) { s -= xstages; round ^= 1u; }
         }
     } else if ((warp == 3 || warp == 1) && lane == 0) {
-        // ---- MMAs: accumulator half h [128 activation rows][128 weight rows] += x tile . w tile h ^T ----
-        // Two issuing threads as in the narrow tile, each with a 256-column accumulator (columns 256 i ..) and
-        // every other k-tile; the halves' MMAs alternate (two independent accumulators run at 36 ns per
-        // instruction where a chain into one runs at 46).
+        // ---- MMAs: accumulator[128 activation rows][256 weight rows] += x tile . w slot^T ----
+        // Two issuing threads as in the narrow tile, each with a 256-column accumulator (columns 256 i ..) and every
+        // other k-tile.  A k-tile is one activation stage and one 32 KB weight slot (the producer warp puts both weight
+        // tiles of the k-tile there, one barrier): one N = 256 instruction per 16 K-elements.
         const uint32_t i = warp == 3 ? 0u : 1u;
-        const uint32_t idesc = tc_idesc(op->i[9] == DT_F16);
+        const uint32_t idesc = tc_idesc_n(op->i[9] == DT_F16, 256);
         const uint64_t ad0 = tc_smem_desc(smem_u32(xs)), bd0 = tc_smem_desc(smem_u32(ring));
         const uint32_t xunits = (uint32_t)xbytes >> 4;
         const uint32_t acc_at = tmem + 256 * i;
         uint32_t acc = 0, s = i, round = 0;
-        uint32_t ws = ws0 + 2 * i, wph = wph0;
-        if (ws >= kTcWSlots) { ws -= kTcWSlots; wph ^= 1u; }
+        uint32_t ws = ws0 + i, wph = wph0;
+        if (ws >= kTcWideSlots) { ws -= kTcWideSlots; wph ^= 1u; }
         for (int kt = (int)i; kt < nk; kt += kTcIssuers) {
-            const uint32_t ws1 = ws + 1 == kTcWSlots ? 0u : ws + 1, wph1 = ws + 1 == kTcWSlots ? wph ^ 1u : wph;
-            if (!wait_barrier(p, c, &c->w_full[ws1], wph1, seq, WHERE_RING_FULL) || !wait_barrier(p, c, &c->w_full[ws], wph, seq, WHERE_RING_FULL) ||
+            if (!wait_barrier(p, c, &c->ww_full[ws], wph, seq, WHERE_RING_FULL) ||
                 !wait_barrier(p, c, &c->x_full[s], ((xpar0 >> s) & 1u) ^ round, seq, WHERE_RING_FULL))
                 break;
             tc_fence_after();
-            const uint64_t ad = ad0 + s * xunits, b0 = bd0 + ws * (kTcTileBytes >> 4), b1 = bd0 + ws1 * (kTcTileBytes >> 4);
+            const uint64_t ad = ad0 + s * xunits, bd = bd0 + ws * (2 * kTcTileBytes >> 4);
 #pragma unroll
             for (int k16 = 0; k16 < 4; ++k16) {
-                tc_mma(acc_at, ad + 2 * k16, b0 + 2 * k16, idesc, acc);
-                tc_mma(acc_at + 128, ad + 2 * k16, b1 + 2 * k16, idesc, acc);
+                tc_mma(acc_at, ad + 2 * k16, bd + 2 * k16, idesc, acc);
                 acc = 1;
             }
-            tc_commit(&c->w_empty[ws]);
-            tc_commit(&c->w_empty[ws1]);
+            if (!check_phase(p, c, &c->x_empty[s], ((xpar0 >> s) & 1u) ^ round, seq, WHERE_CHECK_RELEASE) ||
+                !check_phase(p, c, &c->ww_empty[ws], wph, seq, WHERE_CHECK_RELEASE))
+                break;
             tc_commit(&c->x_empty[s]);
+            tc_commit(&c->ww_empty[ws]);
             s += kTcIssuers;
             if (s >= xstages) { s -= xstages; round ^= 1u; }
-            ws += 2 * kTcIssuers;
-            if (ws >= kTcWSlots) { ws -= kTcWSlots; wph ^= 1u; }
+            ws += kTcIssuers;
+            if (ws >= kTcWideSlots) { ws -= kTcWideSlots; wph ^= 1u; }
         }
         tc_commit(&c->acc_full);
         if (p.trace_cap > 0 && i == 0) c->t_phase[1] = (long long)globaltimer();     // last MMA issued
@@ -195,12 +144,12 @@ __device__ __forceinline__ int op_gemm_tc_wide(const Params& p, Ctrl* c, uint8_t
         if (ok) {
             if (swi) tc_write_rows(op, stage, m0, rows, 64, nh / 2, N / 2);
             else if (op->i[6]) tc_write_rows(op, stage, m0, rows, 128, nh, N);          // split-K partial: reduce-add
-            else tc_write_rows_batched(op, stage, m0, rows, nh, N);
+            else tc_store_rows(op, stage, m0, rows, nh, N);
         }
     }
     tc_fence_before();
     const bool aborting = compute_sync_or(!ok || *(volatile int*)&c->abort);
-    if (t == 0) tc_finish_state(c, uses, xpar0, ws0, wph0, nk, xstages, halves);
+    if (t == 0) tc_finish_state(c, uses, xpar0, ws0, wph0, nk, xstages, true);
     if (aborting) return -1;
     return 0;
 }

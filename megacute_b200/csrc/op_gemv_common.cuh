@@ -66,6 +66,7 @@ struct StageCursor {
     // are still to be copied, through the tensor map `wmap`, from coordinates (kbeg + 64 kt, n0)
     bool gemm;
     int kt, nk, kbeg, n0, wide;
+    bool reread;                 // the weight tiles are read again and again, by the instructions of many row tiles (more than two)
     const void* wmap;
     // ... or, when the host library has packed the weights into tile images (ptr 10), the 16 KB
     // block `wtile0 + kt * wstride` of that array (k-tile-major: wstride = number of n tiles)
@@ -110,6 +111,7 @@ struct StageCursor {
                 // other through the same single-tile slots: `kt` counts weight tiles, `wide` of them per k-tile
                 const int kc = op->i[2] / op->i[4];
                 wide = op->i[10] == 256 ? 2 : 1;
+                reread = op->i[0] > 256;      // (two row tiles run side by side and share the line in flight: measured, evict-first is then the faster)
                 gemm = true; kv = false; seq = in.seq; kt = 0; nk = kc / 64 * wide; kbeg = in.a2 * kc; n0 = in.a1 * 128 * wide;
                 wmap = reinterpret_cast<const uint8_t*>(op->ptr[11]) + 128;
                 wpack = reinterpret_cast<const uint8_t*>(op->ptr[10]);
@@ -183,13 +185,18 @@ __device__ __forceinline__ void producer_loop(const Params& p, Ctrl* c, uint8_t*
     long long t_first = 0;
     int slot_first = 0;
     const unsigned long long stream_policy = l2_policy_evict_first();
+    // weights of a tile GEMM with several row tiles are read once per row tile: those stay in L2 with normal priority
+    unsigned long long keep_policy;
+    asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(keep_policy));
     // tile GEMM weight slots and decode attention KV slots: positions, and which kind of slot the
     // ring's memory currently serves
     int wslot = 0;
     uint32_t wphase = 0;
     int kvslot = 0;
     uint32_t kvphase = 0, kvgo = 0;
-    enum { MODE_STAGES = 0, MODE_WTILES = 1, MODE_KVTILES = 2 };
+    enum { MODE_STAGES = 0, MODE_WTILES = 1, MODE_KVTILES = 2, MODE_WWIDE = 3 };
+    int wwslot = 0;
+    uint32_t wwphase = 0;
     int mode = MODE_STAGES;
     // Wait until the compute side has released every slot of the kind used so far (slot s was last
     // filled in the current round if s < position, else in the previous one).
@@ -199,6 +206,9 @@ __device__ __forceinline__ void producer_loop(const Params& p, Ctrl* c, uint8_t*
             if (kind == MODE_WTILES) {
                 for (int s = 0; s < kTcWSlots && ok; ++s)
                     ok = wait_barrier(p, c, &c->w_empty[s], (wphase ^ (s < wslot ? 1u : 0u)) ^ 1u, rc.seq, WHERE_RING_EMPTY) ? 1 : 0;
+            } else if (kind == MODE_WWIDE) {
+                for (int s = 0; s < kTcWideSlots && ok; ++s)
+                    ok = wait_barrier(p, c, &c->ww_empty[s], (wwphase ^ (s < wwslot ? 1u : 0u)) ^ 1u, rc.seq, WHERE_RING_EMPTY) ? 1 : 0;
             } else if (kind == MODE_KVTILES) {
                 for (int s = 0; s < kKvSlots && ok; ++s)
                     ok = wait_barrier(p, c, &c->kv_empty[s], (kvphase ^ (s < kvslot ? 1u : 0u)) ^ 1u, rc.seq, WHERE_RING_EMPTY) ? 1 : 0;
@@ -254,6 +264,49 @@ __device__ __forceinline__ void producer_loop(const Params& p, Ctrl* c, uint8_t*
             rc.seek(p);
             continue;
         }
+        if (rc.gemm && rc.wide == 2) {
+            // 128 x 256 tile GEMM: the two weight tiles of a k-tile (256 rows x 64 K-elements, adjacent in the packed
+            // array) fill one 32 KB slot and complete one barrier, so that the issuing thread pays one wait, four
+            // N = 256 MMAs and one commit per k-tile and operand (measured stand-alone with two issuing threads:
+            // 0.28 us per k-tile against 0.40 with a barrier pair per 16 KB tile).
+            if (!enter(MODE_WWIDE)) return;
+            const int nkt = rc.nk >> 1;
+            // Two lanes, every other k-tile each.  Lanes run in lockstep, so a step waits for the slower lane's slot: with
+            // as many lanes as slots the four copies left in bursts, once the last slot of the previous burst had been
+            // consumed, and the consumer starved for a copy's latency per burst (0.57 us per k-tile; 0.48 before).
+            constexpr int kLanes = 2;
+            const unsigned long long wpol = rc.reread ? keep_policy : stream_policy;
+            bool mine = true;
+            if (lane < kLanes) {
+                const uint8_t* src = rc.wpack ? rc.wpack + rc.wtile0 * (long long)kTcTileBytes : nullptr;
+                const long long kstep = (long long)rc.wstride * kTcTileBytes;
+                uint32_t sl = (uint32_t)wwslot + lane, ph = wwphase;
+                if (sl >= kTcWideSlots) { sl -= kTcWideSlots; ph ^= 1u; }
+#pragma unroll 1
+                for (int kt = lane; kt < nkt; kt += kLanes) {
+                    if (!wait_barrier(p, c, &c->ww_empty[sl], ph ^ 1u, rc.seq, WHERE_RING_EMPTY)) { mine = false; break; }
+                    if (!check_phase(p, c, &c->ww_full[sl], ph, rc.seq, WHERE_CHECK_ARM)) { mine = false; break; }
+                    uint8_t* dst = ring + sl * (2 * kTcTileBytes);
+                    mbar_arrive_expect_tx(&c->ww_full[sl], 2u * kTcTileBytes);
+                    if (src) {
+                        bulk_g2s_hint(dst, src + kt * kstep, 2u * kTcTileBytes, &c->ww_full[sl], wpol);
+                    } else {
+                        tma_load_2d(dst, rc.wmap, rc.kbeg + kt * 64, rc.n0, &c->ww_full[sl], wpol);
+                        tma_load_2d(dst + kTcTileBytes, rc.wmap, rc.kbeg + kt * 64, rc.n0 + 128, &c->ww_full[sl], wpol);
+                    }
+                    sl += kLanes;
+                    if (sl >= kTcWideSlots) { sl -= kTcWideSlots; ph ^= 1u; }
+                }
+            }
+            const bool ok = __all_sync(0xffffffffu, mine);
+            const uint32_t wpos = (uint32_t)wwslot + (uint32_t)nkt;
+            wwslot = (int)(wpos % kTcWideSlots);
+            wwphase ^= (wpos / kTcWideSlots) & 1u;
+            if (!ok) return;
+            rc.idx += gridDim.x;
+            rc.seek(p);
+            continue;
+        }
         if (rc.gemm) {
             // tile GEMM: one weight k-tile (128 rows x 64 K-elements, 16 KB) per slot -- one plain bulk
             // copy when the weights are packed, one bulk tensor copy otherwise.  Eight single-tile
@@ -265,6 +318,7 @@ __device__ __forceinline__ void producer_loop(const Params& p, Ctrl* c, uint8_t*
             // warp votes) once per tile cost ~950 cycles.
             if (!enter(MODE_WTILES)) return;
             constexpr int kLanes = 4;
+            const unsigned long long wpol = rc.reread ? keep_policy : stream_policy;
             bool mine = true;
             if (lane < kLanes) {
                 const uint8_t* src = rc.wpack ? rc.wpack + rc.wtile0 * (long long)kTcTileBytes : nullptr;
@@ -275,10 +329,11 @@ __device__ __forceinline__ void producer_loop(const Params& p, Ctrl* c, uint8_t*
                 for (int kt = lane; kt < rc.nk; kt += kLanes) {
                     if (!wait_barrier(p, c, &c->w_empty[sl], ph ^ 1u, rc.seq, WHERE_RING_EMPTY)) { mine = false; break; }
                     uint8_t* dst = ring + tc_wslot_off(sl);
+                    if (!check_phase(p, c, &c->w_full[sl], ph, rc.seq, WHERE_CHECK_ARM)) { mine = false; break; }
                     mbar_arrive_expect_tx(&c->w_full[sl], (uint32_t)kTcTileBytes);
                     const int ktile = rc.wide == 2 ? kt >> 1 : kt, half = rc.wide == 2 ? kt & 1 : 0;
-                    if (src) bulk_g2s_hint(dst, src + ktile * kstep + half * kTcTileBytes, (uint32_t)kTcTileBytes, &c->w_full[sl], stream_policy);
-                    else tma_load_2d(dst, rc.wmap, rc.kbeg + ktile * 64, rc.n0 + half * 128, &c->w_full[sl], stream_policy);
+                    if (src) bulk_g2s_hint(dst, src + ktile * kstep + half * kTcTileBytes, (uint32_t)kTcTileBytes, &c->w_full[sl], wpol);
+                    else tma_load_2d(dst, rc.wmap, rc.kbeg + ktile * 64, rc.n0 + half * 128, &c->w_full[sl], wpol);
                     sl += kLanes;
                     if (sl >= kTcWSlots) { sl -= kTcWSlots; ph ^= 1u; }
                 }

@@ -253,7 +253,7 @@ __device__ __forceinline__ void gemv_finisher(const Params& p, Ctrl* c, uint8_t*
         const int arrive_to = lane < in.narrive ? __ldg(p.arrives + in.arrive_off + lane) : -1;
         // Operands of the epilogue may be results of earlier instructions: nothing is read before
         // the compute warps have seen the instruction's dependencies met.
-        bool ok = wait_barrier(p, c, &c->deps_met, (fullpar >> 4) & 1u, seq, WHERE_COMBINE);
+        bool ok = wait_barrier(p, c, &c->deps_met, (fullpar >> 4) & 1u, seq, WHERE_COMBINE, 2);
         fullpar ^= 16u;
         if (!ok) return;
 #pragma unroll 1

@@ -227,7 +227,7 @@ class Program:
         if rc == -4:
             code, cta, warp, seq, where, a, b, c = list(st)[:8]
             names = {1: "dependency counter wait timed out", 2: "shared-memory barrier wait timed out",
-                     3: "bad instruction"}
+                     3: "bad instruction", 4: "self-check: a shared-memory barrier is in a state its protocol rules out"}
             exc = _lib.MegakernelTimeout if code in (1, 2) else _lib.MegakernelError
             raise exc(f"megakernel: {names.get(code, code)} (cta {cta}, warp {warp}, inst {seq}, where {where}, "
                       f"a={a}, b={b}, c={c}); call prog.reset() before reusing the program")

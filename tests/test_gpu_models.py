@@ -482,3 +482,30 @@ def test_tile_linear_wide_tiles(cuda, monkeypatch, M, K, N, act, bias, res):
     assert lin and all(o.bn == 256 for o in lin) and prog.tcgen05_ops == len(lin)
     assert_close(outs, ref)
     assert np.array_equal(prog.counters(), prog.sched.counter_target * 2)
+
+
+def test_wide_tiles_many_per_cta_and_slot_kinds(cuda, monkeypatch):
+    """Several 128 x 256 tiles per CTA (the weight slots' positions and parities carry over from one instruction to the
+    next, and the producer warp fills the next instruction's first slots during this one's epilogue), followed by
+    linears that use the ring's memory differently: a narrow-tile one (16 KB slots) and a streaming one (64 KB stages),
+    and then wide tiles again -- every change of kind drains the slots of the previous one."""
+    monkeypatch.setenv("MEGACUTE_B200_WIDE_TILES", "1")
+    M, K = 8192, 512
+    g = mc.Graph()
+    x = g.input("x", (M, K))
+    x2 = g.input("x2", (4, K))
+    h = g.unary(x, "identity")
+    y1 = g.linear(h, g.param("w1", (1024, K)), act="gelu_tanh")              # wide: 64 x 4 tiles
+    y2 = g.linear(h, g.param("w2", (384, K)))                                 # narrow tiles: 384 is no multiple of 256
+    s1 = g.linear(x2, g.param("w3", (2048, K)))                               # streaming (4 rows)
+    y3 = g.linear(y1, g.param("w4", (512, 1024)), residual=g.input("r", (M, 512)))   # wide again: 64 x 2 tiles, K = 1024
+    g.output(y2)
+    g.output(s1)
+    g.output(y3)
+    t = {"x": rnd((M, K), 1.0, 1), "x2": rnd((4, K), 1.0, 2), "w1": rnd((1024, K), 0.04, 3), "w2": rnd((384, K), 0.04, 4),
+         "w3": rnd((2048, K), 0.04, 5), "w4": rnd((512, 1024), 0.03, 6), "r": rnd((M, 512), 1.0, 7)}
+    outs, ref, _, _, prog = run_both(g, t, cuda, steps=2)
+    lin = [o for o in prog.g.ops if o.kind in ("Linear", "LinearSplit")]
+    assert sorted(o.bn or 128 for o in lin) == [128, 128, 256, 256] and prog.tcgen05_ops == 3
+    assert_close(outs, ref)
+    assert np.array_equal(prog.counters(), prog.sched.counter_target * 2)
