@@ -60,6 +60,7 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
             mbar_init(&c->ww_empty[s], 1);
         }
         c->ww_slot = c->ww_phase = 0;
+        mbar_init(&c->attn_go, 1);
         mbar_init(&c->acc_full, kTcIssuers);
         for (int s = 0; s < kKvSlots; ++s) {
             mbar_init(&c->kv_full[s], 1);
@@ -591,12 +592,11 @@ int mk_program_set_ops(mk_program* p, const mk_op_desc* ops, int n_ops, void* st
             d.ptr[11] = 0;
             uint8_t* maps = h_tmaps + (size_t)k * kMapBytes;
             const long long B = d.i[0], Sq = d.i[1], Sk = d.i[2], H = d.i[3], KVH = d.i[4];
-            // Off unless MEGACUTE_B200_ATTN_TCGEN05=1: measured on 4 x 4096 causal tokens (32 heads, 8 kv heads) the
-            // tcgen05 body takes 4.4 ms against the mma.sync body's 2.1 ms -- its softmax runs on four warps, one
-            // per scheduler, as chains of dependent instructions (0.18 instructions per cycle), while the mma.sync
-            // body spreads the same arithmetic over eight warps.
+            // On unless MEGACUTE_B200_ATTN_TCGEN05=0: measured on 4 x 4096 causal tokens (32 heads, 8 kv heads, 16 layers)
+            // the tcgen05 body (softmax on all eight compute warps, tiles and MMAs fed by the producer warp) takes
+            // 14.5 ms of attention against the mma.sync body's 31 ms.
             const char* attn_tc = getenv("MEGACUTE_B200_ATTN_TCGEN05");
-            if (!attn_tc || attn_tc[0] != '1') continue;
+            if (attn_tc && attn_tc[0] == '0') continue;
             if (tc_off || d.i[5] != 64 || (d.ptr[3] & 15) || d.ld[3] % 8) continue;
             const bool h16 = d.i[8] == mk::DT_F16;
             if (encode_tile_map(maps, d.ptr[0], B * Sq, H * 64, d.ld[0], 128, false, h16) &&

@@ -134,6 +134,8 @@ struct Ctrl {                     // lives in the last kCtrlBytes of shared memo
     unsigned long long kv_go;                // ... (unfused form) the instruction's dependencies are met: the row appended in this launch may be read
     uint32_t kv_cons;                        // ... the compute warps' position in the slots (slot | phase << 8)
     AttnBars attn;
+    unsigned long long attn_go;              // tcgen05 prefill attention: the compute warps are at the instruction (dependencies met,
+                                             // barriers initialised); the feeding thread of the producer warp may start
     uint32_t tmem_base;               // ... tensor-memory address of the accumulator (written by tcgen05.alloc)
     uint32_t x_par;                       // ... bit s: parity of the next completion of x_full[s] and of x_empty[s] (between
                                           //     instructions both have completed equally often); set at an instruction's end

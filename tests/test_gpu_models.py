@@ -181,10 +181,9 @@ def test_mlp_block_config(cuda):
 ])
 @pytest.mark.parametrize("body", ["mma.sync", "tcgen05"])
 def test_prefill_attention(cuda, monkeypatch, B, Sq, Sk, H, KVH, D, causal, body):
-    if body == "tcgen05":
-        if D != 64:
-            pytest.skip("the tcgen05 body takes head_dim 64")
-        monkeypatch.setenv("MEGACUTE_B200_ATTN_TCGEN05", "1")
+    if body == "tcgen05" and D != 64:
+        pytest.skip("the tcgen05 body takes head_dim 64")
+    monkeypatch.setenv("MEGACUTE_B200_ATTN_TCGEN05", "1" if body == "tcgen05" else "0")     # (the default is the tcgen05 body)
     g = mc.Graph()
     q = g.input("q", (B * Sq, H * D))
     kv = g.input("kv", (B * Sk, 2 * KVH * D))          # k and v are column slices of one buffer
