@@ -69,7 +69,7 @@ def llama_stack(B: int, S: int, E: int, H: int, KVH: int, F: int, n: int, eps: f
 
 
 def llama_decode(B: int, E: int, H: int, KVH: int, F: int, n: int, max_seq: int, vocab: int | None = None,
-                 eps: float = 1e-6, fused_step: bool = False) -> Graph:
+                 eps: float = 1e-6, fused_step: bool = False, ragged: bool = False, window: int | None = None) -> Graph:
     """One decode step for B sequences.  States: x (B, E) embedded tokens, pos (1, 1) int32,
     k_cache / v_cache (n*B*max_seq, KVH*D) with layer i at rows [i*B*max_seq, ...) and sequence b of
     it at [b*max_seq, ...).  Output: (B, vocab) logits, or the hidden state without ``vocab``.
@@ -78,7 +78,11 @@ def llama_decode(B: int, E: int, H: int, KVH: int, F: int, n: int, max_seq: int,
     the state is ``ids`` (B, 1) int32 instead of x -- the launch gathers the embedding rows itself and
     overwrites ids with the greedy tokens, so a decode loop is one launch per step with nothing
     around it (the reference's step is index_select + copy_ + launch + argmax,
-    examples/llama/llama1b.py:103-105)."""
+    examples/llama/llama1b.py:103-105).
+
+    ``ragged``: pos is (B, 1), one position per sequence, so sequences of different lengths decode in
+    one batch; ``window``: sliding-window attention over each sequence's last ``window`` tokens.  (The
+    reference has neither: README.md:225-228.)"""
     D = E // H
     g = Graph()
     if fused_step:
@@ -89,7 +93,7 @@ def llama_decode(B: int, E: int, H: int, KVH: int, F: int, n: int, max_seq: int,
     else:
         x = g.state("x", (B, E))
     cos, sin = g.input("cos", (max_seq, D)), g.input("sin", (max_seq, D))
-    pos = g.state("pos", (1, 1), torch.int32)
+    pos = g.state("pos", (B if ragged else 1, 1), torch.int32)
     kc = g.state("k_cache", (n * B * max_seq, KVH * D))
     vc = g.state("v_cache", (n * B * max_seq, KVH * D))
     layer = _stacked(g, llama_param_shapes(E, H, KVH, F), n)
@@ -100,7 +104,7 @@ def llama_decode(B: int, E: int, H: int, KVH: int, F: int, n: int, max_seq: int,
         kci, vci = kc.rows_slice(i * R, R), vc.rows_slice(i * R, R)
         qkv = g.linear(g.rms_norm(x, p["attn_norm"], eps), p["wqkv"])
         q = g.rope_append(qkv, cos, sin, pos, kci, vci, heads=H, kv_heads=KVH, head_dim=D, max_seq=max_seq)
-        a = g.decode_attention(q, kci, vci, pos, heads=H, kv_heads=KVH, head_dim=D, max_seq=max_seq)
+        a = g.decode_attention(q, kci, vci, pos, heads=H, kv_heads=KVH, head_dim=D, max_seq=max_seq, window=window)
         x = g.linear(a, p["wo"], residual=x)
         x = g.linear(g.linear(g.rms_norm(x, p["mlp_norm"], eps), p["wgu"], act="swiglu"), p["wd"], residual=x)
     g.layer = None

@@ -18,7 +18,7 @@
 // the op rotates q and k at pos, the last split also attends the new token from registers and
 // appends k, v to cache row b * max_seq + pos (reference semantics: graph.py:412-418).
 //
-// ptr 0 q, 1 k_cache, 2 v_cache, 3 pos, 4 out, 5 k_new, 6 v_new, 7 cos, 8 sin, 9 part, 10 count
+// ptr 0 q, 1 k_cache, 2 v_cache, 3 pos, 4 out, 5 k_new, 6 v_new, 7 cos, 8 sin, 9 part, 10 count; i 12 pos stride, 13 window
 // i 0 B, 1 H, 2 KVH, 3 D, 4 max_seq, 5 splits, 6 fused, 7 dtype of q / k_new / v_new, 8 out dtype,
 //   9 zero q / k_new / v_new after use (they are fp32 columns of a split-K workspace: the instruction that
 //     writes the pair's output hands them back zeroed, as the SplitFinalize it replaces would),
@@ -57,10 +57,13 @@ __device__ __forceinline__ void decode_body(const Params& p, Ctrl* c, const mk_o
     const bool fused = op->i[6] != 0;
     const int G = H / KVH;
     const int b = a0, kvh = a1, s = a2;
-    const int pos = *reinterpret_cast<const int*>(op->ptr[3]);
+    // one position for the batch, or (i 12: stride) one per sequence; i 13: sliding window, the last `window` tokens
+    // -- the new one included -- of the sequence (0: all of them)
+    const int pos = reinterpret_cast<const int*>(op->ptr[3])[(long long)b * op->i[12]];
     const int n = fused ? pos : pos + 1;
-    const int per = (n + S - 1) / S;
-    const int k_begin = min(n, s * per), k_end = min(n, k_begin + per);
+    const int first = op->i[13] > 0 ? max(0, pos + 1 - op->i[13]) : 0;    // first cache row attended
+    const int per = (n - first + S - 1) / S;
+    const int k_begin = min(n, first + s * per), k_end = min(n, k_begin + per);
     const int nk = k_end - k_begin;                                       // cached keys of this split
     const bool has_new = fused && s == S - 1;
     const int half = D / 2;

@@ -77,7 +77,7 @@ __device__ __forceinline__ void decode_bulk_body(const Params& p, Ctrl* c, const
     const int rb = KVH * D * 2;
     const bool head = warp < KVH;                                     // this warp owns kv head `warp`
     const bool hrow = head && g < G;                                  // this lane's MMA row is a query head
-    const int pos = *reinterpret_cast<const int*>(op->ptr[3]);
+    const int pos = reinterpret_cast<const int*>(op->ptr[3])[(long long)b * op->i[12]];      // (i 12: 0, or the stride of per-sequence positions)
     int k_begin, k_end;
     kv_split_range(fused ? pos : pos + 1, S, s, k_begin, k_end);
     const int nk = k_end - k_begin;

@@ -102,7 +102,7 @@ struct StageCursor {
                 const int KVH = op->i[2], L = op->i[4], S = op->i[5];
                 const bool fused = op->i[6] != 0;
                 // pos is rewritten only by the launch's last instruction, behind every reader's arrival
-                const int posv = *reinterpret_cast<const volatile int*>(op->ptr[3]);
+                const int posv = reinterpret_cast<const volatile int*>(op->ptr[3])[(long long)in.a0 * op->i[12]];
                 int k_begin, k_end;
                 kv_split_range(fused ? posv : posv + 1, S, in.a2, k_begin, k_end);
                 gemm = false; kv = true; seq = in.seq;

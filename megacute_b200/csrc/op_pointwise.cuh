@@ -211,21 +211,23 @@ __device__ __forceinline__ void rope8(const float* x1, const float* x2, const vo
 }
 
 // MK_OP_ROPE_APPEND.  ptr 0 qkv, 1 cos, 2 sin, 3 pos, 4 q_out, 5 k_cache, 6 v_cache
-// i 0 B, 1 H, 2 KVH, 3 D, 4 max_seq, 5 qkv dtype.  args: 0 row tile (8 sequences).
+// i 0 B, 1 H, 2 KVH, 3 D, 4 max_seq, 5 qkv dtype, 6 pos stride.  args: 0 row tile (8 sequences).
 // Cache row written for sequence b: b * max_seq + pos (reference: graph.py:375-379).
 static __device__ __noinline__ void op_rope_append(const mk_op_desc* op, int a0) {
     const int B = op->i[0], H = op->i[1], KVH = op->i[2], D = op->i[3], L = op->i[4], qdt = op->i[5];
-    const int pos = *reinterpret_cast<const int*>(op->ptr[3]);
+    const int* posp = reinterpret_cast<const int*>(op->ptr[3]);
+    const long long pstride = op->i[6];                                   // 0: one position for the batch, else one per sequence
     const int half = D >> 1, hv = half >> 3;
     const int r0 = a0 * kComputeWarps;
     const int rows = min(kComputeWarps, B - r0);
     const void* qkv = reinterpret_cast<const void*>(op->ptr[0]);
-    const __nv_bfloat16* cosr = reinterpret_cast<const __nv_bfloat16*>(op->ptr[1]) + (long long)pos * op->ld[1];
-    const __nv_bfloat16* sinr = reinterpret_cast<const __nv_bfloat16*>(op->ptr[2]) + (long long)pos * op->ld[2];
     const int units = (H + KVH) * hv;
     for (int u = threadIdx.x; u < rows * units; u += kComputeThreads) {
         const int b = r0 + u / units, rem = u % units;
         const int hh = rem / hv, d = (rem % hv) * 8;
+        const int pos = posp[b * pstride];
+        const __nv_bfloat16* cosr = reinterpret_cast<const __nv_bfloat16*>(op->ptr[1]) + (long long)pos * op->ld[1];
+        const __nv_bfloat16* sinr = reinterpret_cast<const __nv_bfloat16*>(op->ptr[2]) + (long long)pos * op->ld[2];
         float x1[8], x2[8], o1[8], o2[8];
         load8(qkv, (long long)b * op->ld[0] + hh * D + d, qdt, x1);
         load8(qkv, (long long)b * op->ld[0] + hh * D + d + half, qdt, x2);
@@ -244,7 +246,7 @@ static __device__ __noinline__ void op_rope_append(const mk_op_desc* op, int a0)
         const int b = r0 + u / nv, v = u % nv;
         float f[8];
         load8(qkv, (long long)b * op->ld[0] + (H + KVH) * D + v * 8, qdt, f);
-        store8(reinterpret_cast<void*>(op->ptr[6]), ((long long)b * L + pos) * op->ld[6] + v * 8, 0, f);
+        store8(reinterpret_cast<void*>(op->ptr[6]), ((long long)b * L + posp[b * pstride]) * op->ld[6] + v * 8, 0, f);
     }
 }
 
@@ -346,12 +348,11 @@ static __device__ __noinline__ void op_argmax(const mk_op_desc* op, int a0, int 
     }
 }
 
-// MK_OP_INCREMENT.  ptr 0 pos.
+// MK_OP_INCREMENT.  ptr 0 pos; i 0 rows of pos, 1 their stride.  One instruction.
 __device__ __forceinline__ void op_increment(const mk_op_desc* op) {
-    if (threadIdx.x == 0) {
-        int* pos = reinterpret_cast<int*>(op->ptr[0]);
-        *pos = *pos + 1;
-    }
+    int* pos = reinterpret_cast<int*>(op->ptr[0]);
+    const int rows = max(1, op->i[0]);
+    for (int r = threadIdx.x; r < rows; r += kComputeThreads) pos[(long long)r * op->i[1]] += 1;
 }
 
 }  // namespace mk

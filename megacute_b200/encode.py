@@ -18,11 +18,13 @@ view's first element.  Field meaning per kind (the kernel side repeats it next t
   NORM         ptr x, out, weight, bias; i R, C, rms, rows per instruction, x dtype, out dtype; f eps
   ATTENTION    ptr q, k, v, out; i batch, seq_q, seq_k, heads, kv_heads, head_dim, causal, out dtype,
                dtype of q / k / v (one for all three: bf16 or fp16); f scale
-  ROPE_APPEND  ptr qkv, cos, sin, pos, q_out, k_cache, v_cache; i B, H, KVH, D, max_seq, qkv dtype
+  ROPE_APPEND  ptr qkv, cos, sin, pos, q_out, k_cache, v_cache; i B, H, KVH, D, max_seq, qkv dtype,
+               pos stride (ints between the positions of consecutive sequences; 0: one position for all)
   DECODE_ATTN  ptr q, k_cache, v_cache, pos, out, k_new, v_new, cos, sin, part, count;
                i B, H, KVH, D, max_seq, splits, fused, q dtype, out dtype, zero inputs, kv heads per
-               instruction, many-sequence form; f scale
-  INCREMENT    ptr pos
+               instruction, many-sequence form, pos stride (0: one position for all), window (0: whole context);
+               f scale
+  INCREMENT    ptr pos; i rows of pos, pos stride
   GATHER       ptr table, ids, out; i rows, cols, table rows, out dtype
   ARGMAX       ptr x, ids, part, count; i rows, cols, chunks, columns per chunk, x dtype
 """
@@ -74,6 +76,11 @@ def validate(op: Op):
     if k == "Attention":
         for name, v in op.view_fields():
             _want(v, (BF16, F16), f"{k}.{name}")
+
+
+def _pos_stride(pos: View) -> int:
+    """int32 elements between the positions of consecutive sequences: 0 when the batch shares one position."""
+    return 0 if pos.rows == 1 else pos.buf.cols
 
 
 def gemv_units(op: Op) -> bool:
@@ -136,12 +143,13 @@ def fill(d, op: Op, addr) -> None:
     elif k == "RopeAppend":
         d.kind = C.OP_ROPE_APPEND
         ptrs = [op.qkv, op.cos, op.sin, op.pos, op.q_out, op.k_cache, op.v_cache]
-        ints = [op.qkv.rows, op.heads, op.kv_heads, op.head_dim, op.max_seq, dt(op.qkv)]
+        ints = [op.qkv.rows, op.heads, op.kv_heads, op.head_dim, op.max_seq, dt(op.qkv), _pos_stride(op.pos)]
     elif k == "DecodeAttention":
         d.kind = C.OP_DECODE_ATTN
         ptrs = [op.q, op.k_cache, op.v_cache, op.pos, op.out, op.k_new, op.v_new, op.cos, op.sin, op.part, op.count]
         ints = [op.batch, op.heads, op.kv_heads, op.head_dim, op.max_seq, op.splits, int(op.k_new is not None),
-                dt(op.q), dt(op.out), int(bool(op.zero_inputs)), int(op.heads_per_inst or 1), int(bool(op.bulk))]
+                dt(op.q), dt(op.out), int(bool(op.zero_inputs)), int(op.heads_per_inst or 1), int(bool(op.bulk)),
+                _pos_stride(op.pos), int(op.window or 0)]
         assert not op.bulk or (op.heads_per_inst == op.kv_heads and op.head_dim == 64 and op.kv_heads <= C.COMPUTE_WARPS)
         assert not op.zero_inputs or dt(op.q) == 1
         assert op.k_new is None or dt(op.k_new) == dt(op.v_new) == dt(op.q)
@@ -150,6 +158,7 @@ def fill(d, op: Op, addr) -> None:
     elif k == "Increment":
         d.kind = C.OP_INCREMENT
         ptrs = [op.pos]
+        ints = [op.pos.rows, _pos_stride(op.pos)]
     elif k == "Gather":
         d.kind = C.OP_GATHER
         ptrs = [op.table, op.ids, op.out]

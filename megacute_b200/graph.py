@@ -124,7 +124,7 @@ OP_TABLE = {
     "DecodeAttention": (("q", "k_cache", "v_cache", "pos", "k_new", "v_new", "cos", "sin", "part", "count"),
                         ("out", "part", "count"),
                         ("batch", "heads", "kv_heads", "head_dim", "max_seq", "scale", "splits", "zero_inputs", "heads_per_inst",
-                         "bulk")),
+                         "bulk", "window")),
     "Increment":       ((), ("pos",), ()),
     # the two ends of a decode step, inside the launch (no counterpart among the reference's ops: its
     # step does them in torch around the launch, examples/llama/llama1b.py:103-105)
@@ -268,13 +268,19 @@ def _chk_attention(o):
         assert o.seq_q == o.seq_k, "causal attention requires seq_q == seq_k"
 
 
+def _chk_pos(pos, batch):
+    """One position for the whole batch, (1, 1), or one per sequence, (batch, 1): the reference's decode ops know only the
+    first (megacute README.md:225-227 lists per-sequence positions as a limitation)."""
+    assert pos.shape in ((1, 1), (batch, 1)) and pos.buf.dtype == torch.int32, "pos is (1, 1) or (batch, 1) int32"
+
+
 def _chk_rope_append(o):
     B, D = o.qkv.rows, o.head_dim
     assert o.qkv.cols == (o.heads + 2 * o.kv_heads) * D
     assert o.q_out.shape == (B, o.heads * D)
     assert o.k_cache.shape == o.v_cache.shape == (B * o.max_seq, o.kv_heads * D)
     assert o.cos.shape == o.sin.shape == (o.max_seq, D) and D % 16 == 0
-    assert o.pos.shape == (1, 1) and o.pos.buf.dtype == torch.int32
+    _chk_pos(o.pos, B)
 
 
 def _chk_decode_attention(o):
@@ -289,11 +295,14 @@ def _chk_decode_attention(o):
     assert D in (64, 128) and o.max_seq % 128 == 0
     assert o.q.shape == o.out.shape == (o.batch, o.heads * D)
     assert o.k_cache.shape == o.v_cache.shape == (o.batch * o.max_seq, o.kv_heads * D)
-    assert o.pos.shape == (1, 1) and o.pos.buf.dtype == torch.int32
+    _chk_pos(o.pos, o.batch)
+    o.window = int(o.window or 0)
+    assert o.window >= 0, "decode attention: window is a number of tokens (0 or None: the whole context)"
+    assert not (o.bulk and o.window), "the many-sequence form of decode attention has no sliding window"
 
 
 def _chk_increment(o):
-    assert o.pos.shape == (1, 1) and o.pos.buf.dtype == torch.int32
+    assert o.pos.cols == 1 and o.pos.buf.dtype == torch.int32
 
 
 def _chk_gather(o):
@@ -465,24 +474,30 @@ class Graph:
 
     def rope_append(self, qkv, cos, sin, pos, k_cache, v_cache, *, heads, kv_heads, head_dim, max_seq,
                     out=None) -> View:
-        """Decode: rotate q and k of one new token per sequence at position ``pos[0, 0]``; write
-        ``k_cache[b*max_seq + pos] = rope(k)`` and ``v_cache[b*max_seq + pos] = v``; return rotated q."""
+        """Decode: rotate q and k of one new token per sequence at position ``pos[0, 0]`` (or ``pos[b, 0]``
+        when pos has one row per sequence); write ``k_cache[b*max_seq + pos] = rope(k)`` and
+        ``v_cache[b*max_seq + pos] = v``; return rotated q."""
         out = out or self.temp((qkv.rows, heads * head_dim))
         self._emit("RopeAppend", qkv=qkv, cos=cos, sin=sin, pos=pos, q_out=out, k_cache=k_cache, v_cache=v_cache,
                    heads=heads, kv_heads=kv_heads, head_dim=head_dim, max_seq=max_seq)
         return out
 
     def decode_attention(self, q, k_cache, v_cache, pos, *, heads, kv_heads, head_dim, max_seq, scale=None,
-                         out=None) -> View:
-        """Decode: one query token per sequence against cache rows [0, pos] of its sequence, GQA."""
+                         out=None, window=None) -> View:
+        """Decode: one query token per sequence against cache rows [0, pos] of its sequence, GQA.
+
+        Beyond the reference (its README.md:225-228 names both as limitations): ``pos`` may be a
+        (batch, 1) column, one position per sequence (a ragged batch; rope_append and increment take
+        the same), and ``window`` = w restricts a sequence to its last w tokens, rows
+        [max(0, pos + 1 - w), pos] (sliding-window attention)."""
         out = out or self.temp(q.shape)
         self._emit("DecodeAttention", q=q, k_cache=k_cache, v_cache=v_cache, pos=pos, out=out, batch=q.rows,
                    heads=heads, kv_heads=kv_heads, head_dim=head_dim, max_seq=max_seq,
-                   scale=float(scale) if scale is not None else head_dim ** -0.5, splits=1)
+                   scale=float(scale) if scale is not None else head_dim ** -0.5, splits=1, window=int(window or 0))
         return out
 
     def increment(self, pos):
-        """``pos += 1`` on device after every reader of pos in the launch."""
+        """``pos += 1`` (every row of it) on device after every reader of pos in the launch."""
         self._emit("Increment", pos=pos)
 
     def gather(self, table, ids, out=None) -> View:

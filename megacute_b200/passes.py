@@ -132,7 +132,7 @@ def bulk_eligible(op: Op) -> bool:
     """Can this decode attention run in the many-sequence form (csrc/op_decode_bulk.cuh)?  One warp per
     kv head, head_dim 64, and cache views that are whole rows of their buffers, 128 bytes per kv head,
     so that consecutive rows are one contiguous run of memory."""
-    if os.environ.get("MEGACUTE_B200_ATT_BULK") == "0":
+    if os.environ.get("MEGACUTE_B200_ATT_BULK") == "0" or getattr(op, "window", 0):      # (no sliding window in that form)
         return False
     whole = all(v.col0 == 0 and v.cols == v.buf.cols for v in (op.k_cache, op.v_cache))
     ok = op.head_dim == 64 and op.kv_heads <= C.COMPUTE_WARPS and whole and op.k_cache.cols == op.kv_heads * 64

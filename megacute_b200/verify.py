@@ -86,20 +86,20 @@ def operand_windows(op) -> dict:
         return {"q": q, "k": kv, "v": kv, "out": q}
     if k == "RopeAppend":
         B, D, L = op.qkv.rows, op.head_dim, op.max_seq
-        return {"qkv": (B, (op.heads + 2 * op.kv_heads) * D), "cos": (L, D), "sin": (L, D), "pos": (1, 1),
+        return {"qkv": (B, (op.heads + 2 * op.kv_heads) * D), "cos": (L, D), "sin": (L, D), "pos": (op.pos.rows, 1),
                 "q_out": (B, op.heads * D), "k_cache": (B * L, op.kv_heads * D), "v_cache": (B * L, op.kv_heads * D)}
     if k == "DecodeAttention":
         B, D, L, S = op.batch, op.head_dim, op.max_seq, op.splits or 1
         G = op.heads // op.kv_heads
         cache = (B * L, op.kv_heads * D)       # the append row is b * L + pos with pos <= L - 1
-        win = {"q": (B, op.heads * D), "k_cache": cache, "v_cache": cache, "pos": (1, 1), "out": (B, op.heads * D)}
+        win = {"q": (B, op.heads * D), "k_cache": cache, "v_cache": cache, "pos": (op.pos.rows, 1), "out": (B, op.heads * D)}
         if op.k_new is not None:
             win.update(k_new=(B, op.kv_heads * D), v_new=(B, op.kv_heads * D), cos=(L, D), sin=(L, D))
         if S > 1:
             win.update(part=(B * op.kv_heads * S, G * D + 2 * G), count=(B * op.kv_heads, 1))
         return win
     if k == "Increment":
-        return {"pos": (1, 1)}
+        return {"pos": (op.pos.rows, 1)}
     if k == "Gather":
         return {"table": op.table.shape, "ids": op.ids.shape, "out": op.out.shape}
     if k == "Argmax":

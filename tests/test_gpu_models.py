@@ -508,3 +508,74 @@ def test_wide_tiles_many_per_cta_and_slot_kinds(cuda, monkeypatch):
     assert sorted(o.bn or 128 for o in lin) == [128, 128, 256, 256] and prog.tcgen05_ops == 3
     assert_close(outs, ref)
     assert np.array_equal(prog.counters(), prog.sched.counter_target * 2)
+
+
+def _ragged_decode(B, ragged_pos, window, n=2, E=256, H=4, KVH=2, F=512, L=256, V=1024):
+    g = llama_decode(B, E, H, KVH, F, n, L, V, 1e-5, ragged=ragged_pos is not None, window=window)
+    w = W.llama_weights(E, H, KVH, F, n, V, 0, "cpu")
+    st, ids = W.llama_decode_state(B, E, H, KVH, n, L, max(ragged_pos) if ragged_pos else 150, V, 1, "cpu")
+    cos, sin = W.rope_tables(L, E // H)
+    if ragged_pos is not None:
+        st["pos"] = torch.tensor(ragged_pos, dtype=torch.int32).reshape(B, 1)
+    st["x"] = w["lm_head"][ids].clone()
+    return g, dict(cos=cos, sin=sin, **w), st
+
+
+@pytest.mark.parametrize("B,bulk", [(1, None), (3, None), (12, None), (33, "0"), (33, "1")])
+def test_decode_ragged_positions(cuda, monkeypatch, B, bulk):
+    """One position per sequence (pos is a (B, 1) column): every sequence ropes, appends and attends at its own length --
+    streaming linears (B <= 8), tile GEMMs, and both forms of the decode attention.  Three steps against the oracle;
+    positions, the cache rows written and the dependency counters exact."""
+    if bulk:
+        monkeypatch.setenv("MEGACUTE_B200_ATT_BULK", bulk)
+    gen = torch.Generator().manual_seed(B)
+    ps = [int(v) for v in torch.randint(5, 200, (B,), generator=gen)]
+    ps[0] = 0                                            # a sequence at its very first token
+    g, params, st = _ragged_decode(B, ps, None)
+    prog = mc.compile(g)
+    assert {bool(o.bulk) for o in prog.g.ops if o.kind == "DecodeAttention"} == {bulk == "1" or (bulk is None and B >= 32)}
+    dp = {k: v.to(cuda) for k, v in params.items()}
+    ds = {k: v.to(cuda) for k, v in st.items()}
+    rs = {k: v.clone() for k, v in st.items()}
+    for step in range(3):
+        logits = prog(**dp, **ds).float().cpu()
+        ref, new = evaluate(g, {**params, **rs})
+        assert rel_l2(logits, ref[0]) < TOL, (step, rel_l2(logits, ref[0]))
+        for n_ in ("pos", "k_cache", "v_cache"):
+            rs[n_] = new[n_]
+        rs["x"] = params["lm_head"][ref[0].argmax(-1)].clone()
+        ds["x"].copy_(rs["x"].to(cuda))
+    prog.check()
+    assert ds["pos"].flatten().tolist() == [p + 3 for p in ps]
+    kc, rk = ds["k_cache"].cpu().float(), rs["k_cache"].float()
+    changed = (kc != st["k_cache"].float()).any(-1).reshape(2, B, 256)
+    want = torch.zeros_like(changed)
+    for b, p in enumerate(ps):
+        want[:, b, p:p + 3] = True
+    assert torch.equal(changed, want) and rel_l2(kc, rk) < TOL
+    assert np.array_equal(prog.counters(), prog.sched.counter_target * 3)
+
+
+@pytest.mark.parametrize("B,window,ragged", [(1, 32, False), (2, 100, False), (5, 17, True), (12, 64, True), (2, 1000, False)])
+def test_decode_sliding_window(cuda, B, window, ragged):
+    """Sliding-window attention: a sequence attends its last `window` tokens (the new one included), whatever the split
+    count; with one position for the batch and with one per sequence; a window beyond the context changes nothing."""
+    ps = [150 - 13 * b for b in range(B)] if ragged else None
+    g, params, st = _ragged_decode(B, ps, window)
+    prog = mc.compile(g)
+    dp = {k: v.to(cuda) for k, v in params.items()}
+    ds = {k: v.to(cuda) for k, v in st.items()}
+    rs = {k: v.clone() for k, v in st.items()}
+    for step in range(2):
+        logits = prog(**dp, **ds).float().cpu()
+        ref, new = evaluate(g, {**params, **rs})
+        assert rel_l2(logits, ref[0]) < TOL, (step, rel_l2(logits, ref[0]))
+        for n_ in ("pos", "k_cache", "v_cache"):
+            rs[n_] = new[n_]
+        rs["x"] = params["lm_head"][ref[0].argmax(-1)].clone()
+        ds["x"].copy_(rs["x"].to(cuda))
+    prog.check()
+    if window < 100:                                     # the window matters: the full-context result differs
+        full, _ = evaluate(llama_decode(B, 256, 4, 2, 512, 2, 256, 1024, 1e-5, ragged=ragged), {**params, **st})
+        win, _ = evaluate(g, {**params, **st})
+        assert rel_l2(win[0], full[0]) > 1e-3

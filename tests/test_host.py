@@ -356,3 +356,51 @@ def test_fused_step_graph_and_oracle():
     _ordered(s, g2)
     with pytest.raises(AssertionError):
         mc.Graph().gather(g.params[0].full, g.states[2].full)        # ids must be an int32 column
+
+
+def test_ragged_positions_and_window_semantics():
+    """The oracle's reading of the two decode extensions: a ragged batch equals its sequences run one by one at their own
+    positions, and passes keep it; a windowed decode attention equals a plain softmax over the window's cache rows."""
+    import torch
+    import megacute_b200 as mc
+    from megacute_b200 import workloads as W
+    from megacute_b200.builders import llama_decode
+    from megacute_b200.passes import run_all
+    from oracle.graph_oracle import evaluate, rel_l2
+    B, E, H, KVH, F, n, L, V = 3, 256, 4, 2, 512, 2, 256, 512
+    w = W.llama_weights(E, H, KVH, F, n, V, 0, "cpu")
+    st, ids = W.llama_decode_state(B, E, H, KVH, n, L, 60, V, 1, "cpu")
+    cos, sin = W.rope_tables(L, E // H)
+    ps = [17, 60, 33]
+    st["pos"] = torch.tensor(ps, dtype=torch.int32).reshape(B, 1)
+    st["x"] = w["lm_head"][ids].clone()
+    g = llama_decode(B, E, H, KVH, F, n, L, V, ragged=True)
+    out, new = evaluate(g, dict(cos=cos, sin=sin, **w, **st))
+    out2, _ = evaluate(run_all(g, 148), dict(cos=cos, sin=sin, **w, **{k: v.clone() for k, v in st.items()}))
+    assert rel_l2(out2[0], out[0]) < 1e-6
+    assert new["pos"].flatten().tolist() == [p + 1 for p in ps]
+    g1 = llama_decode(1, E, H, KVH, F, n, L, V)
+    for b in range(B):
+        pick = lambda c: c.reshape(n, B, L, -1)[:, b].reshape(n * L, -1).clone()
+        st1 = {"x": st["x"][b:b + 1].clone(), "pos": torch.tensor([[ps[b]]], dtype=torch.int32),
+               "k_cache": pick(st["k_cache"]), "v_cache": pick(st["v_cache"])}
+        o1, _ = evaluate(g1, dict(cos=cos, sin=sin, **w, **st1))
+        assert rel_l2(out[0][b:b + 1], o1[0]) < 1e-5
+    # the window, on the attention op alone
+    D, window = E // H, 20
+    ga = mc.Graph()
+    q = ga.input("q", (B, H * D))
+    kc, vc = ga.state("k_cache", (B * L, KVH * D)), ga.state("v_cache", (B * L, KVH * D))
+    pos = ga.state("pos", (B, 1), torch.int32)
+    ga.output(ga.decode_attention(q, kc, vc, pos, heads=H, kv_heads=KVH, head_dim=D, max_seq=L, window=window))
+    t = {"q": torch.randn(B, H * D).bfloat16(), "k_cache": torch.randn(B * L, KVH * D).bfloat16(), "v_cache": torch.randn(B * L, KVH * D).bfloat16(),
+         "pos": st["pos"].clone()}
+    got, _ = evaluate(ga, t)
+    for b in range(B):
+        lo = max(0, ps[b] + 1 - window)
+        k = t["k_cache"].float().reshape(B, L, KVH, D)[b, lo:ps[b] + 1]
+        v = t["v_cache"].float().reshape(B, L, KVH, D)[b, lo:ps[b] + 1]
+        qq = t["q"].float()[b].reshape(KVH, H // KVH, D)
+        sc = torch.einsum("kgd,skd->kgs", qq, k) * D ** -0.5
+        want = torch.einsum("kgs,skd->kgd", torch.softmax(sc, -1), v).reshape(1, H * D)
+        assert rel_l2(got[0][b:b + 1], want) < 1e-5
