@@ -1,7 +1,7 @@
 """Kernel-time measurements of the tensor-bound benchmark configurations (the decode step has its own
 driver, ``bench.py``):
 
-    python -m megacute_b200.measure [mlp_block] [dit] [prefill] [decode_b64_small] [prefill_small]
+    python -m megacute_b200.measure [mlp_block] [dit] [prefill] [decode_b64_small] [prefill_small] [decode_b64_ragged]
 
 * ``mlp_block``: RMS norm -> gate/up + swiglu -> down + residual, 256 rows, 2048 -> 2 x 5632 -> 2048
 * ``dit``: 28 DiT blocks, 32 images x 256 tokens, width 1024, 16 heads, MLP 4096
@@ -9,6 +9,9 @@ driver, ``bench.py``):
 * ``decode_b64_small``, ``prefill_small``: cut-down cases of the same kernels for profiler captures
   (batch-64 decode at context 4096 with 4 layers and a 32768-row lm_head, 2.2 GB of cache; prefill
   with 2 layers): a few GB on the device, a handful of launches
+
+* ``decode_b64_ragged``: the full 16-layer batch-64 decode step with one position per sequence, spread
+  evenly over 256 .. 4096 tokens (a ragged batch: not possible in the reference)
 
 Synthetic bf16 inputs and weights of those shapes; each configuration is compiled once, warmed up
 twice, then timed over a few launches with CUDA events on the launching stream.  Prints one line
@@ -102,8 +105,30 @@ def measure_decode_b64_small(dev):
     return ms, 2 * B * (n * (E * (E + 2 * KVH * D) + E * E + 3 * E * F) + E * vocab), prog
 
 
+def measure_decode_b64_ragged(dev):
+    from megacute_b200.builders import llama_decode
+    c = W.LLAMA_1B
+    B, n, vocab, max_seq = 64, c["n"], c["vocab"], 4096 + 128
+    g = llama_decode(B, c["E"], c["H"], c["KVH"], c["F"], n, max_seq, vocab, c["eps"], ragged=True)
+    prog = mc.compile(g)
+    w = W.llama_weights(c["E"], c["H"], c["KVH"], c["F"], n, vocab, 0, dev)
+    st, _ = W.llama_decode_state(B, c["E"], c["H"], c["KVH"], n, max_seq, 4096, vocab, 1, dev)
+    pos = torch.linspace(256, 4096, B).round().to(torch.int32).reshape(B, 1)
+    st["pos"] = pos.to(dev)
+    cos, sin = W.rope_tables(max_seq, c["E"] // c["H"], c["theta"], dev)
+    args = dict(cos=cos, sin=sin, **w, **st)
+    launches = 6
+    ms = _time(prog, args, launches)
+    kv = int((pos.sum() + B * (2 + (launches - 1) / 2)) * n * 2 * c["KVH"] * (c["E"] // c["H"]) * 2)      # mean over the timed launches
+    print(f"decode_b64_ragged: positions {int(pos.min())} .. {int(pos.max())}, cache bytes per launch {kv}, "
+          f"{(kv + 2471493632) / ms / 1e6:.0f} GB/s of weights + cache")
+    E, F, D, KVH = c["E"], c["F"], c["E"] // c["H"], c["KVH"]
+    return ms, 2 * B * (n * (E * (E + 2 * KVH * D) + E * E + 3 * E * F) + E * vocab), prog
+
+
 CONFIGS = {"mlp_block": measure_mlp_block, "dit": measure_dit, "prefill": measure_prefill,
-           "decode_b64_small": measure_decode_b64_small, "prefill_small": measure_prefill_small}
+           "decode_b64_small": measure_decode_b64_small, "prefill_small": measure_prefill_small,
+           "decode_b64_ragged": measure_decode_b64_ragged}
 DEFAULT = ["mlp_block", "dit", "prefill"]
 
 

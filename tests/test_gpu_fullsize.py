@@ -157,3 +157,38 @@ def test_llama_1b_free_running_greedy(cuda):
     else:
         print(f"free-running greedy decode: identical for {first_split} steps; at step {first_split} the fp32 margin "
               f"between the two candidates is {margin_at_split:.3e}")
+
+
+def test_llama_1b_decode_batch64_ragged(cuda):
+    """Batch-64 decode at full size with one position per sequence (256 .. 4096 tokens, the many-sequence attention
+    with per-sequence split ranges): two steps against the fp32 oracle, positions exact."""
+    B, steps, ctx = 64, 2, 4096
+    c = C1B
+    max_seq = ctx + 128
+    g = llama_decode(B, c["E"], c["H"], c["KVH"], c["F"], c["n"], max_seq, c["vocab"], c["eps"], ragged=True)
+    params = dict(zip(("cos", "sin"), W.rope_tables(max_seq, 64, c["theta"], cuda)),
+                  **W.llama_weights(c["E"], c["H"], c["KVH"], c["F"], c["n"], c["vocab"], 0, cuda))
+    st, ids = W.llama_decode_state(B, c["E"], c["H"], c["KVH"], c["n"], max_seq, ctx, c["vocab"], 1, cuda)
+    pos = torch.linspace(256, ctx, B).round().to(torch.int32).reshape(B, 1)
+    st["pos"] = pos.to(cuda)
+    prog = mc.compile(g)
+    assert all(o.bulk for o in prog.g.ops if o.kind == "DecodeAttention")
+    rs = {k: v.clone() for k, v in st.items()}
+    emb = params["lm_head"]
+    worst = 0.0
+    for step in range(steps):
+        st["x"].copy_(emb[ids])
+        rs["x"] = emb[ids].clone()
+        logits = prog(**params, **st).float()
+        ref, new = evaluate(g, {**params, **rs}, device=cuda)
+        for name in ("pos", "k_cache", "v_cache"):
+            rs[name] = new[name]
+        err = rel_l2(logits, ref[0])
+        worst = max(worst, err)
+        assert torch.isfinite(logits).all() and err < TOL, (step, err)
+        ids = ref[0].argmax(-1)
+        del ref, new
+    prog.check()
+    print(f"batch 64, positions 256 .. {ctx}: worst logits rel-L2 over {steps} steps {worst:.2e}")
+    assert torch.equal(st["pos"].cpu(), pos + steps) and torch.equal(rs["pos"].cpu(), pos + steps)
+    assert np.array_equal(prog.counters(), prog.sched.counter_target * steps)
