@@ -1,6 +1,7 @@
 // Vectorised (128-bit) pointwise, norm and small decode ops.  All read and write global memory
 // directly with 16-byte accesses: they are bandwidth / latency bound and need no staging.
 #pragma once
+#include <type_traits>
 #include "mk_device.cuh"
 
 namespace mk {
@@ -52,6 +53,154 @@ static __device__ __noinline__ void op_finalize(const mk_op_desc* op, int a0, in
     }
 }
 
+// a raw vector of 8 elements: 16 bytes when the element type is known to be 16-bit, else room for fp32
+template <bool SIXTEEN> struct Raw8x;
+template <> struct Raw8x<true> {
+    uint4 v;
+    __device__ __forceinline__ void load(const void* base, long long elem, int) { v = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(base) + elem)); }
+    __device__ __forceinline__ void unpack(int dtype, float* f) const { Raw8 r; r.lo = v; r.hi = v; unpack8_raw(r, dtype == DT_F16 ? DT_F16 : DT_BF16, f); }
+};
+template <> struct Raw8x<false> {
+    Raw8 v;
+    __device__ __forceinline__ void load(const void* base, long long elem, int dtype) { v = load8_raw(base, elem, dtype); }
+    __device__ __forceinline__ void unpack(int dtype, float* f) const { unpack8_raw(v, dtype, f); }
+};
+
+// Binary / modulate tile whose rows all read ONE row of the second (and third) operand -- a per-image gate, scale or
+// shift over that image's tokens: the thread keeps its 8 columns of them and streams a, eight rows in flight when a is 16-bit.
+template <int MODE>
+static __device__ __noinline__ void eltwise_tile_one_group(const mk_op_desc* op, int r0, int col, int rows, int rowp, int rpp) {
+    const int fn = op->i[3], group = op->i[4];
+    const int adt = op->i[6], bdt = op->i[7], cdt = op->i[8], odt = op->i[9];
+    const void* A = reinterpret_cast<const void*>(op->ptr[0]);
+    void* O = reinterpret_cast<void*>(op->ptr[3]);
+    const long long grow = r0 / group;
+    float b[8], cc[8];
+    load8(reinterpret_cast<const void*>(op->ptr[1]), grow * op->ld[1] + col, bdt, b);
+    if (MODE == EW_MODULATE) {
+        load8(reinterpret_cast<const void*>(op->ptr[2]), grow * op->ld[2] + col, cdt, cc);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) b[e] += 1.0f;
+    }
+    auto body = [&](auto tag) {
+        constexpr bool S16 = decltype(tag)::value;
+        constexpr int UN = S16 ? 8 : 4;
+        for (int rr = rowp; rr < rows; rr += UN * rpp) {
+            Raw8x<S16> ra[UN];
+#pragma unroll
+            for (int u = 0; u < UN; ++u)
+                if (rr + u * rpp < rows) ra[u].load(A, (long long)(r0 + rr + u * rpp) * op->ld[0] + col, adt);
+#pragma unroll
+            for (int u = 0; u < UN; ++u) {
+                if (rr + u * rpp >= rows) continue;
+                float a[8];
+                ra[u].unpack(adt, a);
+                if (MODE == EW_MODULATE) {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) a[e] = fmaf(a[e], b[e], cc[e]);
+                } else if (fn == BIN_MUL) {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) a[e] *= b[e];
+                } else if (fn == BIN_ADD) {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) a[e] += b[e];
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) a[e] = apply_bin(fn, a[e], b[e]);
+                }
+                store8(O, (long long)(r0 + rr + u * rpp) * op->ld[3] + col, odt, a);
+            }
+        }
+    };
+    if (adt != DT_F32) body(std::true_type{});
+    else body(std::false_type{});
+}
+
+// One tile of a pointwise op other than rope.  A pointwise instruction is a few thousand elements; with the mode, the
+// function and the tile geometry as run-time switches and divisions inside the vector loop it was instruction-bound
+// (8.7 us for a 32 x 512 modulate tile: ~300 instructions per 8-element vector at a fraction of an instruction per
+// cycle; more loads in flight changed nothing).  Here the mode is a template parameter, the function is switched once
+// per vector, a thread keeps its columns and walks rows (no division in the loop), and two rows are in flight.
+template <int MODE, bool SIXTEEN>
+static __device__ __noinline__ void eltwise_tile(const mk_op_desc* op, int r0, int c0, int rows, int cols) {
+    const int fn = op->i[3], group = op->i[4];
+    const int adt = op->i[6], bdt = op->i[7], cdt = op->i[8], odt = op->i[9];
+    const void* A = reinterpret_cast<const void*>(op->ptr[0]);
+    const void* B = reinterpret_cast<const void*>(op->ptr[1]);
+    const void* Cp = reinterpret_cast<const void*>(op->ptr[2]);
+    void* O = reinterpret_cast<void*>(op->ptr[3]);
+    constexpr bool HASB = MODE != EW_UNARY, HASC = MODE == EW_MODULATE, GROUPED = MODE == EW_BINARY || MODE == EW_MODULATE;
+    const int vpr = cols >> 3;                                   // vectors per row: at most 64
+    // threads cover whole rows side by side: thread -> (row of the pass, vector of the row)
+    const int tpr = vpr <= 1 ? 1 : vpr <= 2 ? 2 : vpr <= 4 ? 4 : vpr <= 8 ? 8 : vpr <= 16 ? 16 : vpr <= 32 ? 32 : 64;   // threads per row
+    const int rpp = kComputeThreads / tpr;                       // rows per pass
+    const int vec = threadIdx.x & (tpr - 1), rowp = threadIdx.x / tpr;
+    if (vec >= vpr) return;
+    const int col = c0 + vec * 8;
+    if (GROUPED && (r0 / group) == ((r0 + rows - 1) / group)) {
+        // every row of the tile reads the same row of b (and c): a thread's column of them is loaded once, and only a streams
+        eltwise_tile_one_group<MODE>(op, r0, col, rows, rowp, rpp);
+        return;
+    }
+    // rows in flight per thread: with 16-bit operands a vector is four registers and a thread's whole share of the tile
+    // (eight rows) fits; otherwise two (more spill, and a spill is an L2 round trip like the loads it was to hide)
+    constexpr int UN = SIXTEEN ? (HASC ? 2 : HASB ? 4 : 8) : 2;
+    for (int rr = rowp; rr < rows; rr += UN * rpp) {
+        Raw8x<SIXTEEN> ra[UN], rb[HASB ? UN : 1], rc[HASC ? UN : 1];
+#pragma unroll
+        for (int u = 0; u < UN; ++u) {
+            const int r = r0 + rr + u * rpp;
+            if (rr + u * rpp >= rows) continue;
+            ra[u].load(A, (long long)r * op->ld[0] + col, adt);
+            const long long rb_row = GROUPED ? r / group : r;
+            if (HASB) rb[u].load(B, rb_row * op->ld[1] + col, bdt);
+            if (HASC) rc[u].load(Cp, rb_row * op->ld[2] + col, cdt);
+        }
+#pragma unroll
+        for (int u = 0; u < UN; ++u) {
+            const int r = r0 + rr + u * rpp;
+            if (rr + u * rpp >= rows) continue;
+            float a[8], b[8], cc[8];
+            ra[u].unpack(adt, a);
+            if (HASB) rb[u].unpack(bdt, b);
+            if (MODE == EW_UNARY) {
+                switch (fn) {
+                    case ACT_NONE: break;
+                    case ACT_SILU:
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) a[e] = a[e] * sigmoidf_(a[e]);
+                        break;
+                    default:
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) a[e] = apply_act(fn, a[e]);
+                }
+            } else if (MODE == EW_BINARY) {
+                switch (fn) {
+                    case BIN_ADD:
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) a[e] += b[e];
+                        break;
+                    case BIN_MUL:
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) a[e] *= b[e];
+                        break;
+                    default:
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) a[e] = apply_bin(fn, a[e], b[e]);
+                }
+            } else if (MODE == EW_SWIGLU) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) a[e] = apply_act(fn, a[e]) * b[e];
+            } else {  // EW_MODULATE: x * (1 + scale[g]) + shift[g]
+                rc[u].unpack(cdt, cc);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) a[e] = fmaf(a[e], 1.0f + b[e], cc[e]);
+            }
+            store8(O, (long long)r * op->ld[3] + col, odt, a);
+        }
+    }
+}
+
 // MK_OP_ELTWISE.  ptr 0 a (x / gate), 1 b (b / up / scale / cos), 2 c (shift / sin), 3 out
 // i 0 R, 1 C, 2 mode, 3 fn (activation or binary code), 4 group (rows of a per row of b; rope: seq),
 //   5 head_dim (rope), 6..9 dtypes of a, b, c, out (DT_*).  args: 0 row tile, 1 col tile.
@@ -90,29 +239,97 @@ static __device__ __noinline__ void op_eltwise(const mk_op_desc* op, int a0, int
         }
         return;
     }
-    const int vpr = cols >> 3;
-    for (int v = threadIdx.x; v < rows * vpr; v += kComputeThreads) {
-        const int r = r0 + v / vpr, col = c0 + (v % vpr) * 8;
-        float a[8], b[8], cc[8];
-        load8(A, (long long)r * op->ld[0] + col, adt, a);
-        if (mode == EW_UNARY) {
-#pragma unroll
-            for (int e = 0; e < 8; ++e) a[e] = apply_act(fn, a[e]);
-        } else if (mode == EW_BINARY) {
-            load8(B, (long long)(r / group) * op->ld[1] + col, bdt, b);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) a[e] = apply_bin(fn, a[e], b[e]);
-        } else if (mode == EW_SWIGLU) {
-            load8(B, (long long)r * op->ld[1] + col, bdt, b);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) a[e] = apply_act(fn, a[e]) * b[e];
-        } else {  // EW_MODULATE: x * (1 + scale[g]) + shift[g]
-            load8(B, (long long)(r / group) * op->ld[1] + col, bdt, b);
-            load8(Cp, (long long)(r / group) * op->ld[2] + col, cdt, cc);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) a[e] = a[e] * (1.0f + b[e]) + cc[e];
+    const bool all16 = adt != DT_F32 && (mode == EW_UNARY || bdt != DT_F32) && (mode != EW_MODULATE || cdt != DT_F32);
+    if (all16) {
+        switch (mode) {
+            case EW_UNARY: eltwise_tile<EW_UNARY, true>(op, r0, c0, rows, cols); break;
+            case EW_BINARY: eltwise_tile<EW_BINARY, true>(op, r0, c0, rows, cols); break;
+            case EW_SWIGLU: eltwise_tile<EW_SWIGLU, true>(op, r0, c0, rows, cols); break;
+            default: eltwise_tile<EW_MODULATE, true>(op, r0, c0, rows, cols); break;
         }
-        store8(O, (long long)r * op->ld[3] + col, odt, a);
+        return;
+    }
+    switch (mode) {
+        case EW_UNARY: eltwise_tile<EW_UNARY, false>(op, r0, c0, rows, cols); break;
+        case EW_BINARY: eltwise_tile<EW_BINARY, false>(op, r0, c0, rows, cols); break;
+        case EW_SWIGLU: eltwise_tile<EW_SWIGLU, false>(op, r0, c0, rows, cols); break;
+        default: eltwise_tile<EW_MODULATE, false>(op, r0, c0, rows, cols); break;
+    }
+}
+
+// A row (or a lane's share of it) of at most NPER (up to 4) vectors per thread stays in registers between the two passes: every
+// vector is requested before the first is used, and gain and bias come in pairs.  (Requested one by one,
+// the vectors of a 2048-column row cost eight L2 round trips in each pass: 11 us per 16-row instruction.)
+template <int NPER>
+__device__ __forceinline__ void norm_kept(const mk_op_desc* op, int r, int first, int step, int nvec, bool live, uint8_t* work) {
+    const int Cc = op->i[1], rms = op->i[2], rpi = op->i[3], xdt = op->i[4], odt = op->i[5];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const void* X = reinterpret_cast<const void*>(op->ptr[0]);
+    void* O = reinterpret_cast<void*>(op->ptr[1]);
+    const void* W = reinterpret_cast<const void*>(op->ptr[2]);
+    const void* Bv = reinterpret_cast<const void*>(op->ptr[3]);
+    Raw8 kr[NPER];
+#pragma unroll
+    for (int u = 0; u < NPER; ++u) {
+        const int v = first + u * step;
+        if (live && v < nvec) kr[u] = load8_raw(X, (long long)r * op->ld[0] + v * 8, xdt);
+    }
+    float s = 0.f, ss = 0.f;
+#pragma unroll
+    for (int u = 0; u < NPER; ++u) {
+        if (live && first + u * step < nvec) {
+            float f[8];
+            unpack8_raw(kr[u], xdt, f);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) { s += f[e]; ss += f[e] * f[e]; }
+        }
+    }
+    s = warp_sum(s);
+    ss = warp_sum(ss);
+    if (rpi == 1) {
+        float* sh = reinterpret_cast<float*>(work);
+        if (lane == 0) { sh[warp * 2] = s; sh[warp * 2 + 1] = ss; }
+        compute_sync();
+        s = 0.f; ss = 0.f;
+#pragma unroll
+        for (int w8 = 0; w8 < kComputeWarps; ++w8) { s += sh[w8 * 2]; ss += sh[w8 * 2 + 1]; }
+    }
+    if (!live) return;
+    const float mean = rms ? 0.f : s / (float)Cc;
+    const float var = ss / (float)Cc - mean * mean;
+    const float rstd = rsqrt_approx(var + op->f[0]);
+    constexpr int NB = NPER < 2 ? NPER : 2;
+#pragma unroll
+    for (int u0 = 0; u0 < NPER; u0 += NB) {
+        Raw8 gw[NB], bw[NB];
+#pragma unroll
+        for (int u = 0; u < NB; ++u) {
+            const int v = first + (u0 + u) * step;
+            if (v < nvec) {
+                if (W) gw[u] = load8_raw(W, v * 8, 0);
+                if (Bv) bw[u] = load8_raw(Bv, v * 8, 0);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < NB; ++u) {
+            const int v = first + (u0 + u) * step;
+            if (v >= nvec) continue;
+            float f[8], g[8];
+            unpack8_raw(kr[u0 + u], xdt, f);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) f[e] = (f[e] - mean) * rstd;
+            if (W) {
+                unpack8_raw(gw[u], 0, g);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) f[e] *= g[e];
+            }
+            if (Bv) {
+                unpack8_raw(bw[u], 0, g);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) f[e] += g[e];
+            }
+            store8(O, (long long)r * op->ld[1] + v * 8, odt, f);
+        }
     }
 }
 
@@ -132,25 +349,27 @@ static __device__ __noinline__ void op_norm(const mk_op_desc* op, int a0, uint8_
     if (rpi == 1) { r = a0; first = threadIdx.x; step = kComputeThreads; }
     else { r = a0 * kComputeWarps + warp; first = lane; step = 32; }
     const bool live = r < R;
+    const int nper = (nvec + step - 1) / step;          // vectors per thread
+    if (nper <= 1) { norm_kept<1>(op, r, first, step, nvec, live, work); return; }
+    if (nper <= 2) { norm_kept<2>(op, r, first, step, nvec, live, work); return; }
+    if (nper <= 4) { norm_kept<4>(op, r, first, step, nvec, live, work); return; }
+    // longer rows: two passes over global memory, four vectors requested at a time
     float s = 0.f, ss = 0.f;
-    // A row that gives every thread at most one vector (decode: one row over the whole CTA, up to
-    // 2048 columns) stays in registers between the two passes, and its gain and bias are requested
-    // together with it: one L2 round trip on the instruction's critical path instead of three.
-    const bool one = nvec <= step;
-    float keep[8], gk[8], bk[8];
-    if (live && one && first < nvec) {
-        load8(X, (long long)r * op->ld[0] + first * 8, xdt, keep);
-        if (W) load8(W, first * 8, 0, gk);
-        if (Bv) load8(Bv, first * 8, 0, bk);
+    constexpr int UN = 4;
+    if (live)
+        for (int v0 = first; v0 < nvec; v0 += UN * step) {
+            Raw8 rx[UN];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) { s += keep[e]; ss += keep[e] * keep[e]; }
-    }
-    if (live && !one)
-        for (int v = first; v < nvec; v += step) {
-            float f[8];
-            load8(X, (long long)r * op->ld[0] + v * 8, xdt, f);
+            for (int u = 0; u < UN; ++u)
+                if (v0 + u * step < nvec) rx[u] = load8_raw(X, (long long)r * op->ld[0] + (v0 + u * step) * 8, xdt);
 #pragma unroll
-            for (int e = 0; e < 8; ++e) { s += f[e]; ss += f[e] * f[e]; }
+            for (int u = 0; u < UN; ++u) {
+                if (v0 + u * step >= nvec) continue;
+                float f[8];
+                unpack8_raw(rx[u], xdt, f);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) { s += f[e]; ss += f[e] * f[e]; }
+            }
         }
     s = warp_sum(s);
     ss = warp_sum(ss);
@@ -166,34 +385,36 @@ static __device__ __noinline__ void op_norm(const mk_op_desc* op, int a0, uint8_
     const float mean = rms ? 0.f : s / (float)Cc;
     const float var = ss / (float)Cc - mean * mean;
     const float rstd = rsqrt_approx(var + eps);
-    if (one) {
-        if (first < nvec) {
+    for (int v0 = first; v0 < nvec; v0 += 2 * step) {
+        Raw8 rx[2], gw[2], bw[2];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                keep[e] = (keep[e] - mean) * rstd;
-                if (W) keep[e] *= gk[e];
-                if (Bv) keep[e] += bk[e];
+        for (int u = 0; u < 2; ++u) {
+            const int v = v0 + u * step;
+            if (v >= nvec) continue;
+            rx[u] = load8_raw(X, (long long)r * op->ld[0] + v * 8, xdt);
+            if (W) gw[u] = load8_raw(W, v * 8, 0);
+            if (Bv) bw[u] = load8_raw(Bv, v * 8, 0);
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int v = v0 + u * step;
+            if (v >= nvec) continue;
+            float f[8], g[8];
+            unpack8_raw(rx[u], xdt, f);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) f[e] = (f[e] - mean) * rstd;
+            if (W) {
+                unpack8_raw(gw[u], 0, g);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) f[e] *= g[e];
             }
-            store8(O, (long long)r * op->ld[1] + first * 8, odt, keep);
-        }
-        return;
-    }
-    for (int v = first; v < nvec; v += step) {
-        float f[8], g[8];
-        load8(X, (long long)r * op->ld[0] + v * 8, xdt, f);
+            if (Bv) {
+                unpack8_raw(bw[u], 0, g);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) f[e] = (f[e] - mean) * rstd;
-        if (W) {
-            load8(W, v * 8, 0, g);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) f[e] *= g[e];
+                for (int e = 0; e < 8; ++e) f[e] += g[e];
+            }
+            store8(O, (long long)r * op->ld[1] + v * 8, odt, f);
         }
-        if (Bv) {
-            load8(Bv, v * 8, 0, g);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) f[e] += g[e];
-        }
-        store8(O, (long long)r * op->ld[1] + v * 8, odt, f);
     }
 }
 
