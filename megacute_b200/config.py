@@ -71,4 +71,4 @@ ARGMAX_MAX_CHUNKS = 256         # column chunks per row of an argmax (the mergin
 ACT_CODE = {None: 0, "identity": 0, "relu": 1, "silu": 2, "gelu_tanh": 3, "gelu": 3, "exp": 4, "neg": 5,
             "sigmoid": 6, "square": 7, "swiglu": 8}
 BINARY_CODE = {"add": 0, "sub": 1, "mul": 2, "max": 3, "min": 4}
-EW_UNARY, EW_BINARY, EW_SWIGLU, EW_MODULATE, EW_ROPE = range(5)
+EW_UNARY, EW_BINARY, EW_SWIGLU, EW_MODULATE, EW_ROPE, EW_GATED = range(6)

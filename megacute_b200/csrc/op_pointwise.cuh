@@ -7,7 +7,7 @@
 namespace mk {
 
 constexpr int kEwRows = 32, kEwCols = 512;                 // config.py EW_ROWS / EW_COLS
-enum { EW_UNARY = 0, EW_BINARY, EW_SWIGLU, EW_MODULATE, EW_ROPE };
+enum { EW_UNARY = 0, EW_BINARY, EW_SWIGLU, EW_MODULATE, EW_ROPE, EW_GATED };
 enum { BIN_ADD = 0, BIN_SUB, BIN_MUL, BIN_MAX, BIN_MIN };
 
 __device__ __forceinline__ float apply_bin(int fn, float a, float b) {
@@ -201,6 +201,54 @@ static __device__ __noinline__ void eltwise_tile(const mk_op_desc* op, int r0, i
     }
 }
 
+// EW_GATED: out = fn(a, b * c[r / group]) -- a gated residual, x + y * gate[image] (passes.fuse_pointwise).  a and b
+// stream (two rows in flight), the gate row of a tile is loaded once when the tile lies in one group.
+static __device__ __noinline__ void eltwise_tile_gated(const mk_op_desc* op, int r0, int c0, int rows, int cols) {
+    const int fn = op->i[3], group = op->i[4];
+    const int adt = op->i[6], bdt = op->i[7], cdt = op->i[8], odt = op->i[9];
+    const void* A = reinterpret_cast<const void*>(op->ptr[0]);
+    const void* B = reinterpret_cast<const void*>(op->ptr[1]);
+    const void* G = reinterpret_cast<const void*>(op->ptr[2]);
+    void* O = reinterpret_cast<void*>(op->ptr[3]);
+    const int vpr = cols >> 3;
+    const int tpr = vpr <= 1 ? 1 : vpr <= 2 ? 2 : vpr <= 4 ? 4 : vpr <= 8 ? 8 : vpr <= 16 ? 16 : vpr <= 32 ? 32 : 64;
+    const int rpp = kComputeThreads / tpr;
+    const int vec = threadIdx.x & (tpr - 1), rowp = threadIdx.x / tpr;
+    if (vec >= vpr) return;
+    const int col = c0 + vec * 8;
+    const bool one = (r0 / group) == ((r0 + rows - 1) / group);
+    float gt[8];
+    if (one) load8(G, (long long)(r0 / group) * op->ld[2] + col, cdt, gt);
+    constexpr int UN = 2;
+    for (int rr = rowp; rr < rows; rr += UN * rpp) {
+        Raw8 ra[UN], rb[UN];
+#pragma unroll
+        for (int u = 0; u < UN; ++u) {
+            const int r = r0 + rr + u * rpp;
+            if (rr + u * rpp >= rows) continue;
+            ra[u] = load8_raw(A, (long long)r * op->ld[0] + col, adt);
+            rb[u] = load8_raw(B, (long long)r * op->ld[1] + col, bdt);
+        }
+#pragma unroll
+        for (int u = 0; u < UN; ++u) {
+            const int r = r0 + rr + u * rpp;
+            if (rr + u * rpp >= rows) continue;
+            float a[8], b[8];
+            unpack8_raw(ra[u], adt, a);
+            unpack8_raw(rb[u], bdt, b);
+            if (!one) load8(G, (long long)(r / group) * op->ld[2] + col, cdt, gt);
+            if (fn == BIN_ADD) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) a[e] = fmaf(b[e], gt[e], a[e]);
+            } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) a[e] = apply_bin(fn, a[e], b[e] * gt[e]);
+            }
+            store8(O, (long long)r * op->ld[3] + col, odt, a);
+        }
+    }
+}
+
 // MK_OP_ELTWISE.  ptr 0 a (x / gate), 1 b (b / up / scale / cos), 2 c (shift / sin), 3 out
 // i 0 R, 1 C, 2 mode, 3 fn (activation or binary code), 4 group (rows of a per row of b; rope: seq),
 //   5 head_dim (rope), 6..9 dtypes of a, b, c, out (DT_*).  args: 0 row tile, 1 col tile.
@@ -239,6 +287,7 @@ static __device__ __noinline__ void op_eltwise(const mk_op_desc* op, int a0, int
         }
         return;
     }
+    if (mode == EW_GATED) { eltwise_tile_gated(op, r0, c0, rows, cols); return; }
     const bool all16 = adt != DT_F32 && (mode == EW_UNARY || bdt != DT_F32) && (mode != EW_MODULATE || cdt != DT_F32);
     if (all16) {
         switch (mode) {
@@ -260,7 +309,7 @@ static __device__ __noinline__ void op_eltwise(const mk_op_desc* op, int a0, int
 // A row (or a lane's share of it) of at most NPER (up to 4) vectors per thread stays in registers between the two passes: every
 // vector is requested before the first is used, and gain and bias come in pairs.  (Requested one by one,
 // the vectors of a 2048-column row cost eight L2 round trips in each pass: 11 us per 16-row instruction.)
-template <int NPER>
+template <int NPER, bool MOD>
 __device__ __forceinline__ void norm_kept(const mk_op_desc* op, int r, int first, int step, int nvec, bool live, uint8_t* work) {
     const int Cc = op->i[1], rms = op->i[2], rpi = op->i[3], xdt = op->i[4], odt = op->i[5];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -268,6 +317,9 @@ __device__ __forceinline__ void norm_kept(const mk_op_desc* op, int r, int first
     void* O = reinterpret_cast<void*>(op->ptr[1]);
     const void* W = reinterpret_cast<const void*>(op->ptr[2]);
     const void* Bv = reinterpret_cast<const void*>(op->ptr[3]);
+    const void* Sc = reinterpret_cast<const void*>(op->ptr[4]);          // adaLN modulation fused in (passes.fuse_pointwise), or null
+    const void* Sh = reinterpret_cast<const void*>(op->ptr[5]);
+    const long long grow = live ? r / max(1, op->i[6]) : 0;
     Raw8 kr[NPER];
 #pragma unroll
     for (int u = 0; u < NPER; ++u) {
@@ -298,16 +350,20 @@ __device__ __forceinline__ void norm_kept(const mk_op_desc* op, int r, int first
     const float mean = rms ? 0.f : s / (float)Cc;
     const float var = ss / (float)Cc - mean * mean;
     const float rstd = rsqrt_approx(var + op->f[0]);
-    constexpr int NB = NPER < 2 ? NPER : 2;
+    constexpr int NB = (NPER < 2 || MOD) ? 1 : 2;                  // (with the modulation's two more operands: one at a time)
 #pragma unroll
     for (int u0 = 0; u0 < NPER; u0 += NB) {
-        Raw8 gw[NB], bw[NB];
+        Raw8 gw[NB], bw[NB], sw[MOD ? NB : 1], tw[MOD ? NB : 1];
 #pragma unroll
         for (int u = 0; u < NB; ++u) {
             const int v = first + (u0 + u) * step;
             if (v < nvec) {
                 if (W) gw[u] = load8_raw(W, v * 8, 0);
                 if (Bv) bw[u] = load8_raw(Bv, v * 8, 0);
+                if (MOD) {
+                    sw[u] = load8_raw(Sc, grow * op->ld[4] + v * 8, op->i[7]);
+                    tw[u] = load8_raw(Sh, grow * op->ld[5] + v * 8, op->i[8]);
+                }
             }
         }
 #pragma unroll
@@ -328,13 +384,22 @@ __device__ __forceinline__ void norm_kept(const mk_op_desc* op, int r, int first
 #pragma unroll
                 for (int e = 0; e < 8; ++e) f[e] += g[e];
             }
+            if (MOD) {
+                float h[8];
+                unpack8_raw(sw[u], op->i[7], g);
+                unpack8_raw(tw[u], op->i[8], h);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) f[e] = fmaf(f[e], 1.0f + g[e], h[e]);
+            }
             store8(O, (long long)r * op->ld[1] + v * 8, odt, f);
         }
     }
 }
 
-// MK_OP_NORM.  ptr 0 x, 1 out, 2 weight, 3 bias; i 0 R, 1 C, 2 rms, 3 rows per instruction (8: one
-// row per warp, 1: one row over the whole CTA), 4 x dtype, 5 out dtype; f 0 eps.  args: 0 row tile.
+// MK_OP_NORM.  ptr 0 x, 1 out, 2 weight, 3 bias, 4 scale, 5 shift (adaLN modulation of the normalised row fused in:
+// out = norm(x) * (1 + scale[r / group]) + shift[r / group]; or null); i 0 R, 1 C, 2 rms, 3 rows per instruction (8: one
+// row per warp, 1: one row over the whole CTA), 4 x dtype, 5 out dtype, 6 group, 7 scale dtype, 8 shift dtype; f 0 eps.
+// args: 0 row tile.
 // var = E[x^2] - mean^2 in fp32 (as the reference's norm kernel, megacute/ops/norm.py:94-114).
 static __device__ __noinline__ void op_norm(const mk_op_desc* op, int a0, uint8_t* work) {
     const int R = op->i[0], Cc = op->i[1], rms = op->i[2], rpi = op->i[3], xdt = op->i[4], odt = op->i[5];
@@ -350,9 +415,10 @@ static __device__ __noinline__ void op_norm(const mk_op_desc* op, int a0, uint8_
     else { r = a0 * kComputeWarps + warp; first = lane; step = 32; }
     const bool live = r < R;
     const int nper = (nvec + step - 1) / step;          // vectors per thread
-    if (nper <= 1) { norm_kept<1>(op, r, first, step, nvec, live, work); return; }
-    if (nper <= 2) { norm_kept<2>(op, r, first, step, nvec, live, work); return; }
-    if (nper <= 4) { norm_kept<4>(op, r, first, step, nvec, live, work); return; }
+    if (op->ptr[4] && nper <= 4) { norm_kept<4, true>(op, r, first, step, nvec, live, work); return; }
+    if (nper <= 1) { norm_kept<1, false>(op, r, first, step, nvec, live, work); return; }
+    if (nper <= 2) { norm_kept<2, false>(op, r, first, step, nvec, live, work); return; }
+    if (nper <= 4) { norm_kept<4, false>(op, r, first, step, nvec, live, work); return; }
     // longer rows: two passes over global memory, four vectors requested at a time
     float s = 0.f, ss = 0.f;
     constexpr int UN = 4;
@@ -412,6 +478,14 @@ static __device__ __noinline__ void op_norm(const mk_op_desc* op, int a0, uint8_
                 unpack8_raw(bw[u], 0, g);
 #pragma unroll
                 for (int e = 0; e < 8; ++e) f[e] += g[e];
+            }
+            if (op->ptr[4]) {                                   // adaLN modulation fused in
+                const long long grow = r / max(1, op->i[6]);
+                float h[8];
+                load8(reinterpret_cast<const void*>(op->ptr[4]), grow * op->ld[4] + v * 8, op->i[7], g);
+                load8(reinterpret_cast<const void*>(op->ptr[5]), grow * op->ld[5] + v * 8, op->i[8], h);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) f[e] = fmaf(f[e], 1.0f + g[e], h[e]);
             }
             store8(O, (long long)r * op->ld[1] + v * 8, odt, f);
         }

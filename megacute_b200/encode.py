@@ -15,7 +15,9 @@ view's first element.  Field meaning per kind (the kernel side repeats it next t
                library when it binds the op to its tcgen05 body: packed weight tiles, tensor maps)
   FINALIZE     ptr ws, out, bias, residual; i R, C, act, out dtype, residual dtype, rows per instruction
   ELTWISE      ptr a, b, c, out; i R, C, mode, fn, group, head_dim, dtypes of a, b, c, out
-  NORM         ptr x, out, weight, bias; i R, C, rms, rows per instruction, x dtype, out dtype; f eps
+               (mode EW_GATED: out = fn(a, b * c[r // group]), a gated residual)
+  NORM         ptr x, out, weight, bias, scale, shift (adaLN modulation fused in, or none); i R, C, rms, rows per
+               instruction, x dtype, out dtype, rows per scale / shift row, their dtypes; f eps
   ATTENTION    ptr q, k, v, out; i batch, seq_q, seq_k, heads, kv_heads, head_dim, causal, out dtype,
                dtype of q / k / v (one for all three: bf16 or fp16); f scale
   ROPE_APPEND  ptr qkv, cos, sin, pos, q_out, k_cache, v_cache; i B, H, KVH, D, max_seq, qkv dtype,
@@ -119,6 +121,8 @@ def fill(d, op: Op, addr) -> None:
         R, Cc = op.out.shape
         if k == "Unary":
             ptrs, ints = [op.x, None, None, op.out], [R, Cc, C.EW_UNARY, C.ACT_CODE[op.fn], 1, 0]
+        elif k == "Binary" and op.gate is not None:         # out = fn(a, b * gate[r // gate_group])
+            ptrs, ints = [op.a, op.b, op.gate, op.out], [R, Cc, C.EW_GATED, C.BINARY_CODE[op.fn], op.gate_group, 0]
         elif k == "Binary":
             ptrs, ints = [op.a, op.b, None, op.out], [R, Cc, C.EW_BINARY, C.BINARY_CODE[op.fn], op.b_group, 0]
         elif k == "SwiGLU":
@@ -130,8 +134,9 @@ def fill(d, op: Op, addr) -> None:
         ints += [dt(v) for v in ptrs]
     elif k == "Norm":
         d.kind = C.OP_NORM
-        ptrs = [op.x, op.out, op.weight, op.bias]
-        ints = [op.x.rows, op.x.cols, int(bool(op.rms)), norm_rows(op.x.rows), dt(op.x), dt(op.out)]
+        ptrs = [op.x, op.out, op.weight, op.bias, op.scale, op.shift]
+        ints = [op.x.rows, op.x.cols, int(bool(op.rms)), norm_rows(op.x.rows), dt(op.x), dt(op.out),
+                int(op.group or 1), dt(op.scale), dt(op.shift)]
         d.f[0] = float(op.eps)
     elif k == "Attention":
         d.kind = C.OP_ATTENTION

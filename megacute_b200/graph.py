@@ -112,10 +112,10 @@ OP_TABLE = {
     "LinearSplit":     (("x", "w", "norm_w"), ("ws",), ("splits", "rms_eps", "bn")),
     "SplitFinalize":   (("ws", "bias", "residual"), ("out", "ws"), ("act",)),
     "Unary":           (("x",), ("out",), ("fn",)),
-    "Binary":          (("a", "b"), ("out",), ("fn", "b_group")),
+    "Binary":          (("a", "b", "gate"), ("out",), ("fn", "b_group", "gate_group")),
     "SwiGLU":          (("gate", "up"), ("out",), ("act",)),
     "Modulate":        (("x", "scale", "shift"), ("out",), ("group",)),
-    "Norm":            (("x", "weight", "bias"), ("out",), ("eps", "rms")),
+    "Norm":            (("x", "weight", "bias", "scale", "shift"), ("out",), ("eps", "rms", "group")),
     "Rope":            (("x", "cos", "sin"), ("out",), ("heads", "head_dim", "seq")),
     "Attention":       (("q", "k", "v"), ("out",),
                         ("batch", "seq_q", "seq_k", "heads", "head_dim", "causal", "scale", "kv_heads")),
@@ -231,6 +231,8 @@ def _chk_binary(o):
     assert o.a.shape == o.out.shape
     assert o.b.cols == o.a.cols
     assert o.a.rows == o.b.rows * o.b_group, "binary: b rows * b_group must equal a rows"
+    if o.gate is not None:          # set by passes.fuse_gated_residual only: out = fn(a, b * gate[r // gate_group])
+        assert o.b_group == 1 and o.gate.shape == (o.a.rows // o.gate_group, o.a.cols)
 
 
 def _chk_swiglu(o):
@@ -248,6 +250,8 @@ def _chk_norm(o):
     for p in (o.weight, o.bias):
         if p is not None:
             assert p.shape == (1, o.x.cols)
+    if o.scale is not None:         # set by passes.fuse_norm_modulate only: out = norm(x) * (1 + scale[r // group]) + shift[r // group]
+        assert o.scale.shape == o.shift.shape == (o.x.rows // o.group, o.x.cols)
 
 
 def _chk_rope(o):

@@ -421,8 +421,43 @@ def split_argmax(g: Graph, sm_count: int) -> Graph:
     return out
 
 
+def fuse_pointwise(g: Graph) -> Graph:
+    """Two pointwise pairs of an adaLN block become one op each (no counterpart among the reference's passes; its graphs
+    run them as written, examples/dit/model.py):
+
+    * ``Norm -> Modulate``: ``norm(x) * (1 + scale[g]) + shift[g]`` in the norm's own pass over the row;
+    * ``Binary(mul, y, gate[g]) -> Binary(add, x, .)``: ``x + y * gate[g]`` (a gated residual).
+
+    Each pair's intermediate is a runtime-private tensor nothing else reads.  A pointwise op over an activation costs
+    one read and one write of it plus a dependency hop: a DiT block drops from eight such ops to four.
+    MEGACUTE_B200_NO_POINTWISE_FUSION=1 keeps the ops apart."""
+    if os.environ.get("MEGACUTE_B200_NO_POINTWISE_FUSION") == "1":
+        return g
+    out = g.derive()
+    ops: list[Op] = []
+    for i, op in enumerate(g.ops):
+        prev = ops[-1] if ops else None
+        private = lambda v: v.buf.kind == "temp" and not _reads_buffer(g.ops[i + 1:], v.buf, g.outputs)
+        if (op.kind == "Modulate" and prev is not None and prev.kind == "Norm" and prev.scale is None
+                and op.x.same(prev.out) and private(prev.out)):
+            ops[-1] = prev.clone(out=op.out, scale=op.scale, shift=op.shift, group=op.group)
+            continue
+        if (op.kind == "Binary" and op.fn == "add" and op.b_group == 1 and op.gate is None and prev is not None
+                and prev.kind == "Binary" and prev.fn == "mul" and prev.gate is None and prev.b_group > 1):
+            for mine, other in ((op.b, op.a), (op.a, op.b)):
+                if mine.same(prev.out) and private(prev.out) and other.shape == op.out.shape:
+                    ops[-1] = op.clone(a=other, b=prev.a, gate=prev.b, gate_group=prev.b_group)
+                    break
+            else:
+                ops.append(op)
+            continue
+        ops.append(op)
+    out.ops = ops
+    return out
+
+
 def run_all(g: Graph, sm_count: int) -> Graph:
-    """The pass pipeline of ``compile`` (reference order: runtime.py:235, plus promote_temps and
-    fuse_finalize_attention)."""
+    """The pass pipeline of ``compile`` (reference order: runtime.py:235, plus wide_tiles, split_argmax,
+    fuse_pointwise, promote_temps and fuse_finalize_attention)."""
     g = split_argmax(split_kv(fuse_rope_attention(wide_tiles(split_k(fold_norms(g), sm_count), sm_count)), sm_count), sm_count)
-    return fuse_finalize_attention(promote_temps(g))
+    return fuse_finalize_attention(promote_temps(fuse_pointwise(g)))

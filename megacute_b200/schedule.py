@@ -163,6 +163,9 @@ def tile_op(op: Op, sm_count: int) -> Tiled:
             gq = op.b_group
             acc = [t(op.a), _acc(op.b, READ, r0 // gq, -(-np.minimum(r1, R) // gq), c0, c1, n=n, covers=False),
                    t(op.out, WRITE)]
+            if op.gate is not None:
+                gg = op.gate_group
+                acc.append(_acc(op.gate, READ, r0 // gg, -(-np.minimum(r1, R) // gg), c0, c1, n=n, covers=False))
         elif k == "SwiGLU":
             acc = [t(op.gate), t(op.up), t(op.out, WRITE)]
         elif k == "Modulate":
@@ -179,6 +182,10 @@ def tile_op(op: Op, sm_count: int) -> Tiled:
         n = len(rt)
         acc = [_acc(op.x, READ, rt * rows, (rt + 1) * rows, n=n), _acc(op.weight, READ, n=n), _acc(op.bias, READ, n=n),
                _acc(op.out, WRITE, rt * rows, (rt + 1) * rows, n=n)]
+        if op.scale is not None:
+            gq = op.group
+            for v in (op.scale, op.shift):
+                acc.append(_acc(v, READ, rt * rows // gq, -(-np.minimum((rt + 1) * rows, R) // gq), n=n, covers=False))
         return Tiled(_args(n, rt), [a for a in acc if a is not None])
     if k == "Attention":
         D, QP = op.head_dim, C.ATTN_BQ

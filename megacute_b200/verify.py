@@ -66,7 +66,10 @@ def operand_windows(op) -> dict:
         return {"x": op.out.shape, "out": op.out.shape}
     if k == "Binary":
         R, Cc = op.out.shape
-        return {"a": (R, Cc), "b": (_ceil(R, op.b_group), Cc), "out": (R, Cc)}
+        w = {"a": (R, Cc), "b": (_ceil(R, op.b_group), Cc), "out": (R, Cc)}
+        if op.gate is not None:
+            w["gate"] = (_ceil(R, op.gate_group), Cc)
+        return w
     if k == "SwiGLU":
         return {"gate": op.out.shape, "up": op.out.shape, "out": op.out.shape}
     if k == "Modulate":
@@ -78,7 +81,10 @@ def operand_windows(op) -> dict:
         return {"x": (R, Cc), "cos": (min(op.seq, R), op.head_dim), "sin": (min(op.seq, R), op.head_dim), "out": (R, Cc)}
     if k == "Norm":
         R, Cc = op.x.shape
-        return {"x": (R, Cc), "out": (R, Cc), "weight": (1, Cc), "bias": (1, Cc)}
+        w = {"x": (R, Cc), "out": (R, Cc), "weight": (1, Cc), "bias": (1, Cc)}
+        if op.scale is not None:
+            w["scale"] = w["shift"] = (_ceil(R, op.group), Cc)
+        return w
     if k == "Attention":
         D = op.head_dim
         q = (op.batch * op.seq_q, op.heads * D)
