@@ -309,7 +309,7 @@ static __device__ __noinline__ void op_eltwise(const mk_op_desc* op, int a0, int
 // A row (or a lane's share of it) of at most NPER (up to 4) vectors per thread stays in registers between the two passes: every
 // vector is requested before the first is used, and gain and bias come in pairs.  (Requested one by one,
 // the vectors of a 2048-column row cost eight L2 round trips in each pass: 11 us per 16-row instruction.)
-template <int NPER, bool MOD>
+template <int NPER, bool MOD, bool X16 = false>
 __device__ __forceinline__ void norm_kept(const mk_op_desc* op, int r, int first, int step, int nvec, bool live, uint8_t* work) {
     const int Cc = op->i[1], rms = op->i[2], rpi = op->i[3], xdt = op->i[4], odt = op->i[5];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -320,18 +320,18 @@ __device__ __forceinline__ void norm_kept(const mk_op_desc* op, int r, int first
     const void* Sc = reinterpret_cast<const void*>(op->ptr[4]);          // adaLN modulation fused in (passes.fuse_pointwise), or null
     const void* Sh = reinterpret_cast<const void*>(op->ptr[5]);
     const long long grow = live ? r / max(1, op->i[6]) : 0;
-    Raw8 kr[NPER];
+    Raw8x<X16> kr[NPER];                                  // (a 16-bit row: four registers per vector, eight vectors per lane fit)
 #pragma unroll
     for (int u = 0; u < NPER; ++u) {
         const int v = first + u * step;
-        if (live && v < nvec) kr[u] = load8_raw(X, (long long)r * op->ld[0] + v * 8, xdt);
+        if (live && v < nvec) kr[u].load(X, (long long)r * op->ld[0] + v * 8, xdt);
     }
     float s = 0.f, ss = 0.f;
 #pragma unroll
     for (int u = 0; u < NPER; ++u) {
         if (live && first + u * step < nvec) {
             float f[8];
-            unpack8_raw(kr[u], xdt, f);
+            kr[u].unpack(xdt, f);
 #pragma unroll
             for (int e = 0; e < 8; ++e) { s += f[e]; ss += f[e] * f[e]; }
         }
@@ -371,7 +371,7 @@ __device__ __forceinline__ void norm_kept(const mk_op_desc* op, int r, int first
             const int v = first + (u0 + u) * step;
             if (v >= nvec) continue;
             float f[8], g[8];
-            unpack8_raw(kr[u0 + u], xdt, f);
+            kr[u0 + u].unpack(xdt, f);
 #pragma unroll
             for (int e = 0; e < 8; ++e) f[e] = (f[e] - mean) * rstd;
             if (W) {
@@ -419,6 +419,7 @@ static __device__ __noinline__ void op_norm(const mk_op_desc* op, int a0, uint8_
     if (nper <= 1) { norm_kept<1, false>(op, r, first, step, nvec, live, work); return; }
     if (nper <= 2) { norm_kept<2, false>(op, r, first, step, nvec, live, work); return; }
     if (nper <= 4) { norm_kept<4, false>(op, r, first, step, nvec, live, work); return; }
+    if (nper <= 8 && xdt != DT_F32 && !op->ptr[4]) { norm_kept<8, false, true>(op, r, first, step, nvec, live, work); return; }
     // longer rows: two passes over global memory, four vectors requested at a time
     float s = 0.f, ss = 0.f;
     constexpr int UN = 4;
