@@ -20,7 +20,7 @@ CSRC = PKG / "csrc"
 CHECK_BUILD = os.environ.get("MEGACUTE_B200_CHECK") == "1"
 LIB_PATH = pathlib.Path(os.environ.get("MEGACUTE_B200_LIB", PKG / ("libmegacute_b200_check.so" if CHECK_BUILD else "libmegacute_b200.so")))
 # Relocatable device code: each op body is its own translation unit so that ptxas allocates its
-# registers independently (csrc/ops.cuh says why).  -maxrregcount is the cap of a 10-warp CTA
+# registers independently (csrc/ops.cuh says why).  -maxrregcount is the cap of an 11-warp CTA
 # (three warps share one SM sub-partition's 16 K registers); callees in other translation units do
 # not see the kernel's __launch_bounds__.
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-rdc=true",

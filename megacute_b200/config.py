@@ -8,7 +8,7 @@ runtime's own choices.
 # ---- CTA shape: 8 compute warps + 1 producer warp that streams weights ahead of them + 1 finisher warp
 COMPUTE_WARPS = 8
 COMPUTE_THREADS = 32 * COMPUTE_WARPS
-NUM_THREADS = COMPUTE_THREADS + 64     # + producer warp + finisher warp
+NUM_THREADS = COMPUTE_THREADS + 96     # + producer warp + finisher warp + feeder warp
 
 # ---- weight-streaming GEMV path (linear with <= 8 activation rows)
 GEMV_MAX_ROWS = 8

@@ -82,6 +82,11 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
     } else if (warp == kFinisherWarp) {
         // ---------------- finisher warp: epilogues of the streaming linear ----------------
         mk_gemv_finisher(p);
+    } else if (warp == kFeederWarp) {
+        // ---------------- feeder warp: tiles and MMAs of the tcgen05 prefill attention ----------------
+        // (a warp of its own rather than a branch of the producer's loop: the call in that loop cost every decode step
+        // 0.5 %, whether or not the graph had such an op; here a graph without one costs a walk over the instruction list)
+        mk_attention_feeder(p);
     } else {
         // ---------------- compute warps ----------------
         // Instruction metadata runs one instruction ahead in shared memory (Meta): while instruction

@@ -14,9 +14,10 @@ namespace mk {
 // ---- CTA shape (mirrors megacute_b200/config.py) --------------------------------------------
 constexpr int kComputeWarps = 8;
 constexpr int kComputeThreads = kComputeWarps * 32;
-constexpr int kThreads = kComputeThreads + 64;           // + one producer warp + one finisher warp
+constexpr int kThreads = kComputeThreads + 96;           // + one producer warp + one finisher warp + one feeder warp
 constexpr int kProducerWarp = kComputeWarps;
 constexpr int kFinisherWarp = kComputeWarps + 1;
+constexpr int kFeederWarp = kComputeWarps + 2;           // tile requests and MMA issue of the tcgen05 prefill attention
 
 // ---- shared memory map -----------------------------------------------------------------------
 constexpr int kGemvRows = 8;                              // weight rows per ring stage

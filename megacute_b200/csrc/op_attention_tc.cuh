@@ -21,8 +21,8 @@
 //                    contiguous) is the MN-major B operand; O lives in tensor memory, columns 256..319
 //   out = O / l      read back with tcgen05.ld, half a row per thread; a fully masked row yields 0
 //
-// Tile requests and MMA issue are ONE thread of the producer warp (mk_attention_tc_feed, called from the producer's
-// walk over the instruction list): it polls the barriers without blocking (mbarrier.test_wait costs ~1 ns) and does
+// Tile requests and MMA issue are ONE thread of the feeder warp (mk_attention_feeder walks the CTA's instruction list
+// for these ops): it polls the barriers without blocking (mbarrier.test_wait costs ~1 ns) and does
 // whatever is possible next -- K_j into two buffers, V_j into one, each refilled as soon as the product that read
 // it has completed; S of block j + 1 (two S tiles in tensor memory) ahead of P V of block j, so the tensor core works
 // on the next scores while the softmax of this block runs.  The compute warps tell it through `attn_go` that the
@@ -91,7 +91,7 @@ __device__ __forceinline__ void tc_mma_i(uint32_t tmem_d, uint64_t adesc, uint64
 // barrier of the two warps (w, w + 4) that share the query rows of tensor-memory quarter q
 __device__ __forceinline__ void at_pair_sync(int q) { asm volatile("bar.sync %0, 64;" ::"r"(2 + q) : "memory"); }
 
-// Tile requests and MMA issue of one instruction: one thread of the producer warp.  Returns false when aborting.
+// Tile requests and MMA issue of one instruction: one thread of the feeder warp.  Returns false when aborting.
 __device__ __forceinline__ bool attention_tc_feed(const Params& p, Ctrl* c, uint8_t* work, const mk_op_desc* op, int b, int h, int qi,
                                                   int seq, uint32_t go_parity) {
     constexpr int D = 64;
@@ -215,7 +215,7 @@ __device__ __forceinline__ int op_attention_tc(const Params& p, Ctrl* c, uint8_t
     }
     compute_sync();
     tc_fence_after();
-    if (t == 0) mbar_arrive(&c->attn_go);                               // the feeding thread (producer warp) may start
+    if (t == 0) mbar_arrive(&c->attn_go);                               // the feeding thread (feeder warp) may start
     const uint32_t tmem = *(volatile uint32_t*)&c->tmem_base;
     uint8_t* ps = work + kAtPOff;
     __nv_bfloat16* xb = reinterpret_cast<__nv_bfloat16*>(work);          // 512 bytes in front of the tiles: 2 x 128 row maxima (bf16),

@@ -80,10 +80,6 @@ struct StageCursor {
     bool kv_gated;           // unfused form: the first copy waits for kv_go
     const uint8_t* kv_src[2];
     long long kv_pitch[2];   // bytes between cache rows
-    // prefill attention on tcgen05 (op_attention_tc.cuh): the producer warp requests its tiles and issues its MMAs
-    bool attn;
-    const mk_op_desc* at_op;
-    int at_a0, at_a1, at_a2;
 
     // position on the next streaming-linear instruction at or after `idx`
     __device__ __forceinline__ void seek(const Params& p) {
@@ -92,12 +88,6 @@ struct StageCursor {
             const int opi = in.opi - 1;
             if (opi < 0 || opi >= p.n_ops) { idx = p.n_insts; return; }
             const mk_op_desc* op = p.ops + opi;
-            attn = false;
-            if (op->kind == MK_OP_ATTENTION && op->ptr[11]) {
-                attn = true; gemm = false; kv = false; seq = in.seq;
-                at_op = op; at_a0 = in.a0; at_a1 = in.a1; at_a2 = in.a2;
-                return;
-            }
             if (op->kind == MK_OP_DECODE_ATTN && op->i[11]) {
                 const int KVH = op->i[2], L = op->i[4], S = op->i[5];
                 const bool fused = op->i[6] != 0;
@@ -151,7 +141,7 @@ struct StageCursor {
     }
     __device__ __forceinline__ bool valid(const Params& p) const { return idx < p.n_insts; }
     __device__ __forceinline__ void advance(const Params& p) {
-        if (gemm || kv || attn) {                     // (the L2 prefetch cursor: whole instruction at once)
+        if (gemm || kv) {                             // (the L2 prefetch cursor: whole instruction at once)
             idx += gridDim.x;
             seek(p);
             return;
@@ -166,7 +156,7 @@ struct StageCursor {
     __device__ __forceinline__ void piece(int lane, const __nv_bfloat16*& src, int& bytes, int& dst_off) const {
         const bool swi = flags & GEMV_F_SWIGLU;
         src = w; bytes = 0; dst_off = 0;
-        if (gemm || kv || attn) return;
+        if (gemm || kv) return;
         if (flags & GEMV_F_UNITS) {
             const int r = lane & 15;
             const int o = o0 + (swi ? g >> 1 : g) * 16 + r;
@@ -181,9 +171,6 @@ struct StageCursor {
         }
     }
 };
-
-// (op_attention_tc.cuh, its own translation unit)
-__device__ bool mk_attention_tc_feed(const Params& p, const mk_op_desc* op, int a0, int a1, int a2, int seq, uint32_t go_parity);
 
 // Producer warp main loop.  TRACE: role-0 records (seq, first stage issued, -, last stage issued).
 template <bool TRACE>
@@ -238,18 +225,7 @@ __device__ __forceinline__ void producer_loop(const Params& p, Ctrl* c, uint8_t*
         mode = kind;
         return true;
     };
-    uint32_t attngo = 0;                             // parity of attn_go for the next tcgen05 attention instruction
     while (rc.valid(p)) {
-        if (rc.attn) {
-            // prefill attention on tcgen05: lane 0 requests the instruction's tiles and issues its MMAs (the ring is not used)
-            int ok = 1;
-            if (lane == 0) ok = mk_attention_tc_feed(p, rc.at_op, rc.at_a0, rc.at_a1, rc.at_a2, rc.seq, attngo) ? 1 : 0;
-            if (!__shfl_sync(0xffffffffu, ok, 0)) return;
-            attngo ^= 1u;
-            rc.idx += gridDim.x;
-            rc.seek(p);
-            continue;
-        }
         if (rc.kv) {
             // decode attention, many-sequence form: one tile of 16 whole cache rows per slot, as four
             // copies of four rows issued by four lanes at once; K and V tiles alternate.  The whole

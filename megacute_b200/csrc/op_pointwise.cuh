@@ -306,11 +306,13 @@ static __device__ __noinline__ void op_eltwise(const mk_op_desc* op, int a0, int
     }
 }
 
-// A row (or a lane's share of it) of at most NPER (up to 4) vectors per thread stays in registers between the two passes: every
+// (Each instance is a function of its own: inlined into one body, the longer variants' registers and spills fell on
+// the one-vector-per-thread case too, which is the norm of every decode step.)
+// A row (or a lane's share of it) of at most NPER vectors per thread stays in registers between the two passes: every
 // vector is requested before the first is used, and gain and bias come in pairs.  (Requested one by one,
 // the vectors of a 2048-column row cost eight L2 round trips in each pass: 11 us per 16-row instruction.)
 template <int NPER, bool MOD, bool X16 = false>
-__device__ __forceinline__ void norm_kept(const mk_op_desc* op, int r, int first, int step, int nvec, bool live, uint8_t* work) {
+static __device__ __noinline__ void norm_kept(const mk_op_desc* op, int r, int first, int step, int nvec, bool live, uint8_t* work) {
     const int Cc = op->i[1], rms = op->i[2], rpi = op->i[3], xdt = op->i[4], odt = op->i[5];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const void* X = reinterpret_cast<const void*>(op->ptr[0]);
@@ -326,6 +328,25 @@ __device__ __forceinline__ void norm_kept(const mk_op_desc* op, int r, int first
         const int v = first + u * step;
         if (live && v < nvec) kr[u].load(X, (long long)r * op->ld[0] + v * 8, xdt);
     }
+    // gain, bias (and modulation) of the first batch are requested with the row: for a row of one vector per thread --
+    // the norm of a decode step -- that is ONE L2 round trip on the instruction's critical path instead of two
+    constexpr int NB = (NPER < 2 || MOD) ? 1 : 2;                  // (with the modulation's two more operands: one at a time)
+    Raw8 gw[NB], bw[NB], sw[MOD ? NB : 1], tw[MOD ? NB : 1];
+    auto request = [&](int u0) {
+#pragma unroll
+        for (int u = 0; u < NB; ++u) {
+            const int v = first + (u0 + u) * step;
+            if (live && v < nvec) {
+                if (W) gw[u] = load8_raw(W, v * 8, 0);
+                if (Bv) bw[u] = load8_raw(Bv, v * 8, 0);
+                if (MOD) {
+                    sw[u] = load8_raw(Sc, grow * op->ld[4] + v * 8, op->i[7]);
+                    tw[u] = load8_raw(Sh, grow * op->ld[5] + v * 8, op->i[8]);
+                }
+            }
+        }
+    };
+    request(0);
     float s = 0.f, ss = 0.f;
 #pragma unroll
     for (int u = 0; u < NPER; ++u) {
@@ -350,22 +371,9 @@ __device__ __forceinline__ void norm_kept(const mk_op_desc* op, int r, int first
     const float mean = rms ? 0.f : s / (float)Cc;
     const float var = ss / (float)Cc - mean * mean;
     const float rstd = rsqrt_approx(var + op->f[0]);
-    constexpr int NB = (NPER < 2 || MOD) ? 1 : 2;                  // (with the modulation's two more operands: one at a time)
 #pragma unroll
     for (int u0 = 0; u0 < NPER; u0 += NB) {
-        Raw8 gw[NB], bw[NB], sw[MOD ? NB : 1], tw[MOD ? NB : 1];
-#pragma unroll
-        for (int u = 0; u < NB; ++u) {
-            const int v = first + (u0 + u) * step;
-            if (v < nvec) {
-                if (W) gw[u] = load8_raw(W, v * 8, 0);
-                if (Bv) bw[u] = load8_raw(Bv, v * 8, 0);
-                if (MOD) {
-                    sw[u] = load8_raw(Sc, grow * op->ld[4] + v * 8, op->i[7]);
-                    tw[u] = load8_raw(Sh, grow * op->ld[5] + v * 8, op->i[8]);
-                }
-            }
-        }
+        if (u0 > 0) request(u0);
 #pragma unroll
         for (int u = 0; u < NB; ++u) {
             const int v = first + (u0 + u) * step;
@@ -416,7 +424,40 @@ static __device__ __noinline__ void op_norm(const mk_op_desc* op, int a0, uint8_
     const bool live = r < R;
     const int nper = (nvec + step - 1) / step;          // vectors per thread
     if (op->ptr[4] && nper <= 4) { norm_kept<4, true>(op, r, first, step, nvec, live, work); return; }
-    if (nper <= 1) { norm_kept<1, false>(op, r, first, step, nvec, live, work); return; }
+    if (nper <= 1) {
+        // one vector per thread -- the norm of every decode step -- is done here, without a further call: the row's
+        // vector, its gain and its bias are requested together (one L2 round trip on the instruction's critical path)
+        float keep[8], gk[8], bk[8];
+        float s = 0.f, ss = 0.f;
+        if (live && first < nvec) {
+            load8(X, (long long)r * op->ld[0] + first * 8, xdt, keep);
+            if (W) load8(W, first * 8, 0, gk);
+            if (Bv) load8(Bv, first * 8, 0, bk);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) { s += keep[e]; ss += keep[e] * keep[e]; }
+        }
+        s = warp_sum(s);
+        ss = warp_sum(ss);
+        if (rpi == 1) {
+            float* sh = reinterpret_cast<float*>(work);
+            if (lane == 0) { sh[warp * 2] = s; sh[warp * 2 + 1] = ss; }
+            compute_sync();
+            s = 0.f; ss = 0.f;
+#pragma unroll
+            for (int w8 = 0; w8 < kComputeWarps; ++w8) { s += sh[w8 * 2]; ss += sh[w8 * 2 + 1]; }
+        }
+        if (!live || first >= nvec) return;
+        const float mean = rms ? 0.f : s / (float)Cc;
+        const float rstd = rsqrt_approx(ss / (float)Cc - mean * mean + eps);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            keep[e] = (keep[e] - mean) * rstd;
+            if (W) keep[e] *= gk[e];
+            if (Bv) keep[e] += bk[e];
+        }
+        store8(O, (long long)r * op->ld[1] + first * 8, odt, keep);
+        return;
+    }
     if (nper <= 2) { norm_kept<2, false>(op, r, first, step, nvec, live, work); return; }
     if (nper <= 4) { norm_kept<4, false>(op, r, first, step, nvec, live, work); return; }
     if (nper <= 8 && xdt != DT_F32 && !op->ptr[4]) { norm_kept<8, false, true>(op, r, first, step, nvec, live, work); return; }

@@ -26,8 +26,9 @@ __device__ int mk_op_gemm_wide(const Params& p, const mk_op_desc* op, int a0, in
 __device__ void mk_op_attention(const mk_op_desc* op, int a0, int a1, int a2);
 // (the tcgen05 body, for ops the host library attached tensor maps to; returns -1 when aborting)
 __device__ int mk_op_attention_tc(const Params& p, const mk_op_desc* op, int a0, int a1, int a2, int seq);
-// (its tile requests and MMA issue, run by one thread of the producer warp; returns false when aborting)
-__device__ bool mk_attention_tc_feed(const Params& p, const mk_op_desc* op, int a0, int a1, int a2, int seq, uint32_t go_parity);
+// body of the feeder warp: walks the CTA's instruction list and, for every prefill attention bound to the tcgen05 body,
+// requests its tiles and issues its MMAs (one thread); runs until the list ends or the CTA aborts
+__device__ void mk_attention_feeder(const Params& p);
 // (waits for its own dependencies and publishes its own arrivals; returns whether the CTA is aborting)
 __device__ bool mk_op_decode_attn(const Params& p, const mk_op_desc* op, int a0, int a1, int a2, int nwait, int wait_off,
                                   int seq, int narrive, int arrive_off);
