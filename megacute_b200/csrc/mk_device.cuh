@@ -146,7 +146,6 @@ struct Ctrl {                     // lives in the last kCtrlBytes of shared memo
     int abort;                    // set once a wait of this CTA gave up or saw the global abort
     int flag;                     // scratch broadcast word (split-KV last arriver)
     long long t_dep;              // tracing: when the dependencies of the current instruction were met
-    long long t_pub;              // tracing: when its arrivals were published (0: the op left no mark)
     long long t_phase[3];         // tracing: op-internal phase marks (role 2 records)
 };
 static_assert(sizeof(Ctrl) <= kCtrlBytes, "Ctrl outgrew its shared-memory slot");
@@ -548,26 +547,6 @@ __device__ __forceinline__ bool publish(const Params& p, Ctrl* c, int narrive, i
     if (first >= 0) red_release_add(p.counters + first, 1);
     for (int k = threadIdx.x + kComputeThreads; k < narrive; k += kComputeThreads) red_release_add(p.counters + tab[k], 1);
     return false;
-}
-
-// An op body is a function of another translation unit, called through the ABI: on entry it saves the callee-saved
-// registers it is going to use to local memory and on return it loads them back -- for the tile GEMM 62 registers
-// of 256 threads, 63 KB each way, with almost no L1 to hold them.  Measured on batch-64 decode: 1.4 us from the end
-// of the dependency wait to the body's first statement.  So the bodies wait for the instruction's dependencies
-// themselves, behind their entry, and publish its arrivals before they return: both transfers then run while the
-// CTA would be waiting for other SMs anyway.
-struct Sync {
-    int nwait, wait_off, narrive, arrive_off;
-};
-__device__ __forceinline__ bool begin_op(const Params& p, Ctrl* c, const Sync& s, int seq) {
-    const bool aborting = wait_deps(p, c, s.nwait, s.wait_off, seq);
-    if (p.trace_cap > 0 && threadIdx.x == 0) c->t_dep = (long long)globaltimer();
-    return aborting;
-}
-__device__ __forceinline__ bool end_op(const Params& p, Ctrl* c, const Sync& s) {
-    const bool aborting = publish(p, c, s.narrive, s.arrive_off);
-    if (p.trace_cap > 0 && threadIdx.x == 0) c->t_pub = (long long)globaltimer();
-    return aborting;
 }
 
 __device__ __forceinline__ void phase_mark(const Params& p, Ctrl* c, int k) {

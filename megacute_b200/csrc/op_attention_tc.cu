@@ -3,11 +3,9 @@
 #include "ops.cuh"
 
 namespace mk {
-__device__ int mk_op_attention_tc(const Params& p, const mk_op_desc* op, int a0, int a1, int a2, int seq, Sync sy) {
+__device__ int mk_op_attention_tc(const Params& p, const mk_op_desc* op, int a0, int a1, int a2, int seq) {
     const SmemMap m = smem_map();
-    if (begin_op(p, m.ctrl, sy, seq)) return -1;
-    if (op_attention_tc(p, m.ctrl, m.work, op, a0, a1, a2, seq) < 0) return -1;
-    return end_op(p, m.ctrl, sy) ? -1 : 0;
+    return op_attention_tc(p, m.ctrl, m.work, op, a0, a1, a2, seq);
 }
 __device__ void mk_attention_feeder(const Params& p) {
     const SmemMap m = smem_map();

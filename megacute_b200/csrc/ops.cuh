@@ -19,15 +19,13 @@ __device__ int mk_op_gemv_units(const Params& p, const mk_op_desc* op, int o0, i
 // body of the finisher warp (op_gemv_mma.cuh): runs until the CTA's instruction list ends
 __device__ void mk_gemv_finisher(const Params& p);
 __device__ int mk_op_gemv_general(const Params& p, const mk_op_desc* op, int o0, int o1, int seq, int packed_pos);
-// The bodies below wait for the instruction's dependencies and publish its arrivals themselves (Sync; begin_op / end_op
-// say why) and return -1 when the CTA is aborting.
-// (tile GEMM; with tensor maps attached it consumes ring slots: returns the ring position)
-__device__ int mk_op_gemm(const Params& p, const mk_op_desc* op, int a0, int a1, int a2, int seq, int packed_pos, Sync sy);
+// (tile GEMM; with tensor maps attached it consumes ring slots: returns the ring position, -1 when aborting)
+__device__ int mk_op_gemm(const Params& p, const mk_op_desc* op, int a0, int a1, int a2, int seq, int packed_pos);
 // (the same with 128 x 256 output tiles; only for ops the host library bound to the tcgen05 body)
-__device__ int mk_op_gemm_wide(const Params& p, const mk_op_desc* op, int a0, int a1, int a2, int seq, int packed_pos, Sync sy);
-__device__ int mk_op_attention(const Params& p, const mk_op_desc* op, int a0, int a1, int a2, int seq, Sync sy);
-// (the tcgen05 body, for ops the host library attached tensor maps to)
-__device__ int mk_op_attention_tc(const Params& p, const mk_op_desc* op, int a0, int a1, int a2, int seq, Sync sy);
+__device__ int mk_op_gemm_wide(const Params& p, const mk_op_desc* op, int a0, int a1, int a2, int seq, int packed_pos);
+__device__ void mk_op_attention(const mk_op_desc* op, int a0, int a1, int a2);
+// (the tcgen05 body, for ops the host library attached tensor maps to; returns -1 when aborting)
+__device__ int mk_op_attention_tc(const Params& p, const mk_op_desc* op, int a0, int a1, int a2, int seq);
 // body of the feeder warp: walks the CTA's instruction list and, for every prefill attention bound to the tcgen05 body,
 // requests its tiles and issues its MMAs (one thread); runs until the list ends or the CTA aborts
 __device__ void mk_attention_feeder(const Params& p);
@@ -37,9 +35,8 @@ __device__ bool mk_op_decode_attn(const Params& p, const mk_op_desc* op, int a0,
 // (many-sequence form: all kv heads of a sequence per instruction, whole cache rows through bulk copies)
 __device__ bool mk_op_decode_bulk(const Params& p, const mk_op_desc* op, int b, int s, int nwait, int wait_off, int seq,
                                   int narrive, int arrive_off);
-// finalize / eltwise / norm / rope_append / increment / gather / argmax; returns 1 for an unknown kind (nothing done
-// but the wait and the arrivals), -1 when aborting
-__device__ int mk_op_pointwise(const Params& p, const mk_op_desc* op, int a0, int a1, int seq, Sync sy);
+// finalize / eltwise / norm / rope_append / increment; returns false for an unknown kind
+__device__ bool mk_op_pointwise(const mk_op_desc* op, int a0, int a1);
 
 struct SmemMap {
     uint8_t* ring;
