@@ -216,8 +216,10 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
     }
     __syncthreads();
     // tensor memory of the tile GEMM (allocated by the CTA's first such instruction) goes back here
-    if (warp == 0 && c->tmem_base != kTcNoTmem)
+    if (warp == 0 && c->tmem_base != kTcNoTmem) {
+        __syncwarp();                       // (.sync.aligned: the whole warp, converged)
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(c->tmem_base), "r"(kTcCols) : "memory");
+    }
 }
 
 // Weight packing for the tcgen05 tile GEMM.  A bulk tensor copy of a 128-row x 64-column tile is 128

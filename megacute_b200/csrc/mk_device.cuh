@@ -546,6 +546,10 @@ __device__ __forceinline__ bool publish(const Params& p, Ctrl* c, int narrive, i
     if (compute_sync_or(*(volatile int*)&c->abort)) return true;
     if (first >= 0) red_release_add(p.counters + first, 1);
     for (int k = threadIdx.x + kComputeThreads; k < narrive; k += kComputeThreads) red_release_add(p.counters + tab[k], 1);
+    // The arriving lanes rejoin their warp here: a tail "if (lane arrives) red; return" may be compiled as an early return
+    // of the other lanes, and the .sync.aligned instructions of the next op body (tcgen05.alloc / ld, mma.sync) want the
+    // whole warp together.
+    __syncwarp();
     return false;
 }
 

@@ -198,9 +198,11 @@ __device__ __forceinline__ int op_attention_tc(const Params& p, Ctrl* c, uint8_t
 
     // ---- tensor memory (shared with the tile GEMM; allocated once per launch) and this instruction's barriers ----
     if (*(volatile uint32_t*)&c->tmem_base == kTcNoTmem) {
-        if (warp == 0)
+        if (warp == 0) {
+            __syncwarp();          // (.sync.aligned: the whole warp, converged)
             asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&c->tmem_base)), "r"(kTcCols)
                          : "memory");
+        }
         tc_fence_before();
     }
     if (t == 0) {

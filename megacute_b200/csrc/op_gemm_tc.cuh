@@ -263,9 +263,11 @@ __device__ __forceinline__ int op_gemm_tc(const Params& p, Ctrl* c, uint8_t* rin
     // (the test is on a word that only changes behind a barrier, so every thread takes the same branch)
     const uint32_t uses = *(volatile uint32_t*)&c->acc_uses;
     if (*(volatile uint32_t*)&c->tmem_base == kTcNoTmem) {     // (the attention op may have allocated it already)
-        if (warp == 0)
+        if (warp == 0) {
+            __syncwarp();          // (.sync.aligned: the whole warp, converged)
             asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&c->tmem_base)), "r"(kTcCols)
                          : "memory");
+        }
         tc_fence_before();
         compute_sync();
         tc_fence_after();
@@ -347,6 +349,7 @@ __device__ __forceinline__ int op_gemm_tc(const Params& p, Ctrl* c, uint8_t* rin
     ok = __shfl_sync(0xffffffffu, ok, 0);
     tc_fence_after();
     phase_mark(p, c, 2);                                                    // accumulator complete
+    __syncwarp();                                                           // (the tensor-memory loads below are .sync.aligned: whole warp, converged)
     // first half: tensor memory -> shared memory.  Warp w reads lanes 32 (w & 3) .. +31 (activation
     // rows) and column half w >> 2; the activation stages are free now (every MMA has completed).
     const int qd = warp & 3, h = warp >> 2;
