@@ -192,3 +192,38 @@ def test_llama_1b_decode_batch64_ragged(cuda):
     print(f"batch 64, positions 256 .. {ctx}: worst logits rel-L2 over {steps} steps {worst:.2e}")
     assert torch.equal(st["pos"].cpu(), pos + steps) and torch.equal(rs["pos"].cpu(), pos + steps)
     assert np.array_equal(prog.counters(), prog.sched.counter_target * steps)
+
+
+def test_decode_batch64_many_launches(cuda):
+    """Six thousand back-to-back launches of a batch-64 decode step (1B-shape widths, four layers, a 32 768-row lm_head):
+    every op kind of the decode path -- tile GEMMs on tcgen05 with split-K reductions, the many-sequence decode
+    attention, norms, gather, argmax -- hands over between the roles of a CTA some 1.5 million times.  A rare fault of
+    such a hand-over (one launch in ten thousand) passes every short test; it does not pass this one.  The logits of
+    the last step of each round of 32 must repeat the first round's."""
+    c = C1B
+    B, ctx, n, vocab = 64, 256, 4, 32768
+    max_seq = ctx + 128
+    g = llama_decode(B, c["E"], c["H"], c["KVH"], c["F"], n, max_seq, vocab, c["eps"])
+    w = W.llama_weights(c["E"], c["H"], c["KVH"], c["F"], n, vocab, 3, cuda)
+    st, ids = W.llama_decode_state(B, c["E"], c["H"], c["KVH"], n, max_seq, ctx, vocab, 4, cuda)
+    st["x"] = w["lm_head"][ids].clone()
+    cos, sin = W.rope_tables(max_seq, 64, c["theta"], cuda)
+    prog = mc.compile(g)
+    args = dict(cos=cos, sin=sin, **w, **st)
+    x0 = st["x"].clone()
+    first = None
+    for rnd in range(6000 // 32):
+        st["pos"].fill_(ctx)
+        st["x"].copy_(x0)
+        for _ in range(32):
+            out = prog(**args)
+        if rnd % 47 == 0:
+            prog.check()
+            last = out[0] if isinstance(out, (tuple, list)) else out
+            cur = last.float().clone()
+            if first is None:
+                first = cur
+            else:       # split-K partial sums arrive in any order: fp32 sums differ in the last bit, some bf16 logits by one ulp
+                assert rel_l2(cur, first) < 5e-3 and bool(torch.isfinite(cur).all())
+    prog.check()
+    assert int(st["pos"].flatten()[0]) == ctx + 32
