@@ -70,6 +70,7 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
         c->kv_cons = 0;
         c->acc_uses = 0;
         c->tmem_base = kTcNoTmem;
+        c->tmem_ready = 0;
         c->abort = 0;
         c->flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -135,12 +136,12 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
             const mk_op_desc* op = &mt->desc[s2];
             const int wait_off = in.nwait <= kMetaWaits ? -1 - s2 : in.wait_off;
             const int arrive_off = in.narrive <= kMetaArrives ? -1 - s2 : in.arrive_off;
-            const long long t0 = TRACE ? (long long)globaltimer() : 0;
-            // the single-row streaming linear and decode attention wait for their dependencies
-            // themselves, after requesting what depends on nothing in this launch
-            const bool self_wait = (op->kind == MK_OP_GEMV && (op->flags & GEMV_F_UNITS)) || op->kind == MK_OP_DECODE_ATTN;
-            if (!self_wait && wait_deps(p, c, in.nwait, wait_off, in.seq)) break;
-            long long t1 = TRACE ? (long long)globaltimer() : 0;
+            const long long t0 = TRACE && threadIdx.x == 0 ? (long long)globaltimer() : 0;
+            if (TRACE && threadIdx.x == 0) c->t_pub = 0;
+            // the streaming linear, decode attention and the tile GEMM wait for the instruction's dependencies behind their
+            // own entry and publish the arrivals before they return (begin_op / end_op say why); the kernel does both
+            // around the bodies whose entry is cheap
+            const Sync sy{in.nwait, wait_off, in.narrive, arrive_off};
             const int ppos = pos.stage | ((int)pos.phase << 8);
             int npos = ppos;
             bool known = true, aborting = false;
@@ -149,33 +150,42 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
                     if (op->flags & GEMV_F_UNITS) {
                         npos = mk_op_gemv_units(p, op, in.a0, in.a1, in.seq, ppos, in.nwait, wait_off, in.narrive, arrive_off);
                         aborting = npos < 0;
-                        if (TRACE) t1 = c->t_dep;
                     } else {
+                        if (wait_deps(p, c, in.nwait, wait_off, in.seq)) { aborting = true; break; }
+                        if (TRACE && threadIdx.x == 0) c->t_dep = (long long)globaltimer();
                         npos = mk_op_gemv_general(p, op, in.a0, in.a1, in.seq, ppos);
+                        aborting = publish(p, c, in.narrive, arrive_off);
                     }
                     break;
                 case MK_OP_GEMM:
-                    npos = (op->i[10] == 256 && op->ptr[11]) ? mk_op_gemm_wide(p, op, in.a0, in.a1, in.a2, in.seq, ppos)
-                                                             : mk_op_gemm(p, op, in.a0, in.a1, in.a2, in.seq, ppos);
+                    npos = (op->i[10] == 256 && op->ptr[11]) ? mk_op_gemm_wide(p, op, in.a0, in.a1, in.a2, in.seq, ppos, sy)
+                                                             : mk_op_gemm(p, op, in.a0, in.a1, in.a2, in.seq, ppos, sy);
                     aborting = npos < 0;
                     break;
                 case MK_OP_ATTENTION:
+                    if (wait_deps(p, c, in.nwait, wait_off, in.seq)) { aborting = true; break; }
+                    if (TRACE && threadIdx.x == 0) c->t_dep = (long long)globaltimer();
                     if (op->ptr[11]) aborting = mk_op_attention_tc(p, op, in.a0, in.a1, in.a2, in.seq) < 0;
                     else mk_op_attention(op, in.a0, in.a1, in.a2);
+                    aborting = publish(p, c, in.narrive, arrive_off) || aborting;
                     break;
                 case MK_OP_DECODE_ATTN:
                     aborting = mk_op_decode_attn(p, op, in.a0, in.a1, in.a2, in.nwait, wait_off, in.seq, in.narrive, arrive_off);
-                    if (TRACE) t1 = c->t_dep;
                     break;
-                default: known = mk_op_pointwise(op, in.a0, in.a1); break;
+                default:
+                    if (wait_deps(p, c, in.nwait, wait_off, in.seq)) { aborting = true; break; }
+                    if (TRACE && threadIdx.x == 0) c->t_dep = (long long)globaltimer();
+                    known = mk_op_pointwise(op, in.a0, in.a1);
+                    aborting = publish(p, c, in.narrive, arrive_off);
+                    break;
             }
             if (!known && threadIdx.x == 0) report(p, c, MK_DEV_BAD_INST, in.seq, 1, op->kind, idx, 0);
             pos.stage = npos & 0xff;
             pos.phase = (uint32_t)(npos >> 8);
-            if (!self_wait) aborting = publish(p, c, in.narrive, arrive_off) || aborting;
-            if (threadIdx.x == 0) {
-                trace_rec<TRACE>(p, 1, slot, in.seq, t0, t1, (long long)globaltimer());
-                if (TRACE && (self_wait || op->kind == MK_OP_GEMM || op->kind == MK_OP_ATTENTION)) trace_rec<TRACE>(p, 2, slot, in.seq, c->t_phase[0], c->t_phase[1], c->t_phase[2]);
+            if (TRACE && threadIdx.x == 0) {
+                const bool marks = op->kind == MK_OP_GEMV || op->kind == MK_OP_DECODE_ATTN || op->kind == MK_OP_GEMM || op->kind == MK_OP_ATTENTION;
+                trace_rec<TRACE>(p, 1, slot, in.seq, t0, c->t_dep, c->t_pub ? c->t_pub : (long long)globaltimer());
+                if (marks) trace_rec<TRACE>(p, 2, slot, in.seq, c->t_phase[0], c->t_phase[1], c->t_phase[2]);
             }
             if (aborting) break;
         }

@@ -138,6 +138,8 @@ struct Ctrl {                     // lives in the last kCtrlBytes of shared memo
     unsigned long long attn_go;              // tcgen05 prefill attention: the compute warps are at the instruction (dependencies met,
                                              // barriers initialised); the feeding thread of the producer warp may start
     uint32_t tmem_base;               // ... tensor-memory address of the accumulator (written by tcgen05.alloc)
+    uint32_t tmem_ready;              // ... 1 once it is allocated; written behind the barrier that follows the allocation, so all
+                                      //     threads of an instruction read the same value (tmem_base changes while they arrive)
     uint32_t x_par;                       // ... bit s: parity of the next completion of x_full[s] and of x_empty[s] (between
                                           //     instructions both have completed equally often); set at an instruction's end
     uint8_t w_slot, w_phase;              // ... the MMA thread's position in the weight slots
@@ -146,6 +148,7 @@ struct Ctrl {                     // lives in the last kCtrlBytes of shared memo
     int abort;                    // set once a wait of this CTA gave up or saw the global abort
     int flag;                     // scratch broadcast word (split-KV last arriver)
     long long t_dep;              // tracing: when the dependencies of the current instruction were met
+    long long t_pub;              // tracing: when its arrivals were published (0: the op left no mark)
     long long t_phase[3];         // tracing: op-internal phase marks (role 2 records)
 };
 static_assert(sizeof(Ctrl) <= kCtrlBytes, "Ctrl outgrew its shared-memory slot");
@@ -551,6 +554,29 @@ __device__ __forceinline__ bool publish(const Params& p, Ctrl* c, int narrive, i
     // whole warp together.
     __syncwarp();
     return false;
+}
+
+// An op body is a function of another translation unit, called through the ABI: on entry it saves the callee-saved
+// registers it is going to use to local memory and on return it loads them back -- for the tile GEMM 62 registers
+// of 256 threads, 63 KB each way, with almost no L1 to hold them.  Measured on batch-64 decode: 1.4 us from the end
+// of the dependency wait to the body's first statement.  So the bodies with a large frame (tile GEMM; the streaming
+// linear and decode attention always did) wait for the instruction's dependencies themselves, behind their entry, and
+// publish its arrivals before they return: both transfers then run while the CTA would be waiting for other SMs
+// anyway (batch-64 decode 1.364 -> 1.31 ms).  With the wait right behind a barrier, the warps reach the body's first
+// statements with empty memory queues and a few hundred cycles apart at times: whatever a body decides there must
+// be decided on words that only change behind a barrier (Ctrl::tmem_ready, not the address tcgen05.alloc writes).
+struct Sync {
+    int nwait, wait_off, narrive, arrive_off;
+};
+__device__ __forceinline__ bool begin_op(const Params& p, Ctrl* c, const Sync& s, int seq) {
+    const bool aborting = wait_deps(p, c, s.nwait, s.wait_off, seq);
+    if (p.trace_cap > 0 && threadIdx.x == 0) c->t_dep = (long long)globaltimer();
+    return aborting;
+}
+__device__ __forceinline__ bool end_op(const Params& p, Ctrl* c, const Sync& s) {
+    const bool aborting = publish(p, c, s.narrive, s.arrive_off);
+    if (p.trace_cap > 0 && threadIdx.x == 0) c->t_pub = (long long)globaltimer();
+    return aborting;
 }
 
 __device__ __forceinline__ void phase_mark(const Params& p, Ctrl* c, int k) {

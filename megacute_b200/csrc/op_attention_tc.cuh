@@ -197,7 +197,8 @@ __device__ __forceinline__ int op_attention_tc(const Params& p, Ctrl* c, uint8_t
     AttnBars* a = &c->attn;
 
     // ---- tensor memory (shared with the tile GEMM; allocated once per launch) and this instruction's barriers ----
-    if (*(volatile uint32_t*)&c->tmem_base == kTcNoTmem) {
+    const bool first_use = *(volatile uint32_t*)&c->tmem_ready == 0;     // (written behind the barrier below: the same for every thread)
+    if (first_use) {
         if (warp == 0) {
             __syncwarp();          // (.sync.aligned: the whole warp, converged)
             asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&c->tmem_base)), "r"(kTcCols)
@@ -217,6 +218,7 @@ __device__ __forceinline__ int op_attention_tc(const Params& p, Ctrl* c, uint8_t
     }
     compute_sync();
     tc_fence_after();
+    if (t == 0 && first_use) c->tmem_ready = 1;
     if (t == 0) mbar_arrive(&c->attn_go);                               // the feeding thread (feeder warp) may start
     const uint32_t tmem = *(volatile uint32_t*)&c->tmem_base;
     uint8_t* ps = work + kAtPOff;

@@ -4,13 +4,15 @@
 #include "ops.cuh"
 
 namespace mk {
-__device__ int mk_op_gemm(const Params& p, const mk_op_desc* op, int a0, int a1, int a2, int seq, int packed_pos) {
+__device__ int mk_op_gemm(const Params& p, const mk_op_desc* op, int a0, int a1, int a2, int seq, int packed_pos, Sync sy) {
     const SmemMap m = smem_map();
+    if (begin_op(p, m.ctrl, sy, seq)) return -1;
     if (op->ptr[11]) {
         // the host library attached tensor maps: tcgen05 body, weights through the producer's ring
         // (the weight tiles have slots and barriers of their own: the ring position is untouched)
         // (128 x 256 tiles have a translation unit of their own, op_gemm_wide.cu: the kernel calls it directly)
-        return op_gemm_tc(p, m.ctrl, m.ring, m.work, op, a0, a1, a2, seq) < 0 ? -1 : packed_pos;
+        if (op_gemm_tc(p, m.ctrl, m.ring, m.work, op, a0, a1, a2, seq) < 0) return -1;
+        return end_op(p, m.ctrl, sy) ? -1 : packed_pos;
     }
     // (a 256-wide output tile, i 10, is two 128-wide ones for this body)
     const int halves = op->i[10] == 256 ? 2 : 1;
@@ -24,6 +26,6 @@ __device__ int mk_op_gemm(const Params& p, const mk_op_desc* op, int a0, int a1,
             op_gemm<128, 32, 4>(op, a0, n, a2, m.work);
         }
     }
-    return packed_pos;
+    return end_op(p, m.ctrl, sy) ? -1 : packed_pos;
 }
 }  // namespace mk

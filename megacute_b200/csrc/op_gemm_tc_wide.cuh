@@ -27,9 +27,10 @@ __device__ __forceinline__ int op_gemm_tc_wide(const Params& p, Ctrl* c, uint8_t
 
     // Tensor memory is allocated by the CTA's first tile GEMM instruction and kept until the kernel
     // ends (the kernel frees it on every path); the permit to allocate is never relinquished.
-    // (the test is on a word that only changes behind a barrier, so every thread takes the same branch)
+    // (the test is on a word that only changes behind a barrier, so every thread takes the same branch -- not on the
+    // address itself, which the allocation writes while the other warps are still arriving at the test)
     const uint32_t uses = *(volatile uint32_t*)&c->acc_uses;
-    if (*(volatile uint32_t*)&c->tmem_base == kTcNoTmem) {     // (the attention op may have allocated it already)
+    if (*(volatile uint32_t*)&c->tmem_ready == 0) {            // (the attention op may have allocated it already)
         if (warp == 0) {
             __syncwarp();          // (.sync.aligned: the whole warp, converged)
             asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&c->tmem_base)), "r"(kTcCols)
@@ -38,6 +39,7 @@ __device__ __forceinline__ int op_gemm_tc_wide(const Params& p, Ctrl* c, uint8_t
         tc_fence_before();
         compute_sync();
         tc_fence_after();
+        if (t == 0) c->tmem_ready = 1;                          // (read again only behind the barrier that ends this instruction)
     }
     const uint32_t tmem = *(volatile uint32_t*)&c->tmem_base;
     const uint32_t apar = uses & 1u;

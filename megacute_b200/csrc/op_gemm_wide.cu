@@ -6,8 +6,10 @@
 #include "ops.cuh"
 
 namespace mk {
-__device__ int mk_op_gemm_wide(const Params& p, const mk_op_desc* op, int a0, int a1, int a2, int seq, int packed_pos) {
+__device__ int mk_op_gemm_wide(const Params& p, const mk_op_desc* op, int a0, int a1, int a2, int seq, int packed_pos, Sync sy) {
     const SmemMap m = smem_map();
-    return op_gemm_tc_wide(p, m.ctrl, m.ring, m.work, op, a0, a1, a2, seq) < 0 ? -1 : packed_pos;
+    if (begin_op(p, m.ctrl, sy, seq)) return -1;
+    if (op_gemm_tc_wide(p, m.ctrl, m.ring, m.work, op, a0, a1, a2, seq) < 0) return -1;
+    return end_op(p, m.ctrl, sy) ? -1 : packed_pos;
 }
 }  // namespace mk

@@ -19,10 +19,12 @@ __device__ int mk_op_gemv_units(const Params& p, const mk_op_desc* op, int o0, i
 // body of the finisher warp (op_gemv_mma.cuh): runs until the CTA's instruction list ends
 __device__ void mk_gemv_finisher(const Params& p);
 __device__ int mk_op_gemv_general(const Params& p, const mk_op_desc* op, int o0, int o1, int seq, int packed_pos);
-// (tile GEMM; with tensor maps attached it consumes ring slots: returns the ring position, -1 when aborting)
-__device__ int mk_op_gemm(const Params& p, const mk_op_desc* op, int a0, int a1, int a2, int seq, int packed_pos);
+// (tile GEMM; with tensor maps attached it consumes ring slots: returns the ring position, -1 when the CTA is aborting.
+// Like the streaming linear and decode attention it waits for the instruction's dependencies and publishes its arrivals
+// itself: Sync; begin_op / end_op say why)
+__device__ int mk_op_gemm(const Params& p, const mk_op_desc* op, int a0, int a1, int a2, int seq, int packed_pos, Sync sy);
 // (the same with 128 x 256 output tiles; only for ops the host library bound to the tcgen05 body)
-__device__ int mk_op_gemm_wide(const Params& p, const mk_op_desc* op, int a0, int a1, int a2, int seq, int packed_pos);
+__device__ int mk_op_gemm_wide(const Params& p, const mk_op_desc* op, int a0, int a1, int a2, int seq, int packed_pos, Sync sy);
 __device__ void mk_op_attention(const mk_op_desc* op, int a0, int a1, int a2);
 // (the tcgen05 body, for ops the host library attached tensor maps to; returns -1 when aborting)
 __device__ int mk_op_attention_tc(const Params& p, const mk_op_desc* op, int a0, int a1, int a2, int seq);
@@ -35,7 +37,7 @@ __device__ bool mk_op_decode_attn(const Params& p, const mk_op_desc* op, int a0,
 // (many-sequence form: all kv heads of a sequence per instruction, whole cache rows through bulk copies)
 __device__ bool mk_op_decode_bulk(const Params& p, const mk_op_desc* op, int b, int s, int nwait, int wait_off, int seq,
                                   int narrive, int arrive_off);
-// finalize / eltwise / norm / rope_append / increment; returns false for an unknown kind
+// finalize / eltwise / norm / rope_append / increment / gather / argmax; returns false for an unknown kind
 __device__ bool mk_op_pointwise(const mk_op_desc* op, int a0, int a1);
 
 struct SmemMap {
