@@ -24,6 +24,7 @@
 #include "mma.cuh"
 #include "op_gemv_common.cuh"
 #include "ops.cuh"
+#include "walk.cuh"
 
 namespace mk {
 
@@ -98,24 +99,13 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
         int slot = 0;
         Meta* mt = &c->meta;
         const int lane = threadIdx.x & 31;
-        auto stage_row = [&](int idx, int s3) {       // lanes 0..3 of the calling warp
-            if (idx < p.n_insts && lane < 4) cp_async16(&mt->inst[s3][lane], p.insts + (long long)idx * 4 + lane, true);
-        };
-        auto stage_op = [&](int s3, int s2) {         // whole calling warp; row s3 must be visible already
-            const int4 w0 = mt->inst[s3][0], w2 = mt->inst[s3][2];
-            const int opi = w0.x - 1;
-            if (opi >= 0 && opi < p.n_ops && lane < 16)
-                cp_async16(reinterpret_cast<uint8_t*>(&mt->desc[s2]) + lane * 16, reinterpret_cast<const uint8_t*>(p.ops + opi) + lane * 16, true);
-            if (w2.x <= kMetaWaits && lane < w2.x) cp_async_small(&mt->waits[s2][lane], p.waits + w2.y + lane, 8);
-            if (w2.z <= kMetaArrives && lane >= 16 && lane - 16 < w2.z) cp_async_small(&mt->arrives[s2][lane - 16], p.arrives + w2.w + lane - 16, 4);
-        };
         if (warp == 1) {
-            stage_row(blockIdx.x, 0);
-            stage_row(blockIdx.x + gridDim.x, 1);
+            stage_row(p, mt, blockIdx.x, 0, lane);
+            stage_row(p, mt, blockIdx.x + gridDim.x, 1, lane);
             cp_async_commit();
             cp_async_wait<0>();
             __syncwarp();
-            if (blockIdx.x < p.n_insts) stage_op(0, 0);
+            if (blockIdx.x < p.n_insts) stage_op(p, mt, 0, 0, lane);
             cp_async_commit();
             cp_async_wait<0>();
         }
@@ -124,8 +114,8 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
             const int s3 = slot % 3, s2 = slot & 1;
             const Inst in = decode_inst(mt->inst[s3]);
             if (warp == 1) {
-                stage_row(idx + 2 * gridDim.x, (slot + 2) % 3);
-                if (idx + gridDim.x < p.n_insts) stage_op((slot + 1) % 3, s2 ^ 1);
+                stage_row(p, mt, idx + 2 * gridDim.x, (slot + 2) % 3, lane);
+                if (idx + gridDim.x < p.n_insts) stage_op(p, mt, (slot + 1) % 3, s2 ^ 1, lane);
                 cp_async_commit();
             }
             const int opi = in.opi - 1;
@@ -141,10 +131,9 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
             // the streaming linear, decode attention and the tile GEMM wait for the instruction's dependencies behind their
             // own entry and publish the arrivals before they return (begin_op / end_op say why); the kernel does both
             // around the bodies whose entry is cheap
-            const Sync sy{in.nwait, wait_off, in.narrive, arrive_off};
-            const int ppos = pos.stage | ((int)pos.phase << 8);
+                        const int ppos = pos.stage | ((int)pos.phase << 8);
             int npos = ppos;
-            bool known = true, aborting = false;
+            bool known = true, aborting = false, traced = false;
             switch (op->kind) {
                 case MK_OP_GEMV:
                     if (op->flags & GEMV_F_UNITS) {
@@ -157,11 +146,17 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
                         aborting = publish(p, c, in.narrive, arrive_off);
                     }
                     break;
-                case MK_OP_GEMM:
-                    npos = (op->i[10] == 256 && op->ptr[11]) ? mk_op_gemm_wide(p, op, in.a0, in.a1, in.a2, in.seq, ppos, sy)
-                                                             : mk_op_gemm(p, op, in.a0, in.a1, in.a2, in.seq, ppos, sy);
-                    aborting = npos < 0;
+                case MK_OP_GEMM: {
+                    // (runs this instruction and the CTA's following ones for as long as they are the body's own: walk.cuh)
+                    const int last = (op->i[10] == 256 && op->ptr[11]) ? mk_run_gemm_wide(p, idx) : mk_run_gemm(p, idx);
+                    aborting = last < 0;
+                    if (!aborting) {
+                        slot += (last - idx) / (int)gridDim.x;
+                        idx = last;
+                    }
+                    traced = true;
                     break;
+                }
                 case MK_OP_ATTENTION:
                     if (wait_deps(p, c, in.nwait, wait_off, in.seq)) { aborting = true; break; }
                     if (TRACE && threadIdx.x == 0) c->t_dep = (long long)globaltimer();
@@ -182,7 +177,7 @@ __global__ void __launch_bounds__(kThreads, 1) megakernel(const __grid_constant_
             if (!known && threadIdx.x == 0) report(p, c, MK_DEV_BAD_INST, in.seq, 1, op->kind, idx, 0);
             pos.stage = npos & 0xff;
             pos.phase = (uint32_t)(npos >> 8);
-            if (TRACE && threadIdx.x == 0) {
+            if (TRACE && threadIdx.x == 0 && !traced) {
                 const bool marks = op->kind == MK_OP_GEMV || op->kind == MK_OP_DECODE_ATTN || op->kind == MK_OP_GEMM || op->kind == MK_OP_ATTENTION;
                 trace_rec<TRACE>(p, 1, slot, in.seq, t0, c->t_dep, c->t_pub ? c->t_pub : (long long)globaltimer());
                 if (marks) trace_rec<TRACE>(p, 2, slot, in.seq, c->t_phase[0], c->t_phase[1], c->t_phase[2]);

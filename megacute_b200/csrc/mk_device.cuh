@@ -148,6 +148,8 @@ struct Ctrl {                     // lives in the last kCtrlBytes of shared memo
     int abort;                    // set once a wait of this CTA gave up or saw the global abort
     int flag;                     // scratch broadcast word (split-KV last arriver)
     long long t_dep;              // tracing: when the dependencies of the current instruction were met
+    long long t_fetch;            // tracing: when a body that keeps the walk (walk.cuh) turned to the current instruction
+    int run_idx;                  // index of the instruction such a body is executing
     long long t_pub;              // tracing: when its arrivals were published (0: the op left no mark)
     long long t_phase[3];         // tracing: op-internal phase marks (role 2 records)
 };
@@ -579,6 +581,21 @@ __device__ __forceinline__ bool end_op(const Params& p, Ctrl* c, const Sync& s) 
     return aborting;
 }
 
+// Instruction metadata runs one instruction ahead in shared memory (Meta): while instruction i executes, warp 1 has
+// asynchronous copies in flight for the row of i + 2 and, from the already staged row of i + 1, for that
+// instruction's op descriptor, waits and arrivals.  The barrier that ends instruction i (publish) makes them visible.
+__device__ __forceinline__ void stage_row(const Params& p, Meta* mt, int idx, int s3, int lane) {       // lanes 0..3 of the calling warp
+    if (idx < p.n_insts && lane < 4) cp_async16(&mt->inst[s3][lane], p.insts + (long long)idx * 4 + lane, true);
+}
+__device__ __forceinline__ void stage_op(const Params& p, Meta* mt, int s3, int s2, int lane) {         // whole calling warp; row s3 must be visible already
+    const int4 w0 = mt->inst[s3][0], w2 = mt->inst[s3][2];
+    const int opi = w0.x - 1;
+    if (opi >= 0 && opi < p.n_ops && lane < 16)
+        cp_async16(reinterpret_cast<uint8_t*>(&mt->desc[s2]) + lane * 16, reinterpret_cast<const uint8_t*>(p.ops + opi) + lane * 16, true);
+    if (w2.x <= kMetaWaits && lane < w2.x) cp_async_small(&mt->waits[s2][lane], p.waits + w2.y + lane, 8);
+    if (w2.z <= kMetaArrives && lane >= 16 && lane - 16 < w2.z) cp_async_small(&mt->arrives[s2][lane - 16], p.arrives + w2.w + lane - 16, 4);
+}
+
 __device__ __forceinline__ void phase_mark(const Params& p, Ctrl* c, int k) {
     if (p.trace_cap > 0 && threadIdx.x == 0) c->t_phase[k] = (long long)globaltimer();
 }
@@ -591,6 +608,14 @@ __device__ __forceinline__ void trace_rec(const Params& p, int role, int slot, l
             long long* r = p.trace + (((long long)blockIdx.x * kTraceRoles + role) * p.trace_cap + slot) * 4;
             r[0] = seq; r[1] = t0; r[2] = t1; r[3] = t2;
         }
+    }
+}
+
+// the same with the tracing decided at run time (walk.cuh)
+__device__ __forceinline__ void trace_rec_rt(const Params& p, int role, int slot, long long seq, long long t0, long long t1, long long t2) {
+    if (slot < p.trace_cap) {
+        long long* r = p.trace + (((long long)blockIdx.x * kTraceRoles + role) * p.trace_cap + slot) * 4;
+        r[0] = seq; r[1] = t0; r[2] = t1; r[3] = t2;
     }
 }
 

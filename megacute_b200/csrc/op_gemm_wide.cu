@@ -4,12 +4,15 @@
 // trips here: batch-64 decode 7 % slower, the MLP block 14 %).
 #include "op_gemm_tc_wide.cuh"
 #include "ops.cuh"
+#include "walk.cuh"
 
 namespace mk {
-__device__ int mk_op_gemm_wide(const Params& p, const mk_op_desc* op, int a0, int a1, int a2, int seq, int packed_pos, Sync sy) {
+__device__ int mk_run_gemm_wide(const Params& p, int idx) {
     const SmemMap m = smem_map();
-    if (begin_op(p, m.ctrl, sy, seq)) return -1;
-    if (op_gemm_tc_wide(p, m.ctrl, m.ring, m.work, op, a0, a1, a2, seq) < 0) return -1;
-    return end_op(p, m.ctrl, sy) ? -1 : packed_pos;
+    return run_own_insts(
+        p, m.ctrl, idx, [](const mk_op_desc* op) { return op->kind == MK_OP_GEMM && op->i[10] == 256 && op->ptr[11] != 0; },
+        [&](const mk_op_desc* op, int a0, int a1, int a2, int seq) -> int {
+            return op_gemm_tc_wide(p, m.ctrl, m.ring, m.work, op, a0, a1, a2, seq);
+        });
 }
 }  // namespace mk

@@ -19,12 +19,13 @@ __device__ int mk_op_gemv_units(const Params& p, const mk_op_desc* op, int o0, i
 // body of the finisher warp (op_gemv_mma.cuh): runs until the CTA's instruction list ends
 __device__ void mk_gemv_finisher(const Params& p);
 __device__ int mk_op_gemv_general(const Params& p, const mk_op_desc* op, int o0, int o1, int seq, int packed_pos);
-// (tile GEMM; with tensor maps attached it consumes ring slots: returns the ring position, -1 when the CTA is aborting.
-// Like the streaming linear and decode attention it waits for the instruction's dependencies and publishes its arrivals
-// itself: Sync; begin_op / end_op say why)
-__device__ int mk_op_gemm(const Params& p, const mk_op_desc* op, int a0, int a1, int a2, int seq, int packed_pos, Sync sy);
+// Tile GEMM.  The kernel's loop has fetched instruction `idx` and chosen this body; the body runs it and every
+// following instruction of the CTA that is its own (walk.cuh), waiting for the dependencies and publishing the
+// arrivals of each itself (begin_op says why).  Returns the index of the last instruction executed, -1 when the CTA is
+// aborting.  (The ring position is untouched: the weight tiles have slots of their own.)
+__device__ int mk_run_gemm(const Params& p, int idx);
 // (the same with 128 x 256 output tiles; only for ops the host library bound to the tcgen05 body)
-__device__ int mk_op_gemm_wide(const Params& p, const mk_op_desc* op, int a0, int a1, int a2, int seq, int packed_pos, Sync sy);
+__device__ int mk_run_gemm_wide(const Params& p, int idx);
 __device__ void mk_op_attention(const mk_op_desc* op, int a0, int a1, int a2);
 // (the tcgen05 body, for ops the host library attached tensor maps to; returns -1 when aborting)
 __device__ int mk_op_attention_tc(const Params& p, const mk_op_desc* op, int a0, int a1, int a2, int seq);
