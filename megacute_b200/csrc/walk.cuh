@@ -37,12 +37,12 @@ __device__ __forceinline__ int run_own_insts(const Params& p, Ctrl* c, int idx, 
         }
         idx = *(volatile int*)&c->run_idx;                      // (the same value: not kept in a register across the body)
         const int slot = (idx - (int)blockIdx.x) / (int)gridDim.x, s3 = slot % 3, s2 = slot & 1;
+        const int seq = mt->inst[s3][3].x;                       // (behind the barrier of publish() warp 1 may already be staging over this row)
         {
             const int4 w2 = mt->inst[s3][2];
             if (publish(p, c, w2.z, w2.z <= kMetaArrives ? -1 - s2 : w2.w)) return -1;
         }
         if (p.trace_cap > 0 && threadIdx.x == 0) {
-            const long long seq = mt->inst[s3][3].x;
             trace_rec_rt(p, 1, slot, seq, c->t_fetch, c->t_dep, (long long)globaltimer());
             trace_rec_rt(p, 2, slot, seq, c->t_phase[0], c->t_phase[1], c->t_phase[2]);
         }

@@ -290,6 +290,42 @@ def test_timeline(cuda):
     assert tl.span_us() > 0 and "Linear" in tl.summary() and len(tl.chrome_events()) > 0
 
 
+def test_timeline_of_tile_gemm_runs(cuda):
+    """A CTA that gets several tile-GEMM instructions in a row runs them inside one call of the body, which then writes
+    the trace records itself: every instruction must still have exactly one record, under its own sequence number,
+    with ordered time stamps and phase marks."""
+    import numpy as np
+    M, K = 4096, 512
+    g = mc.Graph()
+    x = g.input("x", (M, K))
+    y = g.linear(g.unary(x, "identity"), g.param("w1", (1024, K)), act="gelu_tanh")     # 32 x 4 (or 8) tiles: 2 or more per CTA
+    g.output(g.linear(y, g.param("w2", (384, 1024))))                                    # narrow tiles behind them
+    gen = torch.Generator().manual_seed(5)
+    t = {"x": torch.randn(M, K, generator=gen).to(torch.bfloat16), "w1": (torch.randn(1024, K, generator=gen) * 0.04).to(torch.bfloat16),
+         "w2": (torch.randn(384, 1024, generator=gen) * 0.03).to(torch.bfloat16)}
+    prog = mc.compile(g, trace=True)
+    dp = {k: v.to(cuda) for k, v in t.items()}
+    for _ in range(2):
+        prog(**dp)
+    prog.check()
+    tl = prog.timeline()
+    comp = tl.table[tl.table["role"] == 1]
+    assert len(comp) == prog.sched.n and np.array_equal(np.sort(comp["seq"]), np.arange(prog.sched.n))
+    assert bool((comp["t0"] <= comp["t1"]).all()) and bool((comp["t1"] < comp["t2"]).all())
+    per_op = np.bincount(np.asarray(prog.sched.op_of)[comp["seq"]], minlength=len(prog.g.ops))
+    assert np.array_equal(per_op, np.bincount(np.asarray(prog.sched.op_of), minlength=len(prog.g.ops)))
+    # a CTA runs its instructions in list order: sequence numbers rise with the slot
+    for sm in np.unique(comp["sm"])[:8]:
+        rows = comp[comp["sm"] == sm]
+        assert bool((np.diff(rows["seq"]) > 0).all()) and bool((np.diff(rows["t2"]) > 0).all())
+    ph = tl.table[tl.table["role"] == 2]
+    gemm = np.array([prog.g.ops[int(k)].kind in ("Linear", "LinearSplit") for k in np.asarray(prog.sched.op_of)[ph["seq"]]])
+    by_seq = {int(r["seq"]): r for r in comp}
+    for r in ph[gemm][:256]:
+        c = by_seq[int(r["seq"])]
+        assert c["t1"] <= r["t0"] <= r["t1"] <= r["t2"] <= c["t2"], (r, c)
+
+
 # ---------------------------------------------------------------------------------------------
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
