@@ -310,7 +310,7 @@ static __device__ __noinline__ void op_eltwise(const mk_op_desc* op, int a0, int
 // the one-vector-per-thread case too, which is the norm of every decode step.)
 // A row (or a lane's share of it) of at most NPER vectors per thread stays in registers between the two passes: every
 // vector is requested before the first is used, and gain and bias come in pairs.  (Requested one by one,
-// the vectors of a 2048-column row cost eight L2 round trips in each pass: 11 us per 16-row instruction.)
+// the vectors of a 2048-column row cost eight L2 round trips in each pass: 11 us per 8-row instruction.)
 template <int NPER, bool MOD, bool X16 = false>
 static __device__ __noinline__ void norm_kept(const mk_op_desc* op, int r, int first, int step, int nvec, bool live, uint8_t* work) {
     const int Cc = op->i[1], rms = op->i[2], rpi = op->i[3], xdt = op->i[4], odt = op->i[5];
